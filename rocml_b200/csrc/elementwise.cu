@@ -1,0 +1,164 @@
+// Embedding gather, fused residual-add + RMSNorm, SiLU(gate) * up, casts.
+//
+// All arithmetic is 32-bit; only loads and stores use the storage types.
+#include "common.cuh"
+#include "api.h"
+
+using namespace rb;
+
+// ---- embedding: resid[t, :] = f32(table[ids[t], :]) --------------------------------------
+// Replaces the reference's embedding_f16_f32 (rocml-kernels/kernels/embedding.hip:6-18).
+template <typename WT>
+__global__ void embedding_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
+                                 float* __restrict__ out, int H, int vocab, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * H;
+    if (id < 0 || id >= vocab) {  // a token id outside the table: record it, write zeros
+        if (threadIdx.x == 0 && status) atomicExch(status, RB_ERR_BAD_SIZE);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const WT* row = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+extern "C" int rb_embedding(const int* ids, const void* table, int table_dtype, float* out, int T,
+                            int H, int vocab, int* status, void* stream) {
+    if (T <= 0) return RB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == RB_BF16)
+        embedding_kernel<<<T, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, out, H, vocab, status);
+    else if (table_dtype == RB_F32)
+        embedding_kernel<<<T, threads, 0, s>>>(ids, (const float*)table, out, H, vocab, status);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// ---- fused residual add + RMSNorm ---------------------------------------------------------
+// r = resid[row] + sum_s delta[s][row]   (s in fixed order, so the sum never depends on the batch)
+// if write_back: resid[row] = r
+// out[i] = r * rsqrt(mean(r^2) + eps) * w
+// `rows` (optional) picks the source rows; output row i is compact.  One block per output row.
+// Replaces add_inplace_f32 + rmsnorm_f32 (rocml-kernels/kernels/elementwise.hip:7-26,
+// rmsnorm.hip:7-43); product order x * inv_rms * w as there.
+template <typename OT, typename WT>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
+                                   int n_delta, size_t delta_stride, const WT* __restrict__ w,
+                                   OT* __restrict__ out, const int* __restrict__ rows, int H,
+                                   float eps, int write_back) {
+    extern __shared__ float row_buf[];  // H floats + 33 for the reduction
+    float* red = row_buf + H;
+    const int orow = blockIdx.x;
+    const int row = rows ? rows[orow] : orow;
+    if (row < 0) return;  // a padded entry
+    float* r = resid + (size_t)row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + (size_t)row * H + i];
+        row_buf[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float inv = rsqrtf(total / (float)H + eps);
+    OT* o = out + (size_t)orow * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = row_buf[i];
+        if (write_back) r[i] = v;
+        o[i] = from_f32<OT>(v * inv * to_f32(w[i]));
+    }
+}
+
+template <typename OT, typename WT>
+static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, size_t delta_stride,
+                              const void* w, void* out, const int* rows, int n_rows, int H, float eps,
+                              int write_back, cudaStream_t s) {
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 200 * 1024) return RB_ERR_BAD_SIZE;
+    auto k = add_rmsnorm_kernel<OT, WT>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    k<<<n_rows, threads, smem, s>>>(resid, delta, n_delta, delta_stride, (const WT*)w, (OT*)out, rows, H,
+                                    eps, write_back);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delta_stride,
+                              const void* w, int w_dtype, void* out, int out_dtype, const int* rows,
+                              int n_rows, int H, float eps, int write_back, void* stream) {
+    if (n_rows <= 0) return RB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t ds = (size_t)delta_stride;
+    if (out_dtype == RB_BF16 && w_dtype == RB_BF16)
+        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+    if (out_dtype == RB_BF16 && w_dtype == RB_F32)
+        return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+    if (out_dtype == RB_F32 && w_dtype == RB_BF16)
+        return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+    if (out_dtype == RB_F32 && w_dtype == RB_F32)
+        return launch_add_rmsnorm<float, float>(resid, delta, n_delta, ds, w, out, rows, n_rows, H, eps, write_back, s);
+    return RB_ERR_BAD_DTYPE;
+}
+
+// ---- SiLU(gate) * up ------------------------------------------------------------------------
+// in: [T, 2*I] with the gate in columns [0, I) and up in [I, 2I); out: [T, I].
+// silu(g) = g / (1 + exp(-g)) as in rocml-kernels/kernels/silu_mul.hip:15-18.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int I) {
+    const size_t n = (size_t)rows * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        const float g = to_f32(in[t * 2 * I + i]);
+        const float u = to_f32(in[t * 2 * I + I + i]);
+        out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+extern "C" int rb_silu_mul(const void* in, void* out, int dtype, int rows, int I, void* stream) {
+    if (rows <= 0) return RB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = (size_t)rows * I;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+    if (dtype == RB_BF16)
+        silu_mul_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, I);
+    else if (dtype == RB_F32)
+        silu_mul_kernel<<<blocks, threads, 0, s>>>((const float*)in, (float*)out, rows, I);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// ---- casts ------------------------------------------------------------------------------------
+template <typename A, typename B>
+__global__ void cast_kernel(const A* __restrict__ in, B* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<B>(to_f32(in[i]));
+}
+
+extern "C" int rb_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* stream) {
+    if (n <= 0) return RB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (in_dtype == RB_F32 && out_dtype == RB_BF16)
+        cast_kernel<<<blocks, threads, 0, s>>>((const float*)in, (__nv_bfloat16*)out, (size_t)n);
+    else if (in_dtype == RB_BF16 && out_dtype == RB_F32)
+        cast_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (float*)out, (size_t)n);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}

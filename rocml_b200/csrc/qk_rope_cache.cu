@@ -1,0 +1,123 @@
+// Fused per-head RMSNorm of q and k, rotary position encoding, and the write of k and v into
+// the paged cache.
+//
+// One warp per (token, head).  Input row layout: [q heads | k heads | v heads], each head
+// `hd` wide.  q is normalised and rotated in place; k is normalised, rotated and stored at
+// its page; v is stored as it is.  Takes the place of 2x rmsnorm_f32, 2x rope_neox_f32 and
+// scatter_kv_chunk / cast_f32_f16 of the reference (rocml/src/forward/attention_chunk.rs:
+// 128-197); order as there: norm, then rotation, then the cache write, all before attention.
+//
+// Rotation (rocml-kernels/kernels/rope.hip:18-33): for i < rot/2, a = pos * inv_freq[i],
+// (x_i, x_{i+rot/2}) <- (x_i cos a - x_{i+rot/2} sin a, x_i sin a + x_{i+rot/2} cos a).
+// inv_freq comes from the position-encoding part, so another encoding only changes the table.
+#include "common.cuh"
+#include "api.h"
+
+using namespace rb;
+
+template <typename AT, typename WT>
+__global__ void qk_norm_rope_cache_kernel(AT* __restrict__ qkv, int row_stride, int T, int nq, int nkv,
+                                          int hd, const WT* __restrict__ q_norm_w,
+                                          const WT* __restrict__ k_norm_w, float eps,
+                                          const float* __restrict__ inv_freq, int rot_dim,
+                                          const int* __restrict__ positions,
+                                          const int* __restrict__ slot_of_token,
+                                          const int* __restrict__ block_table, int max_pages,
+                                          AT* __restrict__ k_cache, AT* __restrict__ v_cache,
+                                          int write_kv) {
+    extern __shared__ float smem[];
+    const int warps_per_block = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* buf = smem + (size_t)warp * hd;
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    const long long item = (long long)blockIdx.x * warps_per_block + warp;
+    if (item >= (long long)T * heads_total) return;
+    const int t = (int)(item / heads_total);
+    const int h = (int)(item - (long long)t * heads_total);
+    const int slot = slot_of_token[t];
+    if (slot < 0) return;  // padding
+    const int pos = positions[t];
+
+    int kind, head;  // 0 q, 1 k, 2 v
+    if (h < nq) { kind = 0; head = h; }
+    else if (h < nq + nkv) { kind = 1; head = h - nq; }
+    else { kind = 2; head = h - nq - nkv; }
+    AT* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
+
+    AT* dst;
+    if (kind == 0) {
+        dst = src;
+    } else {
+        const int page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
+        if (page < 0) return;  // no page: the host never schedules this; skip rather than fault
+        AT* base = (kind == 1 ? k_cache : v_cache);
+        dst = base + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hd;
+    }
+
+    if (kind == 2) {
+        for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+        return;
+    }
+
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+        const float v = to_f32(src[i]);
+        buf[i] = v;
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const WT* w = kind == 0 ? q_norm_w : k_norm_w;
+    const float inv = w ? rsqrtf(ss / (float)hd + eps) : 1.f;
+    __syncwarp();
+    const int half = inv_freq ? rot_dim / 2 : 0;
+    for (int i = lane; i < half; i += 32) {
+        float x0 = buf[i], x1 = buf[i + half];
+        if (w) { x0 = x0 * inv * to_f32(w[i]); x1 = x1 * inv * to_f32(w[i + half]); }
+        const float a = (float)pos * inv_freq[i];
+        float sn, cs;
+        sincosf(a, &sn, &cs);
+        dst[i] = from_f32<AT>(x0 * cs - x1 * sn);
+        dst[i + half] = from_f32<AT>(x0 * sn + x1 * cs);
+    }
+    for (int i = 2 * half + lane; i < hd; i += 32) {
+        float x = buf[i];
+        if (w) x = x * inv * to_f32(w[i]);
+        dst[i] = from_f32<AT>(x);
+    }
+}
+
+template <typename AT, typename WT>
+static int launch_qk(void* qkv, int row_stride, int T, int nq, int nkv, int hd, const void* qw,
+                     const void* kw, float eps, const float* inv_freq, int rot_dim, const int* positions,
+                     const int* slot_of_token, const int* block_table, int max_pages, void* k_cache,
+                     void* v_cache, int write_kv, cudaStream_t s) {
+    const int warps = 4;
+    const long long items = (long long)T * (nq + (write_kv ? 2 * nkv : 0));
+    const long long blocks = (items + warps - 1) / warps;
+    if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
+    const size_t smem = (size_t)warps * hd * sizeof(float);
+    if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
+    qk_norm_rope_cache_kernel<AT, WT><<<(int)blocks, warps * 32, smem, s>>>(
+        (AT*)qkv, row_stride, T, nq, nkv, hd, (const WT*)qw, (const WT*)kw, eps, inv_freq, rot_dim,
+        positions, slot_of_token, block_table, max_pages, (AT*)k_cache, (AT*)v_cache, write_kv);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_qk_norm_rope_cache(void* qkv, int act_dtype, int row_stride, int T, int nq, int nkv,
+                                     int hd, const void* q_norm_w, const void* k_norm_w, int w_dtype,
+                                     float eps, const float* inv_freq, int rot_dim, const int* positions,
+                                     const int* slot_of_token, const int* block_table, int max_pages,
+                                     void* k_cache, void* v_cache, int write_kv, void* stream) {
+    if (T <= 0) return RB_OK;
+    if (hd <= 0 || hd % 2 || (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > hd))) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+#define RB_QK_ARGS qkv, row_stride, T, nq, nkv, hd, q_norm_w, k_norm_w, eps, inv_freq, rot_dim, positions, \
+                   slot_of_token, block_table, max_pages, k_cache, v_cache, write_kv, s
+    if (act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<__nv_bfloat16, __nv_bfloat16>(RB_QK_ARGS);
+    if (act_dtype == RB_BF16 && w_dtype == RB_F32) return launch_qk<__nv_bfloat16, float>(RB_QK_ARGS);
+    if (act_dtype == RB_F32 && w_dtype == RB_BF16) return launch_qk<float, __nv_bfloat16>(RB_QK_ARGS);
+    if (act_dtype == RB_F32 && w_dtype == RB_F32) return launch_qk<float, float>(RB_QK_ARGS);
+#undef RB_QK_ARGS
+    return RB_ERR_BAD_DTYPE;
+}

@@ -1,0 +1,233 @@
+"""The engine: a model, its cache, and ONE step function.
+
+``step(entries)`` runs exactly the tokens it is given, as one batch, from the cache that
+earlier steps left, and returns the logits at the wanted places.  The sequences of a step
+may have any lengths (whole prompts of unequal length, pieces of prompts, or one token
+each); a step larger than the work space is cut into pieces internally, which changes no
+result.  Steps of one token per sequence are replayed from CUDA graphs captured per batch
+size and context bucket, with the batch padded up to the bucket; padding changes no result
+because padded tokens carry slot -1 and every kernel skips them.
+
+The reference has three entry points for this (one token: rocml/src/forward/mod.rs:246-387;
+a chunk of one prompt: chunk_forward.rs:62-189; the chunk loop: :33-53) and no batch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import SequenceCache
+from ..config import load_model_spec
+from ..errors import CacheError, ConfigError, KernelError, RocmlError
+from ..parts import BuildEnv
+from .batch import BatchBuffers, HostBatch, StepBatch, pack_entries
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def _bucket(n: int, floor: int = 1) -> int:
+    b = floor
+    while b < n:
+        b *= 2
+    return b
+
+
+class Engine:
+    def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
+                 max_step_tokens: int = 4096, use_graphs: bool = True, max_seq_len: Optional[int] = None):
+        self.model = model
+        self.env = model.env
+        self.device = model.env.device
+        self.max_step_tokens = int(max_step_tokens)
+        max_tokens = int(max_tokens)
+        if max_slots is None:
+            max_slots = max(1, min((max_tokens + 63) // 64, 256))
+        self.cache = SequenceCache(
+            model.cache_requirements(), model.reads_cache_of(), max_tokens, max_slots,
+            min(model.spec.max_position, max_seq_len or model.spec.max_position), self.env.act_dtype,
+            self.device, self.max_step_tokens)
+        self.use_graphs = bool(use_graphs) and model.graph_safe and self.device.type == "cuda"
+        self._eager: Dict[Tuple[int, int], BatchBuffers] = {}
+        self._graphs: Dict[Tuple[int, int], dict] = {}
+        self._pool = None
+        self.launches = 0          # steps issued (sub-steps counted)
+        self.last_h2d_bytes = 0
+
+    # ---- construction ----------------------------------------------------------------------------
+    @staticmethod
+    def from_folder(folder: str, dtype: str = "bfloat16", device="cuda:0", **kw) -> "Engine":
+        if dtype not in _DTYPES:
+            raise ConfigError(f"dtype must be one of {sorted(set(_DTYPES))}, found {dtype!r}")
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise KernelError("the engine runs on a CUDA device only; there is no CPU path")
+        spec = load_model_spec(folder)
+        model = Model(spec, BuildEnv(dev, _DTYPES[dtype]))
+        with torch.cuda.device(dev):
+            model.load_folder(folder)
+            return Engine(model, **kw)
+
+    # ---- slots ---------------------------------------------------------------------------------------
+    def new_sequence(self) -> int:
+        return self.cache.alloc_slot()
+
+    def release(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step --------------------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries' tokens; return float32 logits [wanted places, vocab] in the order of
+        the entries and of each entry's ``want`` (None when nothing is wanted).  The tensor may
+        be reused by the next step: read it before stepping again."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries:
+            return None
+        seen = set()
+        vocab = self.model.vocab
+        for e in entries:
+            if e.slot in seen:
+                raise CacheError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if len(e.tokens) == 0:
+                raise RocmlError(f"slot {e.slot}: a step entry needs at least one token")
+            bad = [t for t in e.tokens if not 0 <= int(t) < vocab]
+            if bad:
+                raise RocmlError(f"slot {e.slot}: token id {bad[0]} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise RocmlError(f"slot {e.slot}: wanted place {w} is outside the {len(e.tokens)} tokens given")
+        # room for everything, before anything launches
+        old_lens = [self.cache.grow(e.slot, len(e.tokens)) for e in entries]
+
+        with torch.cuda.device(self.device):
+            total = sum(len(e.tokens) for e in entries)
+            if total <= self.max_step_tokens:
+                pieces = [[(i, 0, len(e.tokens)) for i, e in enumerate(entries)]]
+            else:
+                pieces = self._cut(entries)
+            outs, order = [], []
+            for piece in pieces:
+                slots, olds, toks, wants = [], [], [], []
+                for i, a, b in piece:
+                    e = entries[i]
+                    slots.append(e.slot)
+                    olds.append(old_lens[i] + a)
+                    toks.append(e.tokens[a:b])
+                    w_here = sorted(w for w in set(e.want) if a <= w < b)
+                    wants.append([w - a for w in w_here])
+                    order.extend((i, w) for w in w_here)
+                logits = self._run(slots, olds, toks, wants)
+                for (i, a, b) in piece:
+                    self.cache.commit(entries[i].slot, b - a)
+                if logits is not None:
+                    outs.append(logits)
+            if not outs:
+                return None
+            result = outs[0] if len(outs) == 1 else torch.cat(outs, dim=0)
+            wanted = [(i, w) for i, e in enumerate(entries) for w in e.want]
+            if wanted != order:
+                where = {key: r for r, key in enumerate(order)}
+                idx = torch.tensor([where[k] for k in wanted], dtype=torch.long, device=self.device)
+                result = result.index_select(0, idx)
+            return result
+
+    def _cut(self, entries):
+        """Cut a step that is larger than the work space into pieces of at most
+        max_step_tokens tokens, sequence after sequence, a sequence continuing in the next
+        piece where it was cut (what the reference's chunk loop does for one prompt,
+        rocml/src/forward/chunk_forward.rs:41-51)."""
+        pieces, cur, room = [], [], self.max_step_tokens
+        for i, e in enumerate(entries):
+            a, n = 0, len(e.tokens)
+            while a < n:
+                take = min(room, n - a)
+                cur.append((i, a, a + take))
+                a += take
+                room -= take
+                if room == 0:
+                    pieces.append(cur)
+                    cur, room = [], self.max_step_tokens
+        if cur:
+            pieces.append(cur)
+        return pieces
+
+    # ---- one piece: eager launches or a graph replay ------------------------------------------------------
+    def _run(self, slots, old_lens, token_lists, wants) -> Optional[torch.Tensor]:
+        packed = pack_entries(slots, old_lens, token_lists, wants)
+        token_ids, positions, slot_of_token, cu_q, kv_len, want_rows = packed
+        T, B, W = len(token_ids), len(slots), len(want_rows)
+        q_lens = [len(t) for t in token_lists]
+        is_decode = all(n == 1 for n in q_lens)
+        host = HostBatch(list(slots), q_lens, list(kv_len), list(want_rows))
+        self.cache.flush()
+        self.launches += 1
+        if is_decode and self.use_graphs:
+            return self._run_graph(packed, host, T, B, W)
+        key = (_bucket(T, 64), _bucket(B, 8))
+        if key not in self._eager:
+            self._eager[key] = BatchBuffers(key[0], key[1], key[0], self.device)
+        buf = self._eager[key]
+        buf.fill(*packed, slots, pad_tokens=T, pad_seqs=B, pad_want=W)
+        self.last_h2d_bytes = buf.h2d_bytes
+        batch = self._batch(buf, T, B, W, max(q_lens), max(kv_len), is_decode, host)
+        return self.model.forward(batch, self.cache)
+
+    @staticmethod
+    def _batch(buf: BatchBuffers, T, B, W, max_q, max_kv, is_decode, host, capturing=False) -> StepBatch:
+        return StepBatch(
+            n_tokens=T, n_seqs=B, n_want=W, max_q_len=max_q, max_kv_len=max_kv, is_decode=is_decode,
+            token_ids=buf.token_ids, positions=buf.positions, slot_of_token=buf.slot_of_token,
+            seq_slot=buf.seq_slot, cu_q=buf.cu_q, kv_len=buf.kv_len, want_rows=buf.want_rows, host=host,
+            capturing=capturing)
+
+    def _run_graph(self, packed, host, T, B, W) -> Optional[torch.Tensor]:
+        kv_len = packed[4]
+        b_pad = _bucket(B)
+        ctx_pad = _bucket(max(kv_len), 256)
+        key = (b_pad, ctx_pad)
+        g = self._graphs.get(key)
+        if g is None:
+            g = {"buffers": BatchBuffers(b_pad, b_pad, b_pad, self.device), "graph": None, "logits": None}
+            self._graphs[key] = g
+        buf: BatchBuffers = g["buffers"]
+        buf.fill(*packed, host.seq_slots, pad_tokens=b_pad, pad_seqs=b_pad, pad_want=b_pad)
+        self.last_h2d_bytes = buf.h2d_bytes
+        if g["graph"] is None:
+            # First use of this bucket: run it plainly (this also loads every kernel), then
+            # capture the same launches for the next time.  Capturing executes nothing.
+            batch = self._batch(buf, b_pad, b_pad, b_pad, 1, ctx_pad, True, host)
+            out = self.model.forward(batch, self.cache)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            cap = self._batch(buf, b_pad, b_pad, b_pad, 1, ctx_pad, True, None, capturing=True)
+            with torch.cuda.graph(graph, pool=self._pool):
+                g["logits"] = self.model.forward(cap, self.cache)
+            if self._pool is None:
+                self._pool = graph.pool()
+            g["graph"] = graph
+            return out[:W] if W else None
+        g["graph"].replay()
+        return g["logits"][:W] if W else None
+
+    # ---- facts for measurement --------------------------------------------------------------------------------
+    def kv_bytes_per_token(self) -> int:
+        """Bytes of keys and values one token adds over all layers
+        (rocml/src/budget/mod.rs:47-59: 2 * layers * kv heads * head size * element size)."""
+        n = 0
+        for g in self.cache.kv_groups:
+            n += 2 * g.n_entries * g.req.n_kv_heads * g.req.head_dim * g.k.element_size()
+        return n

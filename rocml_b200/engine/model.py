@@ -1,0 +1,114 @@
+"""A decoder assembled from a ModelSpec: embedding, blocks, the order they run in, final
+norm, head.  It is generic: the architecture lives in the spec, not here.
+
+One forward pass (rocml/src/forward/mod.rs:271-378, chunk_forward.rs:97-188): embedding
+gather into a 32-bit residual stream; the scheduled blocks; the final norm only on the rows
+whose logits are wanted; the head on those rows -> float32 logits.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels
+from ..config.specs import MixerSpec, ModelSpec
+from ..errors import ConfigError
+from ..parts import BuildEnv, build_block, build_norm
+from ..parts.linear import Linear
+from ..weights.decl import TensorDecl
+from ..weights.loader import load_tensors
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, env: BuildEnv):
+        self.spec = spec
+        self.env = env
+        self.hidden = spec.hidden
+        self.vocab = spec.vocab
+        readers = {e.layer for e in spec.schedule if e.reads_cache_of is not None}
+        owners = {e.layer for e in spec.schedule if e.reads_cache_of is None}
+        if readers & owners:
+            raise ConfigError("a layer cannot both keep its own cache and read another's in one schedule")
+        self.blocks = []
+        for i, layer in enumerate(spec.layers):
+            mixer_spec = layer.mixer
+            if i in readers:
+                mixer_spec = MixerSpec(mixer_spec.kind, tuple(sorted({**mixer_spec.params, "shares_cache": True}.items())),
+                                       mixer_spec.position)
+            self.blocks.append(build_block_with(layer, spec.hidden, env, mixer_spec))
+        self.final_norm = build_norm(spec.final_norm, spec.hidden, env)
+        self.head = Linear([spec.head_name[: -len(".weight")]], [spec.vocab], spec.hidden, False, env)
+        self.embed: Optional[torch.Tensor] = None
+        self.status: Optional[torch.Tensor] = None
+
+    # ---- tensors ------------------------------------------------------------------------------
+    def declare(self) -> List[TensorDecl]:
+        out = [TensorDecl(self.spec.embedding_name, (self.vocab, self.hidden), "matrix")]
+        for b in self.blocks:
+            out += b.declare()
+        out += self.final_norm.declare(self.spec.final_norm_name[: -len(".weight")])
+        if not self.spec.tie_embeddings:
+            out += self.head.declare("")
+        return out
+
+    def ignorable(self) -> List[str]:
+        """Tensors a folder may hold that the model does not read: a stored head when the
+        head is tied to the embedding."""
+        return [self.spec.head_name] if self.spec.tie_embeddings else []
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.embed = tensors[self.spec.embedding_name]
+        for b in self.blocks:
+            b.load(tensors)
+        self.final_norm.load(tensors, self.spec.final_norm_name[: -len(".weight")])
+        if self.spec.tie_embeddings:
+            self.head.adopt(self.embed)
+        else:
+            self.head.load(tensors, "")
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.env.device)
+
+    def load_folder(self, folder: str) -> None:
+        self.load(load_tensors(folder, self.declare(), self.env.mode, self.env.device, self.ignorable()))
+
+    # ---- facts ----------------------------------------------------------------------------------
+    @property
+    def graph_safe(self) -> bool:
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+
+    def cache_requirements(self):
+        return [self.blocks[e.layer].mixer.cache_requirement() for e in self.spec.schedule]
+
+    def reads_cache_of(self):
+        return [e.reads_cache_of for e in self.spec.schedule]
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights a step reads once: every scheduled block, the final norm, the head
+        (the embedding rows it gathers are negligible)."""
+        n = sum(self.blocks[e.layer].weight_bytes() for e in self.spec.schedule)
+        return n + self.final_norm.weight_bytes() + self.head.weight_bytes()
+
+    # ---- the pass ---------------------------------------------------------------------------------
+    def forward(self, batch, cache) -> Optional[torch.Tensor]:
+        T = batch.n_tokens
+        resid = torch.empty((T, self.hidden), dtype=torch.float32, device=self.env.device)
+        kernels.embedding(batch.token_ids, self.embed, resid, self.status)
+        pending = None
+        for i, e in enumerate(self.spec.schedule):
+            pending = self.blocks[e.layer].forward(resid, pending, batch, cache.views[i])
+        if batch.n_want == 0:
+            return None
+        xn = self.final_norm.forward(resid, pending, n_rows=batch.n_want, rows=batch.want_rows, write_back=False)
+        logits = torch.empty((batch.n_want, self.vocab), dtype=torch.float32, device=self.env.device)
+        self.head.forward(xn, logits, batch.n_want)
+        return logits
+
+
+def build_block_with(layer, hidden, env, mixer_spec):
+    from ..parts.base import _lookup, _ARRANGEMENTS
+    return _lookup(_ARRANGEMENTS, layer.arrangement, "arrangement")(layer, hidden, env, mixer_spec)
+
+
+def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
+    """The tensors a model of this spec reads from its folder (no device memory is touched)."""
+    return Model(spec, BuildEnv(torch.device("cpu"), torch.bfloat16)).declare()

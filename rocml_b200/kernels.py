@@ -1,0 +1,238 @@
+"""Python face of the CUDA kernel library: one thin function per kernel.
+
+Each function checks devices, element types and layouts, passes raw pointers and the
+current CUDA stream to the C entry point, and turns a non-zero return into
+``KernelError``.  Nothing here computes; there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import library
+from .errors import KernelError
+
+F32, BF16 = 0, 1
+PAGE = 64  # tokens per cache page (RB_PAGE in csrc/common.cuh)
+
+_CODES = {
+    10001: "a size the kernel does not take",
+    10002: "an element type combination that is not built",
+    10003: "a pointer or stride that breaks an alignment rule",
+    10004: "a bounded wait inside a kernel ran out",
+    10005: "a CUDA driver entry point could not be found",
+}
+
+_c = ctypes
+_vp, _i, _ll, _f = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"element type {dt} is not supported by the kernels (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernel arguments must live on a CUDA device; there is no CPU path")
+    return _vp(t.data_ptr())
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        if rc in _CODES:
+            raise KernelError(f"{what}: {_CODES[rc]} (code {rc})")
+        raise KernelError(f"{what}: CUDA error {rc}")
+
+
+def _i32(t: torch.Tensor, name: str):
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+    return _ptr(t)
+
+
+_sigs_done = False
+
+
+def _lib():
+    global _sigs_done
+    lib = library()
+    if not _sigs_done:
+        lib.rb_embedding.argtypes = [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]
+        lib.rb_add_rmsnorm.argtypes = [_vp, _vp, _i, _ll, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp]
+        lib.rb_silu_mul.argtypes = [_vp, _vp, _i, _i, _i, _vp]
+        lib.rb_cast.argtypes = [_vp, _i, _vp, _i, _ll, _vp]
+        lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _vp,
+                                              _vp, _vp, _i, _vp, _vp, _i, _vp]
+        lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _vp]
+        lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
+                                             _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
+        lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
+        lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp]
+        _sigs_done = True
+    return lib
+
+
+# ---- embedding --------------------------------------------------------------------------------
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None):
+    """out[t, :] = float32(table[ids[t], :]); out is [T, H] float32."""
+    T, H = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embedding: out must be contiguous float32, table contiguous")
+    if table.shape[1] != H or ids.numel() < T:
+        raise KernelError("embedding: shapes do not fit")
+    rc = _lib().rb_embedding(_i32(ids, "ids"), _ptr(table), dtype_code(table.dtype), _ptr(out), T, H,
+                             table.shape[0], _ptr(status), _stream())
+    _check(rc, "embedding")
+
+
+# ---- fused residual add + RMSNorm ---------------------------------------------------------------
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+                write_back: bool = True):
+    """resid [T, H] float32 (+= sum of delta [S, T, H] float32); out[i] = rmsnorm(row) * weight.
+
+    With ``rows`` (int32 indices, -1 = skip) output row i comes from source row rows[i]."""
+    T, H = resid.shape
+    if resid.dtype != torch.float32 or not resid.is_contiguous() or not out.is_contiguous():
+        raise KernelError("add_rmsnorm: resid must be contiguous float32, out contiguous")
+    n_delta, stride = 0, 0
+    if delta is not None:
+        if delta.dtype != torch.float32 or not delta.is_contiguous() or delta.dim() != 3 or \
+                delta.shape[1] < T or delta.shape[2] != H:
+            raise KernelError("add_rmsnorm: delta must be contiguous float32 [S, >=T, H]")
+        n_delta, stride = delta.shape[0], delta.stride(0)
+    n = (rows.numel() if rows is not None else T) if n_rows is None else n_rows
+    if out.shape[-1] != H or out.numel() < n * H or weight.numel() != H:
+        raise KernelError("add_rmsnorm: shapes do not fit")
+    rc = _lib().rb_add_rmsnorm(_ptr(resid), _ptr(delta), n_delta, stride, _ptr(weight), dtype_code(weight.dtype),
+                               _ptr(out), dtype_code(out.dtype), None if rows is None else _i32(rows, "rows"),
+                               n, H, float(eps), 1 if write_back else 0, _stream())
+    _check(rc, "add_rmsnorm")
+
+
+def silu_mul(x: torch.Tensor, out: torch.Tensor):
+    """x [T, 2I] = [gate | up] -> out [T, I] = silu(gate) * up."""
+    T, I2 = x.shape
+    if I2 % 2 or out.shape != (T, I2 // 2) or out.dtype != x.dtype or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("silu_mul: shapes or types do not fit")
+    _check(_lib().rb_silu_mul(_ptr(x), _ptr(out), dtype_code(x.dtype), T, I2 // 2, _stream()), "silu_mul")
+
+
+def cast(x: torch.Tensor, out: torch.Tensor):
+    if x.numel() != out.numel() or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("cast: shapes do not fit")
+    _check(_lib().rb_cast(_ptr(x), dtype_code(x.dtype), _ptr(out), dtype_code(out.dtype), x.numel(), _stream()), "cast")
+
+
+# ---- q/k norm + rotary + cache write --------------------------------------------------------------
+
+def qk_norm_rope_cache(qkv: torch.Tensor, n_tokens: int, nq: int, nkv: int, hd: int,
+                       q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                       inv_freq: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
+                       slot_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], write_kv: bool = True):
+    """qkv [T, nq*hd (+ 2*nkv*hd)]: q normalised and rotated in place; k, v written to their pages."""
+    width = (nq + (2 * nkv if write_kv else 0)) * hd
+    if qkv.dim() != 2 or qkv.shape[1] != width or qkv.stride(1) != 1:
+        raise KernelError(f"qk_norm_rope_cache: qkv must be [T, {width}] with unit inner stride")
+    if (q_norm_w is None) != (k_norm_w is None):
+        raise KernelError("qk_norm_rope_cache: give both norm weights or neither")
+    wd = dtype_code(q_norm_w.dtype) if q_norm_w is not None else F32
+    if q_norm_w is not None and (k_norm_w.dtype != q_norm_w.dtype or q_norm_w.numel() != hd or k_norm_w.numel() != hd):
+        raise KernelError("qk_norm_rope_cache: norm weights must share a type and be [head_dim]")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("qk_norm_rope_cache: inv_freq must be float32 [rot_dim / 2]")
+    if write_kv:
+        if k_cache is None or v_cache is None or block_table is None:
+            raise KernelError("qk_norm_rope_cache: cache tensors missing")
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or not k_cache.is_contiguous() or \
+                tuple(k_cache.shape[1:]) != (nkv, PAGE, hd):
+            raise KernelError("qk_norm_rope_cache: cache must be [pages, nkv, 64, hd] of the activations' type")
+    max_pages = block_table.shape[1] if block_table is not None else 0
+    rc = _lib().rb_qk_norm_rope_cache(
+        _ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0), n_tokens, nq, nkv, hd, _ptr(q_norm_w), _ptr(k_norm_w), wd,
+        float(eps), _ptr(inv_freq), rot_dim, _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
+        None if block_table is None else _i32(block_table, "block_table"), max_pages, _ptr(k_cache), _ptr(v_cache),
+        1 if write_kv else 0, _stream())
+    _check(rc, "qk_norm_rope_cache")
+
+
+# ---- matrix products ---------------------------------------------------------------------------------
+
+def gemm_generic(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 m: Optional[int] = None):
+    """out[M, N] = x[M, K] . w[N, K]^T (+ bias float32 [N]) on the CUDA cores, 32-bit accumulation."""
+    M = x.shape[0] if m is None else m
+    N, K = w.shape
+    if x.shape[1] != K or out.shape[1] != N or x.stride(1) != 1 or out.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError("gemm_generic: shapes or strides do not fit")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_generic: bias must be float32 [N]")
+    rc = _lib().rb_gemm_generic(_ptr(x), dtype_code(x.dtype), _ptr(w), dtype_code(w.dtype), _ptr(bias), _ptr(out),
+                                dtype_code(out.dtype), M, N, K, x.stride(0), out.stride(0), _stream())
+    _check(rc, "gemm_generic")
+
+
+# ---- attention ------------------------------------------------------------------------------------------
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                      n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
+                      chunk: int = 0, n_chunks: int = 1, part_acc: Optional[torch.Tensor] = None,
+                      part_ml: Optional[torch.Tensor] = None):
+    """q rows [T, >= nq*hd] (row stride free) -> out rows [T, >= nq*hd]; keys and values from the pages."""
+    if q.stride(-1) != 1 or out.stride(-1) != 1 or q.dtype != out.dtype or k_cache.dtype != q.dtype:
+        raise KernelError("attention_generic: strides or types do not fit")
+    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+        raise KernelError("attention_generic: cache must be [pages, nkv, 64, hd]")
+    rc = _lib().rb_attention_generic(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), dtype_code(q.dtype), _ptr(k_cache), _ptr(v_cache),
+        _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
+        _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(chunk),
+        int(n_chunks), _ptr(part_acc), _ptr(part_ml), _stream())
+    _check(rc, "attention_generic")
+
+
+def attention_merge(part_acc: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                    slot_of_token: torch.Tensor, n_tokens: int, nq: int, hd: int, chunk: int, n_chunks: int,
+                    window: int = 0):
+    rc = _lib().rb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), out.stride(0), dtype_code(out.dtype),
+                                   _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"), n_tokens,
+                                   nq, hd, chunk, n_chunks, int(window), _stream())
+    _check(rc, "attention_merge")
+
+
+# ---- sampling ---------------------------------------------------------------------------------------------
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
+    """out[r] = index of the first largest value of logits[r, :]; logits float32 [R, V]."""
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32:
+        raise KernelError("argmax: logits float32 with unit inner stride, out int32")
+    R = logits.shape[0] if rows is None else rows
+    _check(_lib().rb_argmax(_ptr(logits), logits.stride(0), R, logits.shape[1], _ptr(out), _stream()), "argmax")
+
+
+# ---- tensor-core matrix product (tcgen05) ----------------------------------------------------------------
+
+def gemm_tensor_core_available() -> bool:
+    """True once the tcgen05 kernel is part of the built library."""
+    return hasattr(_lib(), "rb_gemm_tcgen05")
+
+
+def gemm_tcgen05(x, w, out, bias=None, m=None) -> bool:
+    """Placeholder until the tcgen05 kernel is bound; returns False so callers use the plain kernel."""
+    return False

@@ -1,0 +1,119 @@
+"""Grouped-query softmax attention over the paged cache.
+
+Order, as in the reference (rocml/src/forward/attention.rs:56-244, attention_chunk.rs:
+75-325): q, k, v projections (one stacked product) -> per-head RMSNorm of q and k, not v
+-> position encoding of q and k -> k, v written to the cache -> attention of every query
+over its sequence's keys at positions <= its own (and inside the window, if the layer has
+one) -> output projection.  The result is returned as a delta for the residual stream.
+
+Sizes and constants (heads, groups, head size, biases, q/k norm and its eps, window, scale)
+are parameters; a layer that reads another layer's cache projects only q.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels
+from ..cache.requirements import KVRequirement
+from ..config.specs import MixerSpec
+from ..errors import ConfigError
+from ..weights.decl import TensorDecl
+from .base import BuildEnv, Mixer, build_position, register_mixer
+from .linear import Linear
+
+DECODE_CHUNK = 128  # keys per split of decode attention; fixed, so a row's sums never depend on the batch
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec: MixerSpec, hidden: int, env: BuildEnv):
+        p = spec.params
+        self.env = env
+        self.hidden = hidden
+        self.nq = int(p["n_heads"])
+        self.nkv = int(p["n_kv_heads"])
+        self.hd = int(p["head_dim"])
+        if self.nq <= 0 or self.nkv <= 0 or self.nq % self.nkv:
+            raise ConfigError(f"{self.nq} query heads cannot be grouped over {self.nkv} key/value heads")
+        if self.hd % 16 or self.hd > 256:
+            raise ConfigError(f"head size {self.hd} is not supported: multiples of 16 up to 256")
+        self.bias = bool(p.get("bias", False))
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
+        self.window = p.get("window")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
+        self.shares_cache = bool(p.get("shares_cache", False))  # set by the model for a reading layer
+        self.position = build_position(spec.position, self.hd, env)
+        qd, kvd = self.nq * self.hd, self.nkv * self.hd
+        if self.shares_cache:
+            self.qkv = Linear(["q_proj"], [qd], hidden, self.bias, env)
+        else:
+            self.qkv = Linear(["q_proj", "k_proj", "v_proj"], [qd, kvd, kvd], hidden, self.bias, env)
+        self.o = Linear(["o_proj"], [hidden], qd, self.bias, env)
+        self.q_norm_w: Optional[torch.Tensor] = None
+        self.k_norm_w: Optional[torch.Tensor] = None
+
+    def cache_requirement(self):
+        return KVRequirement(self.nkv, self.hd, self.window)
+
+    def declare(self, prefix: str) -> List[TensorDecl]:
+        out = self.qkv.declare(prefix) + self.o.declare(prefix)
+        if self.qk_norm:
+            out.append(TensorDecl(f"{prefix}q_norm.weight", (self.hd,), "norm"))
+            if not self.shares_cache:
+                out.append(TensorDecl(f"{prefix}k_norm.weight", (self.hd,), "norm"))
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
+        self.qkv.load(tensors, prefix)
+        self.o.load(tensors, prefix)
+        if self.qk_norm:
+            self.q_norm_w = tensors[f"{prefix}q_norm.weight"]
+            self.k_norm_w = self.q_norm_w if self.shares_cache else tensors[f"{prefix}k_norm.weight"]
+            if self.k_norm_w.dtype != self.q_norm_w.dtype:
+                self.q_norm_w, self.k_norm_w = self.q_norm_w.float(), self.k_norm_w.float()
+
+    def weight_bytes(self) -> int:
+        return self.qkv.weight_bytes() + self.o.weight_bytes()
+
+    def forward(self, xn, batch, view):
+        T = batch.n_tokens
+        dev, act = xn.device, self.env.act_dtype
+        qd = self.nq * self.hd
+        qkv = torch.empty((T, self.qkv.n), dtype=act, device=dev)
+        self.qkv.forward(xn, qkv, T)
+        kernels.qk_norm_rope_cache(
+            qkv, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+            self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
+            view.block_table, view.k, view.v, write_kv=view.writes and not self.shares_cache)
+        attn = torch.empty((T, qd), dtype=act, device=dev)
+        window = int(self.window) if self.window else 0
+        self.attend(qkv, attn, batch, view, window)
+        delta = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
+        self.o.forward(attn, delta[0], T)
+        return delta
+
+    def attend(self, q, out, batch, view, window):
+        """Softmax attention of the step's queries over the cache.  One token per sequence:
+        keys split in fixed chunks, partial results merged; otherwise whole rows."""
+        if batch.is_decode:
+            chunk = DECODE_CHUNK
+            n_chunks = max(1, (batch.max_kv_len + chunk - 1) // chunk)
+            if n_chunks > 1:
+                T = batch.n_tokens
+                acc = torch.empty((T, self.nq, n_chunks, self.hd), dtype=torch.float32, device=q.device)
+                ml = torch.empty((T, self.nq, n_chunks, 2), dtype=torch.float32, device=q.device)
+                kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
+                                          batch.kv_len, batch.n_seqs, 1, self.nq, self.nkv, self.hd, self.scale,
+                                          window, chunk, n_chunks, acc, ml)
+                kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, self.nq, self.hd,
+                                        chunk, n_chunks, window)
+                return
+        kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
+                                  batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,
+                                  self.scale, window)

@@ -1,0 +1,57 @@
+"""How a layer's parts are arranged."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..config.specs import LayerSpec
+from ..weights.decl import TensorDecl
+from .base import BuildEnv, build_feed_forward, build_mixer, build_norm, register_arrangement
+
+
+@register_arrangement("pre_norm")
+class PreNormBlock:
+    """x += mixer(norm1(x)); x += ff(norm2(x)) (rocml/src/forward/mod.rs:281-340).
+
+    The additions are not done here: each part's result travels on as a *delta*, and the
+    next norm adds it into the 32-bit residual stream in the same kernel that normalises.
+    ``forward`` therefore takes the delta still pending from the layer before and returns
+    its own feed-forward's delta."""
+
+    def __init__(self, spec: LayerSpec, hidden: int, env: BuildEnv, mixer_spec=None):
+        self.spec = spec
+        self.prefix = spec.prefix
+        self.mixer_norm = build_norm(spec.mixer_norm, hidden, env)
+        self.mixer = build_mixer(mixer_spec or spec.mixer, hidden, env)
+        self.ff_norm = build_norm(spec.ff_norm, hidden, env)
+        self.ff = build_feed_forward(spec.feed_forward, hidden, env)
+
+    # Tensor names of the Hugging Face layout: norms beside the parts they precede.
+    def _names(self):
+        p = self.prefix
+        return (f"{p}.input_layernorm", f"{p}.self_attn.", f"{p}.post_attention_layernorm", f"{p}.mlp.")
+
+    def declare(self) -> List[TensorDecl]:
+        n1, mx, n2, ff = self._names()
+        return self.mixer_norm.declare(n1) + self.mixer.declare(mx) + self.ff_norm.declare(n2) + self.ff.declare(ff)
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n1, mx, n2, ff = self._names()
+        self.mixer_norm.load(tensors, n1)
+        self.mixer.load(tensors, mx)
+        self.ff_norm.load(tensors, n2)
+        self.ff.load(tensors, ff)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff))
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff))
+
+    def forward(self, resid, pending, batch, view):
+        xn = self.mixer_norm.forward(resid, pending, batch.n_tokens)
+        delta = self.mixer.forward(xn, batch, view)
+        xn = self.ff_norm.forward(resid, delta, batch.n_tokens)
+        return self.ff.forward(xn, batch)

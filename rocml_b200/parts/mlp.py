@@ -1,0 +1,55 @@
+"""Gated feed-forward: down(act(gate(x)) * up(x)) (rocml/src/forward/ffn.rs:57-107)."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels
+from ..config.specs import FeedForwardSpec
+from ..errors import ConfigError
+from ..weights.decl import TensorDecl
+from .base import BuildEnv, FeedForward, register_feed_forward
+from .linear import Linear
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    """gate and up are one stacked product [T, 2I]; SiLU(gate) * up -> [T, I]; down -> [T, H].
+    The activation is a parameter; 'silu' (g / (1 + exp(-g)), rocml-kernels/kernels/
+    silu_mul.hip:15-18) is the one built."""
+
+    graph_safe = True
+
+    def __init__(self, spec: FeedForwardSpec, hidden: int, env: BuildEnv):
+        p = spec.params
+        self.env = env
+        self.hidden = hidden
+        self.inter = int(p["intermediate"])
+        act = p.get("activation", "silu")
+        if act != "silu":
+            raise ConfigError(f"activation {act!r} is not built (only 'silu')")
+        bias = bool(p.get("bias", False))
+        self.gate_up = Linear(["gate_proj", "up_proj"], [self.inter, self.inter], hidden, bias, env)
+        self.down = Linear(["down_proj"], [hidden], self.inter, bias, env)
+
+    def declare(self, prefix: str) -> List[TensorDecl]:
+        return self.gate_up.declare(prefix) + self.down.declare(prefix)
+
+    def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
+        self.gate_up.load(tensors, prefix)
+        self.down.load(tensors, prefix)
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.weight_bytes() + self.down.weight_bytes()
+
+    def forward(self, xn, batch):
+        T = batch.n_tokens
+        dev, act = xn.device, self.env.act_dtype
+        gu = torch.empty((T, 2 * self.inter), dtype=act, device=dev)
+        self.gate_up.forward(xn, gu, T)
+        h = torch.empty((T, self.inter), dtype=act, device=dev)
+        kernels.silu_mul(gu, h)
+        delta = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
+        self.down.forward(h, delta[0], T)
+        return delta

@@ -1,0 +1,78 @@
+"""Weights from a model folder, by tensor name.
+
+The model declares the tensors it needs (``TensorDecl``); the loader checks the
+whole folder against the declaration first and raises ONE ``WeightsError`` that
+lists every missing tensor, every unexpected tensor and every wrong shape, then
+moves the tensors to the device under the storage rule:
+
+* ``bfloat16`` mode: floating tensors are kept in bfloat16 (float16 is converted);
+  a tensor the file stores in 32-bit stays 32-bit; integer tables become int32.
+* ``float32`` mode: every floating tensor is widened to float32 (exact for
+  bfloat16 and float16 values).
+
+The reference does the same job for GGUF: look each tensor up by name, check its
+shape, convert, upload (rocml/src/weights/mod.rs:37-175, weights/layer.rs:34-64).
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, Iterable, Sequence
+
+import torch
+
+from ..errors import WeightsError
+from .decl import TensorDecl
+from .safetensors_io import ModelFiles
+
+_FLOATS = (torch.float64, torch.float32, torch.float16, torch.bfloat16)
+_INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
+
+
+def storage_dtype(file_dtype: torch.dtype, mode: str, role: str) -> torch.dtype:
+    if role == "int_table" or file_dtype in _INTS:
+        return torch.int32
+    if mode == "float32":
+        return torch.float32
+    if mode != "bfloat16":
+        raise ValueError(f"dtype mode must be 'bfloat16' or 'float32', found {mode!r}")
+    if file_dtype in (torch.float32, torch.float64):
+        return torch.float32
+    return torch.bfloat16
+
+
+def check_against(decls: Sequence[TensorDecl], names: Iterable[str], shape_of: Callable[[str], tuple],
+                  ignorable: Iterable[str] = ()) -> None:
+    """Raise one WeightsError listing everything that does not fit."""
+    have = set(names)
+    want = {d.name: d for d in decls}
+    ignorable = set(ignorable)
+    missing = sorted(n for n in want if n not in have)
+    unexpected = sorted(n for n in have if n not in want and n not in ignorable)
+    wrong = []
+    for n, d in want.items():
+        if n in have and tuple(shape_of(n)) != tuple(d.shape):
+            wrong.append((n, tuple(d.shape), tuple(shape_of(n))))
+    if missing or unexpected or wrong:
+        raise WeightsError(missing, unexpected, sorted(wrong))
+
+
+def load_tensors(folder: str, decls: Sequence[TensorDecl], mode: str, device,
+                 ignorable: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
+    """name -> device tensor for every declared tensor of the folder."""
+    with ModelFiles(folder) as files:
+        check_against(decls, files.names(), files.shape, ignorable)
+        bad_dtype = []
+        for d in decls:
+            ft = files.dtype(d.name)
+            if d.role == "int_table":
+                if ft not in _INTS:
+                    bad_dtype.append(f"{d.name}: integer table stored as {ft}")
+            elif ft not in _FLOATS:
+                bad_dtype.append(f"{d.name}: stored as {ft}, expected a floating type")
+        if bad_dtype:
+            raise WeightsError(other=bad_dtype)
+        out = {}
+        for d in decls:
+            t = files.tensor(d.name)
+            dt = storage_dtype(t.dtype, mode, d.role)
+            out[d.name] = t.to(device=device, dtype=dt, non_blocking=False).contiguous()
+        return out

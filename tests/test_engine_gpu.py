@@ -1,0 +1,121 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16: each request alone
+and whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter
+requests end earlier, one batch after another so that slots are used again."""
+import pytest
+import torch
+
+from tiny_models import CONFIGS, prompt, write_model
+
+pytestmark = pytest.mark.gpu
+
+# Tolerances, as a fraction of the largest |logit| of the row compared.
+# float32: sums of a few hundred float32 terms in another order than the plain implementation
+# (2^-24 per operation, a few thousand operations deep) stay below 1e-5 of the row's scale.
+# bfloat16: activations are rounded to 8 bits of mantissa (2^-9 relative) between kernels,
+# a dozen roundings per layer; 2e-2 of the row's scale bounds that for these depths.
+TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
+
+
+def rel_err(got, want):
+    want = want.to(torch.float64)
+    got = got.to(torch.float64).cpu()
+    scale = want.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
+    return float(((got - want).abs() / scale).max())
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def model_folder(request, tmp_path_factory):
+    name = request.param
+    folder = tmp_path_factory.mktemp(f"tiny_{name}")
+    write_model(str(folder), CONFIGS[name], seed=11 + ord(name), std=0.05)
+    return name, str(folder)
+
+
+@pytest.fixture(scope="module")
+def plain(model_folder):
+    from plain_qwen3 import PlainQwen3
+    return PlainQwen3(model_folder[1], dtype=torch.float64)
+
+
+def lengths_for(name):
+    maxp = CONFIGS[name]["max_position_embeddings"]
+    return [n for n in (1, 7, 33, 64, 65, 100, 129, 200, 256, 300) if n <= maxp]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_prompts(model_folder, plain, dtype):
+    from rocml_b200 import Engine, StepEntry
+    name, folder = model_folder
+    vocab = CONFIGS[name]["vocab_size"]
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024)
+    for n in lengths_for(name):
+        ids = prompt(n, n, vocab)
+        slot = eng.new_sequence()
+        got = eng.step([StepEntry(slot, ids, list(range(n)))])
+        eng.release(slot)
+        assert got.shape == (n, vocab)
+        err = rel_err(got, plain.logits(ids))
+        assert err < TOL[dtype], f"{name} {dtype} n={n}: {err}"
+    eng.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_last_32_one_by_one(model_folder, plain, dtype, graphs):
+    from rocml_b200 import Engine, StepEntry
+    name, folder = model_folder
+    vocab = CONFIGS[name]["vocab_size"]
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024, use_graphs=graphs)
+    for n in [m for m in lengths_for(name) if m > 32][:4]:
+        ids = prompt(100 + n, n, vocab)
+        want = plain.logits(ids)
+        slot = eng.new_sequence()
+        head = n - 32
+        got = [eng.step([StepEntry(slot, ids[:head], [head - 1])]).clone()]
+        for t in range(head, n):
+            got.append(eng.step([StepEntry(slot, [ids[t]], [0])]).clone())
+        eng.release(slot)
+        got = torch.cat(got, dim=0)
+        err = rel_err(got, want[head - 1:])
+        assert err < TOL[dtype], f"{name} {dtype} n={n} graphs={graphs}: {err}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_batches_and_slot_reuse(model_folder, plain, dtype):
+    """Batches of unequal prompts, then one token each; shorter requests end earlier; a second
+    and third batch reuse the slots and pages of the first."""
+    from rocml_b200 import Engine, StepEntry
+    name, folder = model_folder
+    vocab = CONFIGS[name]["vocab_size"]
+    maxp = CONFIGS[name]["max_position_embeddings"]
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024)
+    rounds = [[(5, 8), (70, 3), (17, 12), (1, 5)], [(64, 4), (2, 9), (33, 1)], [(90, 6), (90, 2)]]
+    for r, batch in enumerate(rounds):
+        seqs = []
+        for j, (plen, ndec) in enumerate(batch):
+            total = min(plen + ndec, maxp)
+            ids = prompt(1000 * r + j, total, vocab)
+            seqs.append({"ids": ids, "plen": min(plen, total - 1), "slot": eng.new_sequence(),
+                         "want": plain.logits(ids), "got": []})
+        out = eng.step([StepEntry(s["slot"], s["ids"][:s["plen"]], [s["plen"] - 1]) for s in seqs])
+        for i, s in enumerate(seqs):
+            s["got"].append(out[i].clone())
+            s["pos"] = s["plen"]
+        live = list(seqs)
+        while live:
+            done = [s for s in live if s["pos"] >= len(s["ids"])]
+            for s in done:
+                eng.release(s["slot"])
+            live = [s for s in live if s["pos"] < len(s["ids"])]
+            if not live:
+                break
+            out = eng.step([StepEntry(s["slot"], [s["ids"][s["pos"]]], [0]) for s in live])
+            for i, s in enumerate(live):
+                s["got"].append(out[i].clone())
+                s["pos"] += 1
+        for j, s in enumerate(seqs):
+            got = torch.stack(s["got"])
+            err = rel_err(got, s["want"][s["plen"] - 1:])
+            assert err < TOL[dtype], f"{name} {dtype} round {r} seq {j}: {err}"
+        eng.cache.check_invariants()
+    assert eng.cache.slots.n_held == 0
