@@ -71,7 +71,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         const int r = idx / hd, d = idx - r * hd;
         const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
         float v = 0.f;
-        if (qi < q_len && hg < g)
+        if (r < QB * HG && qi < q_len && hg < g)
             v = to_f32(q[(size_t)(q0 + qi) * q_stride + (size_t)(kvh * g + hg) * hd + d]);
         q_s[idx] = v;
     }
@@ -83,7 +83,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     for (int i = 0; i < RW; ++i) {
         const int r = warp * RW + i;
         const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
-        row_ok[i] = qi < q_len && hg < g;
+        row_ok[i] = r < QB * HG && qi < q_len && hg < g;
         row_pos[i] = pos0 + qi;
         row_lo[i] = window > 0 ? max(0, row_pos[i] - window + 1) : 0;
         m[i] = NEG_BIG;
