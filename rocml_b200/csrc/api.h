@@ -26,6 +26,10 @@ int rb_qk_norm_rope_cache(void* qkv, int act_dtype, int row_stride, int T, int n
 int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, void* out,
                     int out_dtype, int M, int N, int K, long long ldx, long long ldo, void* stream);
 
+int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M, int N,
+                    int K, long long ldx, long long ldo, int splits, long long split_stride, int* status,
+                    void* stream);
+
 int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, int dtype, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
                          const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd,

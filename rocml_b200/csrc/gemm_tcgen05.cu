@@ -1,0 +1,333 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//     out[M, N] = x[M, K] . W[N, K]^T (+ bias), float32 accumulation in tensor memory.
+//
+// Both operands are K-major, so one kernel serves both shapes of the engine by choosing which
+// operand sits on the 128-row side of the MMA:
+//   * many tokens (prefill):  A = x (128 tokens per tile),   B = W (BN features per tile)
+//   * few tokens  (decode):   A = W (128 features per tile), B = x (BN >= tokens, 16..128)
+//     so that the weights, which are all the traffic, stream through full-height MMAs while
+//     the handful of tokens sits on the N side; the tile is written back transposed.
+// Per CTA: warp 0 issues TMA loads into a ring of shared-memory stages (128-byte swizzle),
+// warp 1 allocates tensor memory and issues tcgen05.mma (one elected thread), warps 2-5 read
+// the accumulator with tcgen05.ld and store.  K can be split over blockIdx.z; each split
+// writes its own float32 partial result (the consumer sums them in a fixed order).
+//
+// It stands where the reference has gemv_f16 (decode) and gemm_xwt_f16 (prefill):
+// rocml-kernels/kernels/gemv_f16.hip:8-36, gemm_f16.hip:10-41.
+#include "common.cuh"
+#include "sm100.cuh"
+#include "api.h"
+#include <mutex>
+#include <unordered_map>
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;      // rows of the A operand per tile (UMMA M)
+constexpr int BK = 64;       // bf16 elements per stage row: 128 bytes, one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+template <int BN>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int B_STRIDE = (B_BYTES + 1023) / 1024 * 1024;  // keep every stage 1024-aligned
+    static constexpr int STAGE = A_BYTES + B_STRIDE;
+    static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE;
+    static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+struct Params {
+    int a_rows, b_rows, K;        // extents of the A-side and B-side operands
+    int k_per_split;              // multiple of BK
+    long long ldo;                // row stride of out, in elements
+    long long split_stride;       // elements between the partial results of two splits
+    const float* bias;            // [features] or null; added by split 0 only
+    int* status;
+};
+
+template <int BN, bool SWAP, typename OT>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    OT* __restrict__ out, const Params p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_ready = empty + C::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * BM;   // first row of the A-side operand in this tile
+    const int b0 = blockIdx.y * BN;   // first row of the B-side operand
+    const int k_begin = blockIdx.z * p.k_per_split;
+    const int k_end = min(p.K, k_begin + p.k_per_split);
+    const int n_kb = (k_end - k_begin + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&map_a);
+            tma_prefetch_desc(&map_b);
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < n_kb && ok; ++kb) {
+                const int s = kb % C::STAGES;
+                const uint32_t ph = (kb / C::STAGES) & 1;
+                ok = mbar_wait(&empty[s], ph ^ 1);
+                if (!ok) break;
+                uint8_t* sa = smem + s * C::STAGE;
+                mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
+                tma_load_2d(sa, &map_a, k_begin + kb * BK, a0, &full[s]);
+                tma_load_2d(sa + C::A_BYTES, &map_b, k_begin + kb * BK, b0, &full[s]);
+                ++issued;
+            }
+            if (!ok) {
+                atomicExch(p.status, RB_ERR_TIMEOUT);
+                atomicExch(abort_flag, 1u);
+                // wait (bounded) for the copies this thread still has in flight
+                const int first = issued > C::STAGES ? issued - C::STAGES : 0;
+                for (int kb = first; kb < issued; ++kb)
+                    mbar_wait(&full[kb % C::STAGES], (kb / C::STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int s = kb % C::STAGES;
+                const uint32_t ph = (kb / C::STAGES) & 1;
+                ok = mbar_wait(&full[s], ph);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * C::STAGE);
+                const uint64_t adesc = smem_desc_sw128(sa);
+                const uint64_t bdesc = smem_desc_sw128(sa + C::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // advancing 16 elements (32 bytes) inside the swizzle atom: +2 in 16-byte units
+                    mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(&empty[s]);   // the stage is free once these MMAs have read it
+            }
+            if (!ok) {
+                atomicExch(p.status, RB_ERR_TIMEOUT);
+                atomicExch(abort_flag, 1u);
+            }
+            mma_commit(acc_ready);       // completes when everything issued has finished
+        }
+    } else {
+        // epilogue warps 2..5: warp w may read TMEM lanes 32 * (w % 4) .. + 31
+        const int quarter = warp & 3;
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0));  // warp-uniform
+        tc_fence_after();
+        const bool aborted = !ok || *(volatile uint32_t*)abort_flag != 0;
+        if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
+        if (!aborted && n_kb > 0) {
+            const int ar = a0 + quarter * 32 + lane;   // this thread's row of the A-side operand
+            OT* o = out + (size_t)blockIdx.z * p.split_stride;
+            const bool add_bias = p.bias != nullptr && blockIdx.z == 0;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                float v[16];
+                tmem_ld16(lane_addr + c * 16, v);
+                if (SWAP) {
+                    // A side = features, B side = tokens: out[token][feature]
+                    const float bv = (add_bias && ar < p.a_rows) ? p.bias[ar] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int tok = b0 + c * 16 + i;
+                        if (tok < p.b_rows && ar < p.a_rows)
+                            o[(size_t)tok * p.ldo + ar] = rb::from_f32<OT>(v[i] + bv);
+                    }
+                } else {
+                    // A side = tokens, B side = features: out[token][feature]
+                    if (ar < p.a_rows) {
+                        OT* row = o + (size_t)ar * p.ldo;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int f = b0 + c * 16 + i;
+                            if (f < p.b_rows) row[f] = rb::from_f32<OT>(v[i] + (add_bias ? p.bias[f] : 0.f));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+// ---- host side -------------------------------------------------------------------------------------
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long long rows, K, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.K;
+        h = h * 1000003u ^ (size_t)k.ld;
+        return h * 1000003u ^ (size_t)k.box_rows;
+    }
+};
+
+// A [rows, K] bf16 matrix with row stride `ld` elements, read in boxes of box_rows x 64 with the
+// 128-byte swizzle.  Rows and columns outside the matrix read as zero.  Maps are cached: a
+// weight's map is built once.
+int tensor_map(const void* ptr, long long rows, long long K, long long ld, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{ptr, rows, K, ld, box_rows};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return RB_OK; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return RB_ERR_NO_DRIVER_FN;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return RB_ERR_BAD_SIZE;
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 65536) cache.clear();
+    cache[key] = *out;
+    return RB_OK;
+}
+
+template <int BN, bool SWAP, typename OT>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const Params& p, int splits, cudaStream_t s) {
+    using C = Cfg<BN>;
+    auto k = gemm_tcgen05_kernel<BN, SWAP, OT>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    dim3 grid((p.a_rows + BM - 1) / BM, (p.b_rows + BN - 1) / BN, splits);
+    if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
+    k<<<grid, 192, C::SMEM, s>>>(ma, mb, (OT*)out, p);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+template <bool SWAP, typename OT>
+int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out, const Params& p, int splits,
+                cudaStream_t s) {
+    switch (bn) {
+        case 16: return launch<16, SWAP, OT>(ma, mb, out, p, splits, s);
+        case 32: return launch<32, SWAP, OT>(ma, mb, out, p, splits, s);
+        case 64: return launch<64, SWAP, OT>(ma, mb, out, p, splits, s);
+        case 128: return launch<128, SWAP, OT>(ma, mb, out, p, splits, s);
+        case 256: return launch<256, SWAP, OT>(ma, mb, out, p, splits, s);
+    }
+    return RB_ERR_BAD_SIZE;
+}
+
+}  // namespace
+
+// out[M, N] (+ splits) = x[M, K] . w[N, K]^T.  x, w bfloat16; out bfloat16 or float32.
+// splits > 1: float32 partial results at out + z * split_stride, bias in split 0.
+// Refuses (RB_ERR_BAD_ALIGN) what TMA cannot address: K or ldx not a multiple of 8 elements,
+// or a base pointer off a 16-byte boundary; the caller then uses the plain kernel.
+extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
+                               int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
+                               int* status, void* stream) {
+    if (M <= 0 || N <= 0) return RB_OK;
+    if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
+    if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
+    if (splits > 1 && out_dtype != RB_F32) return RB_ERR_BAD_DTYPE;
+    const int kb_total = (K + BK - 1) / BK;
+    if (splits > kb_total) splits = kb_total;
+    const int kb_per = (kb_total + splits - 1) / splits;
+    if ((long long)(splits - 1) * kb_per >= kb_total) return RB_ERR_BAD_SIZE;  // a split would be empty
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool swap = M <= 128;
+    int bn;
+    if (swap) bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+    else bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
+    Params p;
+    p.K = K;
+    p.k_per_split = kb_per * BK;
+    p.ldo = ldo;
+    p.split_stride = split_stride;
+    p.bias = bias;
+    p.status = status;
+    CUtensorMap ma, mb;
+    int rc;
+    if (swap) {
+        p.a_rows = N; p.b_rows = M;
+        if ((rc = tensor_map(w, N, K, K, BM, &ma)) != RB_OK) return rc;
+        if ((rc = tensor_map(x, M, K, ldx, bn, &mb)) != RB_OK) return rc;
+    } else {
+        p.a_rows = M; p.b_rows = N;
+        if ((rc = tensor_map(x, M, K, ldx, BM, &ma)) != RB_OK) return rc;
+        if ((rc = tensor_map(w, N, K, K, bn, &mb)) != RB_OK) return rc;
+    }
+    if (out_dtype == RB_BF16)
+        return swap ? dispatch_bn<true, __nv_bfloat16>(bn, ma, mb, out, p, splits, s)
+                    : dispatch_bn<false, __nv_bfloat16>(bn, ma, mb, out, p, splits, s);
+    if (out_dtype == RB_F32)
+        return swap ? dispatch_bn<true, float>(bn, ma, mb, out, p, splits, s)
+                    : dispatch_bn<false, float>(bn, ma, mb, out, p, splits, s);
+    return RB_ERR_BAD_DTYPE;
+}

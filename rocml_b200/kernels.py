@@ -80,6 +80,7 @@ def _lib():
                                              _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
         lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
         lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp, _vp]
         _sigs_done = True
     return lib
 
@@ -228,11 +229,51 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
 
 # ---- tensor-core matrix product (tcgen05) ----------------------------------------------------------------
 
-def gemm_tensor_core_available() -> bool:
-    """True once the tcgen05 kernel is part of the built library."""
-    return hasattr(_lib(), "rb_gemm_tcgen05")
+_status = {}
 
 
-def gemm_tcgen05(x, w, out, bias=None, m=None) -> bool:
-    """Placeholder until the tcgen05 kernel is bound; returns False so callers use the plain kernel."""
-    return False
+def status_word(device) -> torch.Tensor:
+    """One int32 per device where kernels record a bounded wait that ran out (or a bad token id)."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Read the device's status word (this synchronises) and raise if a kernel recorded a failure."""
+    key = torch.device(device).index or 0
+    if key in _status:
+        v = int(_status[key].item())
+        if v != 0:
+            _status[key].zero_()
+            raise KernelError(f"a kernel reported failure: {_CODES.get(v, 'code ' + str(v))} (code {v})")
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 m: Optional[int] = None) -> bool:
+    """out = x . w^T on the tensor cores; x, w bfloat16, out bfloat16 [M, N] or float32 [M, N] or
+    float32 [S, M, N] (S partial sums over K, to be added by the consumer).  Returns False when the
+    kernel refuses the layout (K or a row stride not a multiple of 8, a pointer off 16 bytes);
+    the caller then uses the plain kernel."""
+    M = x.shape[0] if m is None else m
+    N, K = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
+            or x.shape[1] != K:
+        raise KernelError("gemm_tcgen05: x and w must be bfloat16, K-major, with matching K")
+    if out.dim() == 3:
+        splits, split_stride, ldo = out.shape[0], out.stride(0), out.stride(1)
+        if out.shape[2] != N or out.stride(2) != 1 or out.dtype != torch.float32:
+            raise KernelError("gemm_tcgen05: partial output must be float32 [S, M, N]")
+    else:
+        splits, split_stride, ldo = 1, 0, out.stride(0)
+        if out.shape[1] != N or out.stride(1) != 1:
+            raise KernelError("gemm_tcgen05: output must be [M, N] with unit inner stride")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tcgen05: bias must be float32 [N]")
+    rc = _lib().rb_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
+                                ldo, splits, split_stride, _ptr(status_word(x.device)), _stream())
+    if rc == 10003:
+        return False
+    _check(rc, "gemm_tcgen05")
+    return True

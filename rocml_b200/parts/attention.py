@@ -94,9 +94,7 @@ class Attention(Mixer):
         attn = torch.empty((T, qd), dtype=act, device=dev)
         window = int(self.window) if self.window else 0
         self.attend(qkv, attn, batch, view, window)
-        delta = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
-        self.o.forward(attn, delta[0], T)
-        return delta
+        return self.o.forward_delta(attn, T)
 
     def attend(self, q, out, batch, view, window):
         """Softmax attention of the step's queries over the cache.  One token per sequence:

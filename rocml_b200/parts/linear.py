@@ -60,11 +60,29 @@ class Linear:
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
+    def _tensor_core(self, x: torch.Tensor) -> bool:
+        return x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.is_cuda
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, m: Optional[int] = None) -> torch.Tensor:
         """out[:M] = x[:M] . W^T (+ bias); ``out`` is [M, N] float32 or of x's type."""
-        w = self.weight
-        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and kernels.gemm_tensor_core_available():
-            if kernels.gemm_tcgen05(x, w, out, self.bias, m):
-                return out
-        kernels.gemm_generic(x, w, out, self.bias, m)
+        if self._tensor_core(x) and kernels.gemm_tcgen05(x, self.weight, out, self.bias, m):
+            return out
+        kernels.gemm_generic(x, self.weight, out, self.bias, m)
         return out
+
+    def forward_delta(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        """The product as a float32 delta [S, M, N] for the residual stream.  With few rows the
+        sum over K is split S ways so that enough thread blocks stream the weight; the S partial
+        results are added, in order, by the norm that consumes the delta.  S depends on the
+        weight's shape and on whether the step is small, never on what else is in the batch."""
+        S = 1
+        if self._tensor_core(x) and m <= 128 and self.k % 8 == 0:
+            tiles = (self.n + 127) // 128
+            S = max(1, min(8, 148 // tiles, self.k // 512))
+        delta = torch.empty((S, m, self.n), dtype=torch.float32, device=x.device)
+        if self._tensor_core(x) and kernels.gemm_tcgen05(x, self.weight, delta, self.bias, m):
+            return delta
+        if S > 1:
+            delta = delta[:1]
+        kernels.gemm_generic(x, self.weight, delta[0], self.bias, m)
+        return delta

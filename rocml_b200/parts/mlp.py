@@ -50,6 +50,4 @@ class GatedMLP(FeedForward):
         self.gate_up.forward(xn, gu, T)
         h = torch.empty((T, self.inter), dtype=act, device=dev)
         kernels.silu_mul(gu, h)
-        delta = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
-        self.down.forward(h, delta[0], T)
-        return delta
+        return self.down.forward_delta(h, T)
