@@ -13,11 +13,14 @@ from .errors import (
     ModelFileMissing, RocmlError, SafetensorsError, UnknownModel, UnsupportedArchitecture, WeightsError,
 )
 from .engine import Engine, Model, StepEntry
+from .engine.generate import Completion, GenerateStats, Request, generate
+from .sampling import SamplingParams
 
 __version__ = "0.1.0"
 
 __all__ = [
-    "config", "parts", "Engine", "Model", "StepEntry", "CacheError", "CacheFull", "ConfigError",
+    "config", "parts", "Engine", "Model", "StepEntry", "Completion", "GenerateStats", "Request",
+    "generate", "SamplingParams", "CacheError", "CacheFull", "ConfigError",
     "ContextOverflow", "ExtensionMissing", "KernelError", "ModelFileMissing", "RocmlError",
     "SafetensorsError", "UnknownModel", "UnsupportedArchitecture", "WeightsError",
 ]

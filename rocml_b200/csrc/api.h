@@ -42,6 +42,9 @@ int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, i
 
 int rb_argmax(const float* logits, long long row_stride, int rows, int V, int* out, void* stream);
 
+int rb_sample(float* logits, long long row_stride, int n, int V, const void* rows, const int* history, int* out,
+              void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -63,6 +63,7 @@ class Engine:
         self._pool = None
         self.launches = 0          # steps issued (sub-steps counted)
         self.last_h2d_bytes = 0
+        self._sampler = None
 
     # ---- construction ----------------------------------------------------------------------------
     @staticmethod
@@ -222,6 +223,42 @@ class Engine:
             return out[:W] if W else None
         g["graph"].replay()
         return g["logits"][:W] if W else None
+
+    # ---- generation: the engine as the loop's executor ------------------------------------------------------
+    @property
+    def max_seq_len(self) -> int:
+        return self.cache.max_seq_len
+
+    def capacity_tokens(self) -> int:
+        return self.cache.n_pages * 64
+
+    def capacity_slots(self) -> int:
+        return self.cache.max_slots
+
+    def run(self, slots, tokens, params, rngs, histories) -> List[int]:
+        """Step the sequences with their next tokens, sample one token each on the GPU, and
+        bring the token ids (nothing else) back to the host."""
+        logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)])
+        if self._sampler is None:
+            from ..sampling import Sampler
+            self._sampler = Sampler(self.device, max_batch=max(self.cache.max_slots, 1))
+        out = self._sampler.sample(logits, params, rngs, histories)
+        from .. import kernels
+        kernels.check_status(self.device)
+        return out
+
+    def generate(self, prompts, max_new_tokens: int = 64, sampling=None, stop_tokens=None,
+                 ignore_eos: bool = False, max_batch: int = 64, on_token=None, stats=None):
+        """Generate for a list of prompts (token id lists).  Returns a list of Completion.
+        ``sampling`` is one SamplingParams for all or a list; stop tokens default to the model's."""
+        from ..sampling import SamplingParams
+        from .generate import Request, generate
+        if sampling is None:
+            sampling = SamplingParams()
+        per = sampling if isinstance(sampling, (list, tuple)) else [sampling] * len(prompts)
+        reqs = [Request(list(p), max_new_tokens, sp, stop_tokens, ignore_eos) for p, sp in zip(prompts, per)]
+        return generate(self, reqs, default_stop=self.model.spec.stop_tokens, max_batch=max_batch,
+                        on_token=on_token, stats=stats)
 
     # ---- facts for measurement --------------------------------------------------------------------------------
     def kv_bytes_per_token(self) -> int:

@@ -80,6 +80,7 @@ def _lib():
                                              _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
         lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
         lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp]
+        lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp, _vp]
         _sigs_done = True
     return lib
@@ -225,6 +226,17 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
         raise KernelError("argmax: logits float32 with unit inner stride, out int32")
     R = logits.shape[0] if rows is None else rows
     _check(_lib().rb_argmax(_ptr(logits), logits.stride(0), R, logits.shape[1], _ptr(out), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, n: int, rows: torch.Tensor, history: Optional[torch.Tensor], out: torch.Tensor):
+    """One token per row of float32 logits [>= n, V].  ``rows`` holds n records of 8 x 32 bits
+    {temperature f32, top_k i32 (0 off), top_p f32 (< 0 off), u f32, penalty f32 (<= 0 off),
+    hist_begin i32, hist_len i32, 0} (an int32 tensor with the floats bit-cast); ``history``
+    int32 ids.  The repeat penalty edits the logits in place."""
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32 or rows.numel() < 8 * n:
+        raise KernelError("sample: logits float32 with unit inner stride, out int32, 8 words per row")
+    _check(_lib().rb_sample(_ptr(logits), logits.stride(0), n, logits.shape[1], _i32(rows, "rows"),
+                            None if history is None else _i32(history, "history"), _ptr(out), _stream()), "sample")
 
 
 # ---- tensor-core matrix product (tcgen05) ----------------------------------------------------------------
