@@ -1,0 +1,277 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-8B layer sizes, random bfloat16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+A step is one decode step of the default batch (8 sequences, prompts of 1,024 tokens, cache
+sized for a context of 4,096 per sequence).  One JSON line goes to stdout:
+
+* ``value``: decoded tokens per second over K steps, timed on the device with CUDA events;
+  the ids sampled by the argmax kernel feed the next step on the device.
+* ``e2e``: the same through the Python entry point (``Engine.generate``): every step copies its
+  inputs from pinned host memory and reads the sampled ids back to the host.
+* ``prefill``: one prompt of 2,048 tokens; ``frac`` = flops / time / measured bf16 peak.
+* ``roofline``: bytes a decode step must read (every weight once + the live sequences' cache)
+  / time, against the measured copy bandwidth.
+* ``points``: decode at batch 1 and 64.
+
+The engine works on one GPU: for ``--gpus`` above 1 it says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = "qwen3-8b"          # catalog entry with the benchmark's layer sizes
+PROMPT = 1024
+PREFILL_TOKENS = 2048
+CTX = 4096
+BATCH = 8
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class Clocks:
+    """Samples nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.path = None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 7:
+                    continue
+                try:
+                    sm.append(float(f[0])); smax.append(float(f[1]))
+                except ValueError:
+                    continue
+                for name, v in zip(names, f[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def build_engine(layers, max_tokens, max_slots):
+    import torch
+    from rocml_b200.config import CATALOG, config_from_dict
+    from rocml_b200.engine import Engine, Model
+    from rocml_b200.parts import BuildEnv
+
+    full = dict(CATALOG[MODEL].config)
+    n_full = full["num_hidden_layers"]
+    if layers:
+        full["num_hidden_layers"] = layers
+    cfg = config_from_dict(full)
+    dev = torch.device("cuda:0")
+    with torch.cuda.device(dev):
+        model = Model(cfg.to_model_spec(), BuildEnv(dev, torch.bfloat16))
+        model.load_random(seed=0)
+        eng = Engine(model, max_tokens=max_tokens, max_slots=max_slots, max_step_tokens=4096, max_seq_len=CTX)
+    return cfg, n_full, eng
+
+
+def prompts(n, length, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n, length), generator=g).tolist()
+
+
+def time_decode(eng, batch, steps, warmup, vocab, seed):
+    """K decode steps of `batch` sequences after prompts of PROMPT tokens, timed with CUDA events.
+    Returns (ms per step, mean cache tokens read per step, kernels launched in the timed region)."""
+    import torch
+    from rocml_b200 import StepEntry, kernels
+    slots = [eng.new_sequence() for _ in range(batch)]
+    ps = prompts(batch, PROMPT, vocab, seed)
+    tok = torch.zeros(max(batch, 1), dtype=torch.int32, device=eng.device)
+    logits = eng.step([StepEntry(s, p, [PROMPT - 1]) for s, p in zip(slots, ps)])
+    kernels.argmax(logits, tok, batch)
+
+    def one():
+        lg = eng.step([StepEntry(s, [0], [0]) for s in slots], device_tokens=tok)
+        kernels.argmax(lg, tok, batch)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    k0 = kernels.launch_count + eng.graph_kernel_launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx_tokens = 0
+    start.record()
+    for _ in range(steps):
+        ctx_tokens += sum(eng.length(s) + 1 for s in slots)
+        one()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launched = kernels.launch_count + eng.graph_kernel_launches - k0
+    kernels.check_status(eng.device)
+    for s in slots:
+        eng.release(s)
+    return ms, ctx_tokens / steps, launched
+
+
+def time_prefill(eng, vocab, runs=3, warmup=2):
+    import torch
+    from rocml_b200 import StepEntry, kernels
+    p = prompts(1, PREFILL_TOKENS, vocab, 99)[0]
+    times = []
+    for i in range(warmup + runs):
+        slot = eng.new_sequence()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.step([StepEntry(slot, p, [PREFILL_TOKENS - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+        eng.release(slot)
+    kernels.check_status(eng.device)
+    return statistics.median(times)
+
+
+def prefill_flops(cfg, layers, T):
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    per_layer = H * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * H + 3 * H * I
+    linear = 2.0 * T * per_layer * layers + 2.0 * V * H           # the head runs on one row
+    attn = 4.0 * cfg.num_attention_heads * cfg.head_dim * (T * (T + 1) / 2) * layers   # causal QK^T and PV
+    return linear + attn
+
+
+def e2e_decode(eng, batch, steps, warmup, vocab):
+    """Decoded tokens per second through Engine.generate: host token ids in, host token ids out,
+    a pinned-memory copy each way in every step."""
+    from rocml_b200 import GenerateStats
+    ps = prompts(batch, PROMPT, vocab, 7)
+    eng.generate(ps, max_new_tokens=max(warmup, 2), stop_tokens=[], ignore_eos=True, max_batch=batch)
+    stats = GenerateStats()
+    eng.generate(ps, max_new_tokens=steps + 1, stop_tokens=[], ignore_eos=True, max_batch=batch, stats=stats)
+    return stats.decode_tokens / stats.decode_seconds, eng.last_h2d_bytes, batch * 4
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "xmiksay/rocml is a Rust + HIP (ROCm, gfx1101) workspace with no Python package; "
+                          "it needs cargo, hipcc and a GGUF checkpoint, none of which exist here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine works on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+
+    import torch
+    pk = peaks()
+    max_slots = 64
+    cfg, n_full, eng = build_engine(args.layers, max_tokens=max_slots * (PROMPT + 64 * 5), max_slots=max_slots)
+    layers = cfg.num_hidden_layers
+    vocab = cfg.vocab_size
+    dev_gb = torch.cuda.memory_allocated() / 1e9
+
+    prefill_ms = time_prefill(eng, vocab)
+    pf = prefill_flops(cfg, layers, PREFILL_TOKENS)
+
+    clocks = Clocks()
+    clocks.start()
+    ms, ctx_tokens, launched = time_decode(eng, BATCH, steps, warmup, vocab, seed=1)
+    clk = clocks.stop()
+    value = BATCH * 1000.0 / ms
+    bytes_step = eng.model.weight_bytes_per_step() + ctx_tokens * eng.kv_bytes_per_token()
+    achieved = bytes_step / (ms * 1e-3) / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            k = max(16, min(steps, 64))
+            m, _, _ = time_decode(eng, b, k, warmup, vocab, seed=10 + b)
+            points[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
+
+    e2e, h2d, d2h = e2e_decode(eng, BATCH, min(steps, 128), warmup, vocab)
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B layer sizes, bf16, random weights, prompts of 1024)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random-init weights",
+        "config": {
+            "model": "Qwen3-8B layer sizes", "layers": layers, "layers_full": n_full,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": vocab,
+            "tied_head": cfg.tie_word_embeddings, "global_batch": BATCH, "prompt_len": PROMPT,
+            "seq_len": CTX, "decode_steps_timed": steps, "parallelism": "single GPU",
+            "l2": "inputs larger than L2: every step reads all weights (GB: %.1f)" % (eng.model.weight_bytes_per_step() / 1e9),
+            "device_gb": round(dev_gb, 1), "peaks": pk["source"],
+        },
+        "clocks": clk,
+        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launched,
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -64,6 +64,8 @@ class Engine:
         self.launches = 0          # steps issued (sub-steps counted)
         self.last_h2d_bytes = 0
         self._sampler = None
+        self._device_tokens = None
+        self.graph_kernel_launches = 0  # kernels run by graph replays
 
     # ---- construction ----------------------------------------------------------------------------
     @staticmethod
@@ -90,10 +92,17 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step --------------------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the entries' tokens; return float32 logits [wanted places, vocab] in the order of
         the entries and of each entry's ``want`` (None when nothing is wanted).  The tensor may
-        be reused by the next step: read it before stepping again."""
+        be reused by the next step: read it before stepping again.
+
+        ``device_tokens`` (int32 on the device, one per entry) replaces the entries' token ids
+        for a step of one token per sequence: the ids a sampling kernel has just written are
+        fed back without passing through the host."""
+        self._device_tokens = device_tokens
+        if device_tokens is not None and any(len(e.tokens) != 1 for e in entries if isinstance(e, StepEntry)):
+            raise RocmlError("device_tokens needs exactly one token per entry")
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return None
@@ -183,6 +192,8 @@ class Engine:
             self._eager[key] = BatchBuffers(key[0], key[1], key[0], self.device)
         buf = self._eager[key]
         buf.fill(*packed, slots, pad_tokens=T, pad_seqs=B, pad_want=W)
+        if self._device_tokens is not None:
+            buf.token_ids[:B].copy_(self._device_tokens[:B], non_blocking=True)
         self.last_h2d_bytes = buf.h2d_bytes
         batch = self._batch(buf, T, B, W, max(q_lens), max(kv_len), is_decode, host)
         return self.model.forward(batch, self.cache)
@@ -206,6 +217,8 @@ class Engine:
             self._graphs[key] = g
         buf: BatchBuffers = g["buffers"]
         buf.fill(*packed, host.seq_slots, pad_tokens=b_pad, pad_seqs=b_pad, pad_want=b_pad)
+        if self._device_tokens is not None:
+            buf.token_ids[:B].copy_(self._device_tokens[:B], non_blocking=True)
         self.last_h2d_bytes = buf.h2d_bytes
         if g["graph"] is None:
             # First use of this bucket: run it plainly (this also loads every kernel), then
@@ -215,13 +228,18 @@ class Engine:
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
             cap = self._batch(buf, b_pad, b_pad, b_pad, 1, ctx_pad, True, None, capturing=True)
+            from .. import kernels
+            before = kernels.launch_count
             with torch.cuda.graph(graph, pool=self._pool):
                 g["logits"] = self.model.forward(cap, self.cache)
+            g["kernels"] = kernels.launch_count - before
+            kernels.launch_count = before  # captured, not launched
             if self._pool is None:
                 self._pool = graph.pool()
             g["graph"] = graph
             return out[:W] if W else None
         g["graph"].replay()
+        self.graph_kernel_launches += g["kernels"]
         return g["logits"][:W] if W else None
 
     # ---- generation: the engine as the loop's executor ------------------------------------------------------

@@ -71,6 +71,17 @@ class Model:
     def load_folder(self, folder: str) -> None:
         self.load(load_tensors(folder, self.declare(), self.env.mode, self.env.device, self.ignorable()))
 
+    def load_random(self, seed: int) -> None:
+        """Random weights made directly on the device (the distributions of the random-weights
+        mode; no folder is written)."""
+        from ..weights.random_init import random_tensor
+        dt = torch.float32 if self.env.mode == "float32" else torch.bfloat16
+        tensors = {}
+        for d in self.declare():
+            t = random_tensor(d, seed, self.env.device, torch.bfloat16)
+            tensors[d.name] = t if d.role == "int_table" else t.to(dt)
+        self.load(tensors)
+
     # ---- facts ----------------------------------------------------------------------------------
     @property
     def graph_safe(self) -> bool:

@@ -49,7 +49,12 @@ def _stream():
     return _vp(torch.cuda.current_stream().cuda_stream)
 
 
+launch_count = 0  # kernel launches issued through this module (graph replays are counted by the engine)
+
+
 def _check(rc: int, what: str):
+    global launch_count
+    launch_count += 1
     if rc != 0:
         if rc in _CODES:
             raise KernelError(f"{what}: {_CODES[rc]} (code {rc})")
