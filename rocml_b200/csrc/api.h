@@ -36,11 +36,17 @@ int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, i
                          float scale, int window, int chunk, int n_chunks, float* part_acc, float* part_ml,
                          void* stream);
 
+int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                        const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
+                        const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window, int n_chunks,
+                        float* part_acc, float* part_ml, void* out, int o_stride, void* stream);
+
 int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, int o_stride, int dtype,
                        const int* positions, const int* slot_of_token, int T, int nq, int hd, int chunk,
                        int n_chunks, int window, void* stream);
 
-int rb_argmax(const float* logits, long long row_stride, int rows, int V, int* out, void* stream);
+int rb_argmax(const float* logits, long long row_stride, int rows, int V, int* out, float* scratch_v,
+              int* scratch_i, int slices, void* stream);
 
 int rb_sample(float* logits, long long row_stride, int n, int V, const void* rows, const int* history, int* out,
               void* stream);

@@ -180,14 +180,17 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 }
 
 // Combine the chunks' partial results of every (token, head), in ascending chunk order.
+// One warp per (token, head): the lanes first walk the chunks for the maximum and the weights
+// exp(m_c - M) (kept in shared memory), then each lane sums its head dimensions over the chunks.
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        T* __restrict__ out, int o_stride, const int* __restrict__ positions,
                                        const int* __restrict__ slot_of_token, int T_tokens, int nq, int hd,
                                        int chunk, int n_chunks, int window) {
+    extern __shared__ float w_s[];   // [warps][n_chunks]
     const int warps = blockDim.x >> 5;
-    const long long item = (long long)blockIdx.x * warps + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * warps + warp;
     if (item >= (long long)T_tokens * nq) return;
     const int t = (int)(item / nq), head = (int)(item % nq);
     if (slot_of_token[t] < 0) return;
@@ -195,21 +198,24 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     const int c_hi = min(n_chunks - 1, pos / chunk);
     const int c_lo = window > 0 ? max(0, pos - window + 1) / chunk : 0;
     const size_t base = ((size_t)t * nq + head) * n_chunks;
+    float* w = w_s + (size_t)warp * n_chunks;
     float M = NEG_BIG;
-    for (int c = c_lo; c <= c_hi; ++c)
+    for (int c = c_lo + lane; c <= c_hi; c += 32)
         if (part_ml[(base + c) * 2 + 1] > 0.f) M = fmaxf(M, part_ml[(base + c) * 2]);
+    M = warp_max(M);
     float L = 0.f;
-    for (int c = c_lo; c <= c_hi; ++c) {
+    for (int c = c_lo + lane; c <= c_hi; c += 32) {
         const float lc = part_ml[(base + c) * 2 + 1];
-        if (lc > 0.f) L += expf(part_ml[(base + c) * 2] - M) * lc;
+        const float wc = lc > 0.f ? expf(part_ml[(base + c) * 2] - M) : 0.f;
+        w[c] = wc;
+        L += wc * lc;
     }
+    L = warp_sum(L);
+    __syncwarp();
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int d = lane; d < hd; d += 32) {
         float a = 0.f;
-        for (int c = c_lo; c <= c_hi; ++c) {
-            const float lc = part_ml[(base + c) * 2 + 1];
-            if (lc > 0.f) a += expf(part_ml[(base + c) * 2] - M) * part_acc[(base + c) * hd + d];
-        }
+        for (int c = c_lo; c <= c_hi; ++c) a = fmaf(w[c], part_acc[(base + c) * hd + d], a);
         out[(size_t)t * o_stride + (size_t)head * hd + d] = from_f32<T>(a * inv);
     }
 }
@@ -270,12 +276,14 @@ extern "C" int rb_attention_merge(const float* part_acc, const float* part_ml, v
     const int warps = 4;
     const long long blocks = ((long long)T * nq + warps - 1) / warps;
     if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
+    const size_t smem = (size_t)warps * n_chunks * sizeof(float);
+    if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
     if (dtype == RB_BF16)
-        attention_merge_kernel<<<(int)blocks, warps * 32, 0, s>>>(part_acc, part_ml, (__nv_bfloat16*)out, o_stride,
+        attention_merge_kernel<<<(int)blocks, warps * 32, smem, s>>>(part_acc, part_ml, (__nv_bfloat16*)out, o_stride,
                                                                   positions, slot_of_token, T, nq, hd, chunk,
                                                                   n_chunks, window);
     else if (dtype == RB_F32)
-        attention_merge_kernel<<<(int)blocks, warps * 32, 0, s>>>(part_acc, part_ml, (float*)out, o_stride,
+        attention_merge_kernel<<<(int)blocks, warps * 32, smem, s>>>(part_acc, part_ml, (float*)out, o_stride,
                                                                   positions, slot_of_token, T, nq, hd, chunk,
                                                                   n_chunks, window);
     else

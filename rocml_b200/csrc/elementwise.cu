@@ -50,26 +50,56 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
                                    int n_delta, size_t delta_stride, const WT* __restrict__ w,
                                    OT* __restrict__ out, const int* __restrict__ rows, int H,
                                    float eps, int write_back) {
-    extern __shared__ float row_buf[];  // H floats + 33 for the reduction
-    float* red = row_buf + H;
+    extern __shared__ __align__(16) float row_buf[];  // H floats (padded to 4) + 33 for the reduction
+    float* red = row_buf + ((H + 3) & ~3);
     const int orow = blockIdx.x;
     const int row = rows ? rows[orow] : orow;
     if (row < 0) return;  // a padded entry
     float* r = resid + (size_t)row * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = r[i];
-        for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + (size_t)row * H + i];
-        row_buf[i] = v;
-        ss += v * v;
+    const bool vec = (H & 3) == 0 && (delta_stride & 3) == 0 && (((uintptr_t)resid | (uintptr_t)delta) & 15) == 0;
+    if (vec) {
+        const int H4 = H >> 2;
+        float4* rb4 = reinterpret_cast<float4*>(row_buf);
+        const float4* r4 = reinterpret_cast<const float4*>(r);
+        for (int i = threadIdx.x; i < H4; i += blockDim.x) {
+            float4 v = r4[i];
+            for (int s = 0; s < n_delta; ++s) {
+                const float4 d = reinterpret_cast<const float4*>(delta + (size_t)s * delta_stride + (size_t)row * H)[i];
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            }
+            rb4[i] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = r[i];
+            for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + (size_t)row * H + i];
+            row_buf[i] = v;
+            ss += v * v;
+        }
     }
     const float total = block_sum(ss, red);
     const float inv = rsqrtf(total / (float)H + eps);
     OT* o = out + (size_t)orow * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = row_buf[i];
-        if (write_back) r[i] = v;
-        o[i] = from_f32<OT>(v * inv * to_f32(w[i]));
+    if (vec) {
+        const int H4 = H >> 2;
+        const float4* rb4 = reinterpret_cast<const float4*>(row_buf);
+        float4* r4 = reinterpret_cast<float4*>(r);
+        for (int i = threadIdx.x; i < H4; i += blockDim.x) {
+            const float4 v = rb4[i];
+            if (write_back) r4[i] = v;
+            o[4 * i] = from_f32<OT>(v.x * inv * to_f32(w[4 * i]));
+            o[4 * i + 1] = from_f32<OT>(v.y * inv * to_f32(w[4 * i + 1]));
+            o[4 * i + 2] = from_f32<OT>(v.z * inv * to_f32(w[4 * i + 2]));
+            o[4 * i + 3] = from_f32<OT>(v.w * inv * to_f32(w[4 * i + 3]));
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = row_buf[i];
+            if (write_back) r[i] = v;
+            o[i] = from_f32<OT>(v * inv * to_f32(w[i]));
+        }
     }
 }
 
@@ -77,7 +107,7 @@ template <typename OT, typename WT>
 static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, size_t delta_stride,
                               const void* w, void* out, const int* rows, int n_rows, int H, float eps,
                               int write_back, cudaStream_t s) {
-    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
     if (smem > 200 * 1024) return RB_ERR_BAD_SIZE;
     auto k = add_rmsnorm_kernel<OT, WT>;
     if (smem > 48 * 1024) {

@@ -49,12 +49,62 @@ __global__ void argmax_kernel(const float* __restrict__ logits, long long row_st
         if (lane == 0) out[blockIdx.x] = c.i == 0x7fffffff ? 0 : c.i;
     }
 }
+
+// Two stages for wide rows: blocks of stage 1 each take a slice of the row, stage 2 (one warp per
+// row) picks among their results.  Slices are in index order and ties keep the smaller index, so
+// the result is the first maximum, as in the single-block kernel.
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, long long row_stride, int V, int per,
+                                      float* __restrict__ pv, int* __restrict__ pi) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.y * row_stride;
+    const int lo = blockIdx.x * per, hi = min(V, lo + per);
+    Best b{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > b.v) { b.v = v; b.i = i; }
+    }
+    b = warp_best(b);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = b.v; si[warp] = b.i; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        Best c{lane < nw ? sv[lane] : -INFINITY, lane < nw ? si[lane] : 0x7fffffff};
+        c = warp_best(c);
+        if (lane == 0) { pv[blockIdx.y * gridDim.x + blockIdx.x] = c.v; pi[blockIdx.y * gridDim.x + blockIdx.x] = c.i; }
+    }
+}
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int n,
+                                    int* __restrict__ out) {
+    const int lane = threadIdx.x;
+    Best b{-INFINITY, 0x7fffffff};
+    for (int i = lane; i < n; i += 32) {
+        Best c{pv[blockIdx.x * n + i], pi[blockIdx.x * n + i]};
+        b = better(b, c);
+    }
+    b = warp_best(b);
+    if (lane == 0) out[blockIdx.x] = b.i == 0x7fffffff ? 0 : b.i;
+}
 }  // namespace
 
-extern "C" int rb_argmax(const float* logits, long long row_stride, int rows, int V, int* out, void* stream) {
+// scratch_v / scratch_i: [rows, slices] work space for rows wider than 8192; slices > 1 selects the
+// two-stage route.
+extern "C" int rb_argmax(const float* logits, long long row_stride, int rows, int V, int* out, float* scratch_v,
+                         int* scratch_i, int slices, void* stream) {
     if (rows <= 0) return RB_OK;
     if (V <= 0) return RB_ERR_BAD_SIZE;
-    argmax_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, row_stride, V, out);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (slices > 1 && scratch_v && scratch_i) {
+        if (rows > 65535) return RB_ERR_BAD_SIZE;
+        const int per = (V + slices - 1) / slices;
+        argmax_partial_kernel<<<dim3(slices, rows), 256, 0, s>>>(logits, row_stride, V, per, scratch_v, scratch_i);
+        RB_LAUNCH_CHECK();
+        argmax_final_kernel<<<rows, 32, 0, s>>>(scratch_v, scratch_i, slices, out);
+        RB_LAUNCH_CHECK();
+        return RB_OK;
+    }
+    argmax_kernel<<<rows, 1024, 0, s>>>(logits, row_stride, V, out);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) pieces the kernels use: mbarriers with
 // bounded waits, TMA tile loads, tensor memory (TMEM) allocation, tcgen05.mma / commit / ld.
 //
-// Every wait is bounded: after `RB_WAIT_NS` nanoseconds it gives up and returns false, and the
+// Every wait is bounded: after `RB_WAIT_CYCLES` clock cycles (about two seconds) it gives up and returns false, and the
 // caller records RB_ERR_TIMEOUT in a status word and unwinds (waits for its own copies, frees
 // TMEM, returns).  Nothing here traps or spins without limit.
 #pragma once
@@ -11,7 +11,7 @@
 
 namespace sm100 {
 
-constexpr unsigned long long RB_WAIT_NS = 2000000000ull;  // 2 s
+constexpr long long RB_WAIT_CYCLES = 4000000000ll;  // about 2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -60,12 +60,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Wait for the phase with the given parity to complete; false if the time limit ran out.
+// The limit is counted in SM clock cycles (cheap to read, unlike %globaltimer, whose read costs
+// about a microsecond and would sit in every pipeline step).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    uint32_t spins = 0;
+    const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 255u) == 0 && globaltimer_ns() - t0 > RB_WAIT_NS) return false;
+        if (clock64() - t0 > RB_WAIT_CYCLES) return false;
     }
     return true;
 }

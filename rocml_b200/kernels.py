@@ -84,7 +84,9 @@ def _lib():
         lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
                                              _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
         lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
-        lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp]
+        lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp]
+        lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
+                                            _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp, _vp]
         _sigs_done = True
@@ -214,6 +216,26 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _check(rc, "attention_generic")
 
 
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                     n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
+                     part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor]) -> bool:
+    """bfloat16 decode attention, one query token per sequence, keys in chunks of 128.  Returns
+    False when the kernel does not take the head size or the alignment (use attention_generic)."""
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or q.stride(-1) != 1 or out.stride(-1) != 1:
+        return False
+    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+        raise KernelError("attention_decode: cache must be [pages, nkv, 64, hd]")
+    rc = _lib().rb_attention_decode(
+        _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
+        _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
+        int(window), int(n_chunks), _ptr(part_acc), _ptr(part_ml), _ptr(out), out.stride(0), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "attention_decode")
+    return True
+
+
 def attention_merge(part_acc: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                     slot_of_token: torch.Tensor, n_tokens: int, nq: int, hd: int, chunk: int, n_chunks: int,
                     window: int = 0):
@@ -225,12 +247,24 @@ def attention_merge(part_acc: torch.Tensor, part_ml: torch.Tensor, out: torch.Te
 
 # ---- sampling ---------------------------------------------------------------------------------------------
 
+_ARGMAX_SLICES = 64
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
-    """out[r] = index of the first largest value of logits[r, :]; logits float32 [R, V]."""
+    """out[r] = index of the first largest value of logits[r, :]; logits float32 [R, V].  Wide rows
+    are searched by 64 blocks each, through a small work space."""
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32:
         raise KernelError("argmax: logits float32 with unit inner stride, out int32")
     R = logits.shape[0] if rows is None else rows
-    _check(_lib().rb_argmax(_ptr(logits), logits.stride(0), R, logits.shape[1], _ptr(out), _stream()), "argmax")
+    V = logits.shape[1]
+    sv = si = None
+    slices = 1
+    if V > 8192:
+        slices = _ARGMAX_SLICES
+        sv = torch.empty((R, slices), dtype=torch.float32, device=logits.device)
+        si = torch.empty((R, slices), dtype=torch.int32, device=logits.device)
+    _check(_lib().rb_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _ptr(sv), _ptr(si), slices, _stream()),
+           "argmax")
 
 
 def sample(logits: torch.Tensor, n: int, rows: torch.Tensor, history: Optional[torch.Tensor], out: torch.Tensor):

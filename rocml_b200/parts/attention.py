@@ -102,15 +102,22 @@ class Attention(Mixer):
         if batch.is_decode:
             chunk = DECODE_CHUNK
             n_chunks = max(1, (batch.max_kv_len + chunk - 1) // chunk)
+            T = batch.n_tokens
+            acc = ml = None
             if n_chunks > 1:
-                T = batch.n_tokens
                 acc = torch.empty((T, self.nq, n_chunks, self.hd), dtype=torch.float32, device=q.device)
                 ml = torch.empty((T, self.nq, n_chunks, 2), dtype=torch.float32, device=q.device)
+            fast = kernels.attention_decode(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
+                                            batch.kv_len, batch.n_seqs, self.nq, self.nkv, self.hd, self.scale,
+                                            window, n_chunks, acc, ml)
+            if not fast and n_chunks > 1:
                 kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                           batch.kv_len, batch.n_seqs, 1, self.nq, self.nkv, self.hd, self.scale,
                                           window, chunk, n_chunks, acc, ml)
+            if n_chunks > 1:
                 kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, self.nq, self.hd,
                                         chunk, n_chunks, window)
+            if fast or n_chunks > 1:
                 return
         kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                   batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,

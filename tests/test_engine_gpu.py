@@ -23,7 +23,7 @@ def rel_err(got, want):
     return float(((got - want).abs() / scale).max())
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def model_folder(request, tmp_path_factory):
     name = request.param
     folder = tmp_path_factory.mktemp(f"tiny_{name}")
@@ -39,7 +39,7 @@ def plain(model_folder):
 
 def lengths_for(name):
     maxp = CONFIGS[name]["max_position_embeddings"]
-    return [n for n in (1, 7, 33, 64, 65, 100, 129, 200, 256, 300) if n <= maxp]
+    return [n for n in (1, 7, 33, 64, 65, 100, 129, 200, 256, 300, 500) if n <= maxp]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -141,3 +141,176 @@ def test_silu_mul(dt):
     want = g / (1 + torch.exp(-g)) * u
     tol = 2 ** -8 if dt == torch.bfloat16 else 1e-6
     assert ((out.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max() < tol
+
+
+# ---- attention over the paged cache --------------------------------------------------------------------
+
+def paged_case(seed, lens, q_lens, nq, nkv, hd, dtype, spike=None):
+    """Sequences with caches of `lens` tokens whose last `q_lens` tokens are this step's queries.
+    Pages are handed out in a scrambled order so that a wrong table shows.  `spike` = (seq, far
+    key position): that key and the last query of the sequence are scaled so that one far score
+    stands out among hundreds."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    n_pages = sum((n + 63) // 64 for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    max_pages = max((n + 63) // 64 for n in lens) + 1
+    table = torch.full((B + 2, max_pages), -1, dtype=torch.int32)
+    slots = list(range(1, B + 1))           # slot 0 stays unused
+    kc = torch.full((n_pages, nkv, 64, hd), float("nan"))
+    vc = torch.full((n_pages, nkv, 64, hd), float("nan"))
+    ks, vs, qs = [], [], []
+    for b, n in enumerate(lens):
+        k = torch.randn(n, nkv, hd, generator=g)
+        v = torch.randn(n, nkv, hd, generator=g)
+        q = torch.randn(q_lens[b], nq, hd, generator=g)
+        if spike is not None and spike[0] == b:
+            k[spike[1]] *= 4.0
+            q[-1] = k[spike[1]].repeat_interleave(nq // nkv, dim=0) * 1.5
+        k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
+        for p in range((n + 63) // 64):
+            page = perm.pop()
+            table[slots[b], p] = page
+            m = min(64, n - p * 64)
+            kc[page, :, :m] = k[p * 64:p * 64 + m].transpose(0, 1)
+            vc[page, :, :m] = v[p * 64:p * 64 + m].transpose(0, 1)
+        ks.append(k); vs.append(v); qs.append(q)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    meta = dict(table=table, seq_slot=torch.tensor(slots, dtype=torch.int32),
+                cu_q=torch.tensor(cu, dtype=torch.int32), kv_len=torch.tensor(lens, dtype=torch.int32))
+    return ks, vs, qs, kc.to(dtype), vc.to(dtype), meta
+
+
+def reference_attention(ks, vs, qs, window, scale):
+    import plain_qwen3 as P
+    outs = []
+    for k, v, q in zip(ks, vs, qs):
+        n, ql = k.shape[0], q.shape[0]
+        full_q = torch.zeros(n, q.shape[1], q.shape[2], dtype=torch.float64)
+        full_q[n - ql:] = q.double()
+        o = P.attention(full_q, k.double(), v.double(), window=window, scale=scale)
+        outs.append(o[n - ql:])
+    return torch.cat(outs, 0)
+
+
+ATT_CASES = [
+    # lens, q_lens, nq, nkv, hd, window
+    ([5, 70, 129], [5, 70, 129], 4, 2, 16, None),        # whole prompts
+    ([200, 64, 1], [30, 1, 1], 6, 1, 32, None),          # a piece of a prompt, single tokens; 6:1 groups
+    ([300, 131], [300, 3], 5, 5, 48, 24),                # a window, no grouping, head size 48
+    ([700], [1], 32, 8, 128, None),                      # one far key among hundreds
+    ([260, 90], [65, 90], 20, 1, 64, 100),               # a group wider than a block's 16 rows
+]
+
+
+@pytest.mark.parametrize("case", range(len(ATT_CASES)))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_generic(case, dtype):
+    from rocml_b200 import kernels
+    lens, q_lens, nq, nkv, hd, window = ATT_CASES[case]
+    spike = (0, 3) if case == 3 else None
+    ks, vs, qs, kc, vc, meta = paged_case(case, lens, q_lens, nq, nkv, hd, dtype, spike)
+    scale = 1.0 / math.sqrt(hd)
+    want = reference_attention(ks, vs, qs, window, scale)
+    q = torch.cat(qs, 0).reshape(-1, nq * hd).to(dtype).to(DEV)
+    out = torch.full_like(q, float("nan"))
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    kernels.attention_generic(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
+                              len(lens), max(q_lens), nq, nkv, hd, scale, window or 0)
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-5
+    err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
+    assert err < tol, err
+
+
+DEC_CASES = [
+    # lens, nq, nkv, hd, window
+    ([700, 1, 129, 64, 128], 32, 8, 128, None),
+    ([300, 131, 65], 8, 2, 64, None),
+    ([513, 40], 6, 3, 128, 70),
+    ([1000], 2, 2, 256, None),
+    ([257, 100, 31], 12, 2, 64, 33),
+]
+
+
+@pytest.mark.parametrize("case", range(len(DEC_CASES)))
+@pytest.mark.parametrize("fast", [True, False])
+def test_attention_decode_split_kv(case, fast):
+    """One query per sequence, keys in chunks of 128, merged: the bfloat16 kernel and the plain kernel."""
+    from rocml_b200 import kernels
+    lens, nq, nkv, hd, window = DEC_CASES[case]
+    spike = (0, 5) if case == 0 else None
+    dtype = torch.bfloat16
+    ks, vs, qs, kc, vc, meta = paged_case(10 + case, lens, [1] * len(lens), nq, nkv, hd, dtype, spike)
+    scale = 1.0 / math.sqrt(hd)
+    want = reference_attention(ks, vs, qs, window, scale)
+    B = len(lens)
+    q = torch.cat(qs, 0).reshape(-1, nq * hd).to(dtype).to(DEV)
+    out = torch.full_like(q, float("nan"))
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    n_chunks = (max(lens) + 127) // 128 + 1     # one more than needed, as a padded graph would have
+    acc = torch.full((B, nq, n_chunks, hd), float("nan"), dtype=torch.float32, device=DEV)
+    ml = torch.full((B, nq, n_chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
+    pos = (d["kv_len"] - 1).to(torch.int32)
+    if fast:
+        assert kernels.attention_decode(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"],
+                                        d["kv_len"], B, nq, nkv, hd, scale, window or 0, n_chunks, acc, ml)
+    else:
+        kernels.attention_generic(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
+                                  B, 1, nq, nkv, hd, scale, window or 0, 128, n_chunks, acc, ml)
+    kernels.attention_merge(acc, ml, out, pos, d["seq_slot"], B, nq, hd, 128, n_chunks, window or 0)
+    err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
+    assert err < 2e-2, err
+
+
+def test_attention_decode_refuses_other_head_sizes():
+    from rocml_b200 import kernels
+    ks, vs, qs, kc, vc, meta = paged_case(1, [10], [1], 2, 1, 48, torch.bfloat16)
+    q = torch.cat(qs, 0).reshape(-1, 96).bfloat16().to(DEV)
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    assert kernels.attention_decode(q, torch.empty_like(q), kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"],
+                                    d["cu_q"], d["kv_len"], 1, 2, 1, 48, 0.1, 0, 1, None, None) is False
+
+
+# ---- q/k norm + rotary + cache write ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype,wd", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("nq,nkv,hd,rot", [(4, 2, 16, 16), (6, 1, 32, 32), (5, 5, 48, 24), (8, 2, 128, 128)])
+def test_qk_norm_rope_cache(dtype, wd, nq, nkv, hd, rot):
+    import plain_qwen3 as P
+    from rocml_b200 import kernels
+    T, eps, theta = 9, 1e-5, 1e4
+    positions = torch.tensor([0, 1, 2, 63, 64, 65, 130, 7, 8], dtype=torch.int32)
+    slots = torch.tensor([1, 1, 1, 1, 1, 1, 1, 2, -1], dtype=torch.int32)   # the last token is padding
+    table = torch.full((3, 4), -1, dtype=torch.int32)
+    table[1, :3] = torch.tensor([5, 0, 3])
+    table[2, :1] = torch.tensor([2])
+    width = (nq + 2 * nkv) * hd
+    x = rnd((T, width), 1, dtype)
+    qw, kw = (1 + 0.1 * rnd((hd,), 2)).to(wd), (1 + 0.1 * rnd((hd,), 3)).to(wd)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).float()
+    kc = torch.zeros((6, nkv, 64, hd), dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    xd = x.to(DEV).clone()
+    kernels.qk_norm_rope_cache(xd, T, nq, nkv, hd, qw.to(DEV), kw.to(DEV), eps, inv.to(DEV), rot, positions.to(DEV),
+                               slots.to(DEV), table.to(DEV), kc, vc)
+    xf = x.double()
+    q = P.rmsnorm(xf[:, :nq * hd].reshape(T, nq, hd), qw.double(), eps)
+    k = P.rmsnorm(xf[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd), kw.double(), eps)
+    v = xf[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+
+    def rope(t):
+        r = P.rope_neox(t[..., :rot], positions.tolist(), theta)
+        return torch.cat([r, t[..., rot:]], -1)
+    q, k = rope(q), rope(k)
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-5
+    got_q = xd.cpu().double()[:, :nq * hd].reshape(T, nq, hd)
+    assert (got_q[:8] - q[:8]).abs().max() < tol
+    assert torch.equal(xd.cpu()[8], x[8])                       # the padded token is untouched
+    for t in range(8):
+        page = int(table[slots[t], positions[t] // 64])
+        off = int(positions[t] % 64)
+        assert (kc[page, :, off].cpu().double() - k[t]).abs().max() < tol
+        assert (vc[page, :, off].cpu().double() - v[t]).abs().max() < tol * 1e-3 + 1e-7
+    assert kc.abs().sum(dim=(1, 3)).count_nonzero() == 8         # nothing else was written

@@ -30,7 +30,15 @@ TINY_C = {
     "use_sliding_window": True, "sliding_window": 24,
     "layer_types": ["full_attention", "sliding_attention", "full_attention", "sliding_attention"],
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# D has the head size (64) and group size (4) that the bfloat16 attention kernels take, so that the
+# engine tests run them and not only the plain kernels.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "hidden_size": 128, "intermediate_size": 320, "num_hidden_layers": 2,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 500,
+    "max_position_embeddings": 512, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False, "attention_bias": False, "hidden_act": "silu",
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def write_model(folder, cfg_dict, seed, std=None):
