@@ -13,22 +13,23 @@ int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delt
                    int w_dtype, void* out, int out_dtype, const int* rows, int n_rows, int H, float eps,
                    int write_back, void* stream);
 
-int rb_silu_mul(const void* in, void* out, int dtype, int rows, int I, void* stream);
+int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype, int rows,
+                int I, void* stream);
 
 int rb_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* stream);
 
-int rb_qk_norm_rope_cache(void* qkv, int act_dtype, int row_stride, int T, int nq, int nkv, int hd,
-                          const void* q_norm_w, const void* k_norm_w, int w_dtype, float eps,
-                          const float* inv_freq, int rot_dim, const int* positions, const int* slot_of_token,
-                          const int* block_table, int max_pages, void* k_cache, void* v_cache, int write_kv,
-                          void* stream);
+int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, void* q_out,
+                          int act_dtype, int q_stride, int T, int nq, int nkv, int hd, const void* q_norm_w,
+                          const void* k_norm_w, int w_dtype, float eps, const float* inv_freq, int rot_dim,
+                          const int* positions, const int* slot_of_token, const int* block_table, int max_pages,
+                          void* k_cache, void* v_cache, int write_kv, void* stream);
 
 int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, void* out,
                     int out_dtype, int M, int N, int K, long long ldx, long long ldo, void* stream);
 
 int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M, int N,
-                    int K, long long ldx, long long ldo, int splits, long long split_stride, int* status,
-                    void* stream);
+                    int K, long long ldx, long long ldo, int splits, long long split_stride, int stages,
+                    int* status, void* stream);
 
 int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, int dtype, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
@@ -36,10 +37,15 @@ int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, i
                          float scale, int window, int chunk, int n_chunks, float* part_acc, float* part_ml,
                          void* stream);
 
+int rb_attention_prefill(const void* q, int q_stride, void* out, int o_stride, const void* k_cache,
+                         const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
+                         const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd, float scale,
+                         int window, void* stream);
+
 int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                         const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window, int n_chunks,
-                        float* part_acc, float* part_ml, void* out, int o_stride, void* stream);
+                        float* part_acc, float* part_ml, int* counters, void* out, int o_stride, void* stream);
 
 int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, int o_stride, int dtype,
                        const int* positions, const int* slot_of_token, int T, int nq, int hd, int chunk,

@@ -40,6 +40,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ kv_len, int nq, int nkv, int hd, float scale, int window,
                          int chunk, int n_chunks, float* __restrict__ part_acc,
                          float* __restrict__ part_ml) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int g = nq / nkv;
     const int HG = g < ROWS ? g : ROWS;           // heads of the group handled by this block
@@ -187,6 +189,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
                                        T* __restrict__ out, int o_stride, const int* __restrict__ positions,
                                        const int* __restrict__ slot_of_token, int T_tokens, int nq, int hd,
                                        int chunk, int n_chunks, int window) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float w_s[];   // [warps][n_chunks]
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -238,7 +242,7 @@ int launch_attn(const void* q, int q_stride, void* out, int o_stride, const void
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid((unsigned)gx, nkv * head_chunks, B);
-    k<<<grid, 128, smem, s>>>((const T*)q, q_stride, (T*)out, o_stride, (const T*)k_cache, (const T*)v_cache,
+    RB_LAUNCH((k), dim3(grid), dim3(128), smem, s, (const T*)q, q_stride, (T*)out, o_stride, (const T*)k_cache, (const T*)v_cache,
                               block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, hd, scale, window,
                               chunk, n_chunks, part_acc, part_ml);
     RB_LAUNCH_CHECK();
@@ -279,11 +283,11 @@ extern "C" int rb_attention_merge(const float* part_acc, const float* part_ml, v
     const size_t smem = (size_t)warps * n_chunks * sizeof(float);
     if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
     if (dtype == RB_BF16)
-        attention_merge_kernel<<<(int)blocks, warps * 32, smem, s>>>(part_acc, part_ml, (__nv_bfloat16*)out, o_stride,
+        RB_LAUNCH((attention_merge_kernel<__nv_bfloat16>), dim3((int)blocks), dim3(warps * 32), smem, s, part_acc, part_ml, (__nv_bfloat16*)out, o_stride,
                                                                   positions, slot_of_token, T, nq, hd, chunk,
                                                                   n_chunks, window);
     else if (dtype == RB_F32)
-        attention_merge_kernel<<<(int)blocks, warps * 32, smem, s>>>(part_acc, part_ml, (float*)out, o_stride,
+        RB_LAUNCH((attention_merge_kernel<float>), dim3((int)blocks), dim3(warps * 32), smem, s, part_acc, part_ml, (float*)out, o_stride,
                                                                   positions, slot_of_token, T, nq, hd, chunk,
                                                                   n_chunks, window);
     else

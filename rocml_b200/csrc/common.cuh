@@ -23,8 +23,41 @@
         cudaError_t e__ = cudaGetLastError();     \
         if (e__ != cudaSuccess) return (int)e__;  \
     } while (0)
+#define RB_LAUNCH(...)                                       \
+    do {                                                     \
+        cudaError_t e__ = rb::launch(__VA_ARGS__);           \
+        if (e__ != cudaSuccess) return (int)e__;             \
+    } while (0)
 
 namespace rb {
+
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Every kernel of the library is launched so that it may be scheduled while its predecessor in the
+// stream is still running: it signals at once that its own successor may be scheduled
+// (pdl_trigger), does whatever does not depend on the predecessor (set-up, and for the matrix
+// products the first tiles of the weights), and only then waits for the predecessor's results
+// (pdl_wait, which returns once the predecessor has finished and its writes are visible).  Without
+// the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();  // defined in launch.cu: on unless RB_PDL=0 is set
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

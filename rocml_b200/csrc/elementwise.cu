@@ -11,6 +11,8 @@ using namespace rb;
 template <typename WT>
 __global__ void embedding_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
                                  float* __restrict__ out, int H, int vocab, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -29,9 +31,9 @@ extern "C" int rb_embedding(const int* ids, const void* table, int table_dtype, 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == RB_BF16)
-        embedding_kernel<<<T, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, out, H, vocab, status);
+        RB_LAUNCH((embedding_kernel<__nv_bfloat16>), dim3(T), dim3(threads), 0, s, ids, (const __nv_bfloat16*)table, out, H, vocab, status);
     else if (table_dtype == RB_F32)
-        embedding_kernel<<<T, threads, 0, s>>>(ids, (const float*)table, out, H, vocab, status);
+        RB_LAUNCH((embedding_kernel<float>), dim3(T), dim3(threads), 0, s, ids, (const float*)table, out, H, vocab, status);
     else
         return RB_ERR_BAD_DTYPE;
     RB_LAUNCH_CHECK();
@@ -50,6 +52,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
                                    int n_delta, size_t delta_stride, const WT* __restrict__ w,
                                    OT* __restrict__ out, const int* __restrict__ rows, int H,
                                    float eps, int write_back) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) float row_buf[];  // H floats (padded to 4) + 33 for the reduction
     float* red = row_buf + ((H + 3) & ~3);
     const int orow = blockIdx.x;
@@ -115,7 +119,7 @@ static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, siz
         if (e != cudaSuccess) return (int)e;
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    k<<<n_rows, threads, smem, s>>>(resid, delta, n_delta, delta_stride, (const WT*)w, (OT*)out, rows, H,
+    RB_LAUNCH((k), dim3(n_rows), dim3(threads), smem, s, resid, delta, n_delta, delta_stride, (const WT*)w, (OT*)out, rows, H,
                                     eps, write_back);
     RB_LAUNCH_CHECK();
     return RB_OK;
@@ -139,40 +143,69 @@ extern "C" int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, lon
 }
 
 // ---- SiLU(gate) * up ------------------------------------------------------------------------
-// in: [T, 2*I] with the gate in columns [0, I) and up in [I, 2I); out: [T, I].
-// silu(g) = g / (1 + exp(-g)) as in rocml-kernels/kernels/silu_mul.hip:15-18.
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int I) {
-    const size_t n = (size_t)rows * I;
+// in: [S][T, 2*I] (S partial sums that are added first, in order), the gate in columns [0, I) and
+// up in [I, 2I); out: [T, I].  silu(g) = g / (1 + exp(-g)) as in
+// rocml-kernels/kernels/silu_mul.hip:15-18.  Four outputs per thread when I is a multiple of 4.
+template <typename IT, typename OT>
+__global__ void silu_mul_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, OT* __restrict__ out,
+                                int rows, int I) {
+    pdl_trigger();
+    pdl_wait();
+    const int I4 = I >> 2;
+    const bool vec = (I & 3) == 0;
+    const size_t n = vec ? (size_t)rows * I4 : (size_t)rows * I;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
          idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / I;
-        const int i = (int)(idx - t * I);
-        const float g = to_f32(in[t * 2 * I + i]);
-        const float u = to_f32(in[t * 2 * I + I + i]);
-        out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+        if (vec) {
+            const size_t t = idx / I4;
+            const int i = (int)(idx - t * I4) * 4;
+            float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int s = 0; s < n_in; ++s) {
+                const IT* p = in + (size_t)s * in_stride + t * 2 * I + i;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { g[j] += to_f32(p[j]); u[j] += to_f32(p[I + j]); }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) out[t * I + i + j] = from_f32<OT>(g[j] / (1.f + expf(-g[j])) * u[j]);
+        } else {
+            const size_t t = idx / I;
+            const int i = (int)(idx - t * I);
+            float g = 0.f, u = 0.f;
+            for (int s = 0; s < n_in; ++s) {
+                g += to_f32(in[(size_t)s * in_stride + t * 2 * I + i]);
+                u += to_f32(in[(size_t)s * in_stride + t * 2 * I + I + i]);
+            }
+            out[idx] = from_f32<OT>(g / (1.f + expf(-g)) * u);
+        }
     }
 }
 
-extern "C" int rb_silu_mul(const void* in, void* out, int dtype, int rows, int I, void* stream) {
+extern "C" int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype,
+                           int rows, int I, void* stream) {
     if (rows <= 0) return RB_OK;
+    if (n_in < 1) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t n = (size_t)rows * I;
+    const size_t n = (I & 3) == 0 ? (size_t)rows * (I >> 2) : (size_t)rows * I;
     const int threads = 256;
-    const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-    if (dtype == RB_BF16)
-        silu_mul_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, I);
-    else if (dtype == RB_F32)
-        silu_mul_kernel<<<blocks, threads, 0, s>>>((const float*)in, (float*)out, rows, I);
+    const size_t want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    typedef __nv_bfloat16 bf;
+    if (in_dtype == RB_BF16 && out_dtype == RB_BF16)
+        RB_LAUNCH((silu_mul_kernel<bf, bf>), dim3(blocks), dim3(threads), 0, s, (const bf*)in, n_in, (size_t)in_stride, (bf*)out, rows, I);
+    else if (in_dtype == RB_F32 && out_dtype == RB_BF16)
+        RB_LAUNCH((silu_mul_kernel<float, bf>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride, (bf*)out, rows, I);
+    else if (in_dtype == RB_F32 && out_dtype == RB_F32)
+        RB_LAUNCH((silu_mul_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride, (float*)out, rows, I);
     else
         return RB_ERR_BAD_DTYPE;
-    RB_LAUNCH_CHECK();
     return RB_OK;
 }
 
 // ---- casts ------------------------------------------------------------------------------------
 template <typename A, typename B>
 __global__ void cast_kernel(const A* __restrict__ in, B* __restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = from_f32<B>(to_f32(in[i]));
 }
@@ -184,9 +217,9 @@ extern "C" int rb_cast(const void* in, int in_dtype, void* out, int out_dtype, l
     const long long want = (n + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (in_dtype == RB_F32 && out_dtype == RB_BF16)
-        cast_kernel<<<blocks, threads, 0, s>>>((const float*)in, (__nv_bfloat16*)out, (size_t)n);
+        RB_LAUNCH((cast_kernel<float, __nv_bfloat16>), dim3(blocks), dim3(threads), 0, s, (const float*)in, (__nv_bfloat16*)out, (size_t)n);
     else if (in_dtype == RB_BF16 && out_dtype == RB_F32)
-        cast_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (float*)out, (size_t)n);
+        RB_LAUNCH((cast_kernel<__nv_bfloat16, float>), dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)in, (float*)out, (size_t)n);
     else
         return RB_ERR_BAD_DTYPE;
     RB_LAUNCH_CHECK();

@@ -18,6 +18,8 @@ template <typename XT, typename WT, typename OT>
 __global__ void __launch_bounds__(256)
 gemm_tn_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* __restrict__ bias,
                OT* __restrict__ out, int M, int N, int K, long long ldx, long long ldo) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -73,7 +75,7 @@ int launch(const void* x, const void* w, const void* bias, void* out, int M, int
            long long ldo, cudaStream_t s) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return RB_ERR_BAD_SIZE;
-    gemm_tn_kernel<XT, WT, OT><<<grid, 256, 0, s>>>((const XT*)x, (const WT*)w, (const float*)bias, (OT*)out, M,
+    RB_LAUNCH((gemm_tn_kernel<XT, WT, OT>), dim3(grid), dim3(256), 0, s, (const XT*)x, (const WT*)w, (const float*)bias, (OT*)out, M,
                                                     N, K, ldx, ldo);
     RB_LAUNCH_CHECK();
     return RB_OK;

@@ -43,11 +43,12 @@ struct Cfg {
 
 struct Params {
     int a_rows, b_rows, K;        // extents of the A-side and B-side operands
-    int k_per_split;              // multiple of BK
+    int splits;                   // the K blocks are dealt out evenly over blockIdx.z
     long long ldo;                // row stride of out, in elements
     long long split_stride;       // elements between the partial results of two splits
     const float* bias;            // [features] or null; added by split 0 only
     int* status;
+    int stages;                   // depth of the shared-memory ring actually used (<= Cfg::STAGES)
 };
 
 template <int BN, bool SWAP, typename OT>
@@ -57,21 +58,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE);
-    uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_ready = empty + C::STAGES;
+    const int S = p.stages;
+    uint64_t* full = (uint64_t*)(smem + S * C::STAGE);
+    uint64_t* empty = full + S;
+    uint64_t* acc_ready = empty + S;
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
     uint32_t* abort_flag = tmem_slot + 1;
 
+    rb::pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * BM;   // first row of the A-side operand in this tile
     const int b0 = blockIdx.y * BN;   // first row of the B-side operand
-    const int k_begin = blockIdx.z * p.k_per_split;
-    const int k_end = min(p.K, k_begin + p.k_per_split);
-    const int n_kb = (k_end - k_begin + BK - 1) / BK;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb_first = (int)((long long)blockIdx.z * kb_total / p.splits);
+    const int n_kb = (int)((long long)(blockIdx.z + 1) * kb_total / p.splits) - kb_first;
+    const int k_begin = kb_first * BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -89,11 +93,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             tma_prefetch_desc(&map_a);
             tma_prefetch_desc(&map_b);
-            int issued = 0;
+            // The weights do not depend on the kernel before this one: their first tiles are
+            // requested at once, then the predecessor's results are waited for, then the
+            // activations' tiles follow.
+            const int pre = n_kb < S ? n_kb : S;
+            for (int kb = 0; kb < pre; ++kb) {
+                uint8_t* sa = smem + kb * C::STAGE;
+                mbar_arrive_expect_tx(&full[kb], C::A_BYTES + C::B_BYTES);
+                if (SWAP) tma_load_2d(sa, &map_a, k_begin + kb * BK, a0, &full[kb]);
+                else tma_load_2d(sa + C::A_BYTES, &map_b, k_begin + kb * BK, b0, &full[kb]);
+            }
+            rb::pdl_wait();
+            for (int kb = 0; kb < pre; ++kb) {
+                uint8_t* sa = smem + kb * C::STAGE;
+                if (SWAP) tma_load_2d(sa + C::A_BYTES, &map_b, k_begin + kb * BK, b0, &full[kb]);
+                else tma_load_2d(sa, &map_a, k_begin + kb * BK, a0, &full[kb]);
+            }
+            int issued = pre;
             bool ok = true;
-            for (int kb = 0; kb < n_kb && ok; ++kb) {
-                const int s = kb % C::STAGES;
-                const uint32_t ph = (kb / C::STAGES) & 1;
+            for (int kb = pre; kb < n_kb && ok; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (kb / S) & 1;
                 ok = mbar_wait(&empty[s], ph ^ 1);
                 if (!ok) break;
                 uint8_t* sa = smem + s * C::STAGE;
@@ -106,9 +126,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 atomicExch(p.status, RB_ERR_TIMEOUT);
                 atomicExch(abort_flag, 1u);
                 // wait (bounded) for the copies this thread still has in flight
-                const int first = issued > C::STAGES ? issued - C::STAGES : 0;
+                const int first = issued > S ? issued - S : 0;
                 for (int kb = first; kb < issued; ++kb)
-                    mbar_wait(&full[kb % C::STAGES], (kb / C::STAGES) & 1);
+                    mbar_wait(&full[kb % S], (kb / S) & 1);
             }
         }
     } else if (warp == 1) {
@@ -116,8 +136,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
             bool ok = true;
             for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % C::STAGES;
-                const uint32_t ph = (kb / C::STAGES) & 1;
+                const int s = kb % S;
+                const uint32_t ph = (kb / S) & 1;
                 ok = mbar_wait(&full[s], ph);
                 if (!ok) break;
                 tc_fence_after();
@@ -254,7 +274,11 @@ int tensor_map(const void* ptr, long long rows, long long K, long long ld, int b
 }
 
 template <int BN, bool SWAP, typename OT>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const Params& p, int splits, cudaStream_t s) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, int splits, cudaStream_t s) {
+    // Few tokens (SWAP): the kernel is bound by memory latency, and several small blocks per
+    // multiprocessor with a shallow ring hide each other's start and end better than one block
+    // with a deep ring (measured: 3 stages beat 5 and 10 on every decode shape).
+    if (p.stages <= 0) p.stages = SWAP ? 3 : Cfg<BN>::STAGES;
     using C = Cfg<BN>;
     auto k = gemm_tcgen05_kernel<BN, SWAP, OT>;
     static bool attr_done = false;
@@ -263,9 +287,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const Params
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
+    if (p.stages < 2 || p.stages > C::STAGES) return RB_ERR_BAD_SIZE;
+    const int smem_bytes = p.stages * C::STAGE + 1024 + 256;
     dim3 grid((p.a_rows + BM - 1) / BM, (p.b_rows + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
-    k<<<grid, 192, C::SMEM, s>>>(ma, mb, (OT*)out, p);
+    RB_LAUNCH((k), dim3(grid), dim3(192), smem_bytes, s, ma, mb, (OT*)out, p);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
@@ -291,15 +317,13 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out,
 // or a base pointer off a 16-byte boundary; the caller then uses the plain kernel.
 extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
                                int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
-                               int* status, void* stream) {
+                               int stages, int* status, void* stream) {
     if (M <= 0 || N <= 0) return RB_OK;
     if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
     if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
     if (splits > 1 && out_dtype != RB_F32) return RB_ERR_BAD_DTYPE;
     const int kb_total = (K + BK - 1) / BK;
-    if (splits > kb_total) splits = kb_total;
-    const int kb_per = (kb_total + splits - 1) / splits;
-    if ((long long)(splits - 1) * kb_per >= kb_total) return RB_ERR_BAD_SIZE;  // a split would be empty
+    if (splits > kb_total) return RB_ERR_BAD_SIZE;  // a split would be empty and its partial result unwritten
     cudaStream_t s = (cudaStream_t)stream;
     const bool swap = M <= 128;
     int bn;
@@ -307,11 +331,12 @@ extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, 
     else bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
     Params p;
     p.K = K;
-    p.k_per_split = kb_per * BK;
+    p.splits = splits;
     p.ldo = ldo;
     p.split_stride = split_stride;
     p.bias = bias;
     p.status = status;
+    p.stages = stages;   // 0: the default of the mode
     CUtensorMap ma, mb;
     int rc;
     if (swap) {

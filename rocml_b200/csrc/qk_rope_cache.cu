@@ -15,16 +15,20 @@
 
 using namespace rb;
 
-template <typename AT, typename WT>
-__global__ void qk_norm_rope_cache_kernel(AT* __restrict__ qkv, int row_stride, int T, int nq, int nkv,
-                                          int hd, const WT* __restrict__ q_norm_w,
-                                          const WT* __restrict__ k_norm_w, float eps,
-                                          const float* __restrict__ inv_freq, int rot_dim,
+// `in` holds the projections: [S][T, row_stride] of type IT, S partial sums added first, in order
+// (S = 1 and IT = AT when the matrix product wrote its result in one piece).  q goes to q_out
+// (which may be `in` itself when S = 1 and the types agree), k and v to the cache.
+template <typename IT, typename AT, typename WT>
+__global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride,
+                                          AT* __restrict__ q_out, int q_stride, int T, int nq, int nkv, int hd,
+                                          const WT* __restrict__ q_norm_w, const WT* __restrict__ k_norm_w,
+                                          float eps, const float* __restrict__ inv_freq, int rot_dim,
                                           const int* __restrict__ positions,
                                           const int* __restrict__ slot_of_token,
                                           const int* __restrict__ block_table, int max_pages,
-                                          AT* __restrict__ k_cache, AT* __restrict__ v_cache,
-                                          int write_kv) {
+                                          AT* __restrict__ k_cache, AT* __restrict__ v_cache, int write_kv) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -42,11 +46,11 @@ __global__ void qk_norm_rope_cache_kernel(AT* __restrict__ qkv, int row_stride, 
     if (h < nq) { kind = 0; head = h; }
     else if (h < nq + nkv) { kind = 1; head = h - nq; }
     else { kind = 2; head = h - nq - nkv; }
-    AT* src = qkv + (size_t)t * row_stride + (size_t)h * hd;
+    const IT* src = in + (size_t)t * row_stride + (size_t)h * hd;
 
     AT* dst;
     if (kind == 0) {
-        dst = src;
+        dst = q_out + (size_t)t * q_stride + (size_t)head * hd;
     } else {
         const int page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
         if (page < 0) return;  // no page: the host never schedules this; skip rather than fault
@@ -54,21 +58,21 @@ __global__ void qk_norm_rope_cache_kernel(AT* __restrict__ qkv, int row_stride, 
         dst = base + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hd;
     }
 
-    if (kind == 2) {
-        for (int i = lane; i < hd; i += 32) dst[i] = src[i];
-        return;
-    }
-
     float ss = 0.f;
     for (int i = lane; i < hd; i += 32) {
-        const float v = to_f32(src[i]);
+        float v = 0.f;
+        for (int s = 0; s < n_in; ++s) v += to_f32(src[(size_t)s * in_stride + i]);
         buf[i] = v;
         ss += v * v;
+    }
+    __syncwarp();
+    if (kind == 2) {
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f32<AT>(buf[i]);
+        return;
     }
     ss = warp_sum(ss);
     const WT* w = kind == 0 ? q_norm_w : k_norm_w;
     const float inv = w ? rsqrtf(ss / (float)hd + eps) : 1.f;
-    __syncwarp();
     const int half = inv_freq ? rot_dim / 2 : 0;
     for (int i = lane; i < half; i += 32) {
         float x0 = buf[i], x1 = buf[i + half];
@@ -86,38 +90,44 @@ __global__ void qk_norm_rope_cache_kernel(AT* __restrict__ qkv, int row_stride, 
     }
 }
 
-template <typename AT, typename WT>
-static int launch_qk(void* qkv, int row_stride, int T, int nq, int nkv, int hd, const void* qw,
-                     const void* kw, float eps, const float* inv_freq, int rot_dim, const int* positions,
-                     const int* slot_of_token, const int* block_table, int max_pages, void* k_cache,
-                     void* v_cache, int write_kv, cudaStream_t s) {
+template <typename IT, typename AT, typename WT>
+static int launch_qk(const void* in, int n_in, long long in_stride, int row_stride, void* q_out, int q_stride,
+                     int T, int nq, int nkv, int hd, const void* qw, const void* kw, float eps,
+                     const float* inv_freq, int rot_dim, const int* positions, const int* slot_of_token,
+                     const int* block_table, int max_pages, void* k_cache, void* v_cache, int write_kv,
+                     cudaStream_t s) {
     const int warps = 4;
     const long long items = (long long)T * (nq + (write_kv ? 2 * nkv : 0));
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
     const size_t smem = (size_t)warps * hd * sizeof(float);
     if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
-    qk_norm_rope_cache_kernel<AT, WT><<<(int)blocks, warps * 32, smem, s>>>(
-        (AT*)qkv, row_stride, T, nq, nkv, hd, (const WT*)qw, (const WT*)kw, eps, inv_freq, rot_dim,
-        positions, slot_of_token, block_table, max_pages, (AT*)k_cache, (AT*)v_cache, write_kv);
-    RB_LAUNCH_CHECK();
+    RB_LAUNCH((qk_norm_rope_cache_kernel<IT, AT, WT>), dim3((int)blocks), dim3(warps * 32), smem, s, (const IT*)in,
+              n_in, (size_t)in_stride, row_stride, (AT*)q_out, q_stride, T, nq, nkv, hd, (const WT*)qw,
+              (const WT*)kw, eps, inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages,
+              (AT*)k_cache, (AT*)v_cache, write_kv);
     return RB_OK;
 }
 
-extern "C" int rb_qk_norm_rope_cache(void* qkv, int act_dtype, int row_stride, int T, int nq, int nkv,
-                                     int hd, const void* q_norm_w, const void* k_norm_w, int w_dtype,
-                                     float eps, const float* inv_freq, int rot_dim, const int* positions,
+extern "C" int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride,
+                                     void* q_out, int act_dtype, int q_stride, int T, int nq, int nkv, int hd,
+                                     const void* q_norm_w, const void* k_norm_w, int w_dtype, float eps,
+                                     const float* inv_freq, int rot_dim, const int* positions,
                                      const int* slot_of_token, const int* block_table, int max_pages,
                                      void* k_cache, void* v_cache, int write_kv, void* stream) {
     if (T <= 0) return RB_OK;
-    if (hd <= 0 || hd % 2 || (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > hd))) return RB_ERR_BAD_SIZE;
+    if (hd <= 0 || hd % 2 || n_in < 1 || (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > hd)))
+        return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-#define RB_QK_ARGS qkv, row_stride, T, nq, nkv, hd, q_norm_w, k_norm_w, eps, inv_freq, rot_dim, positions, \
-                   slot_of_token, block_table, max_pages, k_cache, v_cache, write_kv, s
-    if (act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<__nv_bfloat16, __nv_bfloat16>(RB_QK_ARGS);
-    if (act_dtype == RB_BF16 && w_dtype == RB_F32) return launch_qk<__nv_bfloat16, float>(RB_QK_ARGS);
-    if (act_dtype == RB_F32 && w_dtype == RB_BF16) return launch_qk<float, __nv_bfloat16>(RB_QK_ARGS);
-    if (act_dtype == RB_F32 && w_dtype == RB_F32) return launch_qk<float, float>(RB_QK_ARGS);
+    typedef __nv_bfloat16 bf;
+#define RB_QK_ARGS in, n_in, in_stride, row_stride, q_out, q_stride, T, nq, nkv, hd, q_norm_w, k_norm_w, eps, \
+                   inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages, k_cache, v_cache, write_kv, s
+    if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<bf, bf, bf>(RB_QK_ARGS);
+    if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_F32) return launch_qk<bf, bf, float>(RB_QK_ARGS);
+    if (in_dtype == RB_F32 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<float, bf, bf>(RB_QK_ARGS);
+    if (in_dtype == RB_F32 && act_dtype == RB_BF16 && w_dtype == RB_F32) return launch_qk<float, bf, float>(RB_QK_ARGS);
+    if (in_dtype == RB_F32 && act_dtype == RB_F32 && w_dtype == RB_BF16) return launch_qk<float, float, bf>(RB_QK_ARGS);
+    if (in_dtype == RB_F32 && act_dtype == RB_F32 && w_dtype == RB_F32) return launch_qk<float, float, float>(RB_QK_ARGS);
 #undef RB_QK_ARGS
     return RB_ERR_BAD_DTYPE;
 }

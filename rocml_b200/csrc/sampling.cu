@@ -30,6 +30,8 @@ __device__ __forceinline__ Best warp_best(Best x) {
 
 __global__ void argmax_kernel(const float* __restrict__ logits, long long row_stride, int V,
                               int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.x * row_stride;
@@ -55,6 +57,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, long long row_st
 // the result is the first maximum, as in the single-block kernel.
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, long long row_stride, int V, int per,
                                       float* __restrict__ pv, int* __restrict__ pi) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.y * row_stride;
@@ -77,6 +81,8 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, long lon
 }
 __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int n,
                                     int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x;
     Best b{-INFINITY, 0x7fffffff};
     for (int i = lane; i < n; i += 32) {
@@ -98,13 +104,13 @@ extern "C" int rb_argmax(const float* logits, long long row_stride, int rows, in
     if (slices > 1 && scratch_v && scratch_i) {
         if (rows > 65535) return RB_ERR_BAD_SIZE;
         const int per = (V + slices - 1) / slices;
-        argmax_partial_kernel<<<dim3(slices, rows), 256, 0, s>>>(logits, row_stride, V, per, scratch_v, scratch_i);
+        RB_LAUNCH((argmax_partial_kernel), dim3(dim3(slices, rows)), dim3(256), 0, s, logits, row_stride, V, per, scratch_v, scratch_i);
         RB_LAUNCH_CHECK();
-        argmax_final_kernel<<<rows, 32, 0, s>>>(scratch_v, scratch_i, slices, out);
+        RB_LAUNCH((argmax_final_kernel), dim3(rows), dim3(32), 0, s, scratch_v, scratch_i, slices, out);
         RB_LAUNCH_CHECK();
         return RB_OK;
     }
-    argmax_kernel<<<rows, 1024, 0, s>>>(logits, row_stride, V, out);
+    RB_LAUNCH((argmax_kernel), dim3(rows), dim3(1024), 0, s, logits, row_stride, V, out);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
@@ -268,6 +274,8 @@ __device__ __forceinline__ bool cand_before(float va, int ia, float vb, int ib, 
 __global__ void __launch_bounds__(ST)
 sample_kernel(float* __restrict__ logits, long long row_stride, int V, const SampleRow* __restrict__ rows,
               const int* __restrict__ history, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ Shared sh;
     const SampleRow r = rows[blockIdx.x];
     float* row = logits + (size_t)blockIdx.x * row_stride;
@@ -435,7 +443,7 @@ extern "C" int rb_sample(float* logits, long long row_stride, int n, int V, cons
                          int* out, void* stream) {
     if (n <= 0) return RB_OK;
     if (V <= 0) return RB_ERR_BAD_SIZE;
-    sample_kernel<<<n, ST, 0, (cudaStream_t)stream>>>(logits, row_stride, V, (const SampleRow*)rows, history, out);
+    RB_LAUNCH((sample_kernel), dim3(n), dim3(ST), 0, (cudaStream_t)stream, logits, row_stride, V, (const SampleRow*)rows, history, out);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

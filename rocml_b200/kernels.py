@@ -76,19 +76,21 @@ def _lib():
     if not _sigs_done:
         lib.rb_embedding.argtypes = [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]
         lib.rb_add_rmsnorm.argtypes = [_vp, _vp, _i, _ll, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp]
-        lib.rb_silu_mul.argtypes = [_vp, _vp, _i, _i, _i, _vp]
+        lib.rb_silu_mul.argtypes = [_vp, _i, _i, _ll, _vp, _i, _i, _i, _vp]
         lib.rb_cast.argtypes = [_vp, _i, _vp, _i, _ll, _vp]
-        lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _vp,
-                                              _vp, _vp, _i, _vp, _vp, _i, _vp]
+        lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f,
+                                              _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp]
         lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _vp]
         lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
                                              _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
         lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
         lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp]
+        lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                                             _f, _i, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
-                                            _vp, _vp, _vp, _i, _vp]
+                                            _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
-        lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp, _vp]
+        lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _vp, _vp]
         _sigs_done = True
     return lib
 
@@ -133,12 +135,25 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     _check(rc, "add_rmsnorm")
 
 
+def _partials(x: torch.Tensor, what: str):
+    """(n partial sums, stride between them, row stride) of [T, N] or [S, T, N]."""
+    if x.dim() == 3:
+        if x.stride(2) != 1:
+            raise KernelError(f"{what}: inner stride must be 1")
+        return x.shape[0], x.stride(0), x.stride(1)
+    if x.stride(1) != 1:
+        raise KernelError(f"{what}: inner stride must be 1")
+    return 1, 0, x.stride(0)
+
+
 def silu_mul(x: torch.Tensor, out: torch.Tensor):
-    """x [T, 2I] = [gate | up] -> out [T, I] = silu(gate) * up."""
-    T, I2 = x.shape
-    if I2 % 2 or out.shape != (T, I2 // 2) or out.dtype != x.dtype or not x.is_contiguous() or not out.is_contiguous():
-        raise KernelError("silu_mul: shapes or types do not fit")
-    _check(_lib().rb_silu_mul(_ptr(x), _ptr(out), dtype_code(x.dtype), T, I2 // 2, _stream()), "silu_mul")
+    """x [T, 2I] = [gate | up], or [S, T, 2I] partial sums to be added first -> out [T, I] = silu(gate) * up."""
+    n_in, in_stride, row_stride = _partials(x, "silu_mul")
+    T, I2 = x.shape[-2], x.shape[-1]
+    if I2 % 2 or tuple(out.shape) != (T, I2 // 2) or row_stride != I2 or not out.is_contiguous():
+        raise KernelError("silu_mul: shapes do not fit")
+    _check(_lib().rb_silu_mul(_ptr(x), dtype_code(x.dtype), n_in, in_stride, _ptr(out), dtype_code(out.dtype), T,
+                              I2 // 2, _stream()), "silu_mul")
 
 
 def cast(x: torch.Tensor, out: torch.Tensor):
@@ -149,15 +164,20 @@ def cast(x: torch.Tensor, out: torch.Tensor):
 
 # ---- q/k norm + rotary + cache write --------------------------------------------------------------
 
-def qk_norm_rope_cache(qkv: torch.Tensor, n_tokens: int, nq: int, nkv: int, hd: int,
+def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, nq: int, nkv: int, hd: int,
                        q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                        inv_freq: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
                        slot_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], write_kv: bool = True):
-    """qkv [T, nq*hd (+ 2*nkv*hd)]: q normalised and rotated in place; k, v written to their pages."""
+    """proj [T, nq*hd (+ 2*nkv*hd)] (or [S, T, ...] partial sums): q normalised and rotated into q_out
+    (rows of nq*hd, any row stride; it may be ``proj`` itself); k (normalised, rotated) and v written
+    to their pages."""
     width = (nq + (2 * nkv if write_kv else 0)) * hd
-    if qkv.dim() != 2 or qkv.shape[1] != width or qkv.stride(1) != 1:
-        raise KernelError(f"qk_norm_rope_cache: qkv must be [T, {width}] with unit inner stride")
+    n_in, in_stride, row_stride = _partials(proj, "qk_norm_rope_cache")
+    if proj.shape[-1] != width:
+        raise KernelError(f"qk_norm_rope_cache: projections must be {width} wide")
+    if q_out.stride(-1) != 1 or q_out.shape[-1] < nq * hd:
+        raise KernelError("qk_norm_rope_cache: q_out rows must hold nq * hd elements with unit stride")
     if (q_norm_w is None) != (k_norm_w is None):
         raise KernelError("qk_norm_rope_cache: give both norm weights or neither")
     wd = dtype_code(q_norm_w.dtype) if q_norm_w is not None else F32
@@ -168,13 +188,14 @@ def qk_norm_rope_cache(qkv: torch.Tensor, n_tokens: int, nq: int, nkv: int, hd: 
     if write_kv:
         if k_cache is None or v_cache is None or block_table is None:
             raise KernelError("qk_norm_rope_cache: cache tensors missing")
-        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or not k_cache.is_contiguous() or \
+        if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype or not k_cache.is_contiguous() or \
                 tuple(k_cache.shape[1:]) != (nkv, PAGE, hd):
             raise KernelError("qk_norm_rope_cache: cache must be [pages, nkv, 64, hd] of the activations' type")
     max_pages = block_table.shape[1] if block_table is not None else 0
     rc = _lib().rb_qk_norm_rope_cache(
-        _ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0), n_tokens, nq, nkv, hd, _ptr(q_norm_w), _ptr(k_norm_w), wd,
-        float(eps), _ptr(inv_freq), rot_dim, _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
+        _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, _ptr(q_out), dtype_code(q_out.dtype),
+        q_out.stride(-2), n_tokens, nq, nkv, hd, _ptr(q_norm_w), _ptr(k_norm_w), wd, float(eps), _ptr(inv_freq),
+        rot_dim, _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
         None if block_table is None else _i32(block_table, "block_table"), max_pages, _ptr(k_cache), _ptr(v_cache),
         1 if write_kv else 0, _stream())
     _check(rc, "qk_norm_rope_cache")
@@ -216,12 +237,48 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _check(rc, "attention_generic")
 
 
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                      n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0) -> bool:
+    """bfloat16 flash attention on the tensor cores for any number of query tokens per sequence.
+    Returns False when the kernel does not take the head size or the alignment."""
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
+            q.stride(-1) != 1 or out.stride(-1) != 1:
+        return False
+    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+        raise KernelError("attention_prefill: cache must be [pages, nkv, 64, hd]")
+    rc = _lib().rb_attention_prefill(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"),
+        block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs,
+        max_q_len, nq, nkv, hd, float(scale), int(window), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "attention_prefill")
+    return True
+
+
+_counters = {}
+_COUNTER_INTS = 1 << 20
+
+
+def decode_counters(device) -> torch.Tensor:
+    """Zeroed int32 work space of the decode attention kernel (one counter per sequence and head
+    group); the kernel leaves it zeroed, so one buffer per device serves every launch."""
+    key = torch.device(device).index or 0
+    if key not in _counters:
+        _counters[key] = torch.zeros(_COUNTER_INTS, dtype=torch.int32, device=device)
+    return _counters[key]
+
+
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                      n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
                      part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor]) -> bool:
-    """bfloat16 decode attention, one query token per sequence, keys in chunks of 128.  Returns
+    """bfloat16 decode attention, one query token per sequence, keys in chunks of 128, the chunks
+    merged by the kernel itself; part_acc / part_ml are its work space when n_chunks > 1.  Returns
     False when the kernel does not take the head size or the alignment (use attention_generic)."""
+    if n_seqs * nq > _COUNTER_INTS:
+        return False
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or q.stride(-1) != 1 or out.stride(-1) != 1:
         return False
     if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
@@ -229,7 +286,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     rc = _lib().rb_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
-        int(window), int(n_chunks), _ptr(part_acc), _ptr(part_ml), _ptr(out), out.stride(0), _stream())
+        int(window), int(n_chunks), _ptr(part_acc), _ptr(part_ml), _ptr(decode_counters(q.device)), _ptr(out),
+        out.stride(0), _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_decode")
@@ -302,7 +360,7 @@ def check_status(device) -> None:
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                 m: Optional[int] = None) -> bool:
+                 m: Optional[int] = None, stages: int = 0) -> bool:
     """out = x . w^T on the tensor cores; x, w bfloat16, out bfloat16 [M, N] or float32 [M, N] or
     float32 [S, M, N] (S partial sums over K, to be added by the consumer).  Returns False when the
     kernel refuses the layout (K or a row stride not a multiple of 8, a pointer off 16 bytes);
@@ -323,7 +381,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("gemm_tcgen05: bias must be float32 [N]")
     rc = _lib().rb_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
-                                ldo, splits, split_stride, _ptr(status_word(x.device)), _stream())
+                                ldo, splits, split_stride, stages, _ptr(status_word(x.device)), _stream())
     if rc == 10003:
         return False
     _check(rc, "gemm_tcgen05")

@@ -85,15 +85,15 @@ class Attention(Mixer):
         T = batch.n_tokens
         dev, act = xn.device, self.env.act_dtype
         qd = self.nq * self.hd
-        qkv = torch.empty((T, self.qkv.n), dtype=act, device=dev)
-        self.qkv.forward(xn, qkv, T)
+        proj = self.qkv.forward_auto(xn, T)          # [T, N] or [S, T, N] partial sums
+        q = proj if proj.dim() == 2 else torch.empty((T, qd), dtype=act, device=dev)
         kernels.qk_norm_rope_cache(
-            qkv, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+            proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
             self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
             view.block_table, view.k, view.v, write_kv=view.writes and not self.shares_cache)
         attn = torch.empty((T, qd), dtype=act, device=dev)
         window = int(self.window) if self.window else 0
-        self.attend(qkv, attn, batch, view, window)
+        self.attend(q, attn, batch, view, window)
         return self.o.forward_delta(attn, T)
 
     def attend(self, q, out, batch, view, window):
@@ -110,15 +110,19 @@ class Attention(Mixer):
             fast = kernels.attention_decode(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                             batch.kv_len, batch.n_seqs, self.nq, self.nkv, self.hd, self.scale,
                                             window, n_chunks, acc, ml)
-            if not fast and n_chunks > 1:
+            if fast:
+                return
+            if n_chunks > 1:
                 kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                           batch.kv_len, batch.n_seqs, 1, self.nq, self.nkv, self.hd, self.scale,
                                           window, chunk, n_chunks, acc, ml)
-            if n_chunks > 1:
                 kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, self.nq, self.hd,
                                         chunk, n_chunks, window)
-            if fast or n_chunks > 1:
                 return
+        if kernels.attention_prefill(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
+                                     batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,
+                                     self.scale, window):
+            return
         kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                   batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,
                                   self.scale, window)

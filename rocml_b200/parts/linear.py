@@ -70,19 +70,38 @@ class Linear:
         kernels.gemm_generic(x, self.weight, out, self.bias, m)
         return out
 
+    def _splits(self, m: int) -> int:
+        """How many ways the sum over K is split when few rows stream a large weight.  One
+        thread block reads memory at a small fraction of the device's bandwidth, so the weight's
+        row tiles (128 rows each) are multiplied by K splits until about four blocks per
+        multiprocessor are in flight; each split keeps at least five 64-wide K blocks, and the
+        float32 partial results stay below a sixth of the weight's own bytes.  The count depends
+        on the weight's shape and the step's row count only."""
+        if m > 128 or self.k % 8:
+            return 1
+        tiles = (self.n + 127) // 128
+        by_blocks = (4 * 148) // tiles
+        by_depth = (self.k // 64) // 5
+        by_bytes = int(0.075 * self.k / max(m, 1))
+        return max(1, min(by_blocks, by_depth, by_bytes, 32))
+
     def forward_delta(self, x: torch.Tensor, m: int) -> torch.Tensor:
-        """The product as a float32 delta [S, M, N] for the residual stream.  With few rows the
-        sum over K is split S ways so that enough thread blocks stream the weight; the S partial
-        results are added, in order, by the norm that consumes the delta.  S depends on the
-        weight's shape and on whether the step is small, never on what else is in the batch."""
-        S = 1
-        if self._tensor_core(x) and m <= 128 and self.k % 8 == 0:
-            tiles = (self.n + 127) // 128
-            S = max(1, min(8, 148 // tiles, self.k // 512))
-        delta = torch.empty((S, m, self.n), dtype=torch.float32, device=x.device)
-        if self._tensor_core(x) and kernels.gemm_tcgen05(x, self.weight, delta, self.bias, m):
-            return delta
+        """The product as float32 [S, M, N]: S partial sums over K that the consumer adds in order
+        (a delta for the residual stream, or the input of a kernel that takes partial sums)."""
+        tc = self._tensor_core(x)
+        S = self._splits(m) if tc else 1
+        out = torch.empty((S, m, self.n), dtype=torch.float32, device=x.device)
+        if tc and kernels.gemm_tcgen05(x, self.weight, out, self.bias, m):
+            return out
         if S > 1:
-            delta = delta[:1]
-        kernels.gemm_generic(x, self.weight, delta[0], self.bias, m)
-        return delta
+            out = out[:1]
+        kernels.gemm_generic(x, self.weight, out[0], self.bias, m)
+        return out
+
+    def forward_auto(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        """The product in whichever form is cheapest for the step: [S, M, N] float32 partial sums
+        when few rows stream the weight, else [M, N] in the activations' type."""
+        if self._tensor_core(x) and self._splits(m) > 1:
+            return self.forward_delta(x, m)
+        out = torch.empty((m, self.n), dtype=x.dtype, device=x.device)
+        return self.forward(x, out, m)

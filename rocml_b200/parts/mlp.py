@@ -46,8 +46,7 @@ class GatedMLP(FeedForward):
     def forward(self, xn, batch):
         T = batch.n_tokens
         dev, act = xn.device, self.env.act_dtype
-        gu = torch.empty((T, 2 * self.inter), dtype=act, device=dev)
-        self.gate_up.forward(xn, gu, T)
+        gu = self.gate_up.forward_auto(xn, T)          # [T, 2I] or [S, T, 2I] partial sums
         h = torch.empty((T, self.inter), dtype=act, device=dev)
         kernels.silu_mul(gu, h)
         return self.down.forward_delta(h, T)

@@ -141,6 +141,10 @@ def test_silu_mul(dt):
     want = g / (1 + torch.exp(-g)) * u
     tol = 2 ** -8 if dt == torch.bfloat16 else 1e-6
     assert ((out.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max() < tol
+    parts = torch.stack([x.float() * 0.75, x.float() * 0.25])      # two float32 partial sums
+    out2 = torch.empty((T, I), dtype=dt, device=DEV)
+    kernels.silu_mul(parts, out2)
+    assert ((out2.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max() < tol
 
 
 # ---- attention over the paged cache --------------------------------------------------------------------
@@ -224,6 +228,37 @@ def test_attention_generic(case, dtype):
     assert err < tol, err
 
 
+PRE_CASES = [
+    # lens, q_lens, nq, nkv, hd, window
+    ([5, 70, 129, 64], [5, 70, 129, 64], 8, 2, 64, None),      # whole prompts of unequal length
+    ([700, 200, 65], [190, 1, 65], 8, 2, 128, None),           # pieces of prompts and a single token
+    ([300, 131], [300, 3], 4, 4, 128, 24),                     # a window narrower than a tile
+    ([900], [333], 6, 1, 64, 200),                             # a window that spans tiles; 6:1 groups
+    ([513], [513], 2, 1, 256, None),
+]
+
+
+@pytest.mark.parametrize("case", range(len(PRE_CASES)))
+def test_attention_prefill_tensor_cores(case):
+    from rocml_b200 import kernels
+    lens, q_lens, nq, nkv, hd, window = PRE_CASES[case]
+    dtype = torch.bfloat16
+    spike = (0, 2) if case == 1 else None         # a far key that outweighs hundreds of near ones
+    ks, vs, qs, kc, vc, meta = paged_case(20 + case, lens, q_lens, nq, nkv, hd, dtype, spike)
+    scale = 1.0 / math.sqrt(hd)
+    want = reference_attention(ks, vs, qs, window, scale)
+    q = torch.cat(qs, 0).reshape(-1, nq * hd).to(dtype).to(DEV)
+    out = torch.full_like(q, float("nan"))
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    kc[kc != kc] = 1e30      # what lies beyond a sequence's end in its last page must not matter
+    vc[vc != vc] = 1e30
+    assert kernels.attention_prefill(q, out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], len(lens),
+                                     max(q_lens), nq, nkv, hd, scale, window or 0)
+    err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
+    assert err < 2e-2, err
+
+
 DEC_CASES = [
     # lens, nq, nkv, hd, window
     ([700, 1, 129, 64, 128], 32, 8, 128, None),
@@ -256,10 +291,11 @@ def test_attention_decode_split_kv(case, fast):
     if fast:
         assert kernels.attention_decode(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"],
                                         d["kv_len"], B, nq, nkv, hd, scale, window or 0, n_chunks, acc, ml)
+        assert int(kernels.decode_counters(DEV).abs().sum()) == 0      # the work space is left zeroed
     else:
         kernels.attention_generic(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
                                   B, 1, nq, nkv, hd, scale, window or 0, 128, n_chunks, acc, ml)
-    kernels.attention_merge(acc, ml, out, pos, d["seq_slot"], B, nq, hd, 128, n_chunks, window or 0)
+        kernels.attention_merge(acc, ml, out, pos, d["seq_slot"], B, nq, hd, 128, n_chunks, window or 0)
     err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
     assert err < 2e-2, err
 
@@ -293,7 +329,7 @@ def test_qk_norm_rope_cache(dtype, wd, nq, nkv, hd, rot):
     kc = torch.zeros((6, nkv, 64, hd), dtype=dtype, device=DEV)
     vc = torch.zeros_like(kc)
     xd = x.to(DEV).clone()
-    kernels.qk_norm_rope_cache(xd, T, nq, nkv, hd, qw.to(DEV), kw.to(DEV), eps, inv.to(DEV), rot, positions.to(DEV),
+    kernels.qk_norm_rope_cache(xd, xd, T, nq, nkv, hd, qw.to(DEV), kw.to(DEV), eps, inv.to(DEV), rot, positions.to(DEV),
                                slots.to(DEV), table.to(DEV), kc, vc)
     xf = x.double()
     q = P.rmsnorm(xf[:, :nq * hd].reshape(T, nq, hd), qw.double(), eps)
@@ -314,3 +350,11 @@ def test_qk_norm_rope_cache(dtype, wd, nq, nkv, hd, rot):
         assert (kc[page, :, off].cpu().double() - k[t]).abs().max() < tol
         assert (vc[page, :, off].cpu().double() - v[t]).abs().max() < tol * 1e-3 + 1e-7
     assert kc.abs().sum(dim=(1, 3)).count_nonzero() == 8         # nothing else was written
+    # the same from three float32 partial sums, q into a buffer of its own
+    parts = torch.stack([x.float() * 0.5, x.float() * 0.25, x.float() * 0.25]).to(DEV)
+    q2 = torch.zeros((T, nq * hd), dtype=dtype, device=DEV)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    kernels.qk_norm_rope_cache(parts, q2, T, nq, nkv, hd, qw.to(DEV), kw.to(DEV), eps, inv.to(DEV), rot,
+                               positions.to(DEV), slots.to(DEV), table.to(DEV), kc2, vc2)
+    assert (q2[:8].cpu().double().reshape(8, nq, hd) - q[:8]).abs().max() < tol
+    assert (kc2.cpu().double() - kc.cpu().double()).abs().max() < tol and torch.equal(vc2, vc)
