@@ -1,35 +1,37 @@
 // Decode attention over the paged cache for bfloat16: one query token per sequence, keys split in
-// fixed chunks of 128 (split-KV), the chunks' partial results merged by the block that finishes last.
+// fixed chunks of 64, one page each (split-KV), the chunks' partial results merged by the block that finishes last.
 //
-// It is bound by reading the cache once, so the layout serves the loads: a block of 8 warps takes
-// one (chunk, key/value head, sequence) and up to 4 query heads of the group, which share every key
-// and value it reads.  Inside a warp 8 lanes share a key: each lane holds HD/8 dimensions of the
-// key row (two 16-byte loads at HD = 128; four adjacent keys make one contiguous 1 KB warp load).
-// Every thread first issues ALL its loads (4 keys and 4 values), then computes: partial dots are
-// reduced over the 8 lanes with 3 shuffles, each group of 8 lanes forms the softmax statistics of
-// its own 4 keys, and the 32 groups of the block are merged through shared memory.  The block
-// writes an unnormalised partial result; a counter per (sequence, head group) tells the last block
-// to arrive, which merges all chunks in ascending order and writes the output (the counter is left
-// at zero for the next launch).  Statistics and accumulators are float32; exp is expf.
+// The kernel is bound by reading the cache once.  A block takes one (chunk, key/value head, sequence)
+// and all query heads of the group (up to 16), which share every key and value it reads: the heads
+// are the rows of a 16-row tensor-core tile (mma.sync m16n8k16, float32 accumulation), so the
+// arithmetic costs next to nothing whatever the group size.  Each of the 4 warps copies its own 16
+// keys and 16 values into shared memory with cp.async (16-byte chunks, XOR-swizzled for ldmatrix),
+// computes S = Q K^T, the softmax statistics of its keys and P V, and the warps' results are merged
+// through shared memory.  The block writes an unnormalised partial result; a counter per (sequence,
+// head group) tells the last block to arrive, which merges all chunks in ascending order and writes
+// the output (the counter is left at zero for the next launch).  Softmax is float32, base 2
+// (exp(x) = exp2(x log2 e)).
 //
 // Replaces attn_decode_partial_f16 + attn_decode_reduce_f32 of the reference
 // (rocml-kernels/kernels/attn_decode.hip:93-255): same mathematics (head h reads key/value head
 // h / g, score = (q.k) * scale, max/sum softmax, split over the keys, log-sum-exp merge), other
 // mapping.  Head sizes 64, 128 and 256; other sizes use the plain kernel.
 #include "common.cuh"
+#include "mma_tiles.cuh"
 #include "api.h"
 
 using namespace rb;
+using namespace mma_tiles;
 
 namespace {
-constexpr int CHUNK = 128;        // keys per block
-constexpr int WARPS = 8;
-constexpr int KPT = CHUNK / (WARPS * 4);   // keys per 8-lane group: 4
+constexpr int CHUNK = 64;         // keys per block: one page
+constexpr int WARPS = 4;
+constexpr int WK = CHUNK / WARPS; // keys per warp: 16
+constexpr int ROWS = 16;          // query heads per block (rows of the MMA tile)
 constexpr float NEG_BIG = -1e30f;
+constexpr float LOG2E = 1.4426950408889634f;
 
-struct alignas(16) Pack8 { __nv_bfloat162 v[4]; };  // 8 bf16 = 16 bytes
-
-template <int HD, int GC>
+template <int HD>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
@@ -40,172 +42,151 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         __nv_bfloat16* __restrict__ out, int o_stride) {
     pdl_trigger();
     pdl_wait();
-    constexpr int DPL = HD / 8;          // dimensions per lane
-    constexpr int VEC = DPL / 8;         // 16-byte loads per lane per row
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [16][HD]
+    __nv_bfloat16* KVs = Qs + ROWS * HD;                                    // per warp: K [32][HD], V [32][HD]
+    float* s_o = reinterpret_cast<float*>(KVs);                            // reused after the products: [4][16][HD]
+    __shared__ float s_m[WARPS][ROWS], s_l[WARPS][ROWS];
+    __shared__ int s_last;
+
     const int c = blockIdx.x;
     const int g = nq / nkv;
-    const int head_chunks = g / GC;
+    const int head_chunks = (g + ROWS - 1) / ROWS;
     const int kvh = blockIdx.y / head_chunks;
-    const int h0 = kvh * g + (blockIdx.y % head_chunks) * GC;   // first query head of this block
+    const int hc = blockIdx.y % head_chunks;
+    const int h0 = kvh * g + hc * ROWS;                     // first query head of this block
+    const int rows_valid = min(ROWS, g - hc * ROWS);
     const int b = blockIdx.z;
     const int slot = seq_slot[b];
     if (slot < 0) return;
     const int t = cu_q[b];
     const int pos = kv_len[b] - 1;
-    if (c * CHUNK > pos) return;         // beyond the sequence: takes no part in the merge
+    if (c * CHUNK > pos) return;                            // beyond the sequence: takes no part in the merge
     const int lo = max(window > 0 ? max(0, pos - window + 1) : 0, c * CHUNK);
     const int hi = min(pos, (c + 1) * CHUNK - 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sub = lane & 7, grp = lane >> 3;
+    const int gq = lane >> 2, tq = lane & 3;
     const int* table = block_table + (size_t)slot * max_pages;
 
-    // all loads first: this group's keys are j0 + i * 32 (i < KPT), so that at every i the block
-    // reads 32 adjacent keys
-    const int j0 = c * CHUNK + warp * 4 + grp;
-    Pack8 kk[KPT][VEC], vv[KPT][VEC];
-    bool valid[KPT];
-#pragma unroll
-    for (int i = 0; i < KPT; ++i) {
-        const int j = j0 + i * 32;
-        valid[i] = j >= lo && j <= hi;
-        if (valid[i]) {
-            const int page = table[j / RB_PAGE];
-            const size_t off = (((size_t)page * nkv + kvh) * RB_PAGE + (j % RB_PAGE)) * HD + sub * DPL;
-#pragma unroll
-            for (int v = 0; v < VEC; ++v) {
-                kk[i][v] = *reinterpret_cast<const Pack8*>(k_cache + off + v * 8);
-                vv[i][v] = *reinterpret_cast<const Pack8*>(v_cache + off + v * 8);
-            }
-        } else {
-#pragma unroll
-            for (int v = 0; v < VEC; ++v)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    kk[i][v].v[e] = __float2bfloat162_rn(0.f);
-                    vv[i][v].v[e] = __float2bfloat162_rn(0.f);
-                }
-        }
+    // copies: the query heads (all threads), then each warp its own keys and values
+    load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
+    const int j0 = c * CHUNK + warp * WK;                   // this warp's first key; its 16 keys lie in one page
+    __nv_bfloat16* Kw = KVs + warp * 2 * WK * HD;
+    __nv_bfloat16* Vw = Kw + WK * HD;
+    const bool any = j0 <= hi && j0 + WK - 1 >= lo;
+    if (any) {
+        const int page = table[j0 / RB_PAGE];
+        const size_t off = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE + (j0 % RB_PAGE)) * HD;
+        const int valid = page < 0 ? 0 : min(WK, hi - j0 + 1);   // rows past the sequence's end are zero-filled
+        load_tile<HD>(Kw, k_cache + off, HD, WK, valid, lane, 32);
+        load_tile<HD>(Vw, v_cache + off, HD, WK, valid, lane, 32);
     }
-    // this lane's slice of the query heads
-    float qf[GC][DPL];
-#pragma unroll
-    for (int h = 0; h < GC; ++h) {
-        const __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)(h0 + h) * HD + sub * DPL;
-#pragma unroll
-        for (int v = 0; v < VEC; ++v) {
-            const Pack8 pk = *reinterpret_cast<const Pack8*>(qp + v * 8);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(pk.v[e]);
-                qf[h][v * 8 + 2 * e] = f.x;
-                qf[h][v * 8 + 2 * e + 1] = f.y;
-            }
-        }
-    }
-    // scores of this group's keys
-    float sc[KPT][GC];
-#pragma unroll
-    for (int i = 0; i < KPT; ++i) {
-#pragma unroll
-        for (int h = 0; h < GC; ++h) {
-            float s = 0.f;
-#pragma unroll
-            for (int v = 0; v < VEC; ++v)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 kf = __bfloat1622float2(kk[i][v].v[e]);
-                    s = fmaf(qf[h][v * 8 + 2 * e], kf.x, s);
-                    s = fmaf(qf[h][v * 8 + 2 * e + 1], kf.y, s);
-                }
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            sc[i][h] = valid[i] ? s * scale : NEG_BIG;   // scale after the dot, as the reference does
-        }
-    }
-    // softmax statistics and weighted values of the group's keys
-    __shared__ float s_m[WARPS * 4][GC], s_l[WARPS * 4][GC];
-    __shared__ float s_acc[WARPS][GC][HD + 4];
-    __shared__ int s_last;
-    float m[GC], l[GC], acc[GC][DPL];
-#pragma unroll
-    for (int h = 0; h < GC; ++h) {
-        m[h] = NEG_BIG;
-#pragma unroll
-        for (int i = 0; i < KPT; ++i) m[h] = fmaxf(m[h], sc[i][h]);
-        l[h] = 0.f;
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
-    }
-#pragma unroll
-    for (int i = 0; i < KPT; ++i) {
-        float vf[DPL];
-#pragma unroll
-        for (int v = 0; v < VEC; ++v)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(vv[i][v].v[e]);
-                vf[v * 8 + 2 * e] = f.x;
-                vf[v * 8 + 2 * e + 1] = f.y;
-            }
-#pragma unroll
-        for (int h = 0; h < GC; ++h) {
-            const float p = valid[i] ? expf(sc[i][h] - m[h]) : 0.f;
-            l[h] += p;
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(p, vf[d], acc[h][d]);
-        }
-    }
-    // block maximum per head, then every group rescales its own sums to it
-    const int gi = warp * 4 + grp;
-    if (sub == 0) {
-#pragma unroll
-        for (int h = 0; h < GC; ++h) s_m[gi][h] = m[h];
-    }
-    __syncthreads();
-    float M[GC];
-#pragma unroll
-    for (int h = 0; h < GC; ++h) {
-        float mm = NEG_BIG;
-        for (int i = 0; i < WARPS * 4; ++i) mm = fmaxf(mm, s_m[i][h]);
-        M[h] = mm;
-        const float w = expf(m[h] - mm);      // a group that saw no key has l = 0 and acc = 0
-        l[h] *= w;
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[h][d] *= w;
-        // the 4 groups of the warp are added with shuffles, the 8 warps through shared memory
-        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 8);
-        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 16);
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) {
-            acc[h][d] += __shfl_xor_sync(0xffffffffu, acc[h][d], 8);
-            acc[h][d] += __shfl_xor_sync(0xffffffffu, acc[h][d], 16);
-        }
-        if (grp == 0) {
-            if (sub == 0) s_l[warp][h] = l[h];
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) s_acc[warp][h][sub * DPL + d] = acc[h][d];
-        }
-    }
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
 
-    const size_t row = (size_t)t * nq;
-    for (int idx = threadIdx.x; idx < GC * HD; idx += WARPS * 32) {
-        const int h = idx / HD, d = idx % HD;
+    float m_w[2] = {NEG_BIG, NEG_BIG}, l_w[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    if (any) {
+        const uint32_t qs_base = smem_addr(Qs), ks_base = smem_addr(Kw), vs_base = smem_addr(Vw);
+        float s[WK / 8][4];
+#pragma unroll
+        for (int j = 0; j < WK / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks += 2) {
+            uint32_t qa0[4], qa1[4];
+            const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+            ldmatrix_x4(tile_addr<HD>(qs_base, row, ks * 2 + (lane >> 4)), qa0[0], qa0[1], qa0[2], qa0[3]);
+            ldmatrix_x4(tile_addr<HD>(qs_base, row, ks * 2 + 2 + (lane >> 4)), qa1[0], qa1[1], qa1[2], qa1[3]);
+#pragma unroll
+            for (int j = 0; j < WK / 8; ++j) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(tile_addr<HD>(ks_base, j * 8 + (lane & 7), ks * 2 + (lane >> 3)), b0, b1, b2, b3);
+                mma_bf16(s[j], qa0, b0, b1);
+                mma_bf16(s[j], qa1, b2, b3);
+            }
+        }
+        const float sl2 = scale * LOG2E;
+        float mx = NEG_BIG;     // every row is the same token: one mask for all rows
+#pragma unroll
+        for (int j = 0; j < WK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = j0 + j * 8 + tq * 2 + (e & 1);
+                const bool ok = key >= lo && key <= hi;
+                s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
+            }
+            m_w[0] = fmaxf(m_w[0], fmaxf(s[j][0], s[j][1]));
+            m_w[1] = fmaxf(m_w[1], fmaxf(s[j][2], s[j][3]));
+        }
+        (void)mx;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 1));
+            m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 2));
+        }
+        uint32_t pa[WK / 16][4];
+#pragma unroll
+        for (int j = 0; j < WK / 8; ++j) {
+            const float p0 = exp2f(s[j][0] - m_w[0]), p1 = exp2f(s[j][1] - m_w[0]);
+            const float p2 = exp2f(s[j][2] - m_w[1]), p3 = exp2f(s[j][3] - m_w[1]);
+            l_w[0] += p0 + p1;
+            l_w[1] += p2 + p3;
+            pa[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+            pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
+            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
+        }
+#pragma unroll
+        for (int kk = 0; kk < WK / 16; ++kk) {
+#pragma unroll
+            for (int i = 0; i < HD / 8; i += 2) {
+                uint32_t b0, b1, b2, b3;
+                const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4_trans(tile_addr<HD>(vs_base, row, i + (lane >> 4)), b0, b1, b2, b3);
+                mma_bf16(o[i], pa[kk], b0, b1);
+                mma_bf16(o[i + 1], pa[kk], b2, b3);
+            }
+        }
+    }
+    __syncthreads();   // every warp is done with its keys and values: the space is reused for the merge
+    if (tq == 0) {
+        s_m[warp][gq] = m_w[0]; s_m[warp][gq + 8] = m_w[1];
+        s_l[warp][gq] = l_w[0]; s_l[warp][gq + 8] = l_w[1];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + tq * 2;
+        float* r0 = s_o + ((size_t)warp * ROWS + gq) * HD + d;
+        float* r1 = s_o + ((size_t)warp * ROWS + gq + 8) * HD + d;
+        r0[0] = o[i][0]; r0[1] = o[i][1];
+        r1[0] = o[i][2]; r1[1] = o[i][3];
+    }
+    __syncthreads();
+    const size_t row0 = (size_t)t * nq;
+    for (int idx = threadIdx.x; idx < rows_valid * HD; idx += WARPS * 32) {
+        const int r = idx / HD, d = idx % HD;
+        float M = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_m[w][r]);
         float L = 0.f, A = 0.f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) { L += s_l[w][h]; A += s_acc[w][h][d]; }
-        const int head = h0 + h;
+        for (int w = 0; w < WARPS; ++w) {
+            const float wt = exp2f(s_m[w][r] - M);          // a warp that saw no key has l = 0 and o = 0
+            L = fmaf(wt, s_l[w][r], L);
+            A = fmaf(wt, s_o[((size_t)w * ROWS + r) * HD + d], A);
+        }
+        const int head = h0 + r;
         if (n_chunks > 1) {
-            const size_t pidx = (row + head) * n_chunks + c;
+            const size_t pidx = (row0 + head) * n_chunks + c;
             part_acc[pidx * HD + d] = A;
-            if (d == 0) {
-                float mm = NEG_BIG;
-                for (int i = 0; i < WARPS * 4; ++i) mm = fmaxf(mm, s_m[i][h]);
-                part_ml[pidx * 2] = mm;
-                part_ml[pidx * 2 + 1] = L;
-            }
+            if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
         } else {
             out[(size_t)t * o_stride + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
         }
@@ -225,67 +206,91 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // First every chunk's (maximum, sum) of every row goes to shared memory in one parallel sweep;
+    // then each thread owns one (row, dimension) and adds the chunks in ascending order.  Loads of
+    // different chunks do not depend on one another, so they overlap.
     const int c_hi = pos / CHUNK;
     const int c_lo = window > 0 ? max(0, pos - window + 1) / CHUNK : 0;
-    for (int idx = threadIdx.x; idx < GC * HD; idx += WARPS * 32) {
-        const int h = idx / HD, d = idx % HD;
-        const size_t base = (row + h0 + h) * n_chunks;
+    const int n_act = c_hi - c_lo + 1;
+    float* s_pm = reinterpret_cast<float*>(KVs);            // [rows][n_act]
+    float* s_pl = s_pm + rows_valid * n_act;            // the host checked that both fit
+    for (int idx = threadIdx.x; idx < rows_valid * n_act; idx += WARPS * 32) {
+        const int r = idx / n_act, cc = c_lo + idx % n_act;
+        const size_t base = (row0 + h0 + r) * n_chunks + cc;
+        s_pm[r * n_act + idx % n_act] = __ldcg(part_ml + base * 2);
+        s_pl[r * n_act + idx % n_act] = __ldcg(part_ml + base * 2 + 1);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows_valid * HD; idx += WARPS * 32) {
+        const int r = idx / HD, d = idx % HD;
+        const float* pm = s_pm + r * n_act;
+        const float* pl = s_pl + r * n_act;
         float MM = NEG_BIG;
-        for (int cc = c_lo; cc <= c_hi; ++cc)
-            if (__ldcg(part_ml + (base + cc) * 2 + 1) > 0.f) MM = fmaxf(MM, __ldcg(part_ml + (base + cc) * 2));
+        for (int i = 0; i < n_act; ++i)
+            if (pl[i] > 0.f) MM = fmaxf(MM, pm[i]);
+        const float* pa = part_acc + ((row0 + h0 + r) * n_chunks + c_lo) * HD + d;
         float L = 0.f, A = 0.f;
-        for (int cc = c_lo; cc <= c_hi; ++cc) {
-            const float lc = __ldcg(part_ml + (base + cc) * 2 + 1);
-            if (lc > 0.f) {
-                const float w = expf(__ldcg(part_ml + (base + cc) * 2) - MM);
-                L = fmaf(w, lc, L);
-                A = fmaf(w, __ldcg(part_acc + (base + cc) * HD + d), A);
-            }
+#pragma unroll 8
+        for (int i = 0; i < n_act; ++i) {
+            const float wt = pl[i] > 0.f ? exp2f(pm[i] - MM) : 0.f;
+            L = fmaf(wt, pl[i], L);
+            A = fmaf(wt, __ldcg(pa + (size_t)i * HD), A);
         }
-        out[(size_t)t * o_stride + (size_t)(h0 + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+        out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
     }
 }
 
-template <int HD, int GC>
+template <int HD>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len, int B, int nq, int nkv,
            float scale, int window, int n_chunks, float* part_acc, float* part_ml, int* counters, void* out,
            int o_stride, cudaStream_t s) {
     const int g = nq / nkv;
-    dim3 grid(n_chunks, nkv * (g / GC), B);
+    dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
-    RB_LAUNCH((attention_decode_kernel<HD, GC>), dim3(grid), dim3(WARPS * 32), 0, s, 
-        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-        block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, n_chunks, part_acc, part_ml,
-        counters, (__nv_bfloat16*)out, o_stride);
-    RB_LAUNCH_CHECK();
+    const size_t kv_bytes = (size_t)WARPS * 2 * WK * HD * sizeof(__nv_bfloat16);
+    const size_t merge_bytes = (size_t)WARPS * ROWS * HD * sizeof(float);
+    const size_t smem = (size_t)ROWS * HD * sizeof(__nv_bfloat16) + (kv_bytes > merge_bytes ? kv_bytes : merge_bytes);
+    const size_t region = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
+    const int rows_max = g < ROWS ? g : ROWS;
+    if ((size_t)n_chunks * rows_max * 2 * sizeof(float) > region) return RB_ERR_BAD_SIZE;  // the merge's work space
+    auto k = attention_decode_kernel<HD>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    RB_LAUNCH((k), grid, dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
+              (const __nv_bfloat16*)v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
+              n_chunks, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride);
     return RB_OK;
 }
 }  // namespace
 
-// One query token per sequence (token index cu_q[b]).  chunk is fixed at 128 keys; n_chunks covers
+// One query token per sequence (token index cu_q[b]).  chunk is fixed at 64 keys; n_chunks covers
 // the longest sequence of the batch; with n_chunks == 1 the result is written to `out` directly.
 // Work space: part_acc [T, nq, n_chunks, hd], part_ml [T, nq, n_chunks, 2] and `counters`, at least
-// B * nkv * (group / heads per block) ints that are ZERO on entry and are left zero on exit.
-// Returns RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 (the caller uses the plain kernel).
+// B * nkv * ceil(group / 16) ints that are ZERO on entry and are left zero on exit.
+// Returns RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 and for contexts whose chunk list does
+// not fit the merge's shared memory (65536 tokens at a group of 4 and head size 128); the caller then
+// uses the plain kernel.
 extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                    const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                                    const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
                                    int n_chunks, float* part_acc, float* part_ml, int* counters, void* out,
                                    int o_stride, void* stream) {
     if (B <= 0) return RB_OK;
-    if (nkv <= 0 || nq % nkv || n_chunks < 1) return RB_ERR_BAD_SIZE;
+    if (nkv <= 0 || nq % nkv || n_chunks < 1 || n_chunks > 1024) return RB_ERR_BAD_SIZE;
     if (n_chunks > 1 && (!part_acc || !part_ml || !counters)) return RB_ERR_BAD_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || (q_stride % 8))
         return RB_ERR_BAD_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
-    const int g = nq / nkv;
-    const int gc = g % 4 == 0 ? 4 : (g % 2 == 0 ? 2 : 1);
-#define RB_AD(HD, GC) return launch<HD, GC>(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, \
-                                            kv_len, B, nq, nkv, scale, window, n_chunks, part_acc, part_ml, counters, out, o_stride, s)
-    if (hd == 128) { if (gc == 4) RB_AD(128, 4); if (gc == 2) RB_AD(128, 2); RB_AD(128, 1); }
-    if (hd == 64) { if (gc == 4) RB_AD(64, 4); if (gc == 2) RB_AD(64, 2); RB_AD(64, 1); }
-    if (hd == 256) { if (gc == 4) RB_AD(256, 2); if (gc == 2) RB_AD(256, 2); RB_AD(256, 1); }
+#define RB_AD(HD) return launch<HD>(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, \
+                                    nkv, scale, window, n_chunks, part_acc, part_ml, counters, out, o_stride, s)
+    if (hd == 128) RB_AD(128);
+    if (hd == 64) RB_AD(64);
+    if (hd == 256) RB_AD(256);
 #undef RB_AD
     return RB_ERR_BAD_SIZE;
 }

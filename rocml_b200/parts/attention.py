@@ -24,7 +24,7 @@ from ..weights.decl import TensorDecl
 from .base import BuildEnv, Mixer, build_position, register_mixer
 from .linear import Linear
 
-DECODE_CHUNK = 128  # keys per split of decode attention; fixed, so a row's sums never depend on the batch
+DECODE_CHUNK = 64   # keys per split of decode attention (one page); fixed, so a row's sums never depend on the batch
 
 
 @register_mixer("attention")

@@ -284,7 +284,7 @@ def test_attention_decode_split_kv(case, fast):
     q = torch.cat(qs, 0).reshape(-1, nq * hd).to(dtype).to(DEV)
     out = torch.full_like(q, float("nan"))
     d = {k: v.to(DEV) for k, v in meta.items()}
-    n_chunks = (max(lens) + 127) // 128 + 1     # one more than needed, as a padded graph would have
+    n_chunks = (max(lens) + 63) // 64 + 1     # one more than needed, as a padded graph would have
     acc = torch.full((B, nq, n_chunks, hd), float("nan"), dtype=torch.float32, device=DEV)
     ml = torch.full((B, nq, n_chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
     pos = (d["kv_len"] - 1).to(torch.int32)
@@ -294,8 +294,8 @@ def test_attention_decode_split_kv(case, fast):
         assert int(kernels.decode_counters(DEV).abs().sum()) == 0      # the work space is left zeroed
     else:
         kernels.attention_generic(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
-                                  B, 1, nq, nkv, hd, scale, window or 0, 128, n_chunks, acc, ml)
-        kernels.attention_merge(acc, ml, out, pos, d["seq_slot"], B, nq, hd, 128, n_chunks, window or 0)
+                                  B, 1, nq, nkv, hd, scale, window or 0, 64, n_chunks, acc, ml)
+        kernels.attention_merge(acc, ml, out, pos, d["seq_slot"], B, nq, hd, 64, n_chunks, window or 0)
     err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
     assert err < 2e-2, err
 
