@@ -294,3 +294,71 @@ extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_ca
 #undef RB_AD
     return RB_ERR_BAD_SIZE;
 }
+
+// ---- the same kernel for callers that cannot allocate (see no_alloc.h) -----------------------------
+#include "no_alloc.h"
+#include <cstdio>
+#include <mutex>
+
+namespace {
+constexpr size_t STATIC_ACC_FLOATS = 4u << 20;     // 16 MiB
+constexpr size_t STATIC_ML_FLOATS = 256u << 10;    // 1 MiB
+constexpr size_t STATIC_COUNTERS = 16u << 10;      // 64 KiB
+struct StaticScratch {
+    float acc[STATIC_ACC_FLOATS];
+    float ml[STATIC_ML_FLOATS];
+    int counters[STATIC_COUNTERS];
+};
+// Part of the device image: every GPU that loads the library holds it until the process exits.
+// In host code this name is only a handle for cudaGetSymbolAddress, never an address to pass on.
+static __device__ __align__(256) StaticScratch g_static_scratch;
+
+constexpr int MAX_DEVICES = 64;
+StaticScratch* g_scratch_addr[MAX_DEVICES] = {};
+std::mutex g_scratch_mu;
+
+// The array's address on the current device, looked up once per device.
+int static_scratch(StaticScratch** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return RB_ERR_BAD_SIZE;
+    std::lock_guard<std::mutex> g(g_scratch_mu);
+    if (!g_scratch_addr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_scratch_addr[dev] = static_cast<StaticScratch*>(p);
+    }
+    *out = g_scratch_addr[dev];
+    return RB_OK;
+}
+}  // namespace
+
+extern "C" int rb_attention_decode_static(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                          const int* block_table, int max_pages, const int* seq_slot,
+                                          const int* cu_q, const int* kv_len, int n_seqs, int nq, int nkv, int hd,
+                                          float scale, int window, int n_chunks, void* out, int o_stride,
+                                          void* stream) {
+    if (n_seqs <= 0) return RB_OK;
+    if (nkv <= 0 || nq <= 0 || nq % nkv || hd <= 0 || n_chunks < 1) return RB_ERR_BAD_SIZE;
+    const size_t rows = (size_t)n_seqs * nq * n_chunks;
+    const size_t n_counters = (size_t)n_seqs * nkv * ((nq / nkv + ROWS - 1) / ROWS);
+    if (rows * hd > STATIC_ACC_FLOATS || rows * 2 > STATIC_ML_FLOATS || n_counters > STATIC_COUNTERS) {
+        std::fprintf(stderr,
+                     "rb_attention_decode_static: %d sequences x %d heads x %d chunks x head size %d needs %zu partial "
+                     "floats (limit %zu), %zu max/sum floats (limit %zu), %zu counters (limit %zu)\n",
+                     n_seqs, nq, n_chunks, hd, rows * hd, STATIC_ACC_FLOATS, rows * 2, STATIC_ML_FLOATS, n_counters,
+                     STATIC_COUNTERS);
+        return RB_ERR_SCRATCH_LIMIT;
+    }
+    StaticScratch* sc = nullptr;
+    int rc = static_scratch(&sc);
+    if (rc != RB_OK) return rc;
+    // the counters must start at zero whatever an earlier call left behind
+    cudaError_t e = cudaMemsetAsync(sc->counters, 0, n_counters * sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    return rb_attention_decode(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, n_seqs,
+                               nq, nkv, hd, scale, window, n_chunks, sc->acc, sc->ml, sc->counters, out, o_stride,
+                               stream);
+}
