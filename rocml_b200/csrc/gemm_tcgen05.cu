@@ -51,6 +51,23 @@ struct Params {
     int stages;                   // depth of the shared-memory ring actually used (<= Cfg::STAGES)
 };
 
+// 16 consecutive outputs as 16-byte stores (dst is 16-byte aligned).
+__device__ __forceinline__ void store16(float* dst, const float* v) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+__device__ __forceinline__ void store16(__nv_bfloat16* dst, const float* v) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
 template <int BN, bool SWAP, typename OT>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -169,6 +186,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             OT* o = out + (size_t)blockIdx.z * p.split_stride;
             const bool add_bias = p.bias != nullptr && blockIdx.z == 0;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const bool vec_ok = (((uintptr_t)o | ((uintptr_t)p.ldo * sizeof(OT))) & 15) == 0;
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 float v[16];
@@ -183,13 +201,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             o[(size_t)tok * p.ldo + ar] = rb::from_f32<OT>(v[i] + bv);
                     }
                 } else {
-                    // A side = tokens, B side = features: out[token][feature]
+                    // A side = tokens, B side = features: out[token][feature]; this thread owns 16
+                    // consecutive features of its row: 32 or 64 contiguous bytes, written as 16-byte
+                    // stores when the row is aligned and the chunk lies inside the matrix
                     if (ar < p.a_rows) {
                         OT* row = o + (size_t)ar * p.ldo;
+                        const int f0 = b0 + c * 16;
+                        if (add_bias) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int f = b0 + c * 16 + i;
-                            if (f < p.b_rows) row[f] = rb::from_f32<OT>(v[i] + (add_bias ? p.bias[f] : 0.f));
+                            for (int i = 0; i < 16; ++i) v[i] += (f0 + i < p.b_rows) ? p.bias[f0 + i] : 0.f;
+                        }
+                        if (vec_ok && f0 + 16 <= p.b_rows) {
+                            store16(row + f0, v);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (f0 + i < p.b_rows) row[f0 + i] = rb::from_f32<OT>(v[i]);
                         }
                     }
                 }
