@@ -68,8 +68,19 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
         const float4* r4 = reinterpret_cast<const float4*>(r);
         for (int i = threadIdx.x; i < H4; i += blockDim.x) {
             float4 v = r4[i];
-            for (int s = 0; s < n_delta; ++s) {
-                const float4 d = reinterpret_cast<const float4*>(delta + (size_t)s * delta_stride + (size_t)row * H)[i];
+            const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)row * H) + i;
+            const size_t ds4 = delta_stride >> 2;
+            int s = 0;
+            for (; s + 4 <= n_delta; s += 4) {   // four loads in flight, added in order
+                const float4 a = d4[(size_t)s * ds4], b = d4[(size_t)(s + 1) * ds4];
+                const float4 c = d4[(size_t)(s + 2) * ds4], d = d4[(size_t)(s + 3) * ds4];
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            }
+            for (; s < n_delta; ++s) {
+                const float4 d = d4[(size_t)s * ds4];
                 v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
             }
             rb4[i] = v;

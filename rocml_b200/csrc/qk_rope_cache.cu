@@ -59,11 +59,36 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
     }
 
     float ss = 0.f;
-    for (int i = lane; i < hd; i += 32) {
-        float v = 0.f;
-        for (int s = 0; s < n_in; ++s) v += to_f32(src[(size_t)s * in_stride + i]);
-        buf[i] = v;
-        ss += v * v;
+    if (n_in > 1 && sizeof(IT) == 4 && (hd & 3) == 0 && (in_stride & 3) == 0 && (row_stride & 3) == 0 &&
+        ((uintptr_t)in & 15) == 0) {
+        // partial sums in float32: 16-byte loads, four partial sums in flight, added in order
+        const float4* s4 = reinterpret_cast<const float4*>(src);
+        const size_t st4 = in_stride >> 2;
+        for (int i = lane; i < (hd >> 2); i += 32) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            int s = 0;
+            for (; s + 4 <= n_in; s += 4) {
+                const float4 a = s4[(size_t)s * st4 + i], b = s4[(size_t)(s + 1) * st4 + i];
+                const float4 c = s4[(size_t)(s + 2) * st4 + i], d = s4[(size_t)(s + 3) * st4 + i];
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            }
+            for (; s < n_in; ++s) {
+                const float4 d = s4[(size_t)s * st4 + i];
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            }
+            buf[4 * i] = v.x; buf[4 * i + 1] = v.y; buf[4 * i + 2] = v.z; buf[4 * i + 3] = v.w;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = lane; i < hd; i += 32) {
+            float v = 0.f;
+            for (int s = 0; s < n_in; ++s) v += to_f32(src[(size_t)s * in_stride + i]);
+            buf[i] = v;
+            ss += v * v;
+        }
     }
     __syncwarp();
     if (kind == 2) {

@@ -73,17 +73,18 @@ class Linear:
     def _splits(self, m: int) -> int:
         """How many ways the sum over K is split when few rows stream a large weight.  One
         thread block reads memory at a small fraction of the device's bandwidth, so the weight's
-        row tiles (128 rows each) are multiplied by K splits until about four blocks per
-        multiprocessor are in flight; each split keeps at least five 64-wide K blocks, and the
+        row tiles (128 rows each) are multiplied by K splits until about two blocks per
+        multiprocessor are in flight (more gains little and costs the consumer, which adds the
+        partial sums); each split keeps at least five 64-wide K blocks, at most 8 splits, and the
         float32 partial results stay below a sixth of the weight's own bytes.  The count depends
         on the weight's shape and the step's row count only."""
         if m > 128 or self.k % 8:
             return 1
         tiles = (self.n + 127) // 128
-        by_blocks = (4 * 148) // tiles
+        by_blocks = -(-2 * 148 // tiles)
         by_depth = (self.k // 64) // 5
         by_bytes = int(0.075 * self.k / max(m, 1))
-        return max(1, min(by_blocks, by_depth, by_bytes, 32))
+        return max(1, min(by_blocks, by_depth, by_bytes, 8))
 
     def forward_delta(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """The product as float32 [S, M, N]: S partial sums over K that the consumer adds in order
