@@ -198,6 +198,68 @@ def e2e_decode(eng, batch, steps, warmup, vocab):
     return stats.decode_tokens / stats.decode_seconds, eng.last_h2d_bytes, batch * 4
 
 
+def micro(which):
+    """Kernel microbenchmarks: each kernel launched back to back inside a CUDA graph (no host
+    time), at the Qwen3-8B layer sizes.  Results are printed, one line per case; they feed the
+    notes under profiles/ and are not part of the bench line."""
+    import torch
+    from rocml_b200 import kernels
+    from rocml_b200.config import CATALOG, config_from_dict
+    cfg = config_from_dict(CATALOG[MODEL].config)
+    dev = "cuda:0"
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    nq, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+
+    def in_graph(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); g.replay(); g.replay(); b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1000 / (2 * reps)
+
+    shapes = [("qkv", cfg.q_dim + 2 * cfg.kv_dim, H), ("o", H, cfg.q_dim), ("gate_up", 2 * I, H), ("down", H, I),
+              ("head", V, H)]
+    if which == "gemm-decode":
+        # weights rotate through more than the L2 holds, so every launch streams from HBM
+        for M in (1, 8, 64):
+            for name, N, K in shapes:
+                copies = max(2, int(300e6 / (N * K * 2)) + 1)
+                ws = [torch.randn(N, K, device=dev).bfloat16() for _ in range(copies)]
+                x = torch.randn(M, K, device=dev).bfloat16()
+                for S in (1, 2, 4, 8):
+                    if K // 64 < 5 * S or (name == "head" and S > 2):
+                        continue
+                    out = torch.empty((S, M, N), dtype=torch.float32, device=dev)
+                    for stages in (3, 5):
+                        it = iter(range(10 ** 9))
+                        us = in_graph(lambda: kernels.gemm_tcgen05(x, ws[next(it) % copies], out, None, M, stages), 4 * copies)
+                        print(f"gemm decode M={M} {name} N={N} K={K} splits={S} stages={stages}: {us:.1f} us "
+                              f"{N * K * 2 / us / 1e6:.2f} TB/s", flush=True)
+                del ws
+    elif which == "gemm-prefill":
+        for name, N, K in shapes[:4]:
+            w = torch.randn(N, K, device=dev).bfloat16()
+            x = torch.randn(PREFILL_TOKENS, K, device=dev).bfloat16()
+            for od in (torch.bfloat16, torch.float32):
+                out = torch.empty((PREFILL_TOKENS, N), dtype=od, device=dev)
+                us = in_graph(lambda: kernels.gemm_tcgen05(x, w, out, None, PREFILL_TOKENS), 10)
+                print(f"gemm prefill M={PREFILL_TOKENS} {name} N={N} K={K} out={str(od)[6:]}: {us:.1f} us "
+                      f"{2 * PREFILL_TOKENS * N * K / us / 1e6:.0f} TFLOP/s", flush=True)
+        x = torch.randn(PREFILL_TOKENS, H, device=dev).bfloat16()
+        w = torch.randn(cfg.q_dim + 2 * cfg.kv_dim, H, device=dev).bfloat16()
+        us = in_graph(lambda: torch.matmul(x, w.t()), 10)
+        print(f"library matmul (for scale) qkv: {us:.1f} us {2 * PREFILL_TOKENS * w.shape[0] * H / us / 1e6:.0f} TFLOP/s")
+    else:
+        raise SystemExit(f"unknown --micro {which!r}: gemm-decode or gemm-prefill")
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
@@ -206,7 +268,11 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--micro", default=None, help="kernel microbenchmarks instead of the bench: gemm-decode, gemm-prefill")
     args = ap.parse_args()
+    if args.micro:
+        micro(args.micro)
+        return 0
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
