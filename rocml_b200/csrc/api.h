@@ -14,7 +14,7 @@ int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delt
                    int write_back, void* stream);
 
 int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype, int rows,
-                int I, void* stream);
+                int I, int paired, void* stream);
 
 int rb_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* stream);
 
@@ -29,7 +29,7 @@ int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, cons
 
 int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M, int N,
                     int K, long long ldx, long long ldo, int splits, long long split_stride, int stages,
-                    int* status, void* stream);
+                    int gated, int* status, void* stream);
 
 int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, int dtype, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,

@@ -154,12 +154,13 @@ extern "C" int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, lon
 }
 
 // ---- SiLU(gate) * up ------------------------------------------------------------------------
-// in: [S][T, 2*I] (S partial sums that are added first, in order), the gate in columns [0, I) and
-// up in [I, 2I); out: [T, I].  silu(g) = g / (1 + exp(-g)) as in
+// in: [S][T, 2*I] (S partial sums that are added first, in order); out: [T, I].  The gate of output
+// i sits in column i and its up in column I + i, or, when `paired`, columns alternate in blocks of
+// 16 between gates and ups (gate of output i at (i / 16) * 32 + i % 16, its up 16 columns on).  silu(g) = g / (1 + exp(-g)) as in
 // rocml-kernels/kernels/silu_mul.hip:15-18.  Four outputs per thread when I is a multiple of 4.
 template <typename IT, typename OT>
 __global__ void silu_mul_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, OT* __restrict__ out,
-                                int rows, int I) {
+                                int rows, int I, int paired) {
     pdl_trigger();
     pdl_wait();
     const int I4 = I >> 2;
@@ -172,9 +173,11 @@ __global__ void silu_mul_kernel(const IT* __restrict__ in, int n_in, size_t in_s
             const int i = (int)(idx - t * I4) * 4;
             float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
             for (int s = 0; s < n_in; ++s) {
-                const IT* p = in + (size_t)s * in_stride + t * 2 * I + i;
+                const int gi = paired ? (i >> 4) * 32 + (i & 15) : i;
+                const int up = paired ? 16 : I;
+                const IT* p = in + (size_t)s * in_stride + t * 2 * I + gi;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) { g[j] += to_f32(p[j]); u[j] += to_f32(p[I + j]); }
+                for (int j = 0; j < 4; ++j) { g[j] += to_f32(p[j]); u[j] += to_f32(p[up + j]); }
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) out[t * I + i + j] = from_f32<OT>(g[j] / (1.f + expf(-g[j])) * u[j]);
@@ -183,8 +186,9 @@ __global__ void silu_mul_kernel(const IT* __restrict__ in, int n_in, size_t in_s
             const int i = (int)(idx - t * I);
             float g = 0.f, u = 0.f;
             for (int s = 0; s < n_in; ++s) {
-                g += to_f32(in[(size_t)s * in_stride + t * 2 * I + i]);
-                u += to_f32(in[(size_t)s * in_stride + t * 2 * I + I + i]);
+                const int gi = paired ? (i >> 4) * 32 + (i & 15) : i;
+                g += to_f32(in[(size_t)s * in_stride + t * 2 * I + gi]);
+                u += to_f32(in[(size_t)s * in_stride + t * 2 * I + gi + (paired ? 16 : I)]);
             }
             out[idx] = from_f32<OT>(g / (1.f + expf(-g)) * u);
         }
@@ -192,9 +196,9 @@ __global__ void silu_mul_kernel(const IT* __restrict__ in, int n_in, size_t in_s
 }
 
 extern "C" int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype,
-                           int rows, int I, void* stream) {
+                           int rows, int I, int paired, void* stream) {
     if (rows <= 0) return RB_OK;
-    if (n_in < 1) return RB_ERR_BAD_SIZE;
+    if (n_in < 1 || (paired && I % 16)) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t n = (I & 3) == 0 ? (size_t)rows * (I >> 2) : (size_t)rows * I;
     const int threads = 256;
@@ -202,11 +206,11 @@ extern "C" int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_
     const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
     typedef __nv_bfloat16 bf;
     if (in_dtype == RB_BF16 && out_dtype == RB_BF16)
-        RB_LAUNCH((silu_mul_kernel<bf, bf>), dim3(blocks), dim3(threads), 0, s, (const bf*)in, n_in, (size_t)in_stride, (bf*)out, rows, I);
+        RB_LAUNCH((silu_mul_kernel<bf, bf>), dim3(blocks), dim3(threads), 0, s, (const bf*)in, n_in, (size_t)in_stride, (bf*)out, rows, I, paired);
     else if (in_dtype == RB_F32 && out_dtype == RB_BF16)
-        RB_LAUNCH((silu_mul_kernel<float, bf>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride, (bf*)out, rows, I);
+        RB_LAUNCH((silu_mul_kernel<float, bf>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride, (bf*)out, rows, I, paired);
     else if (in_dtype == RB_F32 && out_dtype == RB_F32)
-        RB_LAUNCH((silu_mul_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride, (float*)out, rows, I);
+        RB_LAUNCH((silu_mul_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride, (float*)out, rows, I, paired);
     else
         return RB_ERR_BAD_DTYPE;
     return RB_OK;

@@ -68,7 +68,7 @@ __device__ __forceinline__ void store16(__nv_bfloat16* dst, const float* v) {
     reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-template <int BN, bool SWAP, typename OT>
+template <int BN, bool SWAP, typename OT, bool GATED>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OT* __restrict__ out, const Params p) {
@@ -187,11 +187,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool add_bias = p.bias != nullptr && blockIdx.z == 0;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             const bool vec_ok = (((uintptr_t)o | ((uintptr_t)p.ldo * sizeof(OT))) & 15) == 0;
+            if (GATED) {
+                // The weight's rows alternate in blocks of 16 between the gate and the up projection
+                // of the same 16 outputs; the tile's value is silu(gate) * up (silu(g) = g / (1 + exp(-g)),
+                // rocml-kernels/kernels/silu_mul.hip:15-18), half as wide as the product.
+                if (SWAP) {
+                    // features on the TMEM lanes: lanes 0-15 of a warp hold gates, lanes 16-31 the ups
+                    const float bv = (add_bias && ar < p.a_rows) ? p.bias[ar] : 0.f;
+                    const int fo = (ar >> 5) * 16 + (lane & 15);
+#pragma unroll 1
+                    for (int c = 0; c < BN / 16; ++c) {
+                        float v[16];
+                        tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float mine = v[i] + bv;
+                            const float up = __shfl_down_sync(0xffffffffu, mine, 16);
+                            const int tok = b0 + c * 16 + i;
+                            if (lane < 16 && tok < p.b_rows && ar < p.a_rows)
+                                o[(size_t)tok * p.ldo + fo] = rb::from_f32<OT>(mine / (1.f + expf(-mine)) * up);
+                        }
+                    }
+                } else {
+                    OT* row = o + (size_t)(ar < p.a_rows ? ar : 0) * p.ldo;
+#pragma unroll 1
+                    for (int c = 0; c < BN / 16; c += 2) {
+                        float g[16], u[16];
+                        tmem_ld16(lane_addr + c * 16, g);
+                        tmem_ld16(lane_addr + (c + 1) * 16, u);
+                        const int f0 = b0 + c * 16;                 // gate columns f0.., up columns f0 + 16..
+                        if (ar < p.a_rows && f0 + 32 <= p.b_rows) {
+                            if (add_bias) {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) { g[i] += p.bias[f0 + i]; u[i] += p.bias[f0 + 16 + i]; }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                            OT* dst = row + (f0 >> 1);
+                            if (vec_ok) store16(dst, g);
+                            else {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) dst[i] = rb::from_f32<OT>(g[i]);
+                            }
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 float v[16];
                 tmem_ld16(lane_addr + c * 16, v);
                 if (SWAP) {
+
                     // A side = features, B side = tokens: out[token][feature]
                     const float bv = (add_bias && ar < p.a_rows) ? p.bias[ar] : 0.f;
 #pragma unroll
@@ -228,6 +275,201 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+
+// ---- many tokens: a persistent kernel with two accumulators ---------------------------------------
+// One block per multiprocessor walks over the output tiles (tokens on the 128-row side, BN features
+// per tile; tiles that share a weight tile are neighbours, so the weight is read from memory once).
+// Tensor memory holds TWO accumulators of BN columns: while the 4 epilogue warps read tile i out of
+// one (bias, the gated activation, conversion, 16-byte stores), the MMA warp already fills the other
+// with tile i + 1, and the TMA warp runs ahead through the same shared-memory ring across tile
+// boundaries.  The epilogue thus costs nothing as long as it is shorter than a tile's main loop.
+template <int BN, typename OT, bool GATED>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               OT* __restrict__ out, const Params p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int S = p.stages;
+    uint64_t* full = (uint64_t*)(smem + S * C::STAGE);
+    uint64_t* empty = full + S;
+    uint64_t* acc_full = empty + S;      // [2]
+    uint64_t* acc_empty = acc_full + 2;  // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    uint32_t* abort_flag = tmem_slot + 1;
+
+    rb::pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (p.a_rows + BM - 1) / BM, n_tiles = (p.b_rows + BN - 1) / BN;
+    const int n_total = m_tiles * n_tiles;
+    const int n_kb = (p.K + BK - 1) / BK;
+    constexpr int TMEM_COLS = 2 * C::TMEM_COLS;   // 512 at BN = 256
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&map_a);
+            tma_prefetch_desc(&map_b);
+            long long it = 0;          // K blocks issued so far, over all tiles: the ring's position
+            bool ok = true, waited = false;
+            for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x) {
+                const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t ph = (uint32_t)((it / S) & 1);
+                    ok = mbar_wait(&empty[s], ph ^ 1);
+                    if (!ok) break;
+                    uint8_t* sa = smem + s * C::STAGE;
+                    mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
+                    tma_load_2d(sa + C::A_BYTES, &map_b, kb * BK, b0, &full[s]);    // weights: independent
+                    if (!waited && (it + 1 == S || (tile + gridDim.x >= n_total && kb + 1 == n_kb))) {
+                        // the ring is primed with weight tiles: now wait for the predecessor's
+                        // results, then send the activations' tiles of everything issued so far
+                        rb::pdl_wait();
+                        waited = true;
+                        for (long long j = 0; j <= it; ++j) {
+                            const int tj = blockIdx.x + (int)(j / n_kb) * gridDim.x;
+                            tma_load_2d(smem + (int)(j % S) * C::STAGE, &map_a, (int)(j % n_kb) * BK,
+                                        (tj % m_tiles) * BM, &full[(int)(j % S)]);
+                        }
+                    } else if (waited) {
+                        tma_load_2d(sa, &map_a, kb * BK, a0, &full[s]);
+                    }
+                }
+            }
+            if (!waited) rb::pdl_wait();
+            if (!ok) {
+                atomicExch(p.status, RB_ERR_TIMEOUT);
+                atomicExch(abort_flag, 1u);
+                const long long first = it > S ? it - S : 0;
+                for (long long j = first; j < it; ++j) mbar_wait(&full[(int)(j % S)], (uint32_t)((j / S) & 1));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+            long long it = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t use = (uint32_t)(local >> 1);
+                ok = mbar_wait(&acc_empty[acc], (use & 1) ^ 1);    // the epilogue has drained this accumulator
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * C::TMEM_COLS;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = (int)(it % S);
+                    ok = mbar_wait(&full[s], (uint32_t)((it / S) & 1));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * C::STAGE);
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sa + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        mma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(&empty[s]);
+                }
+                if (!ok) break;
+                mma_commit(&acc_full[acc]);
+            }
+            if (!ok) {
+                atomicExch(p.status, RB_ERR_TIMEOUT);
+                atomicExch(abort_flag, 1u);
+                mma_commit(&acc_full[0]);     // wake the epilogue, which then sees the abort flag
+                mma_commit(&acc_full[1]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_total; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const uint32_t use = (uint32_t)(local >> 1);
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], use & 1));
+            tc_fence_after();
+            if (!ok || *(volatile uint32_t*)abort_flag != 0) {
+                if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
+                break;
+            }
+            const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * BN;
+            const int ar = a0 + quarter * 32 + lane;
+            const bool add_bias = p.bias != nullptr;
+            const uint32_t lane_addr = tmem_base + acc * C::TMEM_COLS + ((uint32_t)(quarter * 32) << 16);
+            const bool vec_ok = (((uintptr_t)out | ((uintptr_t)p.ldo * sizeof(OT))) & 15) == 0;
+            OT* row = out + (size_t)(ar < p.a_rows ? ar : 0) * p.ldo;
+            if (GATED) {
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; c += 2) {
+                    float g[16], u[16];
+                    tmem_ld16(lane_addr + c * 16, g);
+                    tmem_ld16(lane_addr + (c + 1) * 16, u);
+                    const int f0 = b0 + c * 16;
+                    if (ar < p.a_rows && f0 + 32 <= p.b_rows) {
+                        if (add_bias) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) { g[i] += p.bias[f0 + i]; u[i] += p.bias[f0 + 16 + i]; }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                        OT* dst = row + (f0 >> 1);
+                        if (vec_ok) store16(dst, g);
+                        else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) dst[i] = rb::from_f32<OT>(g[i]);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; ++c) {
+                    float v[16];
+                    tmem_ld16(lane_addr + c * 16, v);
+                    const int f0 = b0 + c * 16;
+                    if (ar < p.a_rows) {
+                        if (add_bias) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] += (f0 + i < p.b_rows) ? p.bias[f0 + i] : 0.f;
+                        }
+                        if (vec_ok && f0 + 16 <= p.b_rows) {
+                            store16(row + f0, v);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (f0 + i < p.b_rows) row[f0 + i] = rb::from_f32<OT>(v[i]);
+                        }
+                    }
+                }
+            }
+            // this warp has read all it needs of the accumulator: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -300,14 +542,14 @@ int tensor_map(const void* ptr, long long rows, long long K, long long ld, int b
     return RB_OK;
 }
 
-template <int BN, bool SWAP, typename OT>
+template <int BN, bool SWAP, typename OT, bool GATED>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, int splits, cudaStream_t s) {
     // Few tokens (SWAP): the kernel is bound by memory latency, and several small blocks per
     // multiprocessor with a shallow ring hide each other's start and end better than one block
     // with a deep ring (measured: 3 stages beat 5 and 10 on every decode shape).
     if (p.stages <= 0) p.stages = SWAP ? 3 : Cfg<BN>::STAGES;
     using C = Cfg<BN>;
-    auto k = gemm_tcgen05_kernel<BN, SWAP, OT>;
+    auto k = gemm_tcgen05_kernel<BN, SWAP, OT, GATED>;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
@@ -323,15 +565,38 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, in
     return RB_OK;
 }
 
-template <bool SWAP, typename OT>
+template <int BN, typename OT, bool GATED>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, cudaStream_t s) {
+    using C = Cfg<BN>;
+    auto k = gemm_tcgen05_persistent_kernel<BN, OT, GATED>;
+    static bool attr_done = false;
+    static int sms = 0;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    if (p.stages <= 0) p.stages = C::STAGES;
+    if (p.stages < 2 || p.stages > C::STAGES) return RB_ERR_BAD_SIZE;
+    const int smem_bytes = p.stages * C::STAGE + 1024 + 256;
+    const long long tiles = (long long)((p.a_rows + BM - 1) / BM) * ((p.b_rows + BN - 1) / BN);
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    RB_LAUNCH((k), dim3(grid), dim3(192), smem_bytes, s, ma, mb, (OT*)out, p);
+    return RB_OK;
+}
+
+template <bool SWAP, typename OT, bool GATED>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out, const Params& p, int splits,
                 cudaStream_t s) {
     switch (bn) {
-        case 16: return launch<16, SWAP, OT>(ma, mb, out, p, splits, s);
-        case 32: return launch<32, SWAP, OT>(ma, mb, out, p, splits, s);
-        case 64: return launch<64, SWAP, OT>(ma, mb, out, p, splits, s);
-        case 128: return launch<128, SWAP, OT>(ma, mb, out, p, splits, s);
-        case 256: return launch<256, SWAP, OT>(ma, mb, out, p, splits, s);
+        case 16: return launch<16, SWAP, OT, GATED>(ma, mb, out, p, splits, s);
+        case 32: return launch<32, SWAP, OT, GATED>(ma, mb, out, p, splits, s);
+        case 64: return launch<64, SWAP, OT, GATED>(ma, mb, out, p, splits, s);
+        case 128: return launch<128, SWAP, OT, GATED>(ma, mb, out, p, splits, s);
+        case 256: return launch<256, SWAP, OT, GATED>(ma, mb, out, p, splits, s);
     }
     return RB_ERR_BAD_SIZE;
 }
@@ -340,15 +605,18 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out,
 
 // out[M, N] (+ splits) = x[M, K] . w[N, K]^T.  x, w bfloat16; out bfloat16 or float32.
 // splits > 1: float32 partial results at out + z * split_stride, bias in split 0.
+// gated: the weight's rows alternate in blocks of 16 between a gate and an up projection; the output
+// is [M, N / 2] = silu(gate) * up (bfloat16, no split).
 // Refuses (RB_ERR_BAD_ALIGN) what TMA cannot address: K or ldx not a multiple of 8 elements,
 // or a base pointer off a 16-byte boundary; the caller then uses the plain kernel.
 extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
                                int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
-                               int stages, int* status, void* stream) {
+                               int stages, int gated, int* status, void* stream) {
     if (M <= 0 || N <= 0) return RB_OK;
     if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
     if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
     if (splits > 1 && out_dtype != RB_F32) return RB_ERR_BAD_DTYPE;
+    if (gated && (splits != 1 || out_dtype != RB_BF16 || N % 32)) return RB_ERR_BAD_SIZE;
     const int kb_total = (K + BK - 1) / BK;
     if (splits > kb_total) return RB_ERR_BAD_SIZE;  // a split would be empty and its partial result unwritten
     cudaStream_t s = (cudaStream_t)stream;
@@ -375,11 +643,28 @@ extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, 
         if ((rc = tensor_map(x, M, K, ldx, BM, &ma)) != RB_OK) return rc;
         if ((rc = tensor_map(w, N, K, K, bn, &mb)) != RB_OK) return rc;
     }
+    if (!swap && splits == 1 && (bn == 256 || bn == 128)) {
+        // many tokens: the persistent kernel with two accumulators (2 x 256 columns fill tensor memory)
+        if (out_dtype == RB_BF16) {
+            if (bn == 256) return gated ? launch_persistent<256, __nv_bfloat16, true>(ma, mb, out, p, s)
+                                        : launch_persistent<256, __nv_bfloat16, false>(ma, mb, out, p, s);
+            return gated ? launch_persistent<128, __nv_bfloat16, true>(ma, mb, out, p, s)
+                         : launch_persistent<128, __nv_bfloat16, false>(ma, mb, out, p, s);
+        }
+        if (out_dtype == RB_F32)
+            return bn == 256 ? launch_persistent<256, float, false>(ma, mb, out, p, s)
+                             : launch_persistent<128, float, false>(ma, mb, out, p, s);
+    }
     if (out_dtype == RB_BF16)
-        return swap ? dispatch_bn<true, __nv_bfloat16>(bn, ma, mb, out, p, splits, s)
-                    : dispatch_bn<false, __nv_bfloat16>(bn, ma, mb, out, p, splits, s);
+    {
+        if (gated)
+            return swap ? dispatch_bn<true, __nv_bfloat16, true>(bn, ma, mb, out, p, splits, s)
+                        : dispatch_bn<false, __nv_bfloat16, true>(bn, ma, mb, out, p, splits, s);
+        return swap ? dispatch_bn<true, __nv_bfloat16, false>(bn, ma, mb, out, p, splits, s)
+                    : dispatch_bn<false, __nv_bfloat16, false>(bn, ma, mb, out, p, splits, s);
+    }
     if (out_dtype == RB_F32)
-        return swap ? dispatch_bn<true, float>(bn, ma, mb, out, p, splits, s)
-                    : dispatch_bn<false, float>(bn, ma, mb, out, p, splits, s);
+        return swap ? dispatch_bn<true, float, false>(bn, ma, mb, out, p, splits, s)
+                    : dispatch_bn<false, float, false>(bn, ma, mb, out, p, splits, s);
     return RB_ERR_BAD_DTYPE;
 }

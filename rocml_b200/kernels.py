@@ -76,7 +76,7 @@ def _lib():
     if not _sigs_done:
         lib.rb_embedding.argtypes = [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]
         lib.rb_add_rmsnorm.argtypes = [_vp, _vp, _i, _ll, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp]
-        lib.rb_silu_mul.argtypes = [_vp, _i, _i, _ll, _vp, _i, _i, _i, _vp]
+        lib.rb_silu_mul.argtypes = [_vp, _i, _i, _ll, _vp, _i, _i, _i, _i, _vp]
         lib.rb_cast.argtypes = [_vp, _i, _vp, _i, _ll, _vp]
         lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f,
                                               _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp]
@@ -90,7 +90,7 @@ def _lib():
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
                                             _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
-        lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
         _sigs_done = True
     return lib
 
@@ -146,14 +146,15 @@ def _partials(x: torch.Tensor, what: str):
     return 1, 0, x.stride(0)
 
 
-def silu_mul(x: torch.Tensor, out: torch.Tensor):
-    """x [T, 2I] = [gate | up], or [S, T, 2I] partial sums to be added first -> out [T, I] = silu(gate) * up."""
+def silu_mul(x: torch.Tensor, out: torch.Tensor, paired: bool = False):
+    """x [T, 2I] = [gate | up], or [S, T, 2I] partial sums to be added first -> out [T, I] = silu(gate) * up.
+    ``paired``: gates and ups alternate in blocks of 16 columns instead of lying in two halves."""
     n_in, in_stride, row_stride = _partials(x, "silu_mul")
     T, I2 = x.shape[-2], x.shape[-1]
     if I2 % 2 or tuple(out.shape) != (T, I2 // 2) or row_stride != I2 or not out.is_contiguous():
         raise KernelError("silu_mul: shapes do not fit")
     _check(_lib().rb_silu_mul(_ptr(x), dtype_code(x.dtype), n_in, in_stride, _ptr(out), dtype_code(out.dtype), T,
-                              I2 // 2, _stream()), "silu_mul")
+                              I2 // 2, 1 if paired else 0, _stream()), "silu_mul")
 
 
 def cast(x: torch.Tensor, out: torch.Tensor):
@@ -360,11 +361,14 @@ def check_status(device) -> None:
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                 m: Optional[int] = None, stages: int = 0) -> bool:
+                 m: Optional[int] = None, stages: int = 0, gated: bool = False) -> bool:
     """out = x . w^T on the tensor cores; x, w bfloat16, out bfloat16 [M, N] or float32 [M, N] or
     float32 [S, M, N] (S partial sums over K, to be added by the consumer).  Returns False when the
     kernel refuses the layout (K or a row stride not a multiple of 8, a pointer off 16 bytes);
-    the caller then uses the plain kernel."""
+    the caller then uses the plain kernel.
+
+    ``gated``: w's rows alternate in blocks of 16 between a gate and an up projection of the same
+    16 outputs, and out is bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue."""
     M = x.shape[0] if m is None else m
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
@@ -376,12 +380,12 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
             raise KernelError("gemm_tcgen05: partial output must be float32 [S, M, N]")
     else:
         splits, split_stride, ldo = 1, 0, out.stride(0)
-        if out.shape[1] != N or out.stride(1) != 1:
-            raise KernelError("gemm_tcgen05: output must be [M, N] with unit inner stride")
+        if out.shape[1] != (N // 2 if gated else N) or out.stride(1) != 1:
+            raise KernelError("gemm_tcgen05: output must be [M, N] (or [M, N / 2] when gated) with unit inner stride")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("gemm_tcgen05: bias must be float32 [N]")
     rc = _lib().rb_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
-                                ldo, splits, split_stride, stages, _ptr(status_word(x.device)), _stream())
+                                ldo, splits, split_stride, stages, 1 if gated else 0, _ptr(status_word(x.device)), _stream())
     if rc == 10003:
         return False
     _check(rc, "gemm_tcgen05")

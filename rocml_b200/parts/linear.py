@@ -34,6 +34,7 @@ class Linear:
         self.env = env
         self.weight: Optional[torch.Tensor] = None
         self.bias: Optional[torch.Tensor] = None  # float32: widening is exact, the vector is tiny
+        self.paired = False
 
     def declare(self, prefix: str) -> List[TensorDecl]:
         out = []
@@ -50,6 +51,33 @@ class Linear:
         self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
         if self.has_bias:
             self.bias = torch.cat([tensors[f"{prefix}{n}.bias"].float() for n in self.names]).contiguous()
+
+    def interleave_pairs(self) -> bool:
+        """For a stack of two equally wide projections (gate, up): reorder the rows so that blocks
+        of 16 gate rows alternate with the 16 up rows of the same outputs.  The tensor-core
+        product can then apply silu(gate) * up in its epilogue (``forward_gated``).  Returns False,
+        and changes nothing, when the sizes or types do not allow it."""
+        if len(self.outs) != 2 or self.outs[0] != self.outs[1] or self.outs[0] % 16 or self.k % 8 or \
+                self.weight.dtype != torch.bfloat16 or not self.weight.is_cuda:
+            return False
+        half = self.outs[0]
+
+        def mix(t):
+            g, u = t[:half], t[half:]
+            shape = (half // 16, 16) + tuple(t.shape[1:])
+            return torch.stack([g.reshape(shape), u.reshape(shape)], dim=1).reshape(t.shape).contiguous()
+        self.weight = mix(self.weight)
+        if self.bias is not None:
+            self.bias = mix(self.bias)
+        self.paired = True
+        return True
+
+    def forward_gated(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        """[M, N / 2] = silu(gate(x)) * up(x) in one kernel (needs ``interleave_pairs``)."""
+        out = torch.empty((m, self.n // 2), dtype=torch.bfloat16, device=x.device)
+        if not kernels.gemm_tcgen05(x, self.weight, out, self.bias, m, gated=True):
+            raise KernelError("the gated matrix product refused a layout that interleave_pairs accepted")
+        return out
 
     def adopt(self, weight: torch.Tensor) -> None:
         """Use an existing tensor as the weight (a tied head reads the embedding table)."""

@@ -39,6 +39,8 @@ class GatedMLP(FeedForward):
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         self.gate_up.load(tensors, prefix)
         self.down.load(tensors, prefix)
+        if self.env.act_dtype == torch.bfloat16:
+            self.gate_up.interleave_pairs()     # silu(gate) * up then happens inside the product
 
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
@@ -46,7 +48,12 @@ class GatedMLP(FeedForward):
     def forward(self, xn, batch):
         T = batch.n_tokens
         dev, act = xn.device, self.env.act_dtype
-        gu = self.gate_up.forward_auto(xn, T)          # [T, 2I] or [S, T, 2I] partial sums
-        h = torch.empty((T, self.inter), dtype=act, device=dev)
-        kernels.silu_mul(gu, h)
+        if self.gate_up.paired and T > 128:
+            # many tokens: the activation happens in the product's epilogue, hidden behind the next tile
+            h = self.gate_up.forward_gated(xn, T)
+        else:
+            # few tokens: the product is split over K, so the activation waits for the partial sums
+            gu = self.gate_up.forward_auto(xn, T)      # [T, 2I] or [S, T, 2I] partial sums
+            h = torch.empty((T, self.inter), dtype=act, device=dev)
+            kernels.silu_mul(gu, h, paired=self.gate_up.paired)
         return self.down.forward_delta(h, T)

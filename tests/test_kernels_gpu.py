@@ -53,6 +53,25 @@ def test_gemm_tcgen05_split_k(M, N, K, S):
     assert err < 1e-5, err
 
 
+@pytest.mark.parametrize("M,I,K", [(1, 208, 96), (8, 12288, 512), (64, 320, 128), (200, 4096, 1024), (2048, 1024, 256)])
+def test_gemm_tcgen05_gated_epilogue(M, I, K):
+    """gate and up rows interleaved in blocks of 16; the product's epilogue gives silu(gate) * up."""
+    from rocml_b200 import kernels
+    x = rnd((M, K), 1, torch.bfloat16).to(DEV)
+    wg, wu = rnd((I, K), 2, torch.bfloat16, 0.2), rnd((I, K), 3, torch.bfloat16, 0.2)
+    bg, bu = rnd((I,), 4), rnd((I,), 5)
+    mix = lambda g, u: torch.stack([g.reshape(I // 16, 16, *g.shape[1:]), u.reshape(I // 16, 16, *u.shape[1:])], 1).reshape(2 * I, *g.shape[1:])
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert kernels.gemm_tcgen05(x, mix(wg, wu).contiguous().to(DEV), out, mix(bg, bu).contiguous().to(DEV), gated=True)
+    kernels.check_status(DEV)
+    xd = x.cpu().double()
+    g = xd @ wg.double().t() + bg.double()
+    u = xd @ wu.double().t() + bu.double()
+    want = g / (1 + torch.exp(-g)) * u
+    err = ((out.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max().item()
+    assert err < 2 ** -7, err
+
+
 def test_gemm_tcgen05_refuses_unaligned_k():
     from rocml_b200 import kernels
     x = rnd((4, 100), 1, torch.bfloat16).to(DEV)  # K = 100: rows are not a multiple of 16 bytes
@@ -145,6 +164,12 @@ def test_silu_mul(dt):
     out2 = torch.empty((T, I), dtype=dt, device=DEV)
     kernels.silu_mul(parts, out2)
     assert ((out2.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max() < tol
+    # gates and ups alternating in blocks of 16 columns
+    xc = x.cpu()
+    mixed = torch.stack([xc[:, :I].reshape(T, I // 16, 16), xc[:, I:].reshape(T, I // 16, 16)], 2).reshape(T, 2 * I)
+    out3 = torch.empty((T, I), dtype=dt, device=DEV)
+    kernels.silu_mul(mixed.contiguous().to(DEV), out3, paired=True)
+    assert torch.equal(out3, out)
 
 
 # ---- attention over the paged cache --------------------------------------------------------------------
