@@ -45,7 +45,8 @@ int rb_attention_prefill(const void* q, int q_stride, void* out, int o_stride, c
 int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                         const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window, int n_chunks,
-                        float* part_acc, float* part_ml, int* counters, void* out, int o_stride, void* stream);
+                        int pages_per_block, float* part_acc, float* part_ml, int* counters, void* out, int o_stride,
+                        void* stream);
 
 int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, int o_stride, int dtype,
                        const int* positions, const int* slot_of_token, int T, int nq, int hd, int chunk,

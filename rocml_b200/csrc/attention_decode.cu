@@ -37,7 +37,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                         const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
-                        float scale, int window, int n_chunks, float* __restrict__ part_acc,
+                        float scale, int window, int n_chunks, int ppb, float* __restrict__ part_acc,
                         float* __restrict__ part_ml, int* __restrict__ counters,
                         __nv_bfloat16* __restrict__ out, int o_stride) {
     pdl_trigger();
@@ -61,37 +61,57 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if (slot < 0) return;
     const int t = cu_q[b];
     const int pos = kv_len[b] - 1;
-    if (c * CHUNK > pos) return;                            // beyond the sequence: takes no part in the merge
-    const int lo = max(window > 0 ? max(0, pos - window + 1) : 0, c * CHUNK);
-    const int hi = min(pos, (c + 1) * CHUNK - 1);
+    // this block's pages: [c * ppb, (c + 1) * ppb), cut at the sequence's end
+    const int page_first = c * ppb;
+    if (page_first * CHUNK > pos) return;                   // beyond the sequence: takes no part in the merge
+    const int page_last = min(pos / CHUNK, page_first + ppb - 1);
+    const int win_lo = window > 0 ? max(0, pos - window + 1) : 0;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;
     const int* table = block_table + (size_t)slot * max_pages;
 
-    // copies: the query heads (all threads), then each warp its own keys and values
+    // Each warp owns 16 keys of every page and two shared-memory buffers for them: while it
+    // works on one page its copies of the next are in flight.
+    __nv_bfloat16* KVw = KVs + warp * 4 * WK * HD;          // [2 buffers][K 16 x HD | V 16 x HD]
+    auto issue = [&](int page_idx, int buf) {
+        const int j0 = page_idx * CHUNK + warp * WK;
+        const int hi = min(pos, (page_idx + 1) * CHUNK - 1);
+        const bool any = page_idx <= page_last && j0 <= hi && j0 + WK - 1 >= win_lo;
+        if (any) {
+            const int page = table[page_idx];
+            const size_t off = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE + warp * WK) * HD;
+            const int valid = page < 0 ? 0 : min(WK, hi - j0 + 1);   // rows past the sequence's end are zero-filled
+            __nv_bfloat16* Kw = KVw + buf * 2 * WK * HD;
+            load_tile<HD>(Kw, k_cache + off, HD, WK, valid, lane, 32);
+            load_tile<HD>(Kw + WK * HD, v_cache + off, HD, WK, valid, lane, 32);
+        }
+        cp_async_commit();
+    };
     load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
-    const int j0 = c * CHUNK + warp * WK;                   // this warp's first key; its 16 keys lie in one page
-    __nv_bfloat16* Kw = KVs + warp * 2 * WK * HD;
-    __nv_bfloat16* Vw = Kw + WK * HD;
-    const bool any = j0 <= hi && j0 + WK - 1 >= lo;
-    if (any) {
-        const int page = table[j0 / RB_PAGE];
-        const size_t off = (((size_t)(page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE + (j0 % RB_PAGE)) * HD;
-        const int valid = page < 0 ? 0 : min(WK, hi - j0 + 1);   // rows past the sequence's end are zero-filled
-        load_tile<HD>(Kw, k_cache + off, HD, WK, valid, lane, 32);
-        load_tile<HD>(Vw, v_cache + off, HD, WK, valid, lane, 32);
-    }
-    cp_async_commit();
+    issue(page_first, 0);
     cp_async_wait<0>();
-    __syncthreads();
+    __syncthreads();                                        // the query heads are in place for every warp
 
     float m_w[2] = {NEG_BIG, NEG_BIG}, l_w[2] = {0.f, 0.f};
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-    if (any) {
-        const uint32_t qs_base = smem_addr(Qs), ks_base = smem_addr(Kw), vs_base = smem_addr(Vw);
+    const uint32_t qs_base = smem_addr(Qs);
+    const float sl2 = scale * LOG2E;
+
+    for (int pg = page_first; pg <= page_last; ++pg) {
+        const int buf = (pg - page_first) & 1;
+        if (pg > page_first) {
+            cp_async_wait<0>();                             // this warp's copies of page pg have landed
+            __syncwarp();
+        }
+        if (pg < page_last) issue(pg + 1, buf ^ 1);         // the other buffer was read in the last round
+        const int j0 = pg * CHUNK + warp * WK;
+        const int hi = min(pos, (pg + 1) * CHUNK - 1);
+        if (!(j0 <= hi && j0 + WK - 1 >= win_lo)) continue;
+        const uint32_t ks_base = smem_addr(KVw + buf * 2 * WK * HD);
+        const uint32_t vs_base = ks_base + WK * HD * 2;
         float s[WK / 8][4];
 #pragma unroll
         for (int j = 0; j < WK / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
@@ -109,24 +129,35 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_bf16(s[j], qa1, b2, b3);
             }
         }
-        const float sl2 = scale * LOG2E;
-        float mx = NEG_BIG;     // every row is the same token: one mask for all rows
+        // every row is the same token: one mask for all rows
+        float mx[2] = {NEG_BIG, NEG_BIG};
 #pragma unroll
         for (int j = 0; j < WK / 8; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = j0 + j * 8 + tq * 2 + (e & 1);
-                const bool ok = key >= lo && key <= hi;
+                const bool ok = key >= win_lo && key <= hi;
                 s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
             }
-            m_w[0] = fmaxf(m_w[0], fmaxf(s[j][0], s[j][1]));
-            m_w[1] = fmaxf(m_w[1], fmaxf(s[j][2], s[j][3]));
+            mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
         }
-        (void)mx;
+        float alpha[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 1));
-            m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 2));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_w[r], mx[r]);
+            alpha[r] = exp2f(m_w[r] - m_new);
+            m_w[r] = m_new;
+            l_w[r] *= alpha[r];
+        }
+        if (pg > page_first) {
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            }
         }
         uint32_t pa[WK / 16][4];
 #pragma unroll
@@ -139,11 +170,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
         }
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
-            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
-        }
-#pragma unroll
         for (int kk = 0; kk < WK / 16; ++kk) {
 #pragma unroll
             for (int i = 0; i < HD / 8; i += 2) {
@@ -154,6 +180,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_bf16(o[i + 1], pa[kk], b2, b3);
             }
         }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {                           // this thread's share of the sums -> the row's sum
+        l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
+        l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
     }
     __syncthreads();   // every warp is done with its keys and values: the space is reused for the merge
     if (tq == 0) {
@@ -197,7 +229,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const int active = pos / CHUNK + 1;
+        const int active = pos / (CHUNK * ppb) + 1;
         int* ctr = counters + (size_t)b * gridDim.y + blockIdx.y;
         const int old = atomicAdd(ctr, 1);
         s_last = old == active - 1;
@@ -209,8 +241,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // First every chunk's (maximum, sum) of every row goes to shared memory in one parallel sweep;
     // then each thread owns one (row, dimension) and adds the chunks in ascending order.  Loads of
     // different chunks do not depend on one another, so they overlap.
-    const int c_hi = pos / CHUNK;
-    const int c_lo = window > 0 ? max(0, pos - window + 1) / CHUNK : 0;
+    const int c_hi = pos / (CHUNK * ppb);
+    const int c_lo = window > 0 ? max(0, pos - window + 1) / (CHUNK * ppb) : 0;
     const int n_act = c_hi - c_lo + 1;
     float* s_pm = reinterpret_cast<float*>(KVs);            // [rows][n_act]
     float* s_pl = s_pm + rows_valid * n_act;            // the host checked that both fit
@@ -243,12 +275,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 template <int HD>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len, int B, int nq, int nkv,
-           float scale, int window, int n_chunks, float* part_acc, float* part_ml, int* counters, void* out,
-           int o_stride, cudaStream_t s) {
+           float scale, int window, int n_chunks, int ppb, float* part_acc, float* part_ml, int* counters,
+           void* out, int o_stride, cudaStream_t s) {
     const int g = nq / nkv;
     dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
-    const size_t kv_bytes = (size_t)WARPS * 2 * WK * HD * sizeof(__nv_bfloat16);
+    const size_t kv_bytes = (size_t)WARPS * 4 * WK * HD * sizeof(__nv_bfloat16);   // two buffers per warp
     const size_t merge_bytes = (size_t)WARPS * ROWS * HD * sizeof(float);
     const size_t smem = (size_t)ROWS * HD * sizeof(__nv_bfloat16) + (kv_bytes > merge_bytes ? kv_bytes : merge_bytes);
     const size_t region = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
@@ -263,13 +295,14 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     }
     RB_LAUNCH((k), grid, dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
               (const __nv_bfloat16*)v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
-              n_chunks, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride);
+              n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride);
     return RB_OK;
 }
 }  // namespace
 
-// One query token per sequence (token index cu_q[b]).  chunk is fixed at 64 keys; n_chunks covers
-// the longest sequence of the batch; with n_chunks == 1 the result is written to `out` directly.
+// One query token per sequence (token index cu_q[b]).  A block takes `pages_per_block` pages of 64
+// keys; n_chunks = ceil(pages of the longest sequence / pages_per_block) blocks cover a sequence;
+// with n_chunks == 1 the result is written to `out` directly.
 // Work space: part_acc [T, nq, n_chunks, hd], part_ml [T, nq, n_chunks, 2] and `counters`, at least
 // B * nkv * ceil(group / 16) ints that are ZERO on entry and are left zero on exit.
 // Returns RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 and for contexts whose chunk list does
@@ -278,16 +311,16 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                    const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                                    const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
-                                   int n_chunks, float* part_acc, float* part_ml, int* counters, void* out,
-                                   int o_stride, void* stream) {
+                                   int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
+                                   int* counters, void* out, int o_stride, void* stream) {
     if (B <= 0) return RB_OK;
-    if (nkv <= 0 || nq % nkv || n_chunks < 1 || n_chunks > 1024) return RB_ERR_BAD_SIZE;
+    if (nkv <= 0 || nq % nkv || n_chunks < 1 || n_chunks > 1024 || pages_per_block < 1) return RB_ERR_BAD_SIZE;
     if (n_chunks > 1 && (!part_acc || !part_ml || !counters)) return RB_ERR_BAD_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || (q_stride % 8))
         return RB_ERR_BAD_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
 #define RB_AD(HD) return launch<HD>(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, \
-                                    nkv, scale, window, n_chunks, part_acc, part_ml, counters, out, o_stride, s)
+                                    nkv, scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, s)
     if (hd == 128) RB_AD(128);
     if (hd == 64) RB_AD(64);
     if (hd == 256) RB_AD(256);
@@ -359,6 +392,6 @@ extern "C" int rb_attention_decode_static(const void* q, int q_stride, const voi
     cudaError_t e = cudaMemsetAsync(sc->counters, 0, n_counters * sizeof(int), (cudaStream_t)stream);
     if (e != cudaSuccess) return (int)e;
     return rb_attention_decode(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, n_seqs,
-                               nq, nkv, hd, scale, window, n_chunks, sc->acc, sc->ml, sc->counters, out, o_stride,
+                               nq, nkv, hd, scale, window, n_chunks, 1, sc->acc, sc->ml, sc->counters, out, o_stride,
                                stream);
 }

@@ -88,7 +88,7 @@ def _lib():
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                              _f, _i, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
-                                            _vp, _vp, _vp, _vp, _i, _vp]
+                                            _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
         _sigs_done = True
@@ -258,6 +258,17 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     return True
 
 
+def decode_split(n_seqs: int, n_kv_groups: int, n_pages: int):
+    """(blocks per sequence, pages per block) for decode attention: enough blocks to keep every
+    multiprocessor busy about four times over, no more, so that a large batch walks several pages
+    per block (one partial result and one merge for all of them) and a single sequence still
+    spreads over the device."""
+    want = -(-4 * 148 // max(1, n_seqs * n_kv_groups))
+    blocks = max(1, min(n_pages, want))
+    ppb = -(-n_pages // blocks)
+    return -(-n_pages // ppb), ppb
+
+
 _counters = {}
 _COUNTER_INTS = 1 << 20
 
@@ -274,9 +285,11 @@ def decode_counters(device) -> torch.Tensor:
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                      n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
-                     part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor]) -> bool:
-    """bfloat16 decode attention, one query token per sequence, keys in chunks of 128, the chunks
-    merged by the kernel itself; part_acc / part_ml are its work space when n_chunks > 1.  Returns
+                     part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
+                     pages_per_block: int = 1) -> bool:
+    """bfloat16 decode attention, one query token per sequence; a block takes ``pages_per_block``
+    pages of 64 keys, ``n_chunks`` blocks cover the longest sequence and are merged by the kernel
+    itself; part_acc / part_ml are its work space when n_chunks > 1.  Returns
     False when the kernel does not take the head size or the alignment (use attention_generic)."""
     if n_seqs * nq > _COUNTER_INTS:
         return False
@@ -287,7 +300,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     rc = _lib().rb_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
-        int(window), int(n_chunks), _ptr(part_acc), _ptr(part_ml), _ptr(decode_counters(q.device)), _ptr(out),
+        int(window), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
+        _ptr(decode_counters(q.device)), _ptr(out),
         out.stride(0), _stream())
     if rc in (10001, 10003):
         return False

@@ -101,15 +101,18 @@ class Attention(Mixer):
         keys split in fixed chunks, partial results merged; otherwise whole rows."""
         if batch.is_decode:
             chunk = DECODE_CHUNK
-            n_chunks = max(1, (batch.max_kv_len + chunk - 1) // chunk)
             T = batch.n_tokens
+            n_pages = max(1, (batch.max_kv_len + chunk - 1) // chunk)
+            groups = self.nkv * ((self.nq // self.nkv + 15) // 16)
+            n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages)
             acc = ml = None
-            if n_chunks > 1:
-                acc = torch.empty((T, self.nq, n_chunks, self.hd), dtype=torch.float32, device=q.device)
-                ml = torch.empty((T, self.nq, n_chunks, 2), dtype=torch.float32, device=q.device)
+            if n_pages > 1:
+                acc = torch.empty((T, self.nq, n_pages, self.hd), dtype=torch.float32, device=q.device)
+                ml = torch.empty((T, self.nq, n_pages, 2), dtype=torch.float32, device=q.device)
             fast = kernels.attention_decode(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                             batch.kv_len, batch.n_seqs, self.nq, self.nkv, self.hd, self.scale,
-                                            window, n_chunks, acc, ml)
+                                            window, n_blocks, acc, ml, ppb)
+            n_chunks = n_pages
             if fast:
                 return
             if n_chunks > 1:

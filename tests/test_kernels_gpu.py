@@ -295,7 +295,7 @@ DEC_CASES = [
 
 
 @pytest.mark.parametrize("case", range(len(DEC_CASES)))
-@pytest.mark.parametrize("fast", [True, False])
+@pytest.mark.parametrize("fast", [True, False, 3, 100])
 def test_attention_decode_split_kv(case, fast):
     """One query per sequence, keys in chunks of 128, merged: the bfloat16 kernel and the plain kernel."""
     from rocml_b200 import kernels
@@ -309,13 +309,14 @@ def test_attention_decode_split_kv(case, fast):
     q = torch.cat(qs, 0).reshape(-1, nq * hd).to(dtype).to(DEV)
     out = torch.full_like(q, float("nan"))
     d = {k: v.to(DEV) for k, v in meta.items()}
-    n_chunks = (max(lens) + 63) // 64 + 1     # one more than needed, as a padded graph would have
+    ppb = 1 if fast in (True, False) else fast        # pages per block of the bfloat16 kernel
+    n_chunks = ((max(lens) + 63) // 64 + ppb - 1) // ppb + 1     # one more than needed, as a padded graph would have
     acc = torch.full((B, nq, n_chunks, hd), float("nan"), dtype=torch.float32, device=DEV)
     ml = torch.full((B, nq, n_chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
     pos = (d["kv_len"] - 1).to(torch.int32)
     if fast:
         assert kernels.attention_decode(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"],
-                                        d["kv_len"], B, nq, nkv, hd, scale, window or 0, n_chunks, acc, ml)
+                                        d["kv_len"], B, nq, nkv, hd, scale, window or 0, n_chunks, acc, ml, ppb)
         assert int(kernels.decode_counters(DEV).abs().sum()) == 0      # the work space is left zeroed
     else:
         kernels.attention_generic(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
