@@ -119,3 +119,37 @@ def test_unequal_batches_and_slot_reuse(model_folder, plain, dtype):
             assert err < TOL[dtype], f"{name} {dtype} round {r} seq {j}: {err}"
         eng.cache.check_invariants()
     assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_the_first_token(model_folder, plain, dtype):
+    """A sequence grown one token at a time from its very first token, across page boundaries and
+    across the context buckets of the captured graphs, next to a second sequence that starts later
+    and ends earlier; every logit row is compared."""
+    from rocml_b200 import Engine, StepEntry
+    name, folder = model_folder
+    vocab = CONFIGS[name]["vocab_size"]
+    n = min(CONFIGS[name]["max_position_embeddings"], 300)
+    ids = prompt(77, n, vocab)
+    start, n_other = n // 3, 40          # the second sequence lives for 40 steps from step n / 3
+    other = prompt(78, n_other, vocab)
+    want, want_other = plain.logits(ids), plain.logits(other)
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024)
+    a = eng.new_sequence()
+    got, got_other, b = [], [], None
+    for t in range(n):
+        entries = [StepEntry(a, [ids[t]], [0])]
+        k = t - start
+        if 0 <= k < n_other:
+            if k == 0:
+                b = eng.new_sequence()
+            entries.append(StepEntry(b, [other[k]], [0]))
+        out = eng.step(entries)
+        got.append(out[0].clone())
+        if len(entries) == 2:
+            got_other.append(out[1].clone())
+            if k == n_other - 1:
+                eng.release(b)
+    err = rel_err(torch.stack(got), want)
+    err_other = rel_err(torch.stack(got_other), want_other)
+    assert err < TOL[dtype] and err_other < TOL[dtype], f"{name} {dtype}: {err} {err_other}"
