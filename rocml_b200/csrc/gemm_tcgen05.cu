@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 #include "api.h"
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -473,6 +474,205 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
 }
 
+
+// ---- many tokens, pairs of CTAs (cta_group::2) -------------------------------------------------------
+// Two CTAs of a cluster compute a 256 x 256 output tile together: each loads its own 128 rows of the
+// tokens and its own HALF (128 rows) of the weight tile, the even CTA's MMA warp issues
+// tcgen05.mma.cta_group::2 (M = 256), which reads both CTAs' shared memory and writes each CTA's 128
+// rows of the accumulator into that CTA's tensor memory.  Per multiprocessor this halves the bytes
+// of the weight operand that are loaded and read from shared memory per MMA, which is what bounds
+// the single-CTA kernel (128 x 256 tiles read 96 bytes per clock of a 128-byte-per-clock port).
+// Persistent, two accumulators, as the single-CTA kernel above.  Barriers: full[] is counted on the
+// leader (both CTAs' TMA loads report there), empty[] and acc_full[] exist in both CTAs and are
+// signalled by multicast commits, acc_empty[] lives in the leader and collects the 8 epilogue warps
+// of the pair.  No TMA multicast is used anywhere.
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGE = 2 * BM * BK * 2;       // A 128 x 64 + B half 128 x 64, bf16: 32 KB
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE + 1024 + 256;
+
+template <typename OT, bool GATED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         OT* __restrict__ out, const Params p) {
+    constexpr int BN = PAIR_BN, S = PAIR_STAGES, A_BYTES = BM * BK * 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + S * PAIR_STAGE);
+    uint64_t* empty = full + S;
+    uint64_t* acc_full = empty + S;      // [2]
+    uint64_t* acc_empty = acc_full + 2;  // [2], used in the leader
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    uint32_t* abort_flag = tmem_slot + 1;
+
+    rb::pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int m_pairs = (p.a_rows + 2 * BM - 1) / (2 * BM), n_tiles = (p.b_rows + BN - 1) / BN;
+    const int n_total = m_pairs * n_tiles;
+    const int n_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_arrive();           // the peer's barriers are initialised before anything signals them
+    cluster_wait();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&map_a);
+            tma_prefetch_desc(&map_b);
+            rb::pdl_wait();
+            long long it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_total && ok; tile += n_pairs) {
+                const int a0 = (tile % m_pairs) * 2 * BM + (int)rank * BM;
+                const int b0 = (tile / m_pairs) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = (int)(it % S);
+                    ok = mbar_wait(&empty[s], (uint32_t)(((it / S) & 1) ^ 1));
+                    if (!ok) break;
+                    uint8_t* sa = smem + s * PAIR_STAGE;
+                    const uint32_t bar = smem_u32(&full[s]) & PEER_BIT_MASK;   // the leader's barrier
+                    if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * PAIR_STAGE);   // both CTAs' bytes
+                    tma_load_2d_pair(sa + A_BYTES, &map_b, kb * BK, b0, bar);
+                    tma_load_2d_pair(sa, &map_a, kb * BK, a0, bar);
+                }
+            }
+            if (!ok) {
+                atomicExch(p.status, RB_ERR_TIMEOUT);
+                atomicExch(abort_flag, 1u);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN);
+            long long it = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_total && ok; tile += n_pairs, ++local) {
+                const int acc = local & 1;
+                const uint32_t use = (uint32_t)(local >> 1);
+                ok = mbar_wait(&acc_empty[acc], (use & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = (int)(it % S);
+                    ok = mbar_wait(&full[s], (uint32_t)((it / S) & 1));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * PAIR_STAGE);
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        mma_bf16_pair(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    mma_commit_pair(&empty[s]);          // frees the stage in both CTAs
+                }
+                if (!ok) break;
+                mma_commit_pair(&acc_full[acc]);         // wakes both CTAs' epilogue warps
+            }
+            if (!ok) {
+                atomicExch(p.status, RB_ERR_TIMEOUT);
+                atomicExch(abort_flag, 1u);
+                mma_commit_pair(&acc_full[0]);
+                mma_commit_pair(&acc_full[1]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = pair; tile < n_total; tile += n_pairs, ++local) {
+            const int acc = local & 1;
+            const uint32_t use = (uint32_t)(local >> 1);
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], use & 1));
+            tc_fence_after();
+            if (!ok || *(volatile uint32_t*)abort_flag != 0) {
+                if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
+                break;
+            }
+            const int a0 = (tile % m_pairs) * 2 * BM + (int)rank * BM, b0 = (tile / m_pairs) * BN;
+            const int ar = a0 + quarter * 32 + lane;
+            const bool add_bias = p.bias != nullptr;
+            const uint32_t lane_addr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            const bool vec_ok = (((uintptr_t)out | ((uintptr_t)p.ldo * sizeof(OT))) & 15) == 0;
+            OT* row = out + (size_t)(ar < p.a_rows ? ar : 0) * p.ldo;
+            if (GATED) {
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; c += 2) {
+                    float g[16], u[16];
+                    tmem_ld16(lane_addr + c * 16, g);
+                    tmem_ld16(lane_addr + (c + 1) * 16, u);
+                    const int f0 = b0 + c * 16;
+                    if (ar < p.a_rows && f0 + 32 <= p.b_rows) {
+                        if (add_bias) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) { g[i] += p.bias[f0 + i]; u[i] += p.bias[f0 + 16 + i]; }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                        OT* dst = row + (f0 >> 1);
+                        if (vec_ok) store16(dst, g);
+                        else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) dst[i] = rb::from_f32<OT>(g[i]);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; ++c) {
+                    float v[16];
+                    tmem_ld16(lane_addr + c * 16, v);
+                    const int f0 = b0 + c * 16;
+                    if (ar < p.a_rows) {
+                        if (add_bias) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] += (f0 + i < p.b_rows) ? p.bias[f0 + i] : 0.f;
+                        }
+                        if (vec_ok && f0 + 16 <= p.b_rows) {
+                            store16(row + f0, v);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (f0 + i < p.b_rows) row[f0 + i] = rb::from_f32<OT>(v[i]);
+                        }
+                    }
+                }
+            }
+            // hand the accumulator back to the leader's MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(&acc_empty[acc]);
+                else mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+            }
+        }
+    }
+    // neither CTA may leave while the other can still read its shared memory or signal its barriers
+    tc_fence_before();
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
 }  // namespace
 
 // ---- host side -------------------------------------------------------------------------------------
@@ -588,6 +788,33 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, P
     return RB_OK;
 }
 
+bool pair_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("RB_GEMM_PAIR");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
+template <typename OT, bool GATED>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, cudaStream_t s) {
+    auto k = gemm_tcgen05_pair_kernel<OT, GATED>;
+    static bool attr_done = false;
+    static int sms = 0;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const long long tiles = (long long)((p.a_rows + 2 * BM - 1) / (2 * BM)) * ((p.b_rows + PAIR_BN - 1) / PAIR_BN);
+    const int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
+    RB_LAUNCH((k), dim3(2 * pairs), dim3(192), PAIR_SMEM, s, ma, mb, (OT*)out, p);
+    return RB_OK;
+}
+
 template <bool SWAP, typename OT, bool GATED>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out, const Params& p, int splits,
                 cudaStream_t s) {
@@ -642,6 +869,15 @@ extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, 
         p.a_rows = M; p.b_rows = N;
         if ((rc = tensor_map(x, M, K, ldx, BM, &ma)) != RB_OK) return rc;
         if ((rc = tensor_map(w, N, K, K, bn, &mb)) != RB_OK) return rc;
+    }
+    if (!swap && splits == 1 && bn == 256 && M > 256 && pair_enabled()) {
+        // many tokens and a wide weight: pairs of CTAs; the weight is read in boxes of 128 rows (a half tile)
+        CUtensorMap mb_half;
+        if ((rc = tensor_map(w, N, K, K, BM, &mb_half)) != RB_OK) return rc;
+        if (out_dtype == RB_BF16)
+            return gated ? launch_pair<__nv_bfloat16, true>(ma, mb_half, out, p, s)
+                         : launch_pair<__nv_bfloat16, false>(ma, mb_half, out, p, s);
+        if (out_dtype == RB_F32) return launch_pair<float, false>(ma, mb_half, out, p, s);
     }
     if (!swap && splits == 1 && (bn == 256 || bn == 128)) {
         // many tokens: the persistent kernel with two accumulators (2 x 256 columns fill tensor memory)
