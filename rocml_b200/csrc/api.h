@@ -22,7 +22,9 @@ int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_s
                           int act_dtype, int q_stride, int T, int nq, int nkv, int hd, const void* q_norm_w,
                           const void* k_norm_w, int w_dtype, float eps, const float* inv_freq, int rot_dim,
                           const int* positions, const int* slot_of_token, const int* block_table, int max_pages,
-                          void* k_cache, void* v_cache, int write_kv, void* stream);
+                          void* k_cache, void* v_cache, int write_kv, const void* cos_sin, void* stream);
+
+int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, void* out, void* stream);
 
 int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, void* out,
                     int out_dtype, int M, int N, int K, long long ldx, long long ldo, void* stream);

@@ -26,7 +26,8 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
                                           const int* __restrict__ positions,
                                           const int* __restrict__ slot_of_token,
                                           const int* __restrict__ block_table, int max_pages,
-                                          AT* __restrict__ k_cache, AT* __restrict__ v_cache, int write_kv) {
+                                          AT* __restrict__ k_cache, AT* __restrict__ v_cache, int write_kv,
+                                          const float2* __restrict__ cs_table) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -102,9 +103,9 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
     for (int i = lane; i < half; i += 32) {
         float x0 = buf[i], x1 = buf[i + half];
         if (w) { x0 = x0 * inv * to_f32(w[i]); x1 = x1 * inv * to_f32(w[i + half]); }
-        const float a = (float)pos * inv_freq[i];
         float sn, cs;
-        sincosf(a, &sn, &cs);
+        if (cs_table) { const float2 c2 = cs_table[(size_t)t * half + i]; cs = c2.x; sn = c2.y; }
+        else sincosf((float)pos * inv_freq[i], &sn, &cs);
         dst[i] = from_f32<AT>(x0 * cs - x1 * sn);
         dst[i + half] = from_f32<AT>(x0 * sn + x1 * cs);
     }
@@ -115,22 +116,113 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
     }
 }
 
+// The same for a head size of 128 with the whole head rotated, the common case: a lane holds 4
+// consecutive dimensions (one 8- or 16-byte load per partial sum), the rotation partner sits 16 lanes
+// away (shuffle), nothing goes through shared memory, and a head is written with 8-byte stores.
+template <typename IT, typename AT, typename WT>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride,
+                                AT* __restrict__ q_out, int q_stride, int T, int nq, int nkv,
+                                const WT* __restrict__ q_norm_w, const WT* __restrict__ k_norm_w, float eps,
+                                const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                const int* __restrict__ slot_of_token, const int* __restrict__ block_table,
+                                int max_pages, AT* __restrict__ k_cache, AT* __restrict__ v_cache, int write_kv,
+                                const float2* __restrict__ cs_table) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int hd = 128;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)T * heads_total) return;
+    const int t = (int)(item / heads_total);
+    const int h = (int)(item - (long long)t * heads_total);
+    const int slot = slot_of_token[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    int kind, head;
+    if (h < nq) { kind = 0; head = h; }
+    else if (h < nq + nkv) { kind = 1; head = h - nq; }
+    else { kind = 2; head = h - nq - nkv; }
+    AT* dst;
+    if (kind == 0) {
+        dst = q_out + (size_t)t * q_stride + (size_t)head * hd;
+    } else {
+        const int page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
+        if (page < 0) return;
+        dst = (kind == 1 ? k_cache : v_cache) + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hd;
+    }
+    const IT* src = in + (size_t)t * row_stride + (size_t)h * hd + lane * 4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_in; ++s) {
+        const IT* p = src + (size_t)s * in_stride;
+        if (sizeof(IT) == 4) {
+            const float4 f = *reinterpret_cast<const float4*>(p);
+            v[0] += f.x; v[1] += f.y; v[2] += f.z; v[3] += f.w;
+        } else {
+            const uint2 raw = *reinterpret_cast<const uint2*>(p);
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y;
+        }
+    }
+    if (kind != 2) {
+        const WT* w = kind == 0 ? q_norm_w : k_norm_w;
+        if (w) {
+            const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+            const float inv = rsqrtf(ss / (float)hd + eps);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = v[j] * inv * to_f32(w[lane * 4 + j]);
+        }
+        if (inv_freq) {
+            // dimension i < 64 pairs with i + 64: lanes 0-15 hold x_i, lanes 16-31 the partners
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+                float sn, cs;
+                if (cs_table) { const float2 c2 = cs_table[(size_t)t * 64 + (lane & 15) * 4 + j]; cs = c2.x; sn = c2.y; }
+                else sincosf((float)pos * inv_freq[(lane & 15) * 4 + j], &sn, &cs);
+                v[j] = lane < 16 ? v[j] * cs - other * sn : other * sn + v[j] * cs;
+            }
+        }
+    }
+    if (sizeof(AT) == 4) {
+        *reinterpret_cast<float4*>(dst + lane * 4) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&lo);
+        raw.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst + lane * 4) = raw;
+    }
+}
+
 template <typename IT, typename AT, typename WT>
 static int launch_qk(const void* in, int n_in, long long in_stride, int row_stride, void* q_out, int q_stride,
                      int T, int nq, int nkv, int hd, const void* qw, const void* kw, float eps,
                      const float* inv_freq, int rot_dim, const int* positions, const int* slot_of_token,
                      const int* block_table, int max_pages, void* k_cache, void* v_cache, int write_kv,
-                     cudaStream_t s) {
+                     const float2* cs_table, cudaStream_t s) {
     const int warps = 4;
     const long long items = (long long)T * (nq + (write_kv ? 2 * nkv : 0));
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
+    const size_t esz = sizeof(IT);
+    if (hd == 128 && (!inv_freq || rot_dim == 128) && (((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)k_cache |
+                                                        (uintptr_t)v_cache) & 15) == 0 &&
+        (row_stride * esz) % 16 == 0 && ((size_t)in_stride * esz) % 16 == 0 && (q_stride * sizeof(AT)) % 16 == 0) {
+        RB_LAUNCH((qk_norm_rope_cache_hd128_kernel<IT, AT, WT>), dim3((int)blocks), dim3(128), 0, s, (const IT*)in, n_in,
+                  (size_t)in_stride, row_stride, (AT*)q_out, q_stride, T, nq, nkv, (const WT*)qw, (const WT*)kw, eps,
+                  inv_freq, positions, slot_of_token, block_table, max_pages, (AT*)k_cache, (AT*)v_cache, write_kv,
+                  cs_table);
+        return RB_OK;
+    }
     const size_t smem = (size_t)warps * hd * sizeof(float);
     if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((qk_norm_rope_cache_kernel<IT, AT, WT>), dim3((int)blocks), dim3(warps * 32), smem, s, (const IT*)in,
               n_in, (size_t)in_stride, row_stride, (AT*)q_out, q_stride, T, nq, nkv, hd, (const WT*)qw,
               (const WT*)kw, eps, inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages,
-              (AT*)k_cache, (AT*)v_cache, write_kv);
+              (AT*)k_cache, (AT*)v_cache, write_kv, cs_table);
     return RB_OK;
 }
 
@@ -139,14 +231,15 @@ extern "C" int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, lon
                                      const void* q_norm_w, const void* k_norm_w, int w_dtype, float eps,
                                      const float* inv_freq, int rot_dim, const int* positions,
                                      const int* slot_of_token, const int* block_table, int max_pages,
-                                     void* k_cache, void* v_cache, int write_kv, void* stream) {
+                                     void* k_cache, void* v_cache, int write_kv, const void* cos_sin, void* stream) {
     if (T <= 0) return RB_OK;
     if (hd <= 0 || hd % 2 || n_in < 1 || (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > hd)))
         return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
 #define RB_QK_ARGS in, n_in, in_stride, row_stride, q_out, q_stride, T, nq, nkv, hd, q_norm_w, k_norm_w, eps, \
-                   inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages, k_cache, v_cache, write_kv, s
+                   inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages, k_cache, v_cache, write_kv, \
+                   (const float2*)cos_sin, s
     if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<bf, bf, bf>(RB_QK_ARGS);
     if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_F32) return launch_qk<bf, bf, float>(RB_QK_ARGS);
     if (in_dtype == RB_F32 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<float, bf, bf>(RB_QK_ARGS);
@@ -155,4 +248,27 @@ extern "C" int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, lon
     if (in_dtype == RB_F32 && act_dtype == RB_F32 && w_dtype == RB_F32) return launch_qk<float, float, float>(RB_QK_ARGS);
 #undef RB_QK_ARGS
     return RB_ERR_BAD_DTYPE;
+}
+
+// cos and sin of pos * inv_freq[i] for every token of a step, [T][half] pairs (cos, sin): computed
+// once per step with full-precision sincosf and read by every layer's rotation.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int T,
+                                  int half, float2* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx - t * half;
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+    out[idx] = make_float2(cs, sn);
+}
+
+extern "C" int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, void* out, void* stream) {
+    if (T <= 0 || half <= 0) return RB_OK;
+    const long long n = (long long)T * half;
+    if (n > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
+    RB_LAUNCH((rope_table_kernel), dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, positions,
+              inv_freq, T, half, (float2*)out);
+    return RB_OK;
 }

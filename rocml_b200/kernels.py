@@ -79,7 +79,8 @@ def _lib():
         lib.rb_silu_mul.argtypes = [_vp, _i, _i, _ll, _vp, _i, _i, _i, _i, _vp]
         lib.rb_cast.argtypes = [_vp, _i, _vp, _i, _ll, _vp]
         lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f,
-                                              _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp]
+                                              _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp]
+        lib.rb_rope_table.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
         lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _vp]
         lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
                                              _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
@@ -169,8 +170,10 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, n
                        q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                        inv_freq: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
                        slot_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
-                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], write_kv: bool = True):
-    """proj [T, nq*hd (+ 2*nkv*hd)] (or [S, T, ...] partial sums): q normalised and rotated into q_out
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], write_kv: bool = True,
+                       cos_sin: Optional[torch.Tensor] = None):
+    """``cos_sin`` (from rope_table, float32 [T, rot_dim / 2, 2]) replaces the kernel's own sincosf.
+    proj [T, nq*hd (+ 2*nkv*hd)] (or [S, T, ...] partial sums): q normalised and rotated into q_out
     (rows of nq*hd, any row stride; it may be ``proj`` itself); k (normalised, rotated) and v written
     to their pages."""
     width = (nq + (2 * nkv if write_kv else 0)) * hd
@@ -198,8 +201,17 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, n
         q_out.stride(-2), n_tokens, nq, nkv, hd, _ptr(q_norm_w), _ptr(k_norm_w), wd, float(eps), _ptr(inv_freq),
         rot_dim, _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
         None if block_table is None else _i32(block_table, "block_table"), max_pages, _ptr(k_cache), _ptr(v_cache),
-        1 if write_kv else 0, _stream())
+        1 if write_kv else 0, _ptr(cos_sin), _stream())
     _check(rc, "qk_norm_rope_cache")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, n_tokens: int) -> torch.Tensor:
+    """float32 [T, half, 2]: (cos, sin) of positions[t] * inv_freq[i], full-precision sincosf."""
+    half = inv_freq.numel()
+    out = torch.empty((n_tokens, half, 2), dtype=torch.float32, device=inv_freq.device)
+    _check(_lib().rb_rope_table(_i32(positions, "positions"), _ptr(inv_freq), n_tokens, half, _ptr(out), _stream()),
+           "rope_table")
+    return out
 
 
 # ---- matrix products ---------------------------------------------------------------------------------

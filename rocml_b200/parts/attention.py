@@ -90,7 +90,8 @@ class Attention(Mixer):
         kernels.qk_norm_rope_cache(
             proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
             self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
-            view.block_table, view.k, view.v, write_kv=view.writes and not self.shares_cache)
+            view.block_table, view.k, view.v, write_kv=view.writes and not self.shares_cache,
+            cos_sin=self.position.cos_sin(batch))
         attn = torch.empty((T, qd), dtype=act, device=dev)
         window = int(self.window) if self.window else 0
         self.attend(q, attn, batch, view, window)

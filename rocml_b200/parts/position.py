@@ -18,6 +18,9 @@ class NoPosition(PositionEncoding):
         self.inv_freq = None
         self.rot_dim = 0
 
+    def cos_sin(self, batch):
+        return None
+
 
 @register_position("rope_neox")
 class RotaryNeox(PositionEncoding):
@@ -35,6 +38,16 @@ class RotaryNeox(PositionEncoding):
         if not spec.theta > 0:
             raise ConfigError(f"rotary base must be positive, found {spec.theta}")
         self.rot_dim = rot
+        self.theta = float(spec.theta)
         i = torch.arange(rot // 2, dtype=torch.float64)
         inv = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / rot)
         self.inv_freq = inv.to(torch.float32).to(env.device)
+
+    def cos_sin(self, batch):
+        """(cos, sin) of every token's angles for this step, computed once and shared by all the
+        layers that use this encoding with the same table."""
+        from .. import kernels
+        key = ("rope_neox", self.rot_dim, self.theta)      # layers with the same encoding share the table
+        if key not in batch.scratch:
+            batch.scratch[key] = kernels.rope_table(batch.positions, self.inv_freq, batch.n_tokens)
+        return batch.scratch[key]
