@@ -10,7 +10,7 @@ from . import config  # registers the built-in architecture
 from . import parts   # registers the built-in parts
 from .errors import (
     CacheError, CacheFull, ConfigError, ContextOverflow, ExtensionMissing, KernelError,
-    ModelFileMissing, RocmlError, SafetensorsError, UnknownModel, UnsupportedArchitecture, WeightsError,
+    MemoryBudget, ModelFileMissing, RocmlError, SafetensorsError, UnknownModel, UnsupportedArchitecture, WeightsError,
 )
 from .engine import Engine, Model, StepEntry
 from .engine.generate import Completion, GenerateStats, Request, generate
@@ -21,6 +21,6 @@ __version__ = "0.1.0"
 __all__ = [
     "config", "parts", "Engine", "Model", "StepEntry", "Completion", "GenerateStats", "Request",
     "generate", "SamplingParams", "CacheError", "CacheFull", "ConfigError",
-    "ContextOverflow", "ExtensionMissing", "KernelError", "ModelFileMissing", "RocmlError",
+    "ContextOverflow", "ExtensionMissing", "KernelError", "MemoryBudget", "ModelFileMissing", "RocmlError",
     "SafetensorsError", "UnknownModel", "UnsupportedArchitecture", "WeightsError",
 ]

@@ -47,6 +47,24 @@ extern "C" int rb_embedding(const int* ids, const void* table, int table_dtype, 
 // `rows` (optional) picks the source rows; output row i is compact.  One block per output row.
 // Replaces add_inplace_f32 + rmsnorm_f32 (rocml-kernels/kernels/elementwise.hip:7-26,
 // rmsnorm.hip:7-43); product order x * inv_rms * w as there.
+// Four consecutive outputs: one 8- or 16-byte store when the row allows it.
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d, bool vec) {
+    if (vec) *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    else { p[0] = a; p[1] = b; p[2] = c; p[3] = d; }
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d, bool vec) {
+    if (vec) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&lo);
+        raw.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = raw;
+    } else {
+        p[0] = __float2bfloat16_rn(a); p[1] = __float2bfloat16_rn(b);
+        p[2] = __float2bfloat16_rn(c); p[3] = __float2bfloat16_rn(d);
+    }
+}
+
 template <typename OT, typename WT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
                                    int n_delta, size_t delta_stride, const WT* __restrict__ w,
@@ -97,6 +115,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
     const float total = block_sum(ss, red);
     const float inv = rsqrtf(total / (float)H + eps);
     OT* o = out + (size_t)orow * H;
+    const bool out_vec = (((uintptr_t)out | ((size_t)H * sizeof(OT))) & 15) == 0;
     if (vec) {
         const int H4 = H >> 2;
         const float4* rb4 = reinterpret_cast<const float4*>(row_buf);
@@ -104,10 +123,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
         for (int i = threadIdx.x; i < H4; i += blockDim.x) {
             const float4 v = rb4[i];
             if (write_back) r4[i] = v;
-            o[4 * i] = from_f32<OT>(v.x * inv * to_f32(w[4 * i]));
-            o[4 * i + 1] = from_f32<OT>(v.y * inv * to_f32(w[4 * i + 1]));
-            o[4 * i + 2] = from_f32<OT>(v.z * inv * to_f32(w[4 * i + 2]));
-            o[4 * i + 3] = from_f32<OT>(v.w * inv * to_f32(w[4 * i + 3]));
+            store4(o + 4 * i, v.x * inv * to_f32(w[4 * i]), v.y * inv * to_f32(w[4 * i + 1]),
+                   v.z * inv * to_f32(w[4 * i + 2]), v.w * inv * to_f32(w[4 * i + 3]), out_vec);
         }
     } else {
         for (int i = threadIdx.x; i < H; i += blockDim.x) {

@@ -53,6 +53,7 @@ class Engine:
         max_tokens = int(max_tokens)
         if max_slots is None:
             max_slots = max(1, min((max_tokens + 63) // 64, 256))
+        self._check_budget(max_tokens)
         self.cache = SequenceCache(
             model.cache_requirements(), model.reads_cache_of(), max_tokens, max_slots,
             min(model.spec.max_position, max_seq_len or model.spec.max_position), self.env.act_dtype,
@@ -66,6 +67,30 @@ class Engine:
         self._sampler = None
         self._device_tokens = None
         self.graph_kernel_launches = 0  # kernels run by graph replays
+
+    # After the weights are resident: does the cache fit what is left, with head room for a step's
+    # activations?  (The reference's check: rocml/src/forward/mod.rs:145-168, 768 MiB of head room,
+    # rocml/src/budget/mod.rs:37; a step of this engine is wider, so the head room scales with it.)
+    def _check_budget(self, max_tokens: int) -> None:
+        if self.device.type != "cuda":
+            return
+        reqs = [r for r, src in zip(self.model.cache_requirements(), self.model.reads_cache_of())
+                if src is None and hasattr(r, "n_kv_heads")]
+        esz = 4 if self.env.act_dtype == torch.float32 else 2
+        per_token = sum(2 * r.n_kv_heads * r.head_dim * esz for r in reqs)
+        if per_token == 0:
+            return
+        widest = max([self.model.hidden] + [getattr(b.ff, "inter", 0) * 2 for b in self.model.blocks])
+        headroom = (768 << 20) + self.max_step_tokens * (widest * esz * 2 + self.model.hidden * 12)
+        free, total = torch.cuda.mem_get_info(self.device)
+        need = ((max_tokens + 63) // 64 * 64) * per_token
+        if need + headroom > free:
+            from ..errors import MemoryBudget
+            fit = max(0, (free - headroom) // per_token // 64 * 64)
+            raise MemoryBudget(max_tokens, int(fit), (
+                f"{need / 2**30:.1f} GiB of keys and values ({per_token} bytes per token) + "
+                f"{headroom / 2**30:.1f} GiB head room for a step against {free / 2**30:.1f} GiB free of "
+                f"{total / 2**30:.1f} GiB"))
 
     # ---- construction ----------------------------------------------------------------------------
     @staticmethod

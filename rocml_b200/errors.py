@@ -87,6 +87,19 @@ class ContextOverflow(RocmlError):
         super().__init__(f"context overflow: {requested} tokens requested, limit is {limit}")
 
 
+class MemoryBudget(RocmlError):
+    """The cache that was asked for does not fit the device memory that is left once the weights
+    are resident (rocml/src/error.rs:46-54, checked at rocml/src/forward/mod.rs:145-161)."""
+
+    def __init__(self, requested_tokens, suggested_tokens, breakdown):
+        self.requested_tokens = requested_tokens
+        self.suggested_tokens = suggested_tokens
+        super().__init__(
+            f"a cache of {requested_tokens} tokens does not fit the device: {breakdown}; "
+            f"about {suggested_tokens} tokens would"
+        )
+
+
 class KernelError(RocmlError):
     """A CUDA kernel refused its sizes, or the CUDA runtime reported an error."""
 

@@ -71,3 +71,11 @@ def test_sampled_generation_is_reproducible_and_seeded_per_sequence(setup):
     b = eng.generate([p, p], max_new_tokens=12, sampling=sp, stop_tokens=[])
     assert [o.tokens for o in a] == [o.tokens for o in b]
     assert a[0].tokens != a[1].tokens     # same prompt, seeds 4 and 5
+
+
+def test_a_cache_larger_than_the_device_is_refused_with_a_suggestion(setup):
+    from rocml_b200 import Engine, MemoryBudget
+    name, folder, _ = setup
+    with pytest.raises(MemoryBudget) as e:
+        Engine.from_folder(folder, dtype="float32", max_tokens=10 ** 10)
+    assert e.value.suggested_tokens > 0 and "GiB" in str(e.value)
