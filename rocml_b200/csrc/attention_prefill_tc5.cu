@@ -1,0 +1,369 @@
+// Flash attention for bfloat16 prompts over the paged cache on the 5th-generation tensor cores:
+// S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory; Q, K and V tiles
+// arrive by TMA; the softmax runs in registers, one thread per query row (a TMEM lane is a row, so no
+// shuffles are needed for row maxima and sums).  Head size 128.
+//
+// A block takes 128 query tokens of one sequence and one query head and walks the keys page by page
+// (a page of the cache is one 64-key tile).  Roles: warp 0 issues TMA loads (Q once, K in a ring of
+// two, V in a ring of one), warp 1 issues the MMAs, warps 2-5 are the 128 softmax threads.
+// Per tile: S_j = Q K_j^T into one of two TMEM buffers (so the tensor core can already form S_{j+1}
+// while the softmax works on S_j); the softmax threads read their row, scale, mask (causal,
+// inclusive; window), update the running maximum and sum in float32 (base 2), write P as bfloat16
+// into shared memory in the operand layout, and, only when some row's maximum has grown by more than
+// 2^8, rescale the O accumulator in tensor memory (otherwise the stale maximum stays in use, which is
+// exact: numerator and denominator carry the same factor); O += P V_j with V read in its natural
+// [key][dimension] order (MN-major operand).  Two blocks share a multiprocessor (96 KB of shared
+// memory and 256 TMEM columns each), so one block's softmax overlaps the other's MMAs.
+//
+// Same mathematics as the reference's attn_prefill_flash_* (rocml-kernels/kernels/
+// attn_prefill_flash_impl.h:46-159): head h reads key/value head h / g, score = (q.k) * scale, query
+// at position p sees keys 0..p, online softmax, o = sum p v / l.  Every wait is bounded.
+#include "common.cuh"
+#include "sm100.cuh"
+#include "api.h"
+#include <mutex>
+#include <unordered_map>
+
+using namespace sm100;
+
+namespace {
+constexpr int HD = 128;
+constexpr int BMQ = 128;      // query rows per block
+constexpr int BNK = 64;       // keys per tile = one page
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float NEG_BIG = -1e30f;
+constexpr float RESCALE_AT = 8.0f;   // rescale O when a row maximum grew by more than 2^8
+
+// shared memory (bytes): Q 2 x [128][64], K ring 2 x (2 x [64][64]), V 2 x [64][64], P [128][64]
+constexpr int Q_BYTES = 2 * BMQ * 64 * 2;       // 32 KB
+constexpr int KV_TILE = 2 * BNK * 64 * 2;       // 16 KB
+constexpr int P_BYTES = BMQ * BNK * 2;          // 16 KB
+constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_TILE + KV_TILE + P_BYTES + 1024 + 256;
+// tensor memory columns: S0 [0, 64), S1 [64, 128), O [128, 256)
+constexpr int TMEM_COLS = 256;
+
+struct Barriers {
+    uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full, o_done;
+    uint32_t tmem_slot, abort_flag;
+};
+
+__global__ void __launch_bounds__(192, 2)
+attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int o_stride,
+                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
+                             const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
+                             float scale, int window, int* __restrict__ status) {
+    rb::pdl_trigger();
+    rb::pdl_wait();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* Qs = smem;
+    uint8_t* Ks = Qs + Q_BYTES;               // [2 stages][16 KB]
+    uint8_t* Vs = Ks + 2 * KV_TILE;
+    uint8_t* Ps = Vs + KV_TILE;
+    Barriers* bar = (Barriers*)(Ps + P_BYTES);
+
+    const int b = blockIdx.z, head = blockIdx.y;
+    const int slot = seq_slot[b];
+    const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
+    const int m0 = blockIdx.x * BMQ;
+    if (slot < 0 || m0 >= q_len) return;
+    const int len = kv_len[b];
+    const int pos0 = len - q_len;
+    const int kvh = head / (nq / nkv);
+    const int rows_here = min(BMQ, q_len - m0);
+    const int hi = pos0 + m0 + rows_here - 1;
+    const int lo = window > 0 ? max(0, pos0 + m0 - window + 1) : 0;
+    const int kt_first = lo / BNK, kt_last = hi / BNK;
+    const int n_tiles = kt_last - kt_first + 1;
+    const int* table = block_table + (size_t)slot * max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar->q_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&bar->k_full[i], 1); mbar_init(&bar->k_empty[i], 1); mbar_init(&bar->s_full[i], 1); }
+        mbar_init(&bar->v_full, 1);
+        mbar_init(&bar->v_empty, 1);
+        mbar_init(&bar->p_full, 128);
+        mbar_init(&bar->o_done, 1);
+        bar->abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&bar->tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bar->tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&map_q);
+            tma_prefetch_desc(&map_k);
+            tma_prefetch_desc(&map_v);
+            mbar_arrive_expect_tx(&bar->q_full, Q_BYTES);
+            tma_load_2d(Qs, &map_q, head * HD, q0 + m0, &bar->q_full);
+            tma_load_2d(Qs + Q_BYTES / 2, &map_q, head * HD + 64, q0 + m0, &bar->q_full);
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int page = table[kt_first + j];
+                const int row = ((page < 0 ? 0 : page) * nkv + kvh) * RB_PAGE;
+                const int s = j & 1;
+                ok = mbar_wait(&bar->k_empty[s], ((j >> 1) & 1) ^ 1);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&bar->k_full[s], KV_TILE);
+                tma_load_2d(Ks + s * KV_TILE, &map_k, 0, row, &bar->k_full[s]);
+                tma_load_2d(Ks + s * KV_TILE + KV_TILE / 2, &map_k, 64, row, &bar->k_full[s]);
+                ok = mbar_wait(&bar->v_empty, (j & 1) ^ 1);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&bar->v_full, KV_TILE);
+                tma_load_2d(Vs, &map_v, 0, row, &bar->v_full);
+                tma_load_2d(Vs + KV_TILE / 2, &map_v, 64, row, &bar->v_full);
+            }
+            if (!ok) { atomicExch(status, RB_ERR_TIMEOUT); atomicExch(&bar->abort_flag, 1u); }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16_f32(BMQ, BNK);          // S = Q K^T: both K-major
+            constexpr uint32_t idesc_o = idesc_bf16_f32_b_mn(BMQ, HD);      // O += P V: V is MN-major
+            const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps), v_addr = smem_u32(Vs);
+            auto issue_s = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(&bar->k_full[s], (j >> 1) & 1)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(Ks + s * KV_TILE);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    // dimension block k / 4 (64 dimensions each), 32 bytes per step inside it
+                    const uint32_t qo = (k >> 2) * (Q_BYTES / 2) + (k & 3) * 32;
+                    const uint32_t ko = (k >> 2) * (KV_TILE / 2) + (k & 3) * 32;
+                    mma_bf16(tmem_base + s * BNK, smem_desc_sw128(q_addr + qo), smem_desc_sw128(k_addr + ko), idesc_s,
+                             k > 0 ? 1u : 0u);
+                }
+                mma_commit(&bar->k_empty[s]);
+                mma_commit(&bar->s_full[s]);
+                return true;
+            };
+            bool ok = mbar_wait(&bar->q_full, 0);
+            if (ok) { tc_fence_after(); ok = issue_s(0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
+                ok = mbar_wait(&bar->p_full, j & 1) && mbar_wait(&bar->v_full, j & 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < BNK / 16; ++k) {
+                    // A = P [128 rows][64 keys], K-major: 32 bytes per 16 keys.  B = V [64 keys][128 dims],
+                    // MN-major: 64-dimension blocks 8 KB apart, groups of 8 keys 1 KB apart, 16 keys = 2 KB.
+                    mma_bf16(tmem_base + 2 * BNK, smem_desc_sw128(p_addr + k * 32),
+                             smem_desc_sw128_ex(v_addr + k * 2048, KV_TILE / 2, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(&bar->v_empty);
+                mma_commit(&bar->o_done);
+            }
+            if (!ok) {
+                atomicExch(status, RB_ERR_TIMEOUT);
+                atomicExch(&bar->abort_flag, 1u);
+                mma_commit(&bar->s_full[0]); mma_commit(&bar->s_full[1]); mma_commit(&bar->o_done);
+            }
+        }
+    } else {
+        // softmax: thread r owns query row r (TMEM lane r)
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int row_pos = pos0 + m0 + r;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const float sl2 = scale * LOG2E;
+        float m_used = NEG_BIG, l_sum = 0.f;
+        bool alive = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            alive = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[s], (j >> 1) & 1)) && *(volatile uint32_t*)&bar->abort_flag == 0;
+            if (!alive) break;
+            tc_fence_after();
+            const int key0 = (kt_first + j) * BNK;
+            float sv[BNK];
+#pragma unroll
+            for (int c = 0; c < BNK / 16; ++c) tmem_ld16(lane_base + s * BNK + c * 16, sv + c * 16);
+            float mx = NEG_BIG;
+#pragma unroll
+            for (int i = 0; i < BNK; ++i) {
+                const int key = key0 + i;
+                const bool ok = key <= row_pos && (window <= 0 || key > row_pos - window);
+                sv[i] = ok ? sv[i] * sl2 : -INFINITY;
+                mx = fmaxf(mx, sv[i]);
+            }
+            // the maximum in use only moves when it would otherwise let p exceed 2^8
+            const bool grow = mx - m_used > RESCALE_AT;
+            const float m_new = grow ? mx : m_used;
+            const float alpha = exp2f(m_used - m_new);          // 1 when the maximum stays
+            m_used = m_new;
+            l_sum *= alpha;
+            uint32_t packed[BNK / 2];
+#pragma unroll
+            for (int i = 0; i < BNK; i += 2) {
+                const float p0 = exp2f(sv[i] - m_used), p1 = exp2f(sv[i + 1] - m_used);
+                l_sum += p0 + p1;
+                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                packed[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            // before P_j replaces P_{j-1} and before O is touched, the MMAs of tile j-1 must be done
+            if (j > 0) {
+                alive = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, (j - 1) & 1));
+                if (!alive) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+                    for (int c = 0; c < HD / 16; ++c) {
+                        float ov[16];
+                        tmem_ld16(lane_base + 2 * BNK + c * 16, ov);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ov[i] *= alpha;
+                        tmem_st16(lane_base + 2 * BNK + c * 16, ov);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // P row r: 128 bytes = 8 chunks of 16 bytes, chunk c stored at c ^ (r & 7) (128-byte swizzle)
+            uint8_t* prow = Ps + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
+                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+            // the last tile may reach past the sequence's end: what lies there in the page is not ours, and
+            // a stale NaN times a zero probability would still poison the sum, so those V rows are zeroed
+            // (after the tile has landed, before the product reads it)
+            if (j == n_tiles - 1) {
+                const int valid = min(BNK, len - key0);
+                if (valid < BNK) {
+                    alive = __all_sync(0xffffffffu, mbar_wait(&bar->v_full, j & 1));
+                    if (!alive) break;
+                    for (int idx = threadIdx.x - 64; idx < (BNK - valid) * 16; idx += 128) {
+                        const int vr = valid + idx / 16, ch = idx % 16;      // row vr, 16-byte chunk ch of its 256 bytes
+                        *reinterpret_cast<uint4*>(Vs + (ch >> 3) * (KV_TILE / 2) + vr * 128 + (((ch & 7) ^ (vr & 7)) << 4)) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                }
+            }
+            tc_fence_before();
+            fence_proxy_async();                 // shared-memory writes become visible to the tensor core
+            mbar_arrive(&bar->p_full);
+        }
+        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, (n_tiles - 1) & 1));
+        if (alive) {
+            tc_fence_after();
+            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            __nv_bfloat16* orow = out + (size_t)(q0 + m0 + r) * o_stride + (size_t)head * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 16; ++c) {
+                float ov[16];
+                tmem_ld16(lane_base + 2 * BNK + c * 16, ov);
+                if (r < rows_here) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(ov[2 * i] * inv, ov[2 * i + 1] * inv);
+                        w[i] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    reinterpret_cast<uint4*>(orow + c * 16)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    reinterpret_cast<uint4*>(orow + c * 16)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(status, RB_ERR_TIMEOUT);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// [rows, cols] bf16 with row stride ld (elements), read in boxes of box_rows x 64 columns, 128-byte swizzle.
+int make_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+    struct Key {
+        const void* p; long long r, c, l; int b;
+        bool operator==(const Key& o) const { return p == o.p && r == o.r && c == o.c && l == o.l && b == o.b; }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const {
+            return ((((size_t)k.p * 1000003u ^ (size_t)k.r) * 1000003u ^ (size_t)k.c) * 1000003u ^ (size_t)k.l) * 31u + k.b;
+        }
+    };
+    static std::mutex mu;
+    static std::unordered_map<Key, CUtensorMap, Hash> cache;
+    Key key{ptr, rows, cols, ld, box_rows};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return RB_OK; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return RB_ERR_NO_DRIVER_FN;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return RB_ERR_BAD_SIZE;
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 65536) cache.clear();
+    cache[key] = *out;
+    return RB_OK;
+}
+}  // namespace
+
+// q rows [T, q_stride] bfloat16 (T = tokens of the step), caches [n_pages, nkv, 64, 128].  Head size 128
+// only; RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).
+extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride,
+                                        const void* k_cache, const void* v_cache, int n_pages,
+                                        const int* block_table, int max_pages, const int* seq_slot,
+                                        const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv,
+                                        int hd, float scale, int window, int* status, void* stream) {
+    if (B <= 0 || max_q_len <= 0 || T <= 0) return RB_OK;
+    if (hd != HD || nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15) ||
+        (q_stride % 8) || (o_stride % 8))
+        return RB_ERR_BAD_ALIGN;
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = make_map(q, T, (long long)nq * HD, q_stride, BMQ, &mq)) != RB_OK) return rc;
+    const long long cache_rows = (long long)n_pages * nkv * RB_PAGE;
+    if ((rc = make_map(k_cache, cache_rows, HD, HD, BNK, &mk)) != RB_OK) return rc;
+    if ((rc = make_map(v_cache, cache_rows, HD, HD, BNK, &mv)) != RB_OK) return rc;
+    auto k = attention_prefill_tc5_kernel;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    dim3 grid((max_q_len + BMQ - 1) / BMQ, nq, B);
+    if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
+    RB_LAUNCH((k), grid, dim3(192), SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
+              block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, status);
+    return RB_OK;
+}

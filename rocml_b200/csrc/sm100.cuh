@@ -152,6 +152,36 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// General shared-memory matrix descriptor with the 128-byte swizzle: leading and stride byte offsets
+// as the operand's layout needs them (K-major: LBO unused, SBO = 1024; MN-major: LBO = distance
+// between 64-element blocks along MN, SBO = distance between groups of 8 rows along K).
+__device__ __forceinline__ uint64_t smem_desc_sw128_ex(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor with B in MN-major order (its N index contiguous in shared memory).
+__host__ __device__ constexpr uint32_t idesc_bf16_f32_b_mn(int M, int N) {
+    return idesc_bf16_f32(M, N) | (1u << 16);
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane, written from registers.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+          "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+          "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // ---- pairs of CTAs (cta_group::2) -------------------------------------------------------------------
 // Two CTAs of a cluster act as one MMA unit: the MMA of the even CTA (the leader) reads A and B
 // halves from BOTH CTAs' shared memory (same offsets) and writes each CTA's 128 accumulator rows

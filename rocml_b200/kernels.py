@@ -88,6 +88,8 @@ def _lib():
         lib.rb_argmax.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp]
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                              _f, _i, _vp]
+        lib.rb_attention_prefill_tc5.argtypes = [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i,
+                                                 _i, _i, _i, _f, _i, _vp, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
                                             _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
@@ -248,6 +250,27 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window), int(chunk),
         int(n_chunks), _ptr(part_acc), _ptr(part_ml), _stream())
     _check(rc, "attention_generic")
+
+
+def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                          n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0) -> bool:
+    """bfloat16 flash attention with tcgen05 (accumulators in tensor memory, TMA loads), head size 128.
+    Returns False when the kernel does not take the head size or the alignment."""
+    if hd != 128 or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
+            q.stride(-1) != 1 or out.stride(-1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        return False
+    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+        raise KernelError("attention_prefill_tc5: cache must be [pages, nkv, 64, hd]")
+    rc = _lib().rb_attention_prefill_tc5(
+        _ptr(q), q.stride(0), n_tokens, _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0],
+        _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
+        _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window),
+        _ptr(status_word(q.device)), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "attention_prefill_tc5")
+    return True
 
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -123,6 +123,10 @@ class Attention(Mixer):
                 kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, self.nq, self.hd,
                                         chunk, n_chunks, window)
                 return
+        if kernels.attention_prefill_tc5(q, batch.n_tokens, out, view.k, view.v, view.block_table, batch.seq_slot,
+                                         batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv,
+                                         self.hd, self.scale, window):
+            return
         if kernels.attention_prefill(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                      batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,
                                      self.scale, window):

@@ -23,7 +23,7 @@ def rel_err(got, want):
     return float(((got - want).abs() / scale).max())
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def model_folder(request, tmp_path_factory):
     name = request.param
     folder = tmp_path_factory.mktemp(f"tiny_{name}")

@@ -7,7 +7,7 @@ from tiny_models import CONFIGS, prompt, write_model
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def setup(request, tmp_path_factory):
     from plain_qwen3 import PlainQwen3
     name = request.param

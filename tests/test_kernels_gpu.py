@@ -284,6 +284,27 @@ def test_attention_prefill_tensor_cores(case):
     assert err < 2e-2, err
 
 
+@pytest.mark.parametrize("case", [1, 2])
+def test_attention_prefill_tcgen05(case):
+    """The tensor-memory kernel (head size 128) on the same cases, and on a longer one."""
+    from rocml_b200 import kernels
+    lens, q_lens, nq, nkv, hd, window = PRE_CASES[case]
+    dtype = torch.bfloat16
+    spike = (0, 2) if case == 1 else None
+    ks, vs, qs, kc, vc, meta = paged_case(20 + case, lens, q_lens, nq, nkv, hd, dtype, spike)
+    scale = 1.0 / math.sqrt(hd)
+    want = reference_attention(ks, vs, qs, window, scale)
+    q = torch.cat(qs, 0).reshape(-1, nq * hd).to(dtype).to(DEV)
+    out = torch.full_like(q, float("nan"))
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    kc, vc = kc.to(DEV), vc.to(DEV)      # beyond a sequence's end the pages hold NaN: it must not matter
+    assert kernels.attention_prefill_tc5(q, q.shape[0], out, kc, vc, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
+                                         len(lens), max(q_lens), nq, nkv, hd, scale, window or 0)
+    kernels.check_status(DEV)
+    err = (out.cpu().double().reshape(want.shape) - want).abs().max().item()
+    assert err < 2e-2, err
+
+
 DEC_CASES = [
     # lens, nq, nkv, hd, window
     ([700, 1, 129, 64, 128], 32, 8, 128, None),

@@ -38,7 +38,15 @@ TINY_D = {
     "max_position_embeddings": 512, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
     "tie_word_embeddings": False, "attention_bias": False, "hidden_act": "silu",
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# E has a head size of 128, which the tensor-memory attention kernel takes, and a window on one layer.
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "hidden_size": 192, "intermediate_size": 256, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 389,
+    "max_position_embeddings": 640, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "attention_bias": False, "hidden_act": "silu",
+    "use_sliding_window": True, "sliding_window": 150, "layer_types": ["full_attention", "sliding_attention"],
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def write_model(folder, cfg_dict, seed, std=None):
