@@ -66,7 +66,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int b = blockIdx.z, head = blockIdx.y;
     const int slot = seq_slot[b];
     const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
-    const int m0 = blockIdx.x * BMQ;
+    // late query tiles see the most keys: they are scheduled first so that the grid's tail is short
+    const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * BMQ;
     if (slot < 0 || m0 >= q_len) return;
     const int len = kv_len[b];
     const int pos0 = len - q_len;
@@ -188,12 +189,19 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #pragma unroll
             for (int c = 0; c < BNK / 16; ++c) tmem_ld16(lane_base + s * BNK + c * 16, sv + c * 16);
             float mx = NEG_BIG;
+            // a tile that every row of this warp sees whole needs no mask
+            const int warp_first_pos = pos0 + m0 + quarter * 32;
+            if (key0 + BNK - 1 <= warp_first_pos && (window <= 0 || key0 > warp_first_pos + 31 - window)) {
 #pragma unroll
-            for (int i = 0; i < BNK; ++i) {
-                const int key = key0 + i;
-                const bool ok = key <= row_pos && (window <= 0 || key > row_pos - window);
-                sv[i] = ok ? sv[i] * sl2 : -INFINITY;
-                mx = fmaxf(mx, sv[i]);
+                for (int i = 0; i < BNK; ++i) { sv[i] *= sl2; mx = fmaxf(mx, sv[i]); }
+            } else {
+#pragma unroll
+                for (int i = 0; i < BNK; ++i) {
+                    const int key = key0 + i;
+                    const bool ok = key <= row_pos && (window <= 0 || key > row_pos - window);
+                    sv[i] = ok ? sv[i] * sl2 : -INFINITY;
+                    mx = fmaxf(mx, sv[i]);
+                }
             }
             // the maximum in use only moves when it would otherwise let p exceed 2^8
             const bool grow = mx - m_used > RESCALE_AT;
