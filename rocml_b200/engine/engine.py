@@ -43,6 +43,14 @@ def _bucket(n: int, floor: int = 1) -> int:
     return b
 
 
+def _ctx_bucket(n: int) -> int:
+    """Context length a captured decode graph is sized for: the next multiple of 256 (of 1024 beyond
+    4096).  Fine steps matter: decode attention deals its blocks out over the bucket, and blocks
+    that lie past the sequences' real end do nothing."""
+    step = 256 if n <= 4096 else 1024
+    return max(step, -(-n // step) * step)
+
+
 class Engine:
     def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
                  max_step_tokens: int = 4096, use_graphs: bool = True, max_seq_len: Optional[int] = None):
@@ -234,7 +242,7 @@ class Engine:
     def _run_graph(self, packed, host, T, B, W) -> Optional[torch.Tensor]:
         kv_len = packed[4]
         b_pad = _bucket(B)
-        ctx_pad = _bucket(max(kv_len), 256)
+        ctx_pad = _ctx_bucket(max(kv_len))
         key = (b_pad, ctx_pad)
         g = self._graphs.get(key)
         if g is None:

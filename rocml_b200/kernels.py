@@ -293,13 +293,20 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     return True
 
 
-def decode_split(n_seqs: int, n_kv_groups: int, n_pages: int):
-    """(blocks per sequence, pages per block) for decode attention: enough blocks to keep every
-    multiprocessor busy about four times over, no more, so that a large batch walks several pages
-    per block (one partial result and one merge for all of them) and a single sequence still
-    spreads over the device."""
-    want = -(-4 * 148 // max(1, n_seqs * n_kv_groups))
-    blocks = max(1, min(n_pages, want))
+_sm_count = {}
+
+
+def decode_split(n_seqs: int, n_kv_groups: int, n_pages: int, device=0):
+    """(blocks per sequence, pages per block) for decode attention.  Three blocks of the kernel fit a
+    multiprocessor; the split is the finest that still runs as ONE wave (blocks per sequence times
+    sequences times key/value head groups within the resident slots), because a second, partly filled
+    wave costs a whole block's latency.  A large batch therefore walks many pages per block (one
+    partial result and one merge for all of them) and a single sequence spreads over the device."""
+    key = torch.device(device).index or 0
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    slots = 3 * _sm_count[key]
+    blocks = max(1, min(n_pages, slots // max(1, n_seqs * n_kv_groups)))
     ppb = -(-n_pages // blocks)
     return -(-n_pages // ppb), ppb
 

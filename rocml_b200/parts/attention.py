@@ -105,7 +105,7 @@ class Attention(Mixer):
             T = batch.n_tokens
             n_pages = max(1, (batch.max_kv_len + chunk - 1) // chunk)
             groups = self.nkv * ((self.nq // self.nkv + 15) // 16)
-            n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages)
+            n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages, q.device)
             acc = ml = None
             if n_pages > 1:
                 acc = torch.empty((T, self.nq, n_pages, self.hd), dtype=torch.float32, device=q.device)
