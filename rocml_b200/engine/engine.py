@@ -286,20 +286,35 @@ class Engine:
     def capacity_slots(self) -> int:
         return self.cache.max_slots
 
-    def run(self, slots, tokens, params, rngs, histories) -> List[int]:
-        """Step the sequences with their next tokens, sample one token each on the GPU, and
-        bring the token ids (nothing else) back to the host."""
-        logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)])
+    def launch(self, slots, tokens, params, rngs, histories, feed_from=None):
+        """Enqueue a step of the sequences with their next tokens and the sampling of one token
+        each, and return a handle at once.  With ``feed_from`` (the handle of the step before,
+        over the same sequences in the same order) the next tokens are the ones that step
+        sampled, taken on the device: ``tokens`` is not read."""
+        device_tokens = None
+        if feed_from is not None:
+            if feed_from.n != len(slots):
+                raise RocmlError("feed_from must hold one token for each sequence of the step")
+            tokens = [[0]] * len(slots)
+            device_tokens = feed_from.device_tokens
+        logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)], device_tokens=device_tokens)
         if self._sampler is None:
             from ..sampling import Sampler
             self._sampler = Sampler(self.device, max_batch=max(self.cache.max_slots, 1))
-        out = self._sampler.sample(logits, params, rngs, histories)
         from .. import kernels
-        kernels.check_status(self.device)
-        return out
+        return self._sampler.launch(logits, params, rngs, histories, status=kernels.status_word(self.device))
+
+    def collect(self, handle) -> List[int]:
+        """Wait for a launched step and bring its token ids (nothing else) back to the host."""
+        return self._sampler.collect(handle)
+
+    def run(self, slots, tokens, params, rngs, histories) -> List[int]:
+        """Step the sequences with their next tokens, sample one token each on the GPU, and
+        bring the token ids back to the host."""
+        return self.collect(self.launch(slots, tokens, params, rngs, histories))
 
     def generate(self, prompts, max_new_tokens: int = 64, sampling=None, stop_tokens=None,
-                 ignore_eos: bool = False, max_batch: int = 64, on_token=None, stats=None):
+                 ignore_eos: bool = False, max_batch: int = 64, on_token=None, stats=None, run_ahead: bool = True):
         """Generate for a list of prompts (token id lists).  Returns a list of Completion.
         ``sampling`` is one SamplingParams for all or a list; stop tokens default to the model's."""
         from ..sampling import SamplingParams
@@ -309,7 +324,7 @@ class Engine:
         per = sampling if isinstance(sampling, (list, tuple)) else [sampling] * len(prompts)
         reqs = [Request(list(p), max_new_tokens, sp, stop_tokens, ignore_eos) for p, sp in zip(prompts, per)]
         return generate(self, reqs, default_stop=self.model.spec.stop_tokens, max_batch=max_batch,
-                        on_token=on_token, stats=stats)
+                        on_token=on_token, stats=stats, run_ahead=run_ahead)
 
     # ---- facts for measurement --------------------------------------------------------------------------------
     def kv_bytes_per_token(self) -> int:

@@ -6,6 +6,12 @@ A sequence ends on a stop token (which is not part of its output), at its token 
 at the end of the context; its slot goes back at once and the batch carries on with the
 rest.  When a batch is finished the next one starts, until every request is served.
 
+While a step runs, the loop may already enqueue the step after it, fed on the device with the
+tokens the running step is about to sample: the host reads each step's tokens one step late,
+and its own work hides behind the GPU's.  It runs ahead only when every sequence of the step
+is sure to go on as far as budget and context decide; a stop token met meanwhile ends its
+sequence as always, and the token that was computed ahead for it is dropped.
+
 The decisions (who is batched with whom, when a sequence ends, what the next step holds) are
 plain host logic over an ``Executor``; the engine is one executor, a scripted fake in the CPU
 tests is another.  The reference's loop does the same for a single sequence: prefill, then
@@ -61,7 +67,8 @@ class GenerateStats:
 
 
 class Executor(Protocol):
-    """What the loop needs from an engine."""
+    """What the loop needs from an engine.  ``launch`` and ``collect`` are optional: an executor
+    that has them lets the loop run one step ahead."""
 
     max_seq_len: int
 
@@ -72,6 +79,25 @@ class Executor(Protocol):
     def run(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], params: Sequence[SamplingParams],
             rngs: Sequence[XorShift64Star], histories: Sequence[Sequence[int]]) -> List[int]:
         """Step the given sequences with the given next tokens and sample one token each."""
+
+    # def launch(self, slots, tokens, params, rngs, histories, feed_from=None) -> handle
+    #     the same, enqueued only; with feed_from (the handle of the step before, same sequences,
+    #     same order) the next tokens are that step's samples and ``tokens`` is not read
+    # def collect(self, handle) -> List[int]
+
+
+class _Sync:
+    """launch/collect over an executor that only has ``run``."""
+
+    def __init__(self, executor):
+        self.run = executor.run
+
+    def launch(self, slots, tokens, params, rngs, histories, feed_from=None):
+        return self.run(slots, tokens, params, rngs, histories)
+
+    @staticmethod
+    def collect(handle):
+        return handle
 
 
 def _pages(n: int) -> int:
@@ -119,9 +145,10 @@ def decide(token: int, n_generated: int, max_new_tokens: int, length_after: int,
 
 def generate(executor: Executor, requests: Sequence[Request], default_stop: Iterable[int] = (),
              max_batch: int = 64, on_token: Optional[Callable[[int, int], bool]] = None,
-             stats: Optional[GenerateStats] = None) -> List[Completion]:
+             stats: Optional[GenerateStats] = None, run_ahead: bool = True) -> List[Completion]:
     """Serve every request; ``on_token(request index, token)`` may return True to end that
-    sequence after the token (the reference's stop callback, resumed.rs:220-230)."""
+    sequence after the token (the reference's stop callback, resumed.rs:220-230).  With
+    ``run_ahead`` off every step is read before the next is enqueued; the tokens are the same."""
     stats = stats if stats is not None else GenerateStats()
     default_stop = set(default_stop)
     limit = executor.max_seq_len
@@ -133,6 +160,8 @@ def generate(executor: Executor, requests: Sequence[Request], default_stop: Iter
             raise RocmlError(f"request {i}: prompt of {len(r.prompt)} tokens exceeds the context of {limit}")
         needs.append(min(len(r.prompt) + max(r.max_new_tokens, 0), limit))
     results: List[Optional[Completion]] = [None] * len(requests)
+    pipelined = run_ahead and hasattr(executor, "launch") and hasattr(executor, "collect")
+    ex = executor if pipelined else _Sync(executor)
     for batch in plan_batches(needs, max_batch, executor.capacity_tokens(), executor.capacity_slots()):
         stats.batches += 1
         live = []
@@ -142,26 +171,31 @@ def generate(executor: Executor, requests: Sequence[Request], default_stop: Iter
                 results[i] = Completion([], "length", len(r.prompt))
                 continue
             stops = default_stop if r.stop_tokens is None else set(r.stop_tokens)
-            live.append({"i": i, "req": r, "slot": executor.new_sequence(), "out": [],
+            live.append({"i": i, "req": r, "slot": executor.new_sequence(), "out": [], "done": False,
                          "history": list(r.prompt), "stops": stops,
                          "rng": XorShift64Star(r.sampling.seed + j), "next": list(r.prompt)})
+        if not live:
+            continue
+
+        def launch(seqs, feed_from=None):
+            return ex.launch([s["slot"] for s in seqs], [s["next"] for s in seqs],
+                             [s["req"].sampling for s in seqs], [s["rng"] for s in seqs],
+                             [s["history"] for s in seqs], feed_from=feed_from)
+
+        flying, handle = live, launch(live)      # the step whose tokens are read next
         first = True
-        while live:
+        while flying:
             t0 = time.perf_counter()
-            tokens = executor.run([s["slot"] for s in live], [s["next"] for s in live],
-                                  [s["req"].sampling for s in live], [s["rng"] for s in live],
-                                  [s["history"] for s in live])
-            dt = time.perf_counter() - t0
-            stats.step_batch_sizes.append(len(live))
-            if first:
-                stats.prefill_seconds += dt
-                stats.prompt_tokens += sum(len(s["next"]) for s in live)
-                first = False
-            else:
-                stats.decode_seconds += dt
-                stats.decode_tokens += len(live)
+            ahead = None
+            if pipelined and all(_goes_on_for_sure(s, limit) for s in flying):
+                ahead = launch(flying, feed_from=handle)
+            tokens = ex.collect(handle)
             still = []
-            for s, tok in zip(live, tokens):
+            n_read = 0
+            for s, tok in zip(flying, tokens):
+                if s["done"]:
+                    continue                      # it ended while this step was already on its way
+                n_read += 1
                 r = s["req"]
                 length_after = len(s["history"]) + 1
                 emit, reason = decide(tok, len(s["out"]), r.max_new_tokens, length_after, limit,
@@ -175,7 +209,34 @@ def generate(executor: Executor, requests: Sequence[Request], default_stop: Iter
                     s["next"] = [tok]
                     still.append(s)
                 else:
+                    s["done"] = True
                     executor.release(s["slot"])
                     results[s["i"]] = Completion(s["out"], reason, len(r.prompt))
-            live = still
+            if ahead is not None and not still:
+                ex.collect(ahead)                 # everyone ended: nothing of that step is kept
+                ahead = None
+            dt = time.perf_counter() - t0
+            stats.step_batch_sizes.append(n_read)
+            if first:
+                stats.prefill_seconds += dt
+                stats.prompt_tokens += sum(len(requests[s["i"]].prompt) for s in flying)
+                first = False
+            else:
+                stats.decode_seconds += dt
+                stats.decode_tokens += n_read
+            if ahead is not None:
+                handle = ahead                    # same rows; ended ones are skipped when it is read
+            elif still:
+                flying, handle = still, launch(still)
+            else:
+                flying = []
     return results
+
+
+def _goes_on_for_sure(s, limit: int) -> bool:
+    """Whether the sequence takes another step after the token now being sampled, as far as
+    budget and context decide (a stop token can still end it).  Sequences with a repeat penalty
+    never run ahead: the penalty reads the history on the host, which is one token behind."""
+    if s["done"] or s["req"].sampling.repeat_penalty is not None:
+        return False
+    return len(s["out"]) + 1 < s["req"].max_new_tokens and len(s["history"]) + 1 <= limit

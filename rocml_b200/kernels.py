@@ -46,7 +46,8 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return _vp(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of torch's current stream on the current device, without building a Stream object
+    return _vp(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 launch_count = 0  # kernel launches issued through this module (graph replays are counted by the engine)
@@ -406,14 +407,22 @@ def status_word(device) -> torch.Tensor:
     return _status[key]
 
 
+def raise_for_status(value: int, device=None) -> None:
+    """Raise if ``value``, a copy of a device's status word, records a failure; the word itself
+    is cleared so that the next step starts clean."""
+    if value != 0:
+        key = torch.device(device).index or 0 if device is not None else None
+        for k, word in _status.items():
+            if key is None or k == key:
+                word.zero_()
+        raise KernelError(f"a kernel reported failure: {_CODES.get(value, 'code ' + str(value))} (code {value})")
+
+
 def check_status(device) -> None:
     """Read the device's status word (this synchronises) and raise if a kernel recorded a failure."""
     key = torch.device(device).index or 0
     if key in _status:
-        v = int(_status[key].item())
-        if v != 0:
-            _status[key].zero_()
-            raise KernelError(f"a kernel reported failure: {_CODES.get(v, 'code ' + str(v))} (code {v})")
+        raise_for_status(int(_status[key].item()), device)
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,

@@ -79,3 +79,30 @@ def test_a_cache_larger_than_the_device_is_refused_with_a_suggestion(setup):
     with pytest.raises(MemoryBudget) as e:
         Engine.from_folder(folder, dtype="float32", max_tokens=10 ** 10)
     assert e.value.suggested_tokens > 0 and "GiB" in str(e.value)
+
+
+def test_running_one_step_ahead_gives_the_same_tokens(setup):
+    """The loop enqueues a step before it has read the one before, feeding the sampled ids back
+    on the device.  With it and without it the tokens are the same: greedy and sampled, with
+    stop tokens that end sequences while a step computed ahead for them is on its way, and
+    over batches that reuse the slots."""
+    from rocml_b200 import Engine, Request, SamplingParams, generate
+    name, folder, plain = setup
+    vocab = CONFIGS[name]["vocab_size"]
+    prompts = [prompt(120 + i, n, vocab) for i, n in enumerate([7, 30, 2, 19, 64, 5])]
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 12, max_slots=3)
+    greedy = [Request(p, 12, stop_tokens=[]) for p in prompts]
+    base = generate(eng, greedy, max_batch=3, run_ahead=False)
+    assert [o.tokens for o in generate(eng, greedy, max_batch=3)] == [o.tokens for o in base]
+    stops = [o.tokens[3 + i % 4] for i, o in enumerate(base)]
+    stopped = [Request(p, 12, stop_tokens=[s]) for p, s in zip(prompts, stops)]
+    a = generate(eng, stopped, max_batch=3, run_ahead=False)
+    b = generate(eng, stopped, max_batch=3)
+    assert [(o.tokens, o.finish_reason) for o in a] == [(o.tokens, o.finish_reason) for o in b]
+    assert any(o.finish_reason == "stop" for o in a)
+    sampled = [Request(p, 12, SamplingParams(0.9, top_k=20, top_p=0.95, seed=4), stop_tokens=[]) for p in prompts]
+    a = generate(eng, sampled, max_batch=3, run_ahead=False)
+    b = generate(eng, sampled, max_batch=3)
+    assert [o.tokens for o in a] == [o.tokens for o in b]
+    eng.cache.check_invariants()
+    assert eng.cache.slots.n_held == 0

@@ -116,3 +116,77 @@ def test_each_sequence_gets_its_own_seed():
     ex = SeedSpy()
     generate(ex, [Request([1], 1, SamplingParams(0.8, seed=5)), Request([2], 1, SamplingParams(0.8, seed=5))])
     assert ex.seeds == [5, 6]
+
+
+class Pipelined(Scripted):
+    """The same script with launch/collect: the loop may enqueue a step before it has read the
+    one before.  Checks what that is allowed to assume."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.open = []          # handles launched and not yet collected, oldest first
+        self.fed = 0
+
+    def launch(self, slots, tokens, params, rngs, histories, feed_from=None):
+        if feed_from is None:
+            assert not self.open, "host tokens for a step while an earlier step is unread"
+            out = Scripted.run(self, slots, tokens, params, rngs, histories)
+        else:
+            assert self.open and feed_from is self.open[-1], "fed from a step that is not the latest"
+            assert list(feed_from["slots"]) == list(slots), "fed step must keep sequences and order"
+            assert len(self.open) == 1, "more than one step ahead"
+            self.fed += 1
+            self.calls.append([(s, ["fed"]) for s in slots])
+            out = []
+            for s in slots:
+                assert s in self.state and self.state[s] is not None
+                self.state[s] += 1
+                out.append(self.state[s])
+        h = {"slots": list(slots), "out": out}
+        self.open.append(h)
+        return h
+
+    def collect(self, handle):
+        assert self.open and handle is self.open[0], "steps are read in the order they were launched"
+        self.open.pop(0)
+        return handle["out"]
+
+
+def test_running_ahead_changes_no_result():
+    import random
+    rnd = random.Random(3)
+    for trial in range(40):
+        reqs = []
+        for _ in range(rnd.randint(1, 7)):
+            first = rnd.randint(1, 50) * 100
+            stop = first + rnd.randint(1, 12)
+            reqs.append(Request([first] + [1] * rnd.randint(0, 5), rnd.randint(0, 9),
+                                stop_tokens=[stop] if rnd.random() < 0.6 else None,
+                                ignore_eos=rnd.random() < 0.2))
+        cb = (lambda i, t: t % 7 == 0) if trial % 3 == 0 else None
+        a, b = Scripted(slots=3, max_seq_len=12), Pipelined(slots=3, max_seq_len=12)
+        sa, sb = GenerateStats(), GenerateStats()
+        out_a = generate(a, reqs, max_batch=3, on_token=cb, stats=sa)
+        out_b = generate(b, reqs, max_batch=3, on_token=cb, stats=sb)
+        assert [(c.tokens, c.finish_reason) for c in out_a] == [(c.tokens, c.finish_reason) for c in out_b]
+        assert not b.state and not b.open and sorted(a.released) == sorted(b.released)
+        assert (sa.prompt_tokens, sa.decode_tokens, sa.batches) == (sb.prompt_tokens, sb.decode_tokens, sb.batches)
+        out_c = generate(Pipelined(slots=3, max_seq_len=12), reqs, max_batch=3, on_token=cb, run_ahead=False)
+        assert [c.tokens for c in out_c] == [c.tokens for c in out_a]
+
+
+def test_running_ahead_feeds_on_the_device_and_stops_for_a_penalty():
+    ex = Pipelined()
+    out = generate(ex, [Request([10], 6), Request([20, 1], 6)])
+    assert [c.tokens for c in out] == [[11, 12, 13, 14, 15, 16], [21, 22, 23, 24, 25, 26]]
+    # prompts from the host, then every further step fed on the device; the last token needs no step
+    assert ex.fed == 5 and ex.calls[0][1][1] == [20, 1] and all(t == ["fed"] for c in ex.calls[1:] for _, t in c)
+    ex = Pipelined()
+    generate(ex, [Request([10], 4, SamplingParams(0.8, repeat_penalty=1.3))])
+    assert ex.fed == 0
+    # a stop token ends one sequence: the step ahead is read, then the rest goes on from host tokens
+    ex = Pipelined()
+    out = generate(ex, [Request([10], 6, stop_tokens=[13]), Request([20], 6)])
+    assert out[0].tokens == [11, 12] and out[1].tokens == [21, 22, 23, 24, 25, 26]
+    assert [len(c) for c in ex.calls] == [2, 2, 2, 2, 1, 1]
+    assert ex.calls[4] == [(1, [24])]
