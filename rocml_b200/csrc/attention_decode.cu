@@ -41,7 +41,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         float* __restrict__ part_ml, int* __restrict__ counters,
                         __nv_bfloat16* __restrict__ out, int o_stride) {
     pdl_trigger();
-    pdl_wait();
+    // Everything up to pdl_wait() below may run while the kernels before this one in the stream are
+    // still running.  It reads the step's integers (copied to the device before the step's first
+    // kernel) and pages of keys and values that EARLIER steps wrote; the one page of a sequence that
+    // receives this step's token, and the queries, are read after the wait.
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [16][HD]
     __nv_bfloat16* KVs = Qs + ROWS * HD;                                    // per warp: K [32][HD], V [32][HD]
@@ -88,8 +91,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
         cp_async_commit();
     };
+    // Two pages in flight per warp.  A page below the one that holds position `pos` was complete
+    // before this step began, so its copies start at once; the others start after the wait.
+    const int new_page = pos / CHUNK;
+    const bool early0 = page_first < new_page, early1 = page_first + 1 < new_page;
+    if (early0) issue(page_first, 0);
+    if (early1) issue(page_first + 1, 1);
+    pdl_wait();
     load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
-    issue(page_first, 0);
+    cp_async_commit();                                      // a group of its own: the wait below covers committed groups only
+    if (!early0) issue(page_first, 0);
+    if (!early1) issue(page_first + 1, 1);                  // commits an empty group beyond page_last
     cp_async_wait<0>();
     __syncthreads();                                        // the query heads are in place for every warp
 
@@ -100,16 +112,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const uint32_t qs_base = smem_addr(Qs);
     const float sl2 = scale * LOG2E;
 
-    for (int pg = page_first; pg <= page_last; ++pg) {
-        const int buf = (pg - page_first) & 1;
-        if (pg > page_first) {
-            cp_async_wait<0>();                             // this warp's copies of page pg have landed
-            __syncwarp();
-        }
-        if (pg < page_last) issue(pg + 1, buf ^ 1);         // the other buffer was read in the last round
+    auto attend_page = [&](int pg, int buf) {
         const int j0 = pg * CHUNK + warp * WK;
         const int hi = min(pos, (pg + 1) * CHUNK - 1);
-        if (!(j0 <= hi && j0 + WK - 1 >= win_lo)) continue;
+        if (!(j0 <= hi && j0 + WK - 1 >= win_lo)) return;
         const uint32_t ks_base = smem_addr(KVw + buf * 2 * WK * HD);
         const uint32_t vs_base = ks_base + WK * HD * 2;
         float s[WK / 8][4];
@@ -180,6 +186,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_bf16(o[i + 1], pa[kk], b2, b3);
             }
         }
+    };
+    for (int pg = page_first; pg <= page_last; ++pg) {
+        const int buf = (pg - page_first) & 1;
+        if (pg >= page_first + 2) {
+            cp_async_wait<1>();                             // page pg has landed; page pg + 1 may be on its way
+            __syncwarp();
+        }
+        attend_page(pg, buf);
+        __syncwarp();                                       // the buffer is free again
+        issue(pg + 2, buf);
     }
     cp_async_wait<0>();
 #pragma unroll

@@ -66,7 +66,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float
 }
 
 template <typename OT, typename WT>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
                                    int n_delta, size_t delta_stride, const WT* __restrict__ w,
                                    OT* __restrict__ out, const int* __restrict__ rows, int H,
                                    float eps, int write_back) {
@@ -88,18 +88,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
             float4 v = r4[i];
             const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)row * H) + i;
             const size_t ds4 = delta_stride >> 2;
-            int s = 0;
-            for (; s + 4 <= n_delta; s += 4) {   // four loads in flight, added in order
-                const float4 a = d4[(size_t)s * ds4], b = d4[(size_t)(s + 1) * ds4];
-                const float4 c = d4[(size_t)(s + 2) * ds4], d = d4[(size_t)(s + 3) * ds4];
-                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-                v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
-                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-            }
-            for (; s < n_delta; ++s) {
-                const float4 d = d4[(size_t)s * ds4];
-                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            // eight partial sums at a time: every load is issued before the first addition, and the
+            // additions keep the partial sums' order (an absent one adds zero)
+            for (int s = 0; s < n_delta; s += 8) {
+                float4 d[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    d[j] = s + j < n_delta ? d4[(size_t)(s + j) * ds4] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v.x += d[j].x; v.y += d[j].y; v.z += d[j].z; v.w += d[j].w; }
             }
             rb4[i] = v;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -146,7 +143,8 @@ static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, siz
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    // one 16-byte column group per thread where the row allows it: a row's loads are all in flight at once
+    const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
     RB_LAUNCH((k), dim3(n_rows), dim3(threads), smem, s, resid, delta, n_delta, delta_stride, (const WT*)w, (OT*)out, rows, H,
                                     eps, write_back);
     RB_LAUNCH_CHECK();
