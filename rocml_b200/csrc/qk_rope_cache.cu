@@ -154,7 +154,16 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
     }
     const IT* src = in + (size_t)t * row_stride + (size_t)h * hd + lane * 4;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < n_in; ++s) {
+    for (int s = 0; sizeof(IT) == 4 && s < n_in; s += 8) {   // eight partial sums in flight, added in order
+        float4 f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            f[j] = s + j < n_in ? *reinterpret_cast<const float4*>(src + (size_t)(s + j) * in_stride)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[0] += f[j].x; v[1] += f[j].y; v[2] += f[j].z; v[3] += f[j].w; }
+    }
+    for (int s = 0; sizeof(IT) != 4 && s < n_in; ++s) {
         const IT* p = src + (size_t)s * in_stride;
         if (sizeof(IT) == 4) {
             const float4 f = *reinterpret_cast<const float4*>(p);

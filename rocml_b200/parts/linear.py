@@ -22,6 +22,16 @@ from ..weights.decl import TensorDecl
 from .base import BuildEnv
 
 
+_SM_COUNT = {}
+
+
+def _sm_count(device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[key]
+
+
 class Linear:
     def __init__(self, names: Sequence[str], out_features: Sequence[int], in_features: int, bias: bool,
                  env: BuildEnv):
@@ -104,15 +114,22 @@ class Linear:
         row tiles (128 rows each) are multiplied by K splits until about two blocks per
         multiprocessor are in flight (more gains little and costs the consumer, which adds the
         partial sums); each split keeps at least five 64-wide K blocks, at most 8 splits, and the
-        float32 partial results stay below a sixth of the weight's own bytes.  The count depends
-        on the weight's shape and the step's row count only."""
+        float32 partial results stay below a sixth of the weight's own bytes.  A product over a
+        very deep K (24 or more K blocks left per split) is split twice as often, as long as all
+        its blocks still fit on the device at once (four per multiprocessor).  The count depends
+        on the weight's shape, the step's row count and the device only."""
         if m > 128 or self.k % 8:
             return 1
+        sms = _sm_count(self.env.device)
         tiles = (self.n + 127) // 128
-        by_blocks = -(-2 * 148 // tiles)
-        by_depth = (self.k // 64) // 5
+        k_blocks = self.k // 64
+        by_blocks = -(-2 * sms // tiles)
+        by_depth = k_blocks // 5
         by_bytes = int(0.075 * self.k / max(m, 1))
-        return max(1, min(by_blocks, by_depth, by_bytes, 8))
+        s = max(1, min(by_blocks, by_depth, by_bytes, 8))
+        if k_blocks // s >= 24 and 2 * s <= by_bytes and 2 * s * tiles <= 4 * sms:
+            s *= 2
+        return s
 
     def forward_delta(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """The product as float32 [S, M, N]: S partial sums over K that the consumer adds in order
