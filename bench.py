@@ -9,7 +9,8 @@ sized for a context of 4,096 per sequence).  One JSON line goes to stdout:
 * ``value``: decoded tokens per second over K steps, timed on the device with CUDA events;
   the ids sampled by the argmax kernel feed the next step on the device.
 * ``e2e``: the same through the Python entry point (``Engine.generate``): every step copies its
-  inputs from pinned host memory and reads the sampled ids back to the host.
+  integers (positions, lengths, slots) from pinned host memory and reads the sampled ids back to the
+  host; the loop enqueues a step, fed on the device with the ids just sampled, before it reads them.
 * ``prefill``: one prompt of 2,048 tokens; ``frac`` = flops / time / measured bf16 peak.
 * ``roofline``: bytes a decode step must read (every weight once + the live sequences' cache)
   / time, against the measured copy bandwidth.
@@ -257,7 +258,44 @@ def micro(which):
         us = in_graph(lambda: torch.matmul(x, w.t()), 10)
         print(f"library matmul (for scale) qkv: {us:.1f} us {2 * PREFILL_TOKENS * w.shape[0] * H / us / 1e6:.0f} TFLOP/s")
     else:
-        raise SystemExit(f"unknown --micro {which!r}: gemm-decode or gemm-prefill")
+        raise SystemExit(f"unknown --micro {which!r}: gemm-decode, gemm-prefill or timeline")
+
+
+def timeline(batch=BATCH, layers=4):
+    """Where a decode step's time goes, kernel by kernel, as the step really runs (inside its CUDA
+    graph, kernels overlapping their predecessors through programmatic dependent launch): start and
+    end of every kernel from the profiler's activity records (CUPTI, no kernel is replayed), and for
+    each kernel the time from its predecessor's end to its own end, which is what it adds to the step."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from rocml_b200 import StepEntry, kernels
+    cfg, n_full, eng = build_engine(layers, batch * (PROMPT + 256), batch)
+    slots = [eng.new_sequence() for _ in range(batch)]
+    ps = prompts(batch, PROMPT, cfg.vocab_size, 3)
+    tok = torch.zeros(batch, dtype=torch.int32, device=eng.device)
+    kernels.argmax(eng.step([StepEntry(s, p, [PROMPT - 1]) for s, p in zip(slots, ps)]), tok, batch)
+
+    def one():
+        kernels.argmax(eng.step([StepEntry(s, [0], [0]) for s in slots], device_tokens=tok), tok, batch)
+
+    for _ in range(6):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            one()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                key=lambda e: e.time_range.start)
+    last = ev[-(len(ev) // 3):]                      # the third step
+    t0, prev_end = last[0].time_range.start, None
+    print(f"decode step, batch {batch}, {layers} layers: start, end, added (us), kernel")
+    for e in last:
+        end = e.time_range.end
+        added = end - (prev_end if prev_end is not None else e.time_range.start)
+        prev_end = max(end, prev_end or end)
+        print(f"{e.time_range.start - t0:9.2f} {end - t0:9.2f} {added:7.2f}  {e.name[:90]}")
+    print(f"step: {prev_end - t0:.1f} us")
 
 
 def main():
@@ -268,8 +306,14 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
-    ap.add_argument("--micro", default=None, help="kernel microbenchmarks instead of the bench: gemm-decode, gemm-prefill")
+    ap.add_argument("--micro", default=None,
+                    help="instead of the bench: gemm-decode, gemm-prefill (kernel microbenchmarks) or timeline "
+                         "(every kernel of one decode step with its start and end)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="batch of --micro timeline")
     args = ap.parse_args()
+    if args.micro == "timeline":
+        timeline(args.batch, args.layers or 4)
+        return 0
     if args.micro:
         micro(args.micro)
         return 0

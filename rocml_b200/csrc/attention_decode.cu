@@ -7,10 +7,13 @@
 // arithmetic costs next to nothing whatever the group size.  Each of the 4 warps copies its own 16
 // keys and 16 values into shared memory with cp.async (16-byte chunks, XOR-swizzled for ldmatrix),
 // computes S = Q K^T, the softmax statistics of its keys and P V, and the warps' results are merged
-// through shared memory.  The block writes an unnormalised partial result; a counter per (sequence,
-// head group) tells the last block to arrive, which merges all chunks in ascending order and writes
-// the output (the counter is left at zero for the next launch).  Softmax is float32, base 2
-// (exp(x) = exp2(x log2 e)).
+// through shared memory.  Then the blocks of one (sequence, head group) merge their partial results,
+// in ascending order of the keys.  Up to 16 of them are launched as one thread-block cluster: each
+// keeps its part in its own shared memory, and after a cluster barrier each merges one slice of the
+// head size, reading the others' parts through distributed shared memory.  More blocks than that
+// write unnormalised partial results to global memory; a counter per (sequence, head group) tells
+// the last block to arrive, which merges all chunks and writes the output (the counter is left at
+// zero for the next launch).  Softmax is float32, base 2 (exp(x) = exp2(x log2 e)).
 //
 // Replaces attn_decode_partial_f16 + attn_decode_reduce_f32 of the reference
 // (rocml-kernels/kernels/attn_decode.hip:93-255): same mathematics (head h reads key/value head
@@ -19,6 +22,7 @@
 #include "common.cuh"
 #include "mma_tiles.cuh"
 #include "api.h"
+#include <cstdlib>
 
 using namespace rb;
 using namespace mma_tiles;
@@ -28,10 +32,24 @@ constexpr int CHUNK = 64;         // keys per block: one page
 constexpr int WARPS = 4;
 constexpr int WK = CHUNK / WARPS; // keys per warp: 16
 constexpr int ROWS = 16;          // query heads per block (rows of the MMA tile)
+constexpr int MAX_CLUSTER = 16;   // blocks of one (sequence, head group) that can form a cluster (8 is the portable size)
 constexpr float NEG_BIG = -1e30f;
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int HD>
+// Blocks of one (sequence, head group) as one thread-block cluster (CL): see the merge below.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster(const float* local, unsigned rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int HD, bool CL>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
@@ -49,6 +67,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [16][HD]
     __nv_bfloat16* KVs = Qs + ROWS * HD;                                    // per warp: K [32][HD], V [32][HD]
     float* s_o = reinterpret_cast<float*>(KVs);                            // reused after the products: [4][16][HD]
+    float* s_part = s_o + WARPS * ROWS * HD;                               // beside it (CL): this block's part [16][HD]
+    __shared__ float s_pm_own[ROWS], s_pl_own[ROWS];                       // its maxima and sums
+    __shared__ float s_gm[ROWS * MAX_CLUSTER], s_gl[ROWS * MAX_CLUSTER];                       // those of all blocks of the cluster
     __shared__ float s_m[WARPS][ROWS], s_l[WARPS][ROWS];
     __shared__ int s_last;
 
@@ -66,7 +87,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int pos = kv_len[b] - 1;
     // this block's pages: [c * ppb, (c + 1) * ppb), cut at the sequence's end
     const int page_first = c * ppb;
-    if (page_first * CHUNK > pos) return;                   // beyond the sequence: takes no part in the merge
+    // beyond the sequence: takes no part in the merge; in a cluster it stays, with an empty result
+    if (!CL && page_first * CHUNK > pos) return;
     const int page_last = min(pos / CHUNK, page_first + ppb - 1);
     const int win_lo = window > 0 ? max(0, pos - window + 1) : 0;
 
@@ -231,13 +253,50 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             A = fmaf(wt, s_o[((size_t)w * ROWS + r) * HD + d], A);
         }
         const int head = h0 + r;
-        if (n_chunks > 1) {
+        if (CL) {
+            s_part[r * HD + d] = A;
+            if (d == 0) { s_pm_own[r] = M; s_pl_own[r] = L; }
+        } else if (n_chunks > 1) {
             const size_t pidx = (row0 + head) * n_chunks + c;
             part_acc[pidx * HD + d] = A;
             if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
         } else {
             out[(size_t)t * o_stride + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
         }
+    }
+    if (CL) {
+        // The blocks of this (sequence, head group) are one cluster: each keeps its partial result in
+        // its own shared memory, and after a cluster barrier each block merges one slice of the head
+        // size, reading every block's part (in ascending order) through distributed shared memory.
+        // Nothing goes through global memory, no counter is needed.
+        cluster_sync_all();
+        const int n = (int)gridDim.x;                        // = the cluster's size
+        for (int idx = threadIdx.x; idx < rows_valid * n; idx += WARPS * 32) {
+            const int r = idx / n, i = idx % n;
+            s_gm[idx] = ld_cluster(&s_pm_own[r], (unsigned)i);
+            s_gl[idx] = ld_cluster(&s_pl_own[r], (unsigned)i);
+        }
+        __syncthreads();
+        const int d_lo = c * HD / n, d_hi = (c + 1) * HD / n;
+        const int width = d_hi - d_lo;
+        for (int idx = threadIdx.x; idx < rows_valid * width; idx += WARPS * 32) {
+            const int r = idx / width, d = d_lo + idx % width;
+            const float* pm = s_gm + r * n;
+            const float* pl = s_gl + r * n;
+            float MM = NEG_BIG;
+            for (int i = 0; i < n; ++i)
+                if (pl[i] > 0.f) MM = fmaxf(MM, pm[i]);
+            float L = 0.f, A = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < n; ++i) {
+                const float wt = pl[i] > 0.f ? exp2f(pm[i] - MM) : 0.f;
+                L = fmaf(wt, pl[i], L);
+                A = fmaf(wt, ld_cluster(&s_part[r * HD + d], (unsigned)i), A);
+            }
+            out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+        }
+        cluster_sync_all();                                  // nobody leaves while its part may still be read
+        return;
     }
     if (n_chunks <= 1) return;
 
@@ -288,6 +347,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
 }
 
+bool cluster_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("RB_DECODE_CLUSTER");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
 template <int HD>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len, int B, int nq, int nkv,
@@ -302,7 +369,25 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     const size_t region = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
     const int rows_max = g < ROWS ? g : ROWS;
     if ((size_t)n_chunks * rows_max * 2 * sizeof(float) > region) return RB_ERR_BAD_SIZE;  // the merge's work space
-    auto k = attention_decode_kernel<HD>;
+    // up to 16 blocks per (sequence, head group): one cluster, merged through shared memory
+    const bool clustered = n_chunks > 1 && n_chunks <= MAX_CLUSTER && cluster_enabled();
+    if (clustered) {
+        auto k = attention_decode_kernel<HD, true>;
+        static bool attr_done = false;
+        if (!attr_done) {
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return (int)e;
+            attr_done = true;
+        }
+        cudaError_t e = launch_clustered(k, grid, dim3(WARPS * 32), (unsigned)n_chunks, smem, s, (const __nv_bfloat16*)q,
+                                         q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                                         block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
+                                         n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride);
+        return e == cudaSuccess ? RB_OK : (int)e;
+    }
+    auto k = attention_decode_kernel<HD, false>;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
