@@ -33,6 +33,9 @@ int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, 
                     int K, long long ldx, long long ldo, int splits, long long split_stride, int stages,
                     int gated, int* status, void* stream);
 
+int rb_gemm_tcgen05_gated_pair(const void* x, const void* w, const float* bias, void* h, int M, int N, int K,
+                               long long ldx, long long ldh, int stages, int* status, void* stream);
+
 int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, int dtype, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
                          const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd,

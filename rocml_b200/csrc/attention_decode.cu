@@ -381,7 +381,7 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
             if (e != cudaSuccess) return (int)e;
             attr_done = true;
         }
-        cudaError_t e = launch_clustered(k, grid, dim3(WARPS * 32), (unsigned)n_chunks, smem, s, (const __nv_bfloat16*)q,
+        cudaError_t e = launch_clustered(k, grid, dim3(WARPS * 32), dim3((unsigned)n_chunks, 1, 1), smem, s, (const __nv_bfloat16*)q,
                                          q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                                          block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
                                          n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride);

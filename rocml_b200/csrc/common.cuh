@@ -59,10 +59,10 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
-// The same with the grid's blocks grouped into clusters of `cluster_x` along x (gridDim.x must be a
-// multiple of it): the blocks of a cluster run at the same time and can read each other's shared memory.
+// The same with the grid's blocks grouped into clusters (every grid extent a multiple of the cluster's):
+// the blocks of a cluster run at the same time and can read and write each other's shared memory.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster_x, size_t smem,
+inline cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem,
                                     cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -71,9 +71,9 @@ inline cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster_x;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;

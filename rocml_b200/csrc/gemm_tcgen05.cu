@@ -69,7 +69,11 @@ __device__ __forceinline__ void store16(__nv_bfloat16* dst, const float* v) {
     reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-template <int BN, bool SWAP, typename OT, bool GATED>
+// CS = 2 (few tokens, a gate/up weight, the sum over K in two halves): the two blocks of a tile are
+// a thread-block cluster.  The second half's block hands its accumulator to the first through
+// distributed shared memory, and the first adds it to its own and writes silu(gate) * up: no
+// partial sums go through global memory and no second kernel has to wait for them.
+template <int BN, bool SWAP, typename OT, bool GATED, int CS>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OT* __restrict__ out, const Params p) {
@@ -82,6 +86,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* acc_ready = empty + S;
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
     uint32_t* abort_flag = tmem_slot + 1;
+    float* handover = (float*)(smem + S * C::STAGE + 256);   // CS: [BN][128] floats from the other half
 
     rb::pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,7 +187,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after();
         const bool aborted = !ok || *(volatile uint32_t*)abort_flag != 0;
         if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
-        if (!aborted && n_kb > 0) {
+        if (CS != 0) {
+            // the second half hands its accumulator over; the first half goes on after the barrier
+            if (!aborted && n_kb > 0 && blockIdx.z != 0) {
+                const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+                const uint32_t dst = map_to_cta(smem_u32(handover + quarter * 32 + lane), 0);
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; ++c) {
+                    float v[16];
+                    tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) st_cluster_f32(dst + (uint32_t)((c * 16 + i) * 128 * 4), v[i]);
+                }
+            }
+        } else if (!aborted && n_kb > 0) {
             const int ar = a0 + quarter * 32 + lane;   // this thread's row of the A-side operand
             OT* o = out + (size_t)blockIdx.z * p.split_stride;
             const bool add_bias = p.bias != nullptr && blockIdx.z == 0;
@@ -267,6 +285,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 if (f0 + i < p.b_rows) row[f0 + i] = rb::from_f32<OT>(v[i]);
                         }
                     }
+                }
+            }
+        }
+    }
+    if (CS != 0) {
+        // every thread of both blocks, whatever happened to it above
+        __syncwarp();
+        cluster_arrive();
+        cluster_wait();
+        if (blockIdx.z == 0 && warp >= 2 && n_kb > 0 && *(volatile uint32_t*)abort_flag == 0) {
+            // features on the TMEM lanes: lanes 0-15 of a warp hold gates, lanes 16-31 the ups
+            const int quarter = warp & 3;
+            const int ar = a0 + quarter * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const float bv = (p.bias != nullptr && ar < p.a_rows) ? p.bias[ar] : 0.f;
+            const int fo = (ar >> 5) * 16 + (lane & 15);
+            const float* other = handover + quarter * 32 + lane;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                float v[16];
+                tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float mine = v[i] + other[(c * 16 + i) * 128] + bv;     // first half + second half
+                    const float up = __shfl_down_sync(0xffffffffu, mine, 16);
+                    const int tok = b0 + c * 16 + i;
+                    if (lane < 16 && tok < p.b_rows && ar < p.a_rows)
+                        out[(size_t)tok * p.ldo + fo] = rb::from_f32<OT>(mine / (1.f + expf(-mine)) * up);
                 }
             }
         }
@@ -742,24 +789,30 @@ int tensor_map(const void* ptr, long long rows, long long K, long long ld, int b
     return RB_OK;
 }
 
-template <int BN, bool SWAP, typename OT, bool GATED>
+template <int BN, bool SWAP, typename OT, bool GATED, int CS = 0>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, int splits, cudaStream_t s) {
     // Few tokens (SWAP): the kernel is bound by memory latency, and several small blocks per
     // multiprocessor with a shallow ring hide each other's start and end better than one block
     // with a deep ring (measured: 3 stages beat 5 and 10 on every decode shape).
     if (p.stages <= 0) p.stages = SWAP ? 3 : Cfg<BN>::STAGES;
     using C = Cfg<BN>;
-    auto k = gemm_tcgen05_kernel<BN, SWAP, OT, GATED>;
+    auto k = gemm_tcgen05_kernel<BN, SWAP, OT, GATED, CS>;
+    constexpr int handover_bytes = CS != 0 ? BN * 128 * 4 : 0;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM + handover_bytes);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
     if (p.stages < 2 || p.stages > C::STAGES) return RB_ERR_BAD_SIZE;
-    const int smem_bytes = p.stages * C::STAGE + 1024 + 256;
+    const int smem_bytes = p.stages * C::STAGE + 1024 + 256 + handover_bytes;
     dim3 grid((p.a_rows + BM - 1) / BM, (p.b_rows + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
+    if (CS != 0) {
+        if (splits != CS) return RB_ERR_BAD_SIZE;
+        cudaError_t e = rb::launch_clustered(k, grid, dim3(192), dim3(1, 1, CS), smem_bytes, s, ma, mb, (OT*)out, p);
+        return e == cudaSuccess ? RB_OK : (int)e;
+    }
     RB_LAUNCH((k), dim3(grid), dim3(192), smem_bytes, s, ma, mb, (OT*)out, p);
     RB_LAUNCH_CHECK();
     return RB_OK;
@@ -836,9 +889,9 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out,
 // is [M, N / 2] = silu(gate) * up (bfloat16, no split).
 // Refuses (RB_ERR_BAD_ALIGN) what TMA cannot address: K or ldx not a multiple of 8 elements,
 // or a base pointer off a 16-byte boundary; the caller then uses the plain kernel.
-extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
-                               int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
-                               int stages, int gated, int* status, void* stream) {
+static int gemm_entry(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
+                      int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
+                      int stages, int gated, int* status, void* stream, int cluster_split) {
     if (M <= 0 || N <= 0) return RB_OK;
     if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
     if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
@@ -869,6 +922,12 @@ extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, 
         p.a_rows = M; p.b_rows = N;
         if ((rc = tensor_map(x, M, K, ldx, BM, &ma)) != RB_OK) return rc;
         if ((rc = tensor_map(w, N, K, K, bn, &mb)) != RB_OK) return rc;
+    }
+    if (cluster_split != 0) {
+        if (cluster_split != 2 || !swap || bn > 32 || out_dtype != RB_BF16 || N % 32 || kb_total < 2) return RB_ERR_BAD_SIZE;
+        p.splits = 2;
+        return bn == 16 ? launch<16, true, __nv_bfloat16, false, 2>(ma, mb, out, p, 2, s)
+                        : launch<32, true, __nv_bfloat16, false, 2>(ma, mb, out, p, 2, s);
     }
     if (!swap && splits == 1 && bn == 256 && M > 256 && pair_enabled()) {
         // many tokens and a wide weight: pairs of CTAs; the weight is read in boxes of 128 rows (a half tile)
@@ -903,4 +962,21 @@ extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, 
         return swap ? dispatch_bn<true, float, false>(bn, ma, mb, out, p, splits, s)
                     : dispatch_bn<false, float, false>(bn, ma, mb, out, p, splits, s);
     return RB_ERR_BAD_DTYPE;
+}
+
+extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
+                               int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
+                               int stages, int gated, int* status, void* stream) {
+    return gemm_entry(x, w, bias, out, out_dtype, M, N, K, ldx, ldo, splits, split_stride, stages, gated, status,
+                      stream, 0);
+}
+
+// h[M, N / 2] = silu(gate) * up (bfloat16, row stride ldh) for at most 32 rows and a gate/up weight
+// whose rows alternate in blocks of 16, with the sum over K done in two halves by the two blocks of a
+// thread-block cluster (see the kernel).  RB_ERR_BAD_SIZE for more rows, N not a multiple of 32, or
+// K of a single 64-wide block; RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
+extern "C" int rb_gemm_tcgen05_gated_pair(const void* x, const void* w, const float* bias, void* h, int M, int N,
+                                          int K, long long ldx, long long ldh, int stages, int* status,
+                                          void* stream) {
+    return gemm_entry(x, w, bias, h, RB_BF16, M, N, K, ldx, ldh, 1, 0, stages, 0, status, stream, 2);
 }

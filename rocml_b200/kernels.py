@@ -95,6 +95,7 @@ def _lib():
                                             _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]
         _sigs_done = True
     return lib
 
@@ -461,4 +462,29 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
     if rc == 10003:
         return False
     _check(rc, "gemm_tcgen05")
+    return True
+
+
+def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                            m: Optional[int] = None) -> bool:
+    """h = silu(gate) * up for at most 32 rows, w's rows alternating in blocks of 16 between gate and
+    up, with the sum over K done in two halves by two blocks that form a thread-block cluster: the
+    second hands its half to the first through shared memory, so no partial sums go through global
+    memory.  h is bfloat16 [M, N / 2].  Returns False when the kernel refuses the sizes or the layout."""
+    M = x.shape[0] if m is None else m
+    N, K = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
+            or x.shape[1] != K:
+        raise KernelError("gemm_tcgen05_gated_pair: x and w must be bfloat16, K-major, with matching K")
+    if h.dtype != torch.bfloat16 or h.shape[1] != N // 2 or h.stride(1) != 1:
+        raise KernelError("gemm_tcgen05_gated_pair: h must be bfloat16 [M, N / 2] with unit inner stride")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tcgen05_gated_pair: bias must be float32 [N]")
+    if M > 32 or N % 32 or K <= 64:
+        return False
+    rc = _lib().rb_gemm_tcgen05_gated_pair(_ptr(x), _ptr(w), _ptr(bias), _ptr(h), M, N, K, x.stride(0), h.stride(0), 0,
+                                           _ptr(status_word(x.device)), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "gemm_tcgen05_gated_pair")
     return True

@@ -89,6 +89,15 @@ class Linear:
             raise KernelError("the gated matrix product refused a layout that interleave_pairs accepted")
         return out
 
+    def forward_gated_pair(self, x: torch.Tensor, m: int) -> Optional[torch.Tensor]:
+        """The same for few rows when the sum over K is split in two: the two halves' blocks form a
+        cluster and the activation is applied where they meet, so no second kernel waits for partial
+        sums.  None when this step's product is split otherwise or the kernel refuses."""
+        if not (self.paired and self._tensor_core(x)) or self._splits(m) != 2:
+            return None
+        out = torch.empty((m, self.n // 2), dtype=torch.bfloat16, device=x.device)
+        return out if kernels.gemm_tcgen05_gated_pair(x, self.weight, out, self.bias, m) else None
+
     def adopt(self, weight: torch.Tensor) -> None:
         """Use an existing tensor as the weight (a tied head reads the embedding table)."""
         if tuple(weight.shape) != (self.n, self.k):

@@ -48,11 +48,15 @@ class GatedMLP(FeedForward):
     def forward(self, xn, batch):
         T = batch.n_tokens
         dev, act = xn.device, self.env.act_dtype
+        h = None
         if self.gate_up.paired and T > 128:
             # many tokens: the activation happens in the product's epilogue, hidden behind the next tile
             h = self.gate_up.forward_gated(xn, T)
-        else:
-            # few tokens: the product is split over K, so the activation waits for the partial sums
+        elif self.gate_up.paired:
+            # few tokens, the sum over K in two halves: the activation happens where the halves meet
+            h = self.gate_up.forward_gated_pair(xn, T)
+        if h is None:
+            # the product is split over K some other way, so the activation waits for the partial sums
             gu = self.gate_up.forward_auto(xn, T)      # [T, 2I] or [S, T, 2I] partial sums
             h = torch.empty((T, self.inter), dtype=act, device=dev)
             kernels.silu_mul(gu, h, paired=self.gate_up.paired)

@@ -72,6 +72,30 @@ def test_gemm_tcgen05_gated_epilogue(M, I, K):
     assert err < 2 ** -7, err
 
 
+@pytest.mark.parametrize("M,I,K", [(1, 208, 256), (8, 12288, 512), (32, 320, 1024), (17, 4096, 4096), (16, 48, 136)])
+def test_gemm_tcgen05_gated_pair_of_blocks(M, I, K):
+    """Few rows, the sum over K in two halves by the two blocks of a cluster: the second hands its
+    accumulator to the first through shared memory, the first writes silu(gate) * up."""
+    from rocml_b200 import kernels
+    x = rnd((M, K), 1, torch.bfloat16).to(DEV)
+    wg, wu = rnd((I, K), 2, torch.bfloat16, 0.2), rnd((I, K), 3, torch.bfloat16, 0.2)
+    bg, bu = rnd((I,), 4), rnd((I,), 5)
+    mix = lambda g, u: torch.stack([g.reshape(I // 16, 16, *g.shape[1:]), u.reshape(I // 16, 16, *u.shape[1:])], 1).reshape(2 * I, *g.shape[1:])
+    w, b = mix(wg, wu).contiguous().to(DEV), mix(bg, bu).contiguous().to(DEV)
+    xd = x.cpu().double()
+    g = xd @ wg.double().t() + bg.double()
+    u = xd @ wu.double().t() + bu.double()
+    want = g / (1 + torch.exp(-g)) * u
+    for _ in range(2):
+        out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        assert kernels.gemm_tcgen05_gated_pair(x, w, out, b)
+        kernels.check_status(DEV)
+        err = ((out.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max().item()
+        assert err < 2 ** -7, err
+    assert kernels.gemm_tcgen05_gated_pair(rnd((40, K), 1, torch.bfloat16).to(DEV), w,
+                                           torch.empty((40, I), dtype=torch.bfloat16, device=DEV)) is False
+
+
 def test_gemm_tcgen05_refuses_unaligned_k():
     from rocml_b200 import kernels
     x = rnd((4, 100), 1, torch.bfloat16).to(DEV)  # K = 100: rows are not a multiple of 16 bytes
