@@ -58,6 +58,13 @@ int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const 
                         int pages_per_block, float* part_acc, float* part_ml, int* counters, void* out, int o_stride,
                         void* stream);
 
+int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, int row_stride, const void* q_norm_w,
+                              const void* k_norm_w, int w_f32, float eps, const float* cos_sin, int write_kv,
+                              void* k_cache, void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
+                              const int* cu_q, const int* kv_len, int B, int nq, int nkv, int hd, float scale,
+                              int window, int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
+                              int* counters, void* out, int o_stride, void* stream);
+
 int rb_attention_merge(const float* part_acc, const float* part_ml, void* out, int o_stride, int dtype,
                        const int* positions, const int* slot_of_token, int T, int nq, int hd, int chunk,
                        int n_chunks, int window, void* stream);

@@ -49,7 +49,86 @@ __device__ __forceinline__ float ld_cluster(const float* local, unsigned rank) {
     return v;
 }
 
-template <int HD, bool CL>
+// FQ (head size 128): the step's projections arrive as they leave the matrix product (float32 partial
+// sums over K, [S][T][q heads | k heads | v heads]) and the kernel does what a kernel of its own would
+// otherwise do between the two: it adds the partial sums, normalises each query head (RMSNorm over the
+// head, float32), rotates it (NEOX pairs i, i + 64; cos/sin from the step's table) and keeps it in
+// shared memory; the one block that reads the page of the new token does the same for that token's key,
+// and writes key and value into the page before it copies the page.
+struct Projections {
+    const float* proj;        // null: queries are read from `q`, the cache is already written
+    int n_in;                 // partial sums
+    long long in_stride;      // elements between two partial sums
+    int row_stride;           // elements between two tokens
+    const void* q_norm_w;     // [128] or null (no norm)
+    const void* k_norm_w;
+    int w_f32;                // the norm weights' type: float32 or bfloat16
+    float eps;
+    const float2* cos_sin;    // [T][64] (cos, sin) or null (no rotation)
+    int write_kv;             // 0: this layer reads a cache that another layer wrote
+    __nv_bfloat16* k_out;     // the cache to write (k_cache / v_cache of the call)
+    __nv_bfloat16* v_out;
+};
+
+// One head of 128 values, 4 per lane: the sum of the partial sums, then (what != 2) RMSNorm with `w`
+// and the rotation by the token's angles.  what: 0 query, 1 key, 2 value.
+__device__ __forceinline__ void project_head(const Projections& pj, const float* src, int what, int t, int lane, float* v) {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    // the norm's weights and the token's angles do not depend on the sums: their loads go out first
+    const void* w = what == 0 ? pj.q_norm_w : (what == 1 ? pj.k_norm_w : nullptr);
+    const bool rotate = what != 2 && pj.cos_sin != nullptr;
+    float wj[4] = {1.f, 1.f, 1.f, 1.f};
+    float2 cs[4];
+    if (w != nullptr) {
+        if (pj.w_f32) {
+            const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(w) + lane * 4);
+            wj[0] = f.x; wj[1] = f.y; wj[2] = f.z; wj[3] = f.w;
+        } else {
+            const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(w) + lane * 4);
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            wj[0] = a.x; wj[1] = a.y; wj[2] = b.x; wj[3] = b.y;
+        }
+    }
+    if (rotate) {
+        const float4* c4 = reinterpret_cast<const float4*>(pj.cos_sin + (size_t)t * 64 + (lane & 15) * 4);
+        const float4 a = c4[0], b = c4[1];
+        cs[0] = make_float2(a.x, a.y); cs[1] = make_float2(a.z, a.w);
+        cs[2] = make_float2(b.x, b.y); cs[3] = make_float2(b.z, b.w);
+    }
+    for (int s = 0; s < pj.n_in; s += 8) {                  // eight partial sums in flight, added in order
+        float4 f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            f[j] = s + j < pj.n_in ? *reinterpret_cast<const float4*>(src + (size_t)(s + j) * pj.in_stride)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[0] += f[j].x; v[1] += f[j].y; v[2] += f[j].z; v[3] += f[j].w; }
+    }
+    if (w != nullptr) {
+        const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+        const float inv = rsqrtf(ss / 128.f + pj.eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = v[j] * inv * wj[j];
+    }
+    if (rotate) {
+        // dimension i < 64 pairs with i + 64: lanes 0-15 hold x_i, lanes 16-31 the partners
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+            v[j] = lane < 16 ? v[j] * cs[j].x - other * cs[j].y : other * cs[j].y + v[j] * cs[j].x;
+        }
+    }
+}
+__device__ __forceinline__ uint2 pack4_bf16(const float* v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    return raw;
+}
+
+template <int HD, bool CL, bool FQ>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
@@ -57,7 +136,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
                         float scale, int window, int n_chunks, int ppb, float* __restrict__ part_acc,
                         float* __restrict__ part_ml, int* __restrict__ counters,
-                        __nv_bfloat16* __restrict__ out, int o_stride) {
+                        __nv_bfloat16* __restrict__ out, int o_stride, const Projections pj) {
     pdl_trigger();
     // Everything up to pdl_wait() below may run while the kernels before this one in the stream are
     // still running.  It reads the step's integers (copied to the device before the step's first
@@ -120,7 +199,32 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if (early0) issue(page_first, 0);
     if (early1) issue(page_first + 1, 1);
     pdl_wait();
-    load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
+    if (FQ) {
+        const float* row = pj.proj + (size_t)t * pj.row_stride;
+        for (int r = warp; r < ROWS; r += WARPS) {          // the query heads of this block
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (r < rows_valid) project_head(pj, row + (size_t)(h0 + r) * HD + lane * 4, 0, t, lane, v);
+            const int chunk = lane >> 1;                    // 8 values per 16-byte chunk, 4 per lane
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(Qs) + r * (HD * 2) + ((chunk ^ (r & 7)) << 4) +
+                                      (lane & 1) * 8) = pack4_bf16(v);
+        }
+        // the new token's key and value, by the one block that reads their page
+        if (pj.write_kv && hc == 0 && page_first <= new_page && new_page <= page_last && warp < 2) {
+            const int page = table[new_page];
+            if (page >= 0) {
+                float v[4];
+                const int head = warp == 0 ? nq + kvh : nq + nkv + kvh;
+                project_head(pj, row + (size_t)head * HD + lane * 4, warp == 0 ? 1 : 2, t, lane, v);
+                __nv_bfloat16* dst = (warp == 0 ? pj.k_out : pj.v_out) +
+                                     (((size_t)page * nkv + kvh) * RB_PAGE + (pos % RB_PAGE)) * HD;
+                *reinterpret_cast<uint2*>(dst + lane * 4) = pack4_bf16(v);
+                __threadfence_block();
+            }
+        }
+        __syncthreads();                                    // before the page of the new token is copied
+    } else {
+        load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
+    }
     cp_async_commit();                                      // a group of its own: the wait below covers committed groups only
     if (!early0) issue(page_first, 0);
     if (!early1) issue(page_first + 1, 1);                  // commits an empty group beyond page_last
@@ -355,11 +459,41 @@ bool cluster_enabled() {
     return on;
 }
 
+template <int HD, bool CL, bool FQ>
+int launch_variant(dim3 grid, size_t smem, cudaStream_t s, const void* q, int q_stride, const void* k_cache,
+                   const void* v_cache, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
+                   const int* kv_len, int nq, int nkv, float scale, int window, int n_chunks, int ppb, float* part_acc,
+                   float* part_ml, int* counters, void* out, int o_stride, const Projections& pj) {
+    auto k = attention_decode_kernel<HD, CL, FQ>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        if (CL) {   // clusters of more than 8 blocks are not portable
+            e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return (int)e;
+        }
+        attr_done = true;
+    }
+    if (CL) {
+        cudaError_t e = launch_clustered(k, grid, dim3(WARPS * 32), dim3(grid.x, 1, 1), smem, s, (const __nv_bfloat16*)q,
+                                         q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                                         block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
+                                         n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj);
+        return e == cudaSuccess ? RB_OK : (int)e;
+    } else {
+        RB_LAUNCH((k), grid, dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
+                  (const __nv_bfloat16*)v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
+                  n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj);
+        return RB_OK;
+    }
+}
+
 template <int HD>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int max_pages, const int* seq_slot, const int* cu_q, const int* kv_len, int B, int nq, int nkv,
            float scale, int window, int n_chunks, int ppb, float* part_acc, float* part_ml, int* counters,
-           void* out, int o_stride, cudaStream_t s) {
+           void* out, int o_stride, const Projections& pj, cudaStream_t s) {
     const int g = nq / nkv;
     dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
@@ -371,33 +505,14 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     if ((size_t)n_chunks * rows_max * 2 * sizeof(float) > region) return RB_ERR_BAD_SIZE;  // the merge's work space
     // up to 16 blocks per (sequence, head group): one cluster, merged through shared memory
     const bool clustered = n_chunks > 1 && n_chunks <= MAX_CLUSTER && cluster_enabled();
-    if (clustered) {
-        auto k = attention_decode_kernel<HD, true>;
-        static bool attr_done = false;
-        if (!attr_done) {
-            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-            if (e != cudaSuccess) return (int)e;
-            attr_done = true;
-        }
-        cudaError_t e = launch_clustered(k, grid, dim3(WARPS * 32), dim3((unsigned)n_chunks, 1, 1), smem, s, (const __nv_bfloat16*)q,
-                                         q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                                         block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
-                                         n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride);
-        return e == cudaSuccess ? RB_OK : (int)e;
-    }
-    auto k = attention_decode_kernel<HD, false>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
-    RB_LAUNCH((k), grid, dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
-              (const __nv_bfloat16*)v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
-              n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride);
-    return RB_OK;
+    const bool fused = pj.proj != nullptr;
+    if (fused && HD != 128) return RB_ERR_BAD_SIZE;
+#define RB_ADV(CL, FQ) launch_variant<HD, CL, FQ>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table, max_pages, \
+                                                   seq_slot, cu_q, kv_len, nq, nkv, scale, window, n_chunks, ppb,        \
+                                                   part_acc, part_ml, counters, out, o_stride, pj)
+    if (HD == 128 && fused) return clustered ? RB_ADV(true, (HD == 128)) : RB_ADV(false, (HD == 128));
+    return clustered ? RB_ADV(true, false) : RB_ADV(false, false);
+#undef RB_ADV
 }
 }  // namespace
 
@@ -409,24 +524,62 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 // Returns RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 and for contexts whose chunk list does
 // not fit the merge's shared memory (65536 tokens at a group of 4 and head size 128); the caller then
 // uses the plain kernel.
-extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
-                                   const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
-                                   const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
-                                   int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
-                                   int* counters, void* out, int o_stride, void* stream) {
+static int decode_entry(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                        const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
+                        const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
+                        int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
+                        int* counters, void* out, int o_stride, const Projections& pj, void* stream) {
     if (B <= 0) return RB_OK;
     if (nkv <= 0 || nq % nkv || n_chunks < 1 || n_chunks > 1024 || pages_per_block < 1) return RB_ERR_BAD_SIZE;
     if (n_chunks > 1 && (!part_acc || !part_ml || !counters)) return RB_ERR_BAD_SIZE;
-    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || (q_stride % 8))
-        return RB_ERR_BAD_ALIGN;
+    if (((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return RB_ERR_BAD_ALIGN;
+    if (pj.proj == nullptr && (((uintptr_t)q & 15) || (q_stride % 8))) return RB_ERR_BAD_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
 #define RB_AD(HD) return launch<HD>(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, \
-                                    nkv, scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, s)
+                                    nkv, scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, s)
     if (hd == 128) RB_AD(128);
     if (hd == 64) RB_AD(64);
     if (hd == 256) RB_AD(256);
 #undef RB_AD
     return RB_ERR_BAD_SIZE;
+}
+
+extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                   const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
+                                   const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
+                                   int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
+                                   int* counters, void* out, int o_stride, void* stream) {
+    Projections none = {};
+    return decode_entry(q, q_stride, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, nkv, hd,
+                        scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, none, stream);
+}
+
+// The same for head size 128 with the step's projections as the matrix product left them:
+// proj [n_in][T][(nq + 2 * nkv) * 128] float32 partial sums (queries, keys, values side by side;
+// in_stride elements between partial sums, row_stride between tokens; with write_kv == 0 only the
+// nq query heads are there).  The kernel adds them, normalises (norm weights [128], float32 if
+// w_f32 else bfloat16, or null) and rotates (cos_sin [T][64] pairs, or null) the query heads itself,
+// and writes the new token's key and value into the cache (write_kv != 0) before reading it.
+// Returns RB_ERR_BAD_SIZE for other head sizes, RB_ERR_BAD_ALIGN for partial sums off 16 bytes.
+extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, int row_stride,
+                                         const void* q_norm_w, const void* k_norm_w, int w_f32, float eps,
+                                         const float* cos_sin, int write_kv, void* k_cache, void* v_cache,
+                                         const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
+                                         const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
+                                         int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
+                                         int* counters, void* out, int o_stride, void* stream) {
+    if (hd != 128 || proj == nullptr || n_in < 1) return RB_ERR_BAD_SIZE;
+    if (((uintptr_t)proj & 15) || (in_stride % 4) || (row_stride % 4) || ((uintptr_t)cos_sin & 7)) return RB_ERR_BAD_ALIGN;
+    if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return RB_ERR_BAD_SIZE;
+    Projections pj;
+    pj.proj = proj; pj.n_in = n_in; pj.in_stride = in_stride; pj.row_stride = row_stride;
+    pj.q_norm_w = q_norm_w; pj.k_norm_w = k_norm_w; pj.w_f32 = w_f32; pj.eps = eps;
+    pj.cos_sin = reinterpret_cast<const float2*>(cos_sin);
+    pj.write_kv = write_kv;
+    pj.k_out = static_cast<__nv_bfloat16*>(k_cache);
+    pj.v_out = static_cast<__nv_bfloat16*>(v_cache);
+    return decode_entry(nullptr, 0, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, nkv, hd,
+                        scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, stream);
 }
 
 // ---- the same kernel for callers that cannot allocate (see no_alloc.h) -----------------------------

@@ -93,6 +93,8 @@ def _lib():
                                                  _i, _i, _i, _f, _i, _vp, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
                                             _i, _vp, _vp, _vp, _vp, _i, _vp]
+        lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp,
+                                                  _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]
@@ -357,6 +359,49 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     if rc in (10001, 10003):
         return False
     _check(rc, "attention_decode")
+    return True
+
+
+def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                           block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                           n_seqs: int, nq: int, nkv: int, hd: int, q_norm_w: Optional[torch.Tensor],
+                           k_norm_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
+                           write_kv: bool, scale: float, window: int, n_chunks: int,
+                           part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
+                           pages_per_block: int = 1) -> bool:
+    """attention_decode for head size 128 that takes the step's projections as the matrix product left
+    them: ``proj`` float32 [S, T, (nq + 2 nkv) * 128] partial sums (or [T, ...]; only the nq query heads
+    when ``write_kv`` is off).  The kernel adds them, applies the per-head norm and the rotation
+    (``cos_sin`` float32 [T, 64, 2] from rope_table) to the queries, and writes the new token's key and
+    value into its page before reading it: the work of qk_norm_rope_cache, without a kernel in between.
+    Returns False when the kernel does not take the sizes (use the two kernels)."""
+    if hd != 128 or proj.dtype != torch.float32 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 \
+            or out.stride(-1) != 1 or n_seqs * nq > _COUNTER_INTS:
+        return False
+    width = (nq + (2 * nkv if write_kv else 0)) * hd
+    n_in, in_stride, row_stride = _partials(proj, "attention_decode_fused")
+    if proj.shape[-1] != width:
+        raise KernelError(f"attention_decode_fused: projections must be {width} wide")
+    if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
+        raise KernelError("attention_decode_fused: cache must be [pages, nkv, 64, hd]")
+    if (q_norm_w is None) != (k_norm_w is None):
+        raise KernelError("attention_decode_fused: give both norm weights or neither")
+    w_f32 = 0
+    if q_norm_w is not None:
+        if q_norm_w.dtype != k_norm_w.dtype or q_norm_w.numel() != hd or k_norm_w.numel() != hd:
+            raise KernelError("attention_decode_fused: norm weights must share a type and be [head_dim]")
+        w_f32 = 1 if q_norm_w.dtype == torch.float32 else 0
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.numel() < n_seqs * hd):
+        raise KernelError("attention_decode_fused: cos_sin must be float32 [T, 64, 2]")
+    rc = _lib().rb_attention_decode_fused(
+        _ptr(proj), n_in, in_stride, row_stride, _ptr(q_norm_w), _ptr(k_norm_w), w_f32, float(eps), _ptr(cos_sin),
+        1 if write_kv else 0, _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
+        _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
+        int(window), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
+        _ptr(decode_counters(out.device)), _ptr(out), out.stride(0), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "attention_decode_fused")
     return True
 
 

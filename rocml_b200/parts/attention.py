@@ -86,16 +86,41 @@ class Attention(Mixer):
         dev, act = xn.device, self.env.act_dtype
         qd = self.nq * self.hd
         proj = self.qkv.forward_auto(xn, T)          # [T, N] or [S, T, N] partial sums
+        attn = torch.empty((T, qd), dtype=act, device=dev)
+        window = int(self.window) if self.window else 0
+        writes = view.writes and not self.shares_cache
+        if batch.is_decode and self._decode_fused(proj, attn, batch, view, window, writes):
+            return self.o.forward_delta(attn, T)
         q = proj if proj.dim() == 2 else torch.empty((T, qd), dtype=act, device=dev)
         kernels.qk_norm_rope_cache(
             proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
             self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
-            view.block_table, view.k, view.v, write_kv=view.writes and not self.shares_cache,
+            view.block_table, view.k, view.v, write_kv=writes,
             cos_sin=self.position.cos_sin(batch))
-        attn = torch.empty((T, qd), dtype=act, device=dev)
-        window = int(self.window) if self.window else 0
         self.attend(q, attn, batch, view, window)
         return self.o.forward_delta(attn, T)
+
+    def _decode_fused(self, proj, out, batch, view, window, writes) -> bool:
+        """One token per sequence, head size 128, float32 projections: the attention kernel itself
+        adds the partial sums, normalises and rotates the queries and writes the new key and value,
+        so no kernel stands between the projection and the attention.  False: not this time."""
+        if self.hd != 128 or proj.dtype != torch.float32 or view.k.dtype != torch.bfloat16:
+            return False
+        rot = self.position.rot_dim if self.position.inv_freq is not None else 0
+        if rot not in (0, self.hd):
+            return False
+        n_pages = max(1, (batch.max_kv_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+        groups = self.nkv * ((self.nq // self.nkv + 15) // 16)
+        n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages, out.device)
+        acc = ml = None
+        if n_pages > 1:
+            T = batch.n_tokens
+            acc = torch.empty((T, self.nq, n_pages, self.hd), dtype=torch.float32, device=out.device)
+            ml = torch.empty((T, self.nq, n_pages, 2), dtype=torch.float32, device=out.device)
+        return kernels.attention_decode_fused(
+            proj, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q, batch.kv_len, batch.n_seqs,
+            self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+            self.position.cos_sin(batch) if rot else None, writes, self.scale, window, n_blocks, acc, ml, ppb)
 
     def attend(self, q, out, batch, view, window):
         """Softmax attention of the step's queries over the cache.  One token per sequence:

@@ -371,6 +371,56 @@ def test_attention_decode_split_kv(case, fast):
     assert err < 2e-2, err
 
 
+@pytest.mark.parametrize("lens,nq,nkv,window,S,norm,rope,grid", [
+    ([700, 1, 129, 64, 128], 32, 8, None, 7, True, True, (1, 1)),      # one page per block: clusters of up to 12
+    ([300, 131, 65], 8, 2, None, 1, True, True, (2, 3)),               # clusters of 2
+    ([513, 40], 6, 3, 70, 3, False, True, (1, 1)),                    # a window, no per-head norm
+    ([1100], 40, 2, None, 2, True, False, (1, 1)),                     # 20 query heads per group: two blocks a group; 18 chunks: merged through global memory
+])
+def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S, norm, rope, grid):
+    """Head size 128: the decode kernel is given the projection's partial sums and does the
+    per-head norm, the rotation and the cache write of the new token itself.  Same output and same
+    cache as the two kernels one after the other."""
+    from rocml_b200 import kernels
+    hd, B = 128, len(lens)
+    ks, vs, qs, kc, vc, meta = paged_case(31, lens, [1] * B, nq, nkv, hd, torch.bfloat16)
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    gen = torch.Generator().manual_seed(5)
+    width = (nq + 2 * nkv) * hd
+    proj = (torch.randn((S, B, width), generator=gen) * (1.0 / S)).to(DEV)
+    qw = (1 + 0.1 * torch.randn(hd, generator=gen)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, generator=gen)).to(DEV) if norm else None
+    pos = (d["kv_len"] - 1).to(torch.int32)
+    slot_of_token = d["seq_slot"]
+    inv_freq = (1e6 ** (-torch.arange(0, hd // 2, dtype=torch.float64) * 2 / hd)).float().to(DEV) if rope else None
+    cs = kernels.rope_table(pos, inv_freq, B) if rope else None
+    scale = 1.0 / math.sqrt(hd)
+    ppb, _ = grid
+    n_chunks = ((max(lens) + 63) // 64 + ppb - 1) // ppb
+    outs, caches = [], []
+    for fused in (False, True):
+        k2, v2 = kc.clone().to(DEV), vc.clone().to(DEV)
+        out = torch.full((B, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        acc = torch.empty((B, nq, n_chunks, hd), dtype=torch.float32, device=DEV)
+        ml = torch.empty((B, nq, n_chunks, 2), dtype=torch.float32, device=DEV)
+        if fused:
+            assert kernels.attention_decode_fused(proj, out, k2, v2, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
+                                                  B, nq, nkv, hd, qw, kw, 1e-6, cs, True, scale, window or 0,
+                                                  n_chunks, acc, ml, ppb)
+        else:
+            q = torch.empty((B, nq * hd), dtype=torch.bfloat16, device=DEV)
+            kernels.qk_norm_rope_cache(proj, q, B, nq, nkv, hd, qw, kw, 1e-6, inv_freq, hd if rope else 0, pos,
+                                       slot_of_token, d["table"], k2, v2, write_kv=True, cos_sin=cs)
+            assert kernels.attention_decode(q, out, k2, v2, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, nq,
+                                            nkv, hd, scale, window or 0, n_chunks, acc, ml, ppb)
+        assert int(kernels.decode_counters(DEV).abs().sum()) == 0
+        outs.append(out.float().cpu())
+        caches.append((torch.nan_to_num(k2.float()).cpu(), torch.nan_to_num(v2.float()).cpu()))
+    assert torch.isfinite(outs[1]).all()
+    assert torch.equal(caches[0][0], caches[1][0]) and torch.equal(caches[0][1], caches[1][1])
+    assert (outs[0] - outs[1]).abs().max().item() < 1e-2
+
+
 def test_attention_decode_refuses_other_head_sizes():
     from rocml_b200 import kernels
     ks, vs, qs, kc, vc, meta = paged_case(1, [10], [1], 2, 1, 48, torch.bfloat16)
