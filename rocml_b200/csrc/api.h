@@ -36,6 +36,11 @@ int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, 
 int rb_gemm_tcgen05_gated_pair(const void* x, const void* w, const float* bias, void* h, int M, int N, int K,
                                long long ldx, long long ldh, int stages, int* status, void* stream);
 
+int rb_gemm_tcgen05_residual(const void* x, const void* w, const float* bias, int M, int N, int K, long long ldx,
+                             int splits, float* resid, long long ld_resid, const void* next_w, int next_w_f32,
+                             void* xhat, long long ld_xhat, float* sumsq, long long ld_sumsq, int stages,
+                             int* status, void* stream);
+
 int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, int dtype, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
                          const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv, int hd,

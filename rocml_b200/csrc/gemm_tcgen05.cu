@@ -50,6 +50,15 @@ struct Params {
     const float* bias;            // [features] or null; added by split 0 only
     int* status;
     int stages;                   // depth of the shared-memory ring actually used (<= Cfg::STAGES)
+    // CS >= 4 (the product is added into the residual stream, see the kernel):
+    float* resid;                 // [tokens][features] float32, updated in place
+    long long resid_ld;
+    const void* next_w;           // the following norm's weight [features], or null
+    int next_w_f32;               // its type: float32 or bfloat16
+    __nv_bfloat16* xhat;          // [tokens][features]: resid * next_w, not yet divided by the row's RMS
+    long long xhat_ld;
+    float* sumsq;                 // [feature groups][tokens]: sums of squares of the new residual rows
+    long long sumsq_ld;
 };
 
 // 16 consecutive outputs as 16-byte stores (dst is 16-byte aligned).
@@ -73,6 +82,13 @@ __device__ __forceinline__ void store16(__nv_bfloat16* dst, const float* v) {
 // a thread-block cluster.  The second half's block hands its accumulator to the first through
 // distributed shared memory, and the first adds it to its own and writes silu(gate) * up: no
 // partial sums go through global memory and no second kernel has to wait for them.
+// CS = 4, 8 or 16 (few tokens, a product that is added to the residual stream, the sum over K in CS
+// parts): the CS blocks of a tile are a cluster.  Each block owns 128 / CS of the tile's features;
+// every block sends each owner its part of them through distributed shared memory, and after one
+// cluster barrier the owner adds the parts in order, adds the bias and the residual, writes the new
+// residual (float32), and for the norm that follows: residual * weight in bfloat16 (the next product's
+// input, to be scaled by the row's 1/RMS in that product's epilogue) and its share of the row's sum
+// of squares.  No partial sums go through global memory and no norm kernel runs in between.
 template <int BN, bool SWAP, typename OT, bool GATED, int CS>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -187,7 +203,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after();
         const bool aborted = !ok || *(volatile uint32_t*)abort_flag != 0;
         if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
-        if (CS != 0) {
+        if (CS >= 4) {
+            // every block sends each owner its rows of the accumulator
+            if (!aborted && n_kb > 0) {
+                constexpr int RPC = 128 / (CS >= 4 ? CS : 4);       // features a block owns
+                const int row = quarter * 32 + lane;
+                const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+                const uint32_t dst = map_to_cta(smem_u32(handover + (size_t)blockIdx.z * BN * RPC + row % RPC), row / RPC);
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; ++c) {
+                    float v[16];
+                    tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) st_cluster_f32(dst + (uint32_t)((c * 16 + i) * RPC * 4), v[i]);
+                }
+            }
+        } else if (CS != 0) {
             // the second half hands its accumulator over; the first half goes on after the barrier
             if (!aborted && n_kb > 0 && blockIdx.z != 0) {
                 const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -294,7 +325,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
         cluster_arrive();
         cluster_wait();
-        if (blockIdx.z == 0 && warp >= 2 && n_kb > 0 && *(volatile uint32_t*)abort_flag == 0) {
+        if (CS >= 4 && warp >= 2) {
+            constexpr int RPC = 128 / (CS >= 4 ? CS : 4);
+            const int e = (warp & 3) * 32 + lane;                   // 0..127 among the epilogue threads
+#pragma unroll 1
+            for (int idx = e; idx < RPC * BN; idx += 128) {
+                const int row_in = idx % RPC, tok = b0 + idx / RPC;
+                const int n = a0 + (int)blockIdx.z * RPC + row_in;
+                const bool valid = tok < p.b_rows && n < p.a_rows;
+                float val = 0.f;
+#pragma unroll
+                for (int src = 0; src < CS; ++src) val += handover[((size_t)src * BN + idx / RPC) * RPC + row_in];
+                float sq = 0.f;
+                if (valid) {
+                    float* rp = p.resid + (size_t)tok * p.resid_ld + n;
+                    const float r_new = *rp + val + (p.bias != nullptr ? p.bias[n] : 0.f);
+                    *rp = r_new;
+                    sq = r_new * r_new;
+                    if (p.xhat != nullptr) {
+                        const float wn = p.next_w_f32 ? static_cast<const float*>(p.next_w)[n]
+                                                      : __bfloat162float(static_cast<const __nv_bfloat16*>(p.next_w)[n]);
+                        p.xhat[(size_t)tok * p.xhat_ld + n] = __float2bfloat16_rn(r_new * wn);
+                    }
+                }
+#pragma unroll
+                for (int o = RPC / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (row_in == 0 && tok < p.b_rows && p.sumsq != nullptr)
+                    p.sumsq[((size_t)blockIdx.x * CS + blockIdx.z) * p.sumsq_ld + tok] = sq;
+            }
+        } else if (blockIdx.z == 0 && warp >= 2 && n_kb > 0 && *(volatile uint32_t*)abort_flag == 0) {
             // features on the TMEM lanes: lanes 0-15 of a warp hold gates, lanes 16-31 the ups
             const int quarter = warp & 3;
             const int ar = a0 + quarter * 32 + lane;
@@ -802,6 +861,10 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, in
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM + handover_bytes);
         if (e != cudaSuccess) return (int)e;
+        if (CS > 8) {   // clusters of more than 8 blocks are not portable
+            e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return (int)e;
+        }
         attr_done = true;
     }
     if (p.stages < 2 || p.stages > C::STAGES) return RB_ERR_BAD_SIZE;
@@ -889,9 +952,17 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out,
 // is [M, N / 2] = silu(gate) * up (bfloat16, no split).
 // Refuses (RB_ERR_BAD_ALIGN) what TMA cannot address: K or ldx not a multiple of 8 elements,
 // or a base pointer off a 16-byte boundary; the caller then uses the plain kernel.
+struct ResidualOut {
+    float* resid; long long resid_ld;
+    const void* next_w; int next_w_f32;
+    void* xhat; long long xhat_ld;
+    float* sumsq; long long sumsq_ld;
+};
+
 static int gemm_entry(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
                       int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
-                      int stages, int gated, int* status, void* stream, int cluster_split) {
+                      int stages, int gated, int* status, void* stream, int cluster_split,
+                      const ResidualOut* ro = nullptr) {
     if (M <= 0 || N <= 0) return RB_OK;
     if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
     if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
@@ -922,6 +993,23 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
         p.a_rows = M; p.b_rows = N;
         if ((rc = tensor_map(x, M, K, ldx, BM, &ma)) != RB_OK) return rc;
         if ((rc = tensor_map(w, N, K, K, bn, &mb)) != RB_OK) return rc;
+    }
+    p.resid = nullptr; p.next_w = nullptr; p.xhat = nullptr; p.sumsq = nullptr;
+    p.resid_ld = p.xhat_ld = p.sumsq_ld = 0; p.next_w_f32 = 0;
+    if (ro != nullptr) {
+        if (!swap || bn != 16 || kb_total < cluster_split || ro->resid == nullptr) return RB_ERR_BAD_SIZE;
+        if (ro->xhat != nullptr && ro->next_w == nullptr) return RB_ERR_BAD_SIZE;
+        p.resid = ro->resid; p.resid_ld = ro->resid_ld;
+        p.next_w = ro->next_w; p.next_w_f32 = ro->next_w_f32;
+        p.xhat = static_cast<__nv_bfloat16*>(ro->xhat); p.xhat_ld = ro->xhat_ld;
+        p.sumsq = ro->sumsq; p.sumsq_ld = ro->sumsq_ld;
+        p.splits = cluster_split;
+        switch (cluster_split) {
+            case 4: return launch<16, true, float, false, 4>(ma, mb, nullptr, p, 4, s);
+            case 8: return launch<16, true, float, false, 8>(ma, mb, nullptr, p, 8, s);
+            case 16: return launch<16, true, float, false, 16>(ma, mb, nullptr, p, 16, s);
+        }
+        return RB_ERR_BAD_SIZE;
     }
     if (cluster_split != 0) {
         if (cluster_split != 2 || !swap || bn > 32 || out_dtype != RB_BF16 || N % 32 || kb_total < 2) return RB_ERR_BAD_SIZE;
@@ -979,4 +1067,19 @@ extern "C" int rb_gemm_tcgen05_gated_pair(const void* x, const void* w, const fl
                                           int K, long long ldx, long long ldh, int stages, int* status,
                                           void* stream) {
     return gemm_entry(x, w, bias, h, RB_BF16, M, N, K, ldx, ldh, 1, 0, stages, 0, status, stream, 2);
+}
+
+// resid[M, N] += x[M, K] . w[N, K]^T (+ bias) for at most 16 rows, the sum over K in `splits` (4, 8
+// or 16) parts by the blocks of a thread-block cluster (see the kernel); resid is float32 with row
+// stride ld_resid.  For the norm that follows, optionally: xhat[M, N] = bfloat16(resid * next_w)
+// (next_w [N], float32 if next_w_f32 else bfloat16) and sumsq[(N / 128) * splits groups][M], each
+// group's share of the new rows' sums of squares (group g at sumsq + g * ld_sumsq).
+// RB_ERR_BAD_SIZE for more rows or other split counts; RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
+extern "C" int rb_gemm_tcgen05_residual(const void* x, const void* w, const float* bias, int M, int N, int K,
+                                        long long ldx, int splits, float* resid, long long ld_resid,
+                                        const void* next_w, int next_w_f32, void* xhat, long long ld_xhat,
+                                        float* sumsq, long long ld_sumsq, int stages, int* status, void* stream) {
+    if (M > 16 || (splits != 4 && splits != 8 && splits != 16)) return RB_ERR_BAD_SIZE;
+    ResidualOut ro{resid, ld_resid, next_w, next_w_f32, xhat, ld_xhat, sumsq, ld_sumsq};
+    return gemm_entry(x, w, bias, nullptr, RB_F32, M, N, K, ldx, 0, 1, 0, stages, 0, status, stream, splits, &ro);
 }

@@ -98,6 +98,8 @@ def _lib():
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05_residual.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _ll, _vp, _i, _vp, _ll, _vp,
+                                                 _ll, _i, _vp, _vp]
         _sigs_done = True
     return lib
 
@@ -532,4 +534,43 @@ def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, b
     if rc in (10001, 10003):
         return False
     _check(rc, "gemm_tcgen05_gated_pair")
+    return True
+
+
+def gemm_tcgen05_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, splits: int,
+                          bias: Optional[torch.Tensor] = None, next_w: Optional[torch.Tensor] = None,
+                          xhat: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None,
+                          m: Optional[int] = None) -> bool:
+    """resid += x . w^T (+ bias) for at most 16 rows, the sum over K in ``splits`` (4, 8, 16) parts by
+    the blocks of a thread-block cluster that exchange their parts through shared memory.  For the
+    norm that follows: ``xhat`` bfloat16 [M, N] = resid * next_w (the row's 1/RMS is applied by the
+    consumer) and ``sumsq`` float32 [ceil(N / 128) * splits, >= M], whose column m sums to the sum of
+    squares of row m.  Returns False when the kernel refuses the sizes or the layout."""
+    M = x.shape[0] if m is None else m
+    N, K = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
+            or x.shape[1] != K:
+        raise KernelError("gemm_tcgen05_residual: x and w must be bfloat16, K-major, with matching K")
+    if resid.dtype != torch.float32 or resid.shape[1] != N or resid.stride(1) != 1:
+        raise KernelError("gemm_tcgen05_residual: resid must be float32 [M, N] with unit inner stride")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tcgen05_residual: bias must be float32 [N]")
+    if xhat is not None:
+        if next_w is None or next_w.numel() != N or next_w.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("gemm_tcgen05_residual: xhat needs the norm's weight [N], float32 or bfloat16")
+        if xhat.dtype != torch.bfloat16 or xhat.shape[1] != N or xhat.stride(1) != 1:
+            raise KernelError("gemm_tcgen05_residual: xhat must be bfloat16 [M, N] with unit inner stride")
+    if sumsq is not None and (sumsq.dtype != torch.float32 or sumsq.stride(1) != 1 or sumsq.shape[1] < M
+                              or sumsq.shape[0] != ((N + 127) // 128) * splits):
+        raise KernelError("gemm_tcgen05_residual: sumsq must be float32 [ceil(N / 128) * splits, >= M]")
+    if M > 16 or splits not in (4, 8, 16) or (K + 63) // 64 < splits:
+        return False
+    rc = _lib().rb_gemm_tcgen05_residual(
+        _ptr(x), _ptr(w), _ptr(bias), M, N, K, x.stride(0), splits, _ptr(resid), resid.stride(0), _ptr(next_w),
+        1 if (next_w is not None and next_w.dtype == torch.float32) else 0, _ptr(xhat),
+        xhat.stride(0) if xhat is not None else 0, _ptr(sumsq), sumsq.stride(0) if sumsq is not None else 0, 0,
+        _ptr(status_word(x.device)), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "gemm_tcgen05_residual")
     return True

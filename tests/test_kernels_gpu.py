@@ -96,6 +96,37 @@ def test_gemm_tcgen05_gated_pair_of_blocks(M, I, K):
                                            torch.empty((40, I), dtype=torch.bfloat16, device=DEV)) is False
 
 
+@pytest.mark.parametrize("M,N,K,S,wdt", [(1, 4096, 4096, 8, torch.bfloat16), (8, 520, 1024, 4, torch.float32),
+                                         (16, 256, 12288, 16, torch.bfloat16), (3, 1000, 512, 8, torch.float32)])
+def test_gemm_tcgen05_adds_into_the_residual_stream(M, N, K, S, wdt):
+    """The product of few rows, added to the float32 residual by the blocks of a cluster, with what the
+    following norm needs: residual * weight in bfloat16 and the rows' sums of squares in shares."""
+    from rocml_b200 import kernels
+    x = rnd((M, K), 4, torch.bfloat16).to(DEV)
+    w = rnd((N, K), 5, torch.bfloat16, 0.05).to(DEV)
+    bias = rnd((N,), 6).to(DEV)
+    nw = (1 + 0.1 * rnd((N,), 7)).to(wdt).to(DEV)
+    resid0 = rnd((M, N), 8)
+    want = resid0.double() + x.cpu().double() @ w.cpu().double().t() + bias.cpu().double()
+    for _ in range(2):
+        resid = resid0.clone().to(DEV)
+        xhat = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        sumsq = torch.full((((N + 127) // 128) * S, M), float("nan"), dtype=torch.float32, device=DEV)
+        assert kernels.gemm_tcgen05_residual(x, w, resid, S, bias, nw, xhat, sumsq)
+        kernels.check_status(DEV)
+        scale = want.abs().clamp_min(1.0)
+        assert ((resid.cpu().double() - want).abs() / scale).max().item() < 1e-5
+        assert ((xhat.cpu().double() - want * nw.cpu().double()).abs() / scale).max().item() < 2 ** -7
+        got_ss = sumsq.cpu().double().sum(0)
+        assert ((got_ss - (want ** 2).sum(1)).abs() / (want ** 2).sum(1)).max().item() < 1e-5
+    # only the addition, nothing for a norm
+    resid = resid0.clone().to(DEV)
+    assert kernels.gemm_tcgen05_residual(x, w, resid, S, bias)
+    assert ((resid.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max().item() < 1e-5
+    assert kernels.gemm_tcgen05_residual(rnd((17, K), 1, torch.bfloat16).to(DEV), w,
+                                         torch.zeros((17, N), device=DEV), S) is False
+
+
 def test_gemm_tcgen05_refuses_unaligned_k():
     from rocml_b200 import kernels
     x = rnd((4, 100), 1, torch.bfloat16).to(DEV)  # K = 100: rows are not a multiple of 16 bytes
