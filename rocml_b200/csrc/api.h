@@ -34,7 +34,8 @@ int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, 
                     int gated, int* status, void* stream);
 
 int rb_gemm_tcgen05_gated_pair(const void* x, const void* w, const float* bias, void* h, int M, int N, int K,
-                               long long ldx, long long ldh, int stages, int* status, void* stream);
+                               long long ldx, long long ldh, const float* row_sumsq, int row_groups,
+                               long long row_sumsq_ld, float row_eps, int stages, int* status, void* stream);
 
 int rb_gemm_tcgen05_residual(const void* x, const void* w, const float* bias, int M, int N, int K, long long ldx,
                              int splits, float* resid, long long ld_resid, const void* next_w, int next_w_f32,
@@ -65,7 +66,8 @@ int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const 
 
 int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, int row_stride, const void* q_norm_w,
                               const void* k_norm_w, int w_f32, float eps, const float* cos_sin, int write_kv,
-                              void* k_cache, void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
+                              const float* row_sumsq, int row_groups, long long row_sumsq_ld, float row_eps,
+                              int row_width, void* k_cache, void* v_cache, const int* block_table, int max_pages, const int* seq_slot,
                               const int* cu_q, const int* kv_len, int B, int nq, int nkv, int hd, float scale,
                               int window, int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
                               int* counters, void* out, int o_stride, void* stream);

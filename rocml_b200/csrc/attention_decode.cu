@@ -68,11 +68,18 @@ struct Projections {
     int write_kv;             // 0: this layer reads a cache that another layer wrote
     __nv_bfloat16* k_out;     // the cache to write (k_cache / v_cache of the call)
     __nv_bfloat16* v_out;
+    // The rows the projection was made from may still lack their norm's 1/RMS (they were residual *
+    // weight): then the sums are scaled by it here, from shares of the rows' sums of squares.
+    const float* row_sumsq;   // [row_groups][tokens], or null
+    int row_groups;
+    long long row_sumsq_ld;
+    float row_eps, row_inv_width;
 };
 
 // One head of 128 values, 4 per lane: the sum of the partial sums, then (what != 2) RMSNorm with `w`
 // and the rotation by the token's angles.  what: 0 query, 1 key, 2 value.
-__device__ __forceinline__ void project_head(const Projections& pj, const float* src, int what, int t, int lane, float* v) {
+__device__ __forceinline__ void project_head(const Projections& pj, const float* src, int what, int t, int lane,
+                                             float rstd, float* v) {
     v[0] = v[1] = v[2] = v[3] = 0.f;
     // the norm's weights and the token's angles do not depend on the sums: their loads go out first
     const void* w = what == 0 ? pj.q_norm_w : (what == 1 ? pj.k_norm_w : nullptr);
@@ -105,6 +112,7 @@ __device__ __forceinline__ void project_head(const Projections& pj, const float*
 #pragma unroll
         for (int j = 0; j < 8; ++j) { v[0] += f[j].x; v[1] += f[j].y; v[2] += f[j].z; v[3] += f[j].w; }
     }
+    v[0] *= rstd; v[1] *= rstd; v[2] *= rstd; v[3] *= rstd;
     if (w != nullptr) {
         const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
         const float inv = rsqrtf(ss / 128.f + pj.eps);
@@ -201,9 +209,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     pdl_wait();
     if (FQ) {
         const float* row = pj.proj + (size_t)t * pj.row_stride;
+        float rstd = 1.f;
+        if (pj.row_sumsq != nullptr) {                      // every warp for itself: a few loads and a reduction
+            float acc = 0.f;
+            for (int gi = lane; gi < pj.row_groups; gi += 32) acc += pj.row_sumsq[(size_t)gi * pj.row_sumsq_ld + t];
+            rstd = rsqrtf(warp_sum(acc) * pj.row_inv_width + pj.row_eps);
+        }
         for (int r = warp; r < ROWS; r += WARPS) {          // the query heads of this block
             float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (r < rows_valid) project_head(pj, row + (size_t)(h0 + r) * HD + lane * 4, 0, t, lane, v);
+            if (r < rows_valid) project_head(pj, row + (size_t)(h0 + r) * HD + lane * 4, 0, t, lane, rstd, v);
             const int chunk = lane >> 1;                    // 8 values per 16-byte chunk, 4 per lane
             *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(Qs) + r * (HD * 2) + ((chunk ^ (r & 7)) << 4) +
                                       (lane & 1) * 8) = pack4_bf16(v);
@@ -214,7 +228,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             if (page >= 0) {
                 float v[4];
                 const int head = warp == 0 ? nq + kvh : nq + nkv + kvh;
-                project_head(pj, row + (size_t)head * HD + lane * 4, warp == 0 ? 1 : 2, t, lane, v);
+                project_head(pj, row + (size_t)head * HD + lane * 4, warp == 0 ? 1 : 2, t, lane, rstd, v);
                 __nv_bfloat16* dst = (warp == 0 ? pj.k_out : pj.v_out) +
                                      (((size_t)page * nkv + kvh) * RB_PAGE + (pos % RB_PAGE)) * HD;
                 *reinterpret_cast<uint2*>(dst + lane * 4) = pack4_bf16(v);
@@ -560,10 +574,14 @@ extern "C" int rb_attention_decode(const void* q, int q_stride, const void* k_ca
 // nq query heads are there).  The kernel adds them, normalises (norm weights [128], float32 if
 // w_f32 else bfloat16, or null) and rotates (cos_sin [T][64] pairs, or null) the query heads itself,
 // and writes the new token's key and value into the cache (write_kv != 0) before reading it.
+// With row_sumsq (shares [row_groups][>= T] of the sums of squares of the rows the projection was made
+// from, over row_width values each) the sums are first scaled by rsqrt(sum / row_width + row_eps).
 // Returns RB_ERR_BAD_SIZE for other head sizes, RB_ERR_BAD_ALIGN for partial sums off 16 bytes.
 extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long in_stride, int row_stride,
                                          const void* q_norm_w, const void* k_norm_w, int w_f32, float eps,
-                                         const float* cos_sin, int write_kv, void* k_cache, void* v_cache,
+                                         const float* cos_sin, int write_kv, const float* row_sumsq, int row_groups,
+                                         long long row_sumsq_ld, float row_eps, int row_width,
+                                         void* k_cache, void* v_cache,
                                          const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                                          const int* kv_len, int B, int nq, int nkv, int hd, float scale, int window,
                                          int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
@@ -578,6 +596,9 @@ extern "C" int rb_attention_decode_fused(const float* proj, int n_in, long long 
     pj.write_kv = write_kv;
     pj.k_out = static_cast<__nv_bfloat16*>(k_cache);
     pj.v_out = static_cast<__nv_bfloat16*>(v_cache);
+    pj.row_sumsq = row_sumsq; pj.row_groups = row_groups; pj.row_sumsq_ld = row_sumsq_ld;
+    pj.row_eps = row_eps; pj.row_inv_width = row_width > 0 ? 1.f / (float)row_width : 0.f;
+    if (row_sumsq != nullptr && (row_groups < 1 || row_width < 1)) return RB_ERR_BAD_SIZE;
     return decode_entry(nullptr, 0, k_cache, v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, B, nq, nkv, hd,
                         scale, window, n_chunks, pages_per_block, part_acc, part_ml, counters, out, o_stride, pj, stream);
 }

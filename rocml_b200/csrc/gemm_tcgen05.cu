@@ -59,6 +59,11 @@ struct Params {
     long long xhat_ld;
     float* sumsq;                 // [feature groups][tokens]: sums of squares of the new residual rows
     long long sumsq_ld;
+    // CS == 2: the input rows still lack the norm's 1/RMS; it is applied to the product instead
+    const float* row_sumsq;       // [row_groups][tokens] shares of the input rows' sums of squares, or null
+    int row_groups;
+    long long row_sumsq_ld;
+    float row_eps, row_inv_width; // 1/RMS = rsqrt(sum * row_inv_width + row_eps)
 };
 
 // 16 consecutive outputs as 16-byte stores (dst is 16-byte aligned).
@@ -103,6 +108,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
     uint32_t* abort_flag = tmem_slot + 1;
     float* handover = (float*)(smem + S * C::STAGE + 256);   // CS: [BN][128] floats from the other half
+    __shared__ float s_rstd[CS == 2 ? BN : 1];               // CS == 2: the tokens' 1/RMS
 
     rb::pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -220,6 +226,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         } else if (CS != 0) {
             // the second half hands its accumulator over; the first half goes on after the barrier
+            if (blockIdx.z == 0 && p.row_sumsq != nullptr) {
+                // meanwhile: the 1/RMS of this tile's tokens, from the shares the kernel before left
+                rb::pdl_wait();
+                for (int j = quarter; j < BN; j += 4) {
+                    const int tok = b0 + j;
+                    float acc = 0.f;
+                    if (tok < p.b_rows)
+                        for (int gi = lane; gi < p.row_groups; gi += 32) acc += p.row_sumsq[(size_t)gi * p.row_sumsq_ld + tok];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (lane == 0) s_rstd[j] = rsqrtf(acc * p.row_inv_width + p.row_eps);
+                }
+            }
             if (!aborted && n_kb > 0 && blockIdx.z != 0) {
                 const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
                 const uint32_t dst = map_to_cta(smem_u32(handover + quarter * 32 + lane), 0);
@@ -368,7 +387,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tmem_ld16(lane_addr + c * 16, v);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float mine = v[i] + other[(c * 16 + i) * 128] + bv;     // first half + second half
+                    const float rs = p.row_sumsq != nullptr ? s_rstd[c * 16 + i] : 1.f;
+                    const float mine = (v[i] + other[(c * 16 + i) * 128]) * rs + bv;   // first half + second half
                     const float up = __shfl_down_sync(0xffffffffu, mine, 16);
                     const int tok = b0 + c * 16 + i;
                     if (lane < 16 && tok < p.b_rows && ar < p.a_rows)
@@ -952,6 +972,10 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out,
 // is [M, N / 2] = silu(gate) * up (bfloat16, no split).
 // Refuses (RB_ERR_BAD_ALIGN) what TMA cannot address: K or ldx not a multiple of 8 elements,
 // or a base pointer off a 16-byte boundary; the caller then uses the plain kernel.
+struct RowScale {
+    const float* sumsq; int groups; long long ld; float eps; int width;
+};
+
 struct ResidualOut {
     float* resid; long long resid_ld;
     const void* next_w; int next_w_f32;
@@ -962,7 +986,7 @@ struct ResidualOut {
 static int gemm_entry(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
                       int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
                       int stages, int gated, int* status, void* stream, int cluster_split,
-                      const ResidualOut* ro = nullptr) {
+                      const ResidualOut* ro = nullptr, const RowScale* rsc = nullptr) {
     if (M <= 0 || N <= 0) return RB_OK;
     if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
     if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
@@ -993,6 +1017,12 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
         p.a_rows = M; p.b_rows = N;
         if ((rc = tensor_map(x, M, K, ldx, BM, &ma)) != RB_OK) return rc;
         if ((rc = tensor_map(w, N, K, K, bn, &mb)) != RB_OK) return rc;
+    }
+    p.row_sumsq = nullptr; p.row_groups = 0; p.row_sumsq_ld = 0; p.row_eps = 0.f; p.row_inv_width = 0.f;
+    if (rsc != nullptr && rsc->sumsq != nullptr) {
+        if (cluster_split != 2 || rsc->groups < 1 || rsc->width < 1) return RB_ERR_BAD_SIZE;
+        p.row_sumsq = rsc->sumsq; p.row_groups = rsc->groups; p.row_sumsq_ld = rsc->ld;
+        p.row_eps = rsc->eps; p.row_inv_width = 1.f / (float)rsc->width;
     }
     p.resid = nullptr; p.next_w = nullptr; p.xhat = nullptr; p.sumsq = nullptr;
     p.resid_ld = p.xhat_ld = p.sumsq_ld = 0; p.next_w_f32 = 0;
@@ -1061,12 +1091,17 @@ extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, 
 
 // h[M, N / 2] = silu(gate) * up (bfloat16, row stride ldh) for at most 32 rows and a gate/up weight
 // whose rows alternate in blocks of 16, with the sum over K done in two halves by the two blocks of a
-// thread-block cluster (see the kernel).  RB_ERR_BAD_SIZE for more rows, N not a multiple of 32, or
-// K of a single 64-wide block; RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
+// thread-block cluster (see the kernel).  With row_sumsq (shares [row_groups][>= M] of the sums of squares
+// of the rows that x was made from, row_sumsq_ld apart) x is taken as not yet divided by its rows' RMS
+// over K values: the product is scaled by rsqrt(sum / K + row_eps) before the bias.
+// RB_ERR_BAD_SIZE for more rows, N not a multiple of 32, or K of a single 64-wide block;
+// RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
 extern "C" int rb_gemm_tcgen05_gated_pair(const void* x, const void* w, const float* bias, void* h, int M, int N,
-                                          int K, long long ldx, long long ldh, int stages, int* status,
-                                          void* stream) {
-    return gemm_entry(x, w, bias, h, RB_BF16, M, N, K, ldx, ldh, 1, 0, stages, 0, status, stream, 2);
+                                          int K, long long ldx, long long ldh, const float* row_sumsq,
+                                          int row_groups, long long row_sumsq_ld, float row_eps, int stages,
+                                          int* status, void* stream) {
+    RowScale rsc{row_sumsq, row_groups, row_sumsq_ld, row_eps, K};
+    return gemm_entry(x, w, bias, h, RB_BF16, M, N, K, ldx, ldh, 1, 0, stages, 0, status, stream, 2, nullptr, &rsc);
 }
 
 // resid[M, N] += x[M, K] . w[N, K]^T (+ bias) for at most 16 rows, the sum over K in `splits` (4, 8

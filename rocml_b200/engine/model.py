@@ -105,8 +105,15 @@ class Model:
         resid = torch.empty((T, self.hidden), dtype=torch.float32, device=self.env.device)
         kernels.embedding(batch.token_ids, self.embed, resid, self.status)
         pending = None
-        for i, e in enumerate(self.spec.schedule):
-            pending = self.blocks[e.layer].forward(resid, pending, batch, cache.views[i])
+        sched = self.spec.schedule
+        for i, e in enumerate(sched):
+            block = self.blocks[e.layer]
+            if getattr(block, "chains", False):
+                # a block may prepare the first norm of the block that follows it
+                nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
+                pending = block.forward(resid, pending, batch, cache.views[i], next_block=nxt)
+            else:
+                pending = block.forward(resid, pending, batch, cache.views[i])
         if batch.n_want == 0:
             return None
         xn = self.final_norm.forward(resid, pending, n_rows=batch.n_want, rows=batch.want_rows, write_back=False)

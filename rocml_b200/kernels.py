@@ -93,11 +93,12 @@ def _lib():
                                                  _i, _i, _i, _f, _i, _vp, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
                                             _i, _vp, _vp, _vp, _vp, _i, _vp]
-        lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp,
+        lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _i, _ll, _f, _i,
+                                                  _vp, _vp, _vp, _i, _vp, _vp,
                                                   _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
-        lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _i, _ll, _f, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_residual.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _ll, _vp, _i, _vp, _ll, _vp,
                                                  _ll, _i, _vp, _vp]
         _sigs_done = True
@@ -370,12 +371,14 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
                            k_norm_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
                            write_kv: bool, scale: float, window: int, n_chunks: int,
                            part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor],
-                           pages_per_block: int = 1) -> bool:
+                           pages_per_block: int = 1, rowscale=None, row_width: int = 0) -> bool:
     """attention_decode for head size 128 that takes the step's projections as the matrix product left
     them: ``proj`` float32 [S, T, (nq + 2 nkv) * 128] partial sums (or [T, ...]; only the nq query heads
     when ``write_kv`` is off).  The kernel adds them, applies the per-head norm and the rotation
     (``cos_sin`` float32 [T, 64, 2] from rope_table) to the queries, and writes the new token's key and
     value into its page before reading it: the work of qk_norm_rope_cache, without a kernel in between.
+    ``rowscale`` = (sumsq float32 [G, >= T], eps) with ``row_width``: the rows the projection was made
+    from were residual * norm weight; the sums are scaled by rsqrt(sum / row_width + eps) first.
     Returns False when the kernel does not take the sizes (use the two kernels)."""
     if hd != 128 or proj.dtype != torch.float32 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 \
             or out.stride(-1) != 1 or n_seqs * nq > _COUNTER_INTS:
@@ -397,7 +400,8 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
         raise KernelError("attention_decode_fused: cos_sin must be float32 [T, 64, 2]")
     rc = _lib().rb_attention_decode_fused(
         _ptr(proj), n_in, in_stride, row_stride, _ptr(q_norm_w), _ptr(k_norm_w), w_f32, float(eps), _ptr(cos_sin),
-        1 if write_kv else 0, _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
+        1 if write_kv else 0, *_row_scale(rowscale, n_seqs, "attention_decode_fused"), int(row_width),
+        _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
         int(window), int(n_chunks), int(pages_per_block), _ptr(part_acc), _ptr(part_ml),
         _ptr(decode_counters(out.device)), _ptr(out), out.stride(0), _stream())
@@ -512,12 +516,25 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
     return True
 
 
+def _row_scale(rowscale, m: int, what: str):
+    """(pointer, groups, stride, eps) of a deferred 1/RMS: ``rowscale`` = (sumsq float32 [G, >= M], eps)."""
+    if rowscale is None:
+        return None, 0, 0, 0.0
+    sumsq, eps = rowscale
+    if sumsq.dtype != torch.float32 or sumsq.dim() != 2 or sumsq.stride(1) != 1 or sumsq.shape[1] < m:
+        raise KernelError(f"{what}: the rows' sums of squares must be float32 [groups, >= rows]")
+    return _ptr(sumsq), sumsq.shape[0], sumsq.stride(0), float(eps)
+
+
 def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                            m: Optional[int] = None) -> bool:
+                            m: Optional[int] = None, rowscale=None) -> bool:
     """h = silu(gate) * up for at most 32 rows, w's rows alternating in blocks of 16 between gate and
     up, with the sum over K done in two halves by two blocks that form a thread-block cluster: the
     second hands its half to the first through shared memory, so no partial sums go through global
-    memory.  h is bfloat16 [M, N / 2].  Returns False when the kernel refuses the sizes or the layout."""
+    memory.  h is bfloat16 [M, N / 2].  ``rowscale`` = (sumsq float32 [G, >= M], eps): x's rows are
+    residual * norm weight, not yet divided by their RMS; column m of sumsq sums to row m's sum of
+    squares over K values, and the product is scaled by rsqrt(sum / K + eps) before the bias.
+    Returns False when the kernel refuses the sizes or the layout."""
     M = x.shape[0] if m is None else m
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
@@ -529,7 +546,8 @@ def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, b
         raise KernelError("gemm_tcgen05_gated_pair: bias must be float32 [N]")
     if M > 32 or N % 32 or K <= 64:
         return False
-    rc = _lib().rb_gemm_tcgen05_gated_pair(_ptr(x), _ptr(w), _ptr(bias), _ptr(h), M, N, K, x.stride(0), h.stride(0), 0,
+    rc = _lib().rb_gemm_tcgen05_gated_pair(_ptr(x), _ptr(w), _ptr(bias), _ptr(h), M, N, K, x.stride(0), h.stride(0),
+                                           *_row_scale(rowscale, M, "gemm_tcgen05_gated_pair"), 0,
                                            _ptr(status_word(x.device)), _stream())
     if rc in (10001, 10003):
         return False

@@ -1,7 +1,8 @@
 """Parts a layer is put together from: mixers, feed-forwards, norms, position encodings,
 and their arrangement in a block.  Importing this package registers the built-in kinds."""
 from .base import (
-    BuildEnv, FeedForward, Mixer, Norm, Part, PositionEncoding, build_block, build_feed_forward,
+    BuildEnv, DeferredNorm, FeedForward, Mixer, Norm, Part, PositionEncoding, ResidualSink, build_block,
+    build_feed_forward,
     build_mixer, build_norm, build_position, register_arrangement, register_feed_forward,
     register_mixer, register_norm, register_position, registered,
 )
@@ -13,7 +14,7 @@ from .mlp import GatedMLP
 from .block import PreNormBlock
 
 __all__ = [
-    "BuildEnv", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "build_block",
+    "BuildEnv", "DeferredNorm", "ResidualSink", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "build_block",
     "build_feed_forward", "build_mixer", "build_norm", "build_position", "register_arrangement",
     "register_feed_forward", "register_mixer", "register_norm", "register_position", "registered",
     "Linear", "RMSNorm", "NoPosition", "RotaryNeox", "Attention", "GatedMLP", "PreNormBlock",

@@ -21,7 +21,7 @@ from ..cache.requirements import KVRequirement
 from ..config.specs import MixerSpec
 from ..errors import ConfigError
 from ..weights.decl import TensorDecl
-from .base import BuildEnv, Mixer, build_position, register_mixer
+from .base import BuildEnv, DeferredNorm, Mixer, build_position, register_mixer
 from .linear import Linear
 
 DECODE_CHUNK = 64   # keys per split of decode attention (one page); fixed, so a row's sums never depend on the batch
@@ -81,26 +81,47 @@ class Attention(Mixer):
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()
 
-    def forward(self, xn, batch, view):
+    can_sink = True        # forward() accepts sink=ResidualSink (see parts.base)
+
+    def takes_deferred(self, batch) -> bool:
+        """Whether forward() can be handed a DeferredNorm for this step: the decode kernel that takes
+        the projections applies the rows' 1/RMS, which a bias inside the projection would spoil."""
+        return (batch.is_decode and self.hd == 128 and not self.bias and self.env.act_dtype == torch.bfloat16
+                and self.qkv.weight is not None and self.qkv.weight.dtype == torch.bfloat16
+                and self.qkv._splits(batch.n_tokens) > 1
+                and (self.position.inv_freq is None or self.position.rot_dim == self.hd))
+
+    def forward(self, xn, batch, view, sink=None):
         T = batch.n_tokens
-        dev, act = xn.device, self.env.act_dtype
+        dev, act = self.env.device, self.env.act_dtype
         qd = self.nq * self.hd
-        proj = self.qkv.forward_auto(xn, T)          # [T, N] or [S, T, N] partial sums
         attn = torch.empty((T, qd), dtype=act, device=dev)
         window = int(self.window) if self.window else 0
         writes = view.writes and not self.shares_cache
-        if batch.is_decode and self._decode_fused(proj, attn, batch, view, window, writes):
-            return self.o.forward_delta(attn, T)
-        q = proj if proj.dim() == 2 else torch.empty((T, qd), dtype=act, device=dev)
-        kernels.qk_norm_rope_cache(
-            proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
-            self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
-            view.block_table, view.k, view.v, write_kv=writes,
-            cos_sin=self.position.cos_sin(batch))
-        self.attend(q, attn, batch, view, window)
+        done = False
+        if isinstance(xn, DeferredNorm):
+            proj = self.qkv.forward_auto(xn.x, T)
+            done = self._decode_fused(proj, attn, batch, view, window, writes, xn.rowscale, xn.width)
+            if not done:
+                xn = xn.materialize()     # the kernel declined after all: the norm's own kernel, then as always
+        if not done:
+            proj = self.qkv.forward_auto(xn, T)      # [T, N] or [S, T, N] partial sums
+            done = batch.is_decode and self._decode_fused(proj, attn, batch, view, window, writes)
+        if not done:
+            q = proj if proj.dim() == 2 else torch.empty((T, qd), dtype=act, device=dev)
+            kernels.qk_norm_rope_cache(
+                proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+                self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
+                view.block_table, view.k, view.v, write_kv=writes,
+                cos_sin=self.position.cos_sin(batch))
+            self.attend(q, attn, batch, view, window)
+        if sink is not None:
+            deferred = self.o.forward_residual(attn, T, sink)
+            if deferred is not None:
+                return deferred
         return self.o.forward_delta(attn, T)
 
-    def _decode_fused(self, proj, out, batch, view, window, writes) -> bool:
+    def _decode_fused(self, proj, out, batch, view, window, writes, rowscale=None, row_width=0) -> bool:
         """One token per sequence, head size 128, float32 projections: the attention kernel itself
         adds the partial sums, normalises and rotates the queries and writes the new key and value,
         so no kernel stands between the projection and the attention.  False: not this time."""
@@ -120,7 +141,8 @@ class Attention(Mixer):
         return kernels.attention_decode_fused(
             proj, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q, batch.kv_len, batch.n_seqs,
             self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
-            self.position.cos_sin(batch) if rot else None, writes, self.scale, window, n_blocks, acc, ml, ppb)
+            self.position.cos_sin(batch) if rot else None, writes, self.scale, window, n_blocks, acc, ml, ppb,
+            rowscale=rowscale, row_width=row_width)
 
     def attend(self, q, out, batch, view, window):
         """Softmax attention of the step's queries over the cache.  One token per sequence:

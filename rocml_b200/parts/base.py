@@ -33,6 +33,40 @@ class BuildEnv:
         return "float32" if self.act_dtype == torch.float32 else "bfloat16"
 
 
+@dataclass
+class ResidualSink:
+    """An offer to a part: instead of returning its result as a delta, add it into ``resid`` itself and
+    prepare the input of ``norm``, the norm that follows, as a ``DeferredNorm``.  A part may decline by
+    returning a delta as always.  Only parts that set ``can_sink`` are made the offer."""
+
+    resid: torch.Tensor       # [T, H] float32
+    norm: "Norm"
+
+
+@dataclass
+class DeferredNorm:
+    """The output of a norm whose division by the rows' RMS has not happened yet: ``x`` is
+    residual * weight in the activations' type (the residual already holds every delta), and column t of
+    ``sumsq`` [groups, >= T] float32 sums to row t's sum of squares over ``width`` values.  A part that
+    multiplies ``x`` by a matrix applies rsqrt(sum / width + eps) to the product instead.  Only parts
+    whose ``takes_deferred(batch)`` says so are handed one."""
+
+    x: torch.Tensor
+    sumsq: torch.Tensor
+    eps: float
+    width: int
+    norm: "Norm"
+    resid: torch.Tensor
+
+    @property
+    def rowscale(self):
+        return self.sumsq, self.eps
+
+    def materialize(self) -> torch.Tensor:
+        """The rows as the norm itself would have produced them (one more kernel)."""
+        return self.norm.forward(self.resid, None, self.x.shape[0], write_back=False)
+
+
 class Part:
     """Common face: tensors declared, tensors loaded."""
 

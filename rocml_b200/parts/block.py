@@ -1,13 +1,14 @@
 """How a layer's parts are arranged."""
 from __future__ import annotations
 
+import os
 from typing import Dict, List
 
 import torch
 
 from ..config.specs import LayerSpec
 from ..weights.decl import TensorDecl
-from .base import BuildEnv, build_feed_forward, build_mixer, build_norm, register_arrangement
+from .base import BuildEnv, ResidualSink, build_feed_forward, build_mixer, build_norm, register_arrangement
 
 
 @register_arrangement("pre_norm")
@@ -50,8 +51,32 @@ class PreNormBlock:
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff))
 
-    def forward(self, resid, pending, batch, view):
-        xn = self.mixer_norm.forward(resid, pending, batch.n_tokens)
-        delta = self.mixer.forward(xn, batch, view)
-        xn = self.ff_norm.forward(resid, delta, batch.n_tokens)
+    chains = True          # forward() accepts next_block (see below)
+
+    def forward(self, resid, pending, batch, view, next_block=None):
+        """``pending`` is what the layer before left: a delta, or a DeferredNorm when it has added its
+        result into the residual itself and prepared this layer's first norm.  For a decode step of
+        few tokens the parts are offered to do the same for the norm that follows them
+        (ResidualSink), when the part after that norm can take the deferred rows: the norm kernels
+        then disappear from the step.  RB_DEFER=0 turns the offers off."""
+        T = batch.n_tokens
+        offers = batch.is_decode and T <= 16 and _defer_enabled()
+        xn = self.mixer_norm.forward(resid, pending, T)
+        if offers and getattr(self.mixer, "can_sink", False) and _takes(self.ff, batch):
+            delta = self.mixer.forward(xn, batch, view, sink=ResidualSink(resid, self.ff_norm))
+        else:
+            delta = self.mixer.forward(xn, batch, view)
+        xn = self.ff_norm.forward(resid, delta, T)
+        nxt = getattr(next_block, "mixer", None)
+        if offers and nxt is not None and getattr(self.ff, "can_sink", False) and _takes(nxt, batch):
+            return self.ff.forward(xn, batch, sink=ResidualSink(resid, next_block.mixer_norm))
         return self.ff.forward(xn, batch)
+
+
+def _takes(part, batch) -> bool:
+    f = getattr(part, "takes_deferred", None)
+    return bool(f(batch)) if f is not None else False
+
+
+def _defer_enabled() -> bool:
+    return os.environ.get("RB_DEFER", "1") != "0"

@@ -19,7 +19,7 @@ import torch
 from .. import kernels
 from ..errors import KernelError
 from ..weights.decl import TensorDecl
-from .base import BuildEnv
+from .base import BuildEnv, DeferredNorm
 
 
 _SM_COUNT = {}
@@ -89,14 +89,39 @@ class Linear:
             raise KernelError("the gated matrix product refused a layout that interleave_pairs accepted")
         return out
 
-    def forward_gated_pair(self, x: torch.Tensor, m: int) -> Optional[torch.Tensor]:
+    def forward_gated_pair(self, x: torch.Tensor, m: int, rowscale=None) -> Optional[torch.Tensor]:
         """The same for few rows when the sum over K is split in two: the two halves' blocks form a
         cluster and the activation is applied where they meet, so no second kernel waits for partial
         sums.  None when this step's product is split otherwise or the kernel refuses."""
         if not (self.paired and self._tensor_core(x)) or self._splits(m) != 2:
             return None
         out = torch.empty((m, self.n // 2), dtype=torch.bfloat16, device=x.device)
-        return out if kernels.gemm_tcgen05_gated_pair(x, self.weight, out, self.bias, m) else None
+        return out if kernels.gemm_tcgen05_gated_pair(x, self.weight, out, self.bias, m, rowscale=rowscale) else None
+
+    def residual_splits(self, m: int) -> int:
+        """In how many parts ``forward_residual`` would split the sum over K for m rows (0: it would not
+        take the step at all)."""
+        if m > 16 or self.weight is None or self.weight.dtype != torch.bfloat16 or self.k % 8:
+            return 0
+        # clusters of 8: larger ones leave too few of them resident at once (a cluster needs all its
+        # blocks on neighbouring multiprocessors)
+        s = self._splits(m)
+        s = 8 if s >= 8 else (4 if s >= 4 else 0)
+        return s if s and self.k // 64 >= s else 0
+
+    def forward_residual(self, x: torch.Tensor, m: int, sink) -> Optional[DeferredNorm]:
+        """sink.resid += x . W^T (+ bias) for a few rows, inside the product (the K splits exchange their
+        parts through shared memory), together with what ``sink.norm`` needs: returns its deferred
+        rows, or None when this step's product cannot be done that way (use ``forward_delta``)."""
+        s = self.residual_splits(m)
+        norm = sink.norm
+        if not s or not self._tensor_core(x) or not getattr(norm, "deferrable", False) or norm.weight is None:
+            return None
+        xhat = torch.empty((m, self.n), dtype=torch.bfloat16, device=x.device)
+        sumsq = torch.empty((((self.n + 127) // 128) * s, m), dtype=torch.float32, device=x.device)
+        if not kernels.gemm_tcgen05_residual(x, self.weight, sink.resid, s, self.bias, norm.weight, xhat, sumsq, m):
+            return None
+        return DeferredNorm(xhat, sumsq, norm.eps, self.n, norm, sink.resid)
 
     def adopt(self, weight: torch.Tensor) -> None:
         """Use an existing tensor as the weight (a tied head reads the embedding table)."""

@@ -9,7 +9,7 @@ from .. import kernels
 from ..config.specs import FeedForwardSpec
 from ..errors import ConfigError
 from ..weights.decl import TensorDecl
-from .base import BuildEnv, FeedForward, register_feed_forward
+from .base import BuildEnv, DeferredNorm, FeedForward, register_feed_forward
 from .linear import Linear
 
 
@@ -45,14 +45,27 @@ class GatedMLP(FeedForward):
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
-    def forward(self, xn, batch):
+    can_sink = True        # forward() accepts sink=ResidualSink (see parts.base)
+
+    def takes_deferred(self, batch) -> bool:
+        """Whether forward() can be handed a DeferredNorm for this step: only the product of two blocks
+        that applies the activation itself also applies the rows' 1/RMS."""
         T = batch.n_tokens
-        dev, act = xn.device, self.env.act_dtype
+        return (self.gate_up.paired and T <= 32 and self.gate_up.weight.dtype == torch.bfloat16
+                and self.gate_up._splits(T) == 2 and self.gate_up.k > 64)
+
+    def forward(self, xn, batch, sink=None):
+        T = batch.n_tokens
+        dev, act = self.env.device, self.env.act_dtype
         h = None
-        if self.gate_up.paired and T > 128:
+        if isinstance(xn, DeferredNorm):
+            h = self.gate_up.forward_gated_pair(xn.x, T, rowscale=xn.rowscale)
+            if h is None:
+                xn = xn.materialize()     # the kernel declined after all: the norm's own kernel, then as always
+        if h is None and self.gate_up.paired and T > 128:
             # many tokens: the activation happens in the product's epilogue, hidden behind the next tile
             h = self.gate_up.forward_gated(xn, T)
-        elif self.gate_up.paired:
+        elif h is None and self.gate_up.paired:
             # few tokens, the sum over K in two halves: the activation happens where the halves meet
             h = self.gate_up.forward_gated_pair(xn, T)
         if h is None:
@@ -60,4 +73,8 @@ class GatedMLP(FeedForward):
             gu = self.gate_up.forward_auto(xn, T)      # [T, 2I] or [S, T, 2I] partial sums
             h = torch.empty((T, self.inter), dtype=act, device=dev)
             kernels.silu_mul(gu, h, paired=self.gate_up.paired)
+        if sink is not None:
+            deferred = self.down.forward_residual(h, T, sink)
+            if deferred is not None:
+                return deferred
         return self.down.forward_delta(h, T)

@@ -8,7 +8,7 @@ import torch
 from .. import kernels
 from ..config.specs import NormSpec
 from ..weights.decl import TensorDecl
-from .base import BuildEnv, Norm, register_norm
+from .base import BuildEnv, DeferredNorm, Norm, register_norm
 
 
 @register_norm("rmsnorm")
@@ -33,7 +33,14 @@ class RMSNorm(Norm):
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
+    deferrable = True     # a product's epilogue can prepare this norm's input (see parts.base.DeferredNorm)
+
     def forward(self, resid, delta, n_rows: Optional[int] = None, rows=None, write_back=True):
+        if isinstance(delta, DeferredNorm):
+            # the part before has added its result into the residual already
+            if delta.norm is self and rows is None:
+                return delta            # and prepared this norm's rows: nothing to launch
+            delta = None
         n = (rows.numel() if rows is not None else resid.shape[0]) if n_rows is None else n_rows
         out = torch.empty((n, self.size), dtype=self.env.act_dtype, device=resid.device)
         kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows, n_rows=n, write_back=write_back)

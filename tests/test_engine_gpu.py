@@ -153,3 +153,63 @@ def test_long_decoding_from_the_first_token(model_folder, plain, dtype):
     err = rel_err(torch.stack(got), want)
     err_other = rel_err(torch.stack(got_other), want_other)
     assert err < TOL[dtype] and err_other < TOL[dtype], f"{name} {dtype}: {err} {err_other}"
+
+
+DEFER_CFG = {
+    "architectures": ["Qwen3ForCausalLM"], "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 3,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 300,
+    "max_position_embeddings": 512, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "attention_bias": False, "hidden_act": "silu",
+}
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_decode_without_norm_kernels(tmp_path, monkeypatch, graphs):
+    """Few tokens per step, head size 128: the products that feed the residual stream add into it
+    themselves and prepare the next norm's rows, whose 1/RMS the following product applies, so a layer
+    runs no norm kernel.  The library picks this from the weights' sizes; here a small model is made to
+    split its sums as a large one would.  Two sequences of unequal lengths, decoded next to each other
+    from their first token, against the plain implementation, and against the same engine with the
+    offers turned off."""
+    from plain_qwen3 import PlainQwen3
+    from rocml_b200 import Engine, StepEntry, kernels
+    from rocml_b200.parts.linear import Linear
+    folder = str(tmp_path / "m")
+    write_model(folder, DEFER_CFG, seed=5, std=0.06)
+    plain = PlainQwen3(folder, dtype=torch.float32)
+    monkeypatch.setattr(Linear, "_splits", lambda self, m: 1 if m > 16 else (2 if self.k == 256 else 8))
+    calls = {"residual": 0, "norm": 0}
+    real_res, real_norm = kernels.gemm_tcgen05_residual, kernels.add_rmsnorm
+    monkeypatch.setattr(kernels, "gemm_tcgen05_residual",
+                        lambda *a, **k: calls.__setitem__("residual", calls["residual"] + 1) or real_res(*a, **k))
+    monkeypatch.setattr(kernels, "add_rmsnorm",
+                        lambda *a, **k: calls.__setitem__("norm", calls["norm"] + 1) or real_norm(*a, **k))
+    vocab = DEFER_CFG["vocab_size"]
+    ids = [prompt(5, 140, vocab), prompt(6, 90, vocab)]
+    want = [plain.logits(x) for x in ids]
+    results = {}
+    for defer in ("1", "0"):
+        monkeypatch.setenv("RB_DEFER", defer)
+        calls["residual"] = calls["norm"] = 0
+        eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024, use_graphs=graphs)
+        slots = [eng.new_sequence(), eng.new_sequence()]
+        got = [[], []]
+        for t in range(140):
+            live = [j for j in range(2) if t < len(ids[j])]
+            out = eng.step([StepEntry(slots[j], [ids[j][t]], [0]) for j in live])
+            for r, j in enumerate(live):
+                got[j].append(out[r].clone())
+        results[defer] = [torch.stack(g) for g in got]
+        for j in range(2):
+            assert rel_err(results[defer][j], want[j]) < TOL["bfloat16"]
+        if defer == "1":
+            # two products a layer went into the residual (the last layer's feed-forward has no norm to
+            # prepare), and only the first layer's first norm and the final norm ran as kernels
+            n_layers = DEFER_CFG["num_hidden_layers"]
+            if not graphs:
+                assert calls["residual"] == 140 * (2 * n_layers - 1)
+                assert calls["norm"] == 140 * 2
+        else:
+            assert calls["residual"] == 0
+    for j in range(2):
+        assert rel_err(results["1"][j], results["0"][j].double().cpu()) < TOL["bfloat16"]
