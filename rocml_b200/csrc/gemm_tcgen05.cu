@@ -877,18 +877,20 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, in
     using C = Cfg<BN>;
     auto k = gemm_tcgen05_kernel<BN, SWAP, OT, GATED, CS>;
     constexpr int handover_bytes = CS != 0 ? BN * 128 * 4 : 0;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM + handover_bytes);
+    if (p.stages < 2 || p.stages > C::STAGES) return RB_ERR_BAD_SIZE;
+    const int smem_bytes = p.stages * C::STAGE + 1024 + 256 + handover_bytes;
+    // The kernel's shared-memory allowance is raised to what a launch needs, no further: how many
+    // clusters the device holds at once is worked out from the allowance, not from the launch.
+    static int allowance = 0;
+    if (smem_bytes > allowance) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return (int)e;
         if (CS > 8) {   // clusters of more than 8 blocks are not portable
             e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             if (e != cudaSuccess) return (int)e;
         }
-        attr_done = true;
+        allowance = smem_bytes;
     }
-    if (p.stages < 2 || p.stages > C::STAGES) return RB_ERR_BAD_SIZE;
-    const int smem_bytes = p.stages * C::STAGE + 1024 + 256 + handover_bytes;
     dim3 grid((p.a_rows + BM - 1) / BM, (p.b_rows + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     if (CS != 0) {
