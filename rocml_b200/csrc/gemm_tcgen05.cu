@@ -1029,19 +1029,24 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
     p.resid = nullptr; p.next_w = nullptr; p.xhat = nullptr; p.sumsq = nullptr;
     p.resid_ld = p.xhat_ld = p.sumsq_ld = 0; p.next_w_f32 = 0;
     if (ro != nullptr) {
-        if (!swap || bn != 16 || kb_total < cluster_split || ro->resid == nullptr) return RB_ERR_BAD_SIZE;
+        if (!swap || bn > 64 || kb_total < cluster_split || ro->resid == nullptr) return RB_ERR_BAD_SIZE;
         if (ro->xhat != nullptr && ro->next_w == nullptr) return RB_ERR_BAD_SIZE;
         p.resid = ro->resid; p.resid_ld = ro->resid_ld;
         p.next_w = ro->next_w; p.next_w_f32 = ro->next_w_f32;
         p.xhat = static_cast<__nv_bfloat16*>(ro->xhat); p.xhat_ld = ro->xhat_ld;
         p.sumsq = ro->sumsq; p.sumsq_ld = ro->sumsq_ld;
         p.splits = cluster_split;
-        switch (cluster_split) {
-            case 4: return launch<16, true, float, false, 4>(ma, mb, nullptr, p, 4, s);
-            case 8: return launch<16, true, float, false, 8>(ma, mb, nullptr, p, 8, s);
-            case 16: return launch<16, true, float, false, 16>(ma, mb, nullptr, p, 16, s);
-        }
+#define RB_RS(BN_)                                                                              \
+        switch (cluster_split) {                                                                \
+            case 4: return launch<BN_, true, float, false, 4>(ma, mb, nullptr, p, 4, s);        \
+            case 8: return launch<BN_, true, float, false, 8>(ma, mb, nullptr, p, 8, s);        \
+            case 16: return launch<BN_, true, float, false, 16>(ma, mb, nullptr, p, 16, s);     \
+        }                                                                                       \
         return RB_ERR_BAD_SIZE;
+        if (bn == 16) { RB_RS(16) }
+        if (bn == 32) { RB_RS(32) }
+        RB_RS(64)
+#undef RB_RS
     }
     if (cluster_split != 0) {
         if (cluster_split != 2 || !swap || bn > 32 || out_dtype != RB_BF16 || N % 32 || kb_total < 2) return RB_ERR_BAD_SIZE;
@@ -1106,7 +1111,7 @@ extern "C" int rb_gemm_tcgen05_gated_pair(const void* x, const void* w, const fl
     return gemm_entry(x, w, bias, h, RB_BF16, M, N, K, ldx, ldh, 1, 0, stages, 0, status, stream, 2, nullptr, &rsc);
 }
 
-// resid[M, N] += x[M, K] . w[N, K]^T (+ bias) for at most 16 rows, the sum over K in `splits` (4, 8
+// resid[M, N] += x[M, K] . w[N, K]^T (+ bias) for at most 64 rows, the sum over K in `splits` (4, 8
 // or 16) parts by the blocks of a thread-block cluster (see the kernel); resid is float32 with row
 // stride ld_resid.  For the norm that follows, optionally: xhat[M, N] = bfloat16(resid * next_w)
 // (next_w [N], float32 if next_w_f32 else bfloat16) and sumsq[(N / 128) * splits groups][M], each
@@ -1116,7 +1121,7 @@ extern "C" int rb_gemm_tcgen05_residual(const void* x, const void* w, const floa
                                         long long ldx, int splits, float* resid, long long ld_resid,
                                         const void* next_w, int next_w_f32, void* xhat, long long ld_xhat,
                                         float* sumsq, long long ld_sumsq, int stages, int* status, void* stream) {
-    if (M > 16 || (splits != 4 && splits != 8 && splits != 16)) return RB_ERR_BAD_SIZE;
+    if (M > 64 || (splits != 4 && splits != 8 && splits != 16)) return RB_ERR_BAD_SIZE;
     ResidualOut ro{resid, ld_resid, next_w, next_w_f32, xhat, ld_xhat, sumsq, ld_sumsq};
     return gemm_entry(x, w, bias, nullptr, RB_F32, M, N, K, ldx, 0, 1, 0, stages, 0, status, stream, splits, &ro);
 }

@@ -559,7 +559,7 @@ def gemm_tcgen05_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
                           bias: Optional[torch.Tensor] = None, next_w: Optional[torch.Tensor] = None,
                           xhat: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None,
                           m: Optional[int] = None) -> bool:
-    """resid += x . w^T (+ bias) for at most 16 rows, the sum over K in ``splits`` (4, 8, 16) parts by
+    """resid += x . w^T (+ bias) for at most 64 rows, the sum over K in ``splits`` (4, 8, 16) parts by
     the blocks of a thread-block cluster that exchange their parts through shared memory.  For the
     norm that follows: ``xhat`` bfloat16 [M, N] = resid * next_w (the row's 1/RMS is applied by the
     consumer) and ``sumsq`` float32 [ceil(N / 128) * splits, >= M], whose column m sums to the sum of
@@ -581,7 +581,7 @@ def gemm_tcgen05_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
     if sumsq is not None and (sumsq.dtype != torch.float32 or sumsq.stride(1) != 1 or sumsq.shape[1] < M
                               or sumsq.shape[0] != ((N + 127) // 128) * splits):
         raise KernelError("gemm_tcgen05_residual: sumsq must be float32 [ceil(N / 128) * splits, >= M]")
-    if M > 16 or splits not in (4, 8, 16) or (K + 63) // 64 < splits:
+    if M > 64 or splits not in (4, 8, 16) or (K + 63) // 64 < splits:
         return False
     rc = _lib().rb_gemm_tcgen05_residual(
         _ptr(x), _ptr(w), _ptr(bias), M, N, K, x.stride(0), splits, _ptr(resid), resid.stride(0), _ptr(next_w),

@@ -56,11 +56,11 @@ class PreNormBlock:
     def forward(self, resid, pending, batch, view, next_block=None):
         """``pending`` is what the layer before left: a delta, or a DeferredNorm when it has added its
         result into the residual itself and prepared this layer's first norm.  For a decode step of
-        few tokens the parts are offered to do the same for the norm that follows them
+        up to 16 tokens the parts are offered to do the same for the norm that follows them
         (ResidualSink), when the part after that norm can take the deferred rows: the norm kernels
         then disappear from the step.  RB_DEFER=0 turns the offers off."""
         T = batch.n_tokens
-        offers = batch.is_decode and T <= 16 and _defer_enabled()
+        offers = batch.is_decode and T <= 16 and _defer_enabled()     # beyond 16 tokens the norm kernels are cheaper (measured)
         xn = self.mixer_norm.forward(resid, pending, T)
         if offers and getattr(self.mixer, "can_sink", False) and _takes(self.ff, batch):
             delta = self.mixer.forward(xn, batch, view, sink=ResidualSink(resid, self.ff_norm))

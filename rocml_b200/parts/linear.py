@@ -101,7 +101,7 @@ class Linear:
     def residual_splits(self, m: int) -> int:
         """In how many parts ``forward_residual`` would split the sum over K for m rows (0: it would not
         take the step at all)."""
-        if m > 16 or self.weight is None or self.weight.dtype != torch.bfloat16 or self.k % 8:
+        if m > 64 or self.weight is None or self.weight.dtype != torch.bfloat16 or self.k % 8:
             return 0
         # clusters of 8: larger ones leave too few of them resident at once (a cluster needs all its
         # blocks on neighbouring multiprocessors)

@@ -97,7 +97,9 @@ def test_gemm_tcgen05_gated_pair_of_blocks(M, I, K):
 
 
 @pytest.mark.parametrize("M,N,K,S,wdt", [(1, 4096, 4096, 8, torch.bfloat16), (8, 520, 1024, 4, torch.float32),
-                                         (16, 256, 12288, 16, torch.bfloat16), (3, 1000, 512, 8, torch.float32)])
+                                         (16, 256, 12288, 16, torch.bfloat16), (3, 1000, 512, 8, torch.float32),
+                                         (33, 520, 1024, 8, torch.bfloat16), (64, 4096, 512, 8, torch.float32),
+                                         (20, 300, 2048, 16, torch.bfloat16)])
 def test_gemm_tcgen05_adds_into_the_residual_stream(M, N, K, S, wdt):
     """The product of few rows, added to the float32 residual by the blocks of a cluster, with what the
     following norm needs: residual * weight in bfloat16 and the rows' sums of squares in shares."""
@@ -123,8 +125,8 @@ def test_gemm_tcgen05_adds_into_the_residual_stream(M, N, K, S, wdt):
     resid = resid0.clone().to(DEV)
     assert kernels.gemm_tcgen05_residual(x, w, resid, S, bias)
     assert ((resid.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max().item() < 1e-5
-    assert kernels.gemm_tcgen05_residual(rnd((17, K), 1, torch.bfloat16).to(DEV), w,
-                                         torch.zeros((17, N), device=DEV), S) is False
+    assert kernels.gemm_tcgen05_residual(rnd((65, K), 1, torch.bfloat16).to(DEV), w,
+                                         torch.zeros((65, N), device=DEV), S) is False
 
 
 def test_gemm_tcgen05_refuses_unaligned_k():
