@@ -132,10 +132,75 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ r
     }
 }
 
+// The same for many rows (prompts): a row per block of 128 or 256 threads, each thread keeping up to
+// eight 16-byte groups of the row in registers, so that the row is read once, all its loads are in
+// flight together, and several rows share a multiprocessor.  Needs 16-byte alignment throughout and
+// H <= 8 * 4 * threads.
+template <typename OT, typename WT, int THREADS>
+__global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __restrict__ resid, const float* __restrict__ delta,
+                                                                   int n_delta, size_t delta_stride,
+                                                                   const WT* __restrict__ w, OT* __restrict__ out,
+                                                                   const int* __restrict__ rows, int H, float eps,
+                                                                   int write_back) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[33];
+    const int orow = blockIdx.x;
+    const int row = rows ? rows[orow] : orow;
+    if (row < 0) return;  // a padded entry
+    const int H4 = H >> 2;
+    float4* r4 = reinterpret_cast<float4*>(resid + (size_t)row * H);
+    float4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * THREADS;
+        v[j] = i < H4 ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int s = 0; s < n_delta; ++s) {                     // partial sums in their order
+        const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)s * delta_stride + (size_t)row * H);
+        float4 d[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = threadIdx.x + j * THREADS;
+            d[j] = i < H4 ? d4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[j].x += d[j].x; v[j].y += d[j].y; v[j].z += d[j].z; v[j].w += d[j].w; }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+    OT* o = out + (size_t)orow * H;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * THREADS;
+        if (i < H4) {
+            if (write_back) r4[i] = v[j];
+            store4(o + 4 * i, v[j].x * inv * to_f32(w[4 * i]), v[j].y * inv * to_f32(w[4 * i + 1]),
+                   v[j].z * inv * to_f32(w[4 * i + 2]), v[j].w * inv * to_f32(w[4 * i + 3]), true);
+        }
+    }
+}
+
 template <typename OT, typename WT>
 static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, size_t delta_stride,
                               const void* w, void* out, const int* rows, int n_rows, int H, float eps,
                               int write_back, cudaStream_t s) {
+    // many rows: the register kernel, when everything is 16-byte aligned and a row fits its threads
+    const bool aligned = (H & 3) == 0 && (delta_stride & 3) == 0 &&
+                         ((((uintptr_t)resid | (uintptr_t)delta) & 15) == 0) &&
+                         ((((uintptr_t)out | ((size_t)H * sizeof(OT))) & 15) == 0) && (((uintptr_t)w & (4 * sizeof(WT) - 1)) == 0);
+    if (n_rows > 64 && aligned && H <= 8 * 4 * 256) {
+        if (H <= 8 * 4 * 128)
+            RB_LAUNCH((add_rmsnorm_rows_kernel<OT, WT, 128>), dim3(n_rows), dim3(128), 0, s, resid, delta, n_delta,
+                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back);
+        else
+            RB_LAUNCH((add_rmsnorm_rows_kernel<OT, WT, 256>), dim3(n_rows), dim3(256), 0, s, resid, delta, n_delta,
+                      delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back);
+        RB_LAUNCH_CHECK();
+        return RB_OK;
+    }
     const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
     if (smem > 200 * 1024) return RB_ERR_BAD_SIZE;
     auto k = add_rmsnorm_kernel<OT, WT>;

@@ -179,12 +179,13 @@ def test_embedding_reports_a_bad_id():
     kernels.check_status(DEV)  # cleared
 
 
-@pytest.mark.parametrize("H", [72, 1000, 4096, 5120])
+@pytest.mark.parametrize("H,T", [(72, 7), (1000, 7), (4096, 7), (5120, 7), (4096, 150), (1000, 90), (5120, 70), (8200, 66)])
 @pytest.mark.parametrize("od,wd", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                    (torch.bfloat16, torch.float32)])
-def test_add_rmsnorm(H, od, wd):
+def test_add_rmsnorm(H, T, od, wd):
+    """Few rows (a block's shared memory holds the row) and many rows (the row stays in registers)."""
     from rocml_b200 import kernels
-    T, S, eps = 7, 3, 1e-5
+    S, eps = 3, 1e-5
     resid = rnd((T, H), 1, scale=2.0)
     delta = rnd((S, T, H), 2)
     w = (1 + 0.1 * rnd((H,), 3)).to(wd)
