@@ -113,6 +113,21 @@ class StepBatch:
 def pack_entries(slots: Sequence[int], old_lens: Sequence[int], token_lists: Sequence[Sequence[int]],
                  wants: Sequence[Sequence[int]]):
     """Flatten per-sequence token lists into the arrays of a step."""
+    for toks, want in zip(token_lists, wants):
+        n = len(toks)
+        for w in want:
+            if not 0 <= w < n:
+                raise ValueError(f"wanted place {w} is outside the {n} tokens given")
+    if sum(len(t) for t in token_lists) > 256:
+        # prompts: whole arrays at a time
+        lens = [len(t) for t in token_lists]
+        cu_q = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        token_ids = np.concatenate([np.asarray(t, dtype=np.int64) for t in token_lists])
+        positions = np.concatenate([np.arange(o, o + n, dtype=np.int64) for o, n in zip(old_lens, lens)])
+        slot_of_token = np.repeat(np.asarray(slots, dtype=np.int64), lens)
+        kv_len = [o + n for o, n in zip(old_lens, lens)]
+        want_rows = [int(cu_q[i]) + w for i, want in enumerate(wants) for w in want]
+        return token_ids, positions, slot_of_token, [int(c) for c in cu_q], kv_len, want_rows
     token_ids, positions, slot_of_token, cu_q, kv_len, want_rows = [], [], [], [0], [], []
     for slot, old, toks, want in zip(slots, old_lens, token_lists, wants):
         base = len(token_ids)
@@ -122,8 +137,5 @@ def pack_entries(slots: Sequence[int], old_lens: Sequence[int], token_lists: Seq
         slot_of_token.extend([slot] * n)
         cu_q.append(base + n)
         kv_len.append(old + n)
-        for w in want:
-            if not 0 <= w < n:
-                raise ValueError(f"wanted place {w} is outside the {n} tokens given")
-            want_rows.append(base + w)
+        want_rows.extend(base + w for w in want)
     return token_ids, positions, slot_of_token, cu_q, kv_len, want_rows

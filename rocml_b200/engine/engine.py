@@ -147,7 +147,11 @@ class Engine:
             seen.add(e.slot)
             if len(e.tokens) == 0:
                 raise RocmlError(f"slot {e.slot}: a step entry needs at least one token")
-            bad = [t for t in e.tokens if not 0 <= int(t) < vocab]
+            if len(e.tokens) > 64:
+                arr = np.asarray(e.tokens)
+                bad = arr[(arr < 0) | (arr >= vocab)][:1].tolist()
+            else:
+                bad = [t for t in e.tokens if not 0 <= int(t) < vocab]
             if bad:
                 raise RocmlError(f"slot {e.slot}: token id {bad[0]} is outside the vocabulary of {vocab}")
             for w in e.want:
