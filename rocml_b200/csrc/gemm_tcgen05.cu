@@ -64,6 +64,21 @@ struct Params {
     int row_groups;
     long long row_sumsq_ld;
     float row_eps, row_inv_width; // 1/RMS = rsqrt(sum * row_inv_width + row_eps)
+    // pair kernel, EPI == 2: the product is a prompt's q | k | v projection with heads of 128
+    __nv_bfloat16* q_out;         // [tokens][nq * 128], row stride q_ld
+    long long q_ld;
+    __nv_bfloat16* k_cache;       // [pages][nkv][64][128]
+    __nv_bfloat16* v_cache;
+    const int* positions;         // per token
+    const int* slot_of_token;     // per token, < 0: padding
+    const int* block_table;       // [slots][max_pages]
+    int max_pages;
+    const void* q_norm_w;         // [128] or null
+    const void* k_norm_w;
+    int norm_w_f32;
+    float norm_eps;
+    const float2* cos_sin;        // [tokens][64] (cos, sin), or null
+    int nq, nkv;
 };
 
 // 16 consecutive outputs as 16-byte stores (dst is 16-byte aligned).
@@ -617,7 +632,11 @@ constexpr int PAIR_STAGE = 2 * BM * BK * 2;       // A 128 x 64 + B half 128 x 6
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE + 1024 + 256;
 
-template <typename OT, bool GATED>
+// EPI: 0 plain, 1 SiLU(gate) * up (rows of the weight interleaved by 16), 2 a prompt's q | k | v projection
+// with heads of 128: a tile's 256 columns are two whole heads and an epilogue thread owns a token, so
+// the per-head RMSNorm and the rotation (pairs i, i + 64) are done on the accumulator itself, and
+// the queries go to their own tensor, keys and values straight into their cache pages.
+template <typename OT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          OT* __restrict__ out, const Params p) {
@@ -736,7 +755,77 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint32_t lane_addr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
             const bool vec_ok = (((uintptr_t)out | ((uintptr_t)p.ldo * sizeof(OT))) & 15) == 0;
             OT* row = out + (size_t)(ar < p.a_rows ? ar : 0) * p.ldo;
-            if (GATED) {
+            if (EPI == 2) {
+                int slot = -1, pos = 0, page = -2;         // page -2: not looked up yet
+                if (ar < p.a_rows) { slot = p.slot_of_token[ar]; pos = p.positions[ar]; }
+#pragma unroll 1
+                for (int hh = 0; hh < BN / 128; ++hh) {
+                    const int col0 = b0 + hh * 128;
+                    if (col0 >= p.b_rows) break;
+                    const int head = col0 >> 7;
+                    const int kind = head < p.nq ? 0 : (head < p.nq + p.nkv ? 1 : 2);
+                    __nv_bfloat16* dst = nullptr;
+                    if (slot >= 0) {
+                        if (kind == 0) {
+                            dst = p.q_out + (size_t)ar * p.q_ld + (size_t)head * 128;
+                        } else {
+                            if (page == -2) page = p.block_table[(size_t)slot * p.max_pages + (pos / RB_PAGE)];
+                            const int hk = kind == 1 ? head - p.nq : head - p.nq - p.nkv;
+                            if (page >= 0)
+                                dst = (kind == 1 ? p.k_cache : p.v_cache) +
+                                      (((size_t)page * p.nkv + hk) * RB_PAGE + (pos % RB_PAGE)) * 128;
+                        }
+                    }
+                    const uint32_t hbase = lane_addr + hh * 128;
+                    const void* w = kind == 0 ? p.q_norm_w : (kind == 1 ? p.k_norm_w : nullptr);
+                    float inv = 1.f;
+                    if (w != nullptr) {
+                        float ss = 0.f;
+#pragma unroll 1
+                        for (int c = 0; c < 8; ++c) {
+                            float v[16];
+                            tmem_ld16(hbase + c * 16, v);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const float x = v[i] + (add_bias ? p.bias[col0 + c * 16 + i] : 0.f);
+                                ss += x * x;
+                            }
+                        }
+                        inv = rsqrtf(ss / 128.f + p.norm_eps);
+                    }
+                    const bool rotate = kind != 2 && p.cos_sin != nullptr;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        float lo[16], hi[16];
+                        tmem_ld16(hbase + c * 16, lo);
+                        tmem_ld16(hbase + (c + 4) * 16, hi);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int d = c * 16 + i;
+                            float a = lo[i], b = hi[i];
+                            if (add_bias) { a += p.bias[col0 + d]; b += p.bias[col0 + 64 + d]; }
+                            if (w != nullptr) {
+                                const float wa = p.norm_w_f32 ? static_cast<const float*>(w)[d]
+                                                              : __bfloat162float(static_cast<const __nv_bfloat16*>(w)[d]);
+                                const float wb = p.norm_w_f32 ? static_cast<const float*>(w)[64 + d]
+                                                              : __bfloat162float(static_cast<const __nv_bfloat16*>(w)[64 + d]);
+                                a = a * inv * wa;
+                                b = b * inv * wb;
+                            }
+                            if (rotate) {
+                                const float2 cs = p.cos_sin[(size_t)(ar < p.a_rows ? ar : 0) * 64 + d];
+                                const float ra = a * cs.x - b * cs.y, rb2 = a * cs.y + b * cs.x;
+                                a = ra; b = rb2;
+                            }
+                            lo[i] = a; hi[i] = b;
+                        }
+                        if (dst != nullptr) {
+                            store16(dst + c * 16, lo);
+                            store16(dst + 64 + c * 16, hi);
+                        }
+                    }
+                }
+            } else if (EPI == 1) {
 #pragma unroll 1
                 for (int c = 0; c < BN / 16; c += 2) {
                     float g[16], u[16];
@@ -934,9 +1023,9 @@ bool pair_enabled() {
     return on;
 }
 
-template <typename OT, bool GATED>
+template <typename OT, int EPI>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, cudaStream_t s) {
-    auto k = gemm_tcgen05_pair_kernel<OT, GATED>;
+    auto k = gemm_tcgen05_pair_kernel<OT, EPI>;
     static bool attr_done = false;
     static int sms = 0;
     if (!attr_done) {
@@ -974,6 +1063,15 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* out,
 // is [M, N / 2] = silu(gate) * up (bfloat16, no split).
 // Refuses (RB_ERR_BAD_ALIGN) what TMA cannot address: K or ldx not a multiple of 8 elements,
 // or a base pointer off a 16-byte boundary; the caller then uses the plain kernel.
+struct RopeOut {
+    void* q_out; long long q_ld;
+    void* k_cache; void* v_cache;
+    const int* positions; const int* slot_of_token; const int* block_table; int max_pages;
+    const void* q_norm_w; const void* k_norm_w; int norm_w_f32; float norm_eps;
+    const float* cos_sin;
+    int nq, nkv;
+};
+
 struct RowScale {
     const float* sumsq; int groups; long long ld; float eps; int width;
 };
@@ -988,7 +1086,7 @@ struct ResidualOut {
 static int gemm_entry(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
                       int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
                       int stages, int gated, int* status, void* stream, int cluster_split,
-                      const ResidualOut* ro = nullptr, const RowScale* rsc = nullptr) {
+                      const ResidualOut* ro = nullptr, const RowScale* rsc = nullptr, const RopeOut* rope = nullptr) {
     if (M <= 0 || N <= 0) return RB_OK;
     if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
     if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
@@ -1054,14 +1152,36 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
         return bn == 16 ? launch<16, true, __nv_bfloat16, false, 2>(ma, mb, out, p, 2, s)
                         : launch<32, true, __nv_bfloat16, false, 2>(ma, mb, out, p, 2, s);
     }
+    p.q_out = nullptr; p.k_cache = p.v_cache = nullptr; p.positions = p.slot_of_token = p.block_table = nullptr;
+    p.q_norm_w = p.k_norm_w = nullptr; p.cos_sin = nullptr;
+    p.q_ld = 0; p.max_pages = 0; p.norm_w_f32 = 0; p.norm_eps = 0.f; p.nq = p.nkv = 0;
+    if (rope != nullptr) {
+        // a prompt's q | k | v projection: only the kernel of CTA pairs has this epilogue
+        if (swap || splits != 1 || bn != 256 || M <= 256 || !pair_enabled() || N % 128 || rope->nq < 1 || rope->nkv < 0 ||
+            (N != rope->nq * 128 && N != (rope->nq + 2 * rope->nkv) * 128))
+            return RB_ERR_BAD_SIZE;
+        if (((uintptr_t)rope->q_out & 15) || (rope->q_ld % 8) || ((uintptr_t)rope->k_cache & 15) || ((uintptr_t)rope->v_cache & 15) ||
+            ((uintptr_t)rope->cos_sin & 7))
+            return RB_ERR_BAD_ALIGN;
+        p.q_out = static_cast<__nv_bfloat16*>(rope->q_out); p.q_ld = rope->q_ld;
+        p.k_cache = static_cast<__nv_bfloat16*>(rope->k_cache); p.v_cache = static_cast<__nv_bfloat16*>(rope->v_cache);
+        p.positions = rope->positions; p.slot_of_token = rope->slot_of_token; p.block_table = rope->block_table;
+        p.max_pages = rope->max_pages;
+        p.q_norm_w = rope->q_norm_w; p.k_norm_w = rope->k_norm_w; p.norm_w_f32 = rope->norm_w_f32; p.norm_eps = rope->norm_eps;
+        p.cos_sin = reinterpret_cast<const float2*>(rope->cos_sin);
+        p.nq = rope->nq; p.nkv = rope->nkv;
+        CUtensorMap mb_half;
+        if ((rc = tensor_map(w, N, K, K, BM, &mb_half)) != RB_OK) return rc;
+        return launch_pair<__nv_bfloat16, 2>(ma, mb_half, nullptr, p, s);
+    }
     if (!swap && splits == 1 && bn == 256 && M > 256 && pair_enabled()) {
         // many tokens and a wide weight: pairs of CTAs; the weight is read in boxes of 128 rows (a half tile)
         CUtensorMap mb_half;
         if ((rc = tensor_map(w, N, K, K, BM, &mb_half)) != RB_OK) return rc;
         if (out_dtype == RB_BF16)
-            return gated ? launch_pair<__nv_bfloat16, true>(ma, mb_half, out, p, s)
-                         : launch_pair<__nv_bfloat16, false>(ma, mb_half, out, p, s);
-        if (out_dtype == RB_F32) return launch_pair<float, false>(ma, mb_half, out, p, s);
+            return gated ? launch_pair<__nv_bfloat16, 1>(ma, mb_half, out, p, s)
+                         : launch_pair<__nv_bfloat16, 0>(ma, mb_half, out, p, s);
+        if (out_dtype == RB_F32) return launch_pair<float, 0>(ma, mb_half, out, p, s);
     }
     if (!swap && splits == 1 && (bn == 256 || bn == 128)) {
         // many tokens: the persistent kernel with two accumulators (2 x 256 columns fill tensor memory)
@@ -1124,4 +1244,25 @@ extern "C" int rb_gemm_tcgen05_residual(const void* x, const void* w, const floa
     if (M > 64 || (splits != 4 && splits != 8 && splits != 16)) return RB_ERR_BAD_SIZE;
     ResidualOut ro{resid, ld_resid, next_w, next_w_f32, xhat, ld_xhat, sumsq, ld_sumsq};
     return gemm_entry(x, w, bias, nullptr, RB_F32, M, N, K, ldx, 0, 1, 0, stages, 0, status, stream, splits, &ro);
+}
+
+// A prompt's q | k | v projection with heads of 128 (more than 256 rows): x[M, K] . w[N, K]^T (+ bias),
+// N = (nq + 2 nkv) * 128, or nq * 128 for a layer that reads another layer's cache.  In the
+// product's epilogue every head of every token is normalised (q_norm_w / k_norm_w [128], float32 if
+// norm_w_f32 else bfloat16, or null: no norm; values are never normalised) and rotated (cos_sin
+// [M][64] pairs, or null), queries go to q_out [M][nq * 128] (row stride q_ld), keys and values into
+// their pages (k_cache, v_cache [pages][nkv][64][128]; the page of token t is
+// block_table[slot_of_token[t]][positions[t] / 64]; tokens with a negative slot are skipped).
+// RB_ERR_BAD_SIZE when the sizes do not fit this kernel (the caller runs the product and the
+// rotation kernel one after the other), RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
+extern "C" int rb_gemm_tcgen05_qkv_rope(const void* x, const void* w, const float* bias, int M, int N, int K,
+                                        long long ldx, void* q_out, long long q_ld, void* k_cache, void* v_cache,
+                                        const int* positions, const int* slot_of_token, const int* block_table,
+                                        int max_pages, const void* q_norm_w, const void* k_norm_w, int norm_w_f32,
+                                        float norm_eps, const float* cos_sin, int nq, int nkv, int stages,
+                                        int* status, void* stream) {
+    RopeOut rope{q_out, q_ld, k_cache, v_cache, positions, slot_of_token, block_table, max_pages,
+                 q_norm_w, k_norm_w, norm_w_f32, norm_eps, cos_sin, nq, nkv};
+    return gemm_entry(x, w, bias, nullptr, RB_BF16, M, N, K, ldx, 0, 1, 0, stages, 0, status, stream, 0, nullptr,
+                      nullptr, &rope);
 }

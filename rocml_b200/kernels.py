@@ -99,6 +99,8 @@ def _lib():
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _i, _ll, _f, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05_qkv_rope.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _vp,
+                                                 _vp, _i, _f, _vp, _i, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_residual.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _ll, _vp, _i, _vp, _ll, _vp,
                                                  _ll, _i, _vp, _vp]
         _sigs_done = True
@@ -591,4 +593,55 @@ def gemm_tcgen05_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
     if rc in (10001, 10003):
         return False
     _check(rc, "gemm_tcgen05_residual")
+    return True
+
+
+def gemm_tcgen05_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, nq: int, nkv: int,
+                          q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                          cos_sin: Optional[torch.Tensor], positions: torch.Tensor, slot_of_token: torch.Tensor,
+                          block_table: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                          v_cache: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
+                          m: Optional[int] = None) -> bool:
+    """A prompt's q | k | v projection (more than 256 rows, heads of 128) with the per-head norm, the
+    rotation and the cache write done in the product's epilogue: q_out bfloat16 [M, nq * 128] receives the
+    queries, the keys and values go into their pages.  w is [(nq + 2 nkv) * 128, K], or [nq * 128, K] for
+    a layer that only reads a cache (then the cache arguments are unused).  ``cos_sin`` float32
+    [M, 64, 2] from rope_table, or None for no rotation.  Returns False when the kernel does not take
+    the sizes (run the product and qk_norm_rope_cache instead)."""
+    M = x.shape[0] if m is None else m
+    N, K = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
+            or x.shape[1] != K:
+        raise KernelError("gemm_tcgen05_qkv_rope: x and w must be bfloat16, K-major, with matching K")
+    writes = N == (nq + 2 * nkv) * 128
+    if M <= 256 or N % 256 or not (writes or N == nq * 128) or K % 8:
+        return False
+    if q_out.dtype != torch.bfloat16 or q_out.stride(1) != 1 or q_out.shape[1] < nq * 128:
+        raise KernelError("gemm_tcgen05_qkv_rope: q_out must be bfloat16 rows of nq * 128 with unit inner stride")
+    if writes:
+        if k_cache is None or v_cache is None or block_table is None:
+            raise KernelError("gemm_tcgen05_qkv_rope: cache tensors missing")
+        if k_cache.dtype != torch.bfloat16 or not k_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, PAGE, 128) \
+                or k_cache.shape != v_cache.shape or not v_cache.is_contiguous():
+            raise KernelError("gemm_tcgen05_qkv_rope: cache must be bfloat16 [pages, nkv, 64, 128]")
+    if (q_norm_w is None) != (k_norm_w is None):
+        raise KernelError("gemm_tcgen05_qkv_rope: give both norm weights or neither")
+    w_f32 = 0
+    if q_norm_w is not None:
+        if q_norm_w.dtype != k_norm_w.dtype or q_norm_w.numel() != 128 or k_norm_w.numel() != 128:
+            raise KernelError("gemm_tcgen05_qkv_rope: norm weights must share a type and be [128]")
+        w_f32 = 1 if q_norm_w.dtype == torch.float32 else 0
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.numel() < M * 128):
+        raise KernelError("gemm_tcgen05_qkv_rope: cos_sin must be float32 [M, 64, 2]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tcgen05_qkv_rope: bias must be float32 [N]")
+    rc = _lib().rb_gemm_tcgen05_qkv_rope(
+        _ptr(x), _ptr(w), _ptr(bias), M, N, K, x.stride(0), _ptr(q_out), q_out.stride(0), _ptr(k_cache), _ptr(v_cache),
+        _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
+        None if block_table is None else _i32(block_table, "block_table"),
+        block_table.shape[1] if block_table is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), w_f32, float(eps),
+        _ptr(cos_sin), nq, nkv, 0, _ptr(status_word(x.device)), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "gemm_tcgen05_qkv_rope")
     return True

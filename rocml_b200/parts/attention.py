@@ -24,6 +24,12 @@ from ..weights.decl import TensorDecl
 from .base import BuildEnv, DeferredNorm, Mixer, build_position, register_mixer
 from .linear import Linear
 
+# From this many tokens in a step the q | k | v projection normalises, rotates and caches in its own
+# epilogue.  With fewer tokens a block has too few tiles to hide that epilogue behind the next tile's
+# main loop, and the rotation kernel after a plain product is as fast or faster (measured at 1,024 and
+# 2,048 tokens against 4,096).
+PROMPT_FUSED_MIN_TOKENS = 4096
+
 DECODE_CHUNK = 64   # keys per split of decode attention (one page); fixed, so a row's sums never depend on the batch
 
 
@@ -104,6 +110,8 @@ class Attention(Mixer):
             done = self._decode_fused(proj, attn, batch, view, window, writes, xn.rowscale, xn.width)
             if not done:
                 xn = xn.materialize()     # the kernel declined after all: the norm's own kernel, then as always
+        if not done and not batch.is_decode and self._prompt_fused(xn, attn, batch, view, window, writes):
+            done = True
         if not done:
             proj = self.qkv.forward_auto(xn, T)      # [T, N] or [S, T, N] partial sums
             done = batch.is_decode and self._decode_fused(proj, attn, batch, view, window, writes)
@@ -120,6 +128,28 @@ class Attention(Mixer):
             if deferred is not None:
                 return deferred
         return self.o.forward_delta(attn, T)
+
+    def _prompt_fused(self, xn, out, batch, view, window, writes) -> bool:
+        """Many tokens, head size 128: the projection's own epilogue normalises and rotates the heads
+        and writes keys and values into the cache, so the projections never go through memory.
+        False: not this time (other sizes, a partial rotation, few tokens)."""
+        if self.hd != 128 or self.env.act_dtype != torch.bfloat16 or not isinstance(xn, torch.Tensor) \
+                or xn.dtype != torch.bfloat16 or self.qkv.weight is None or self.qkv.weight.dtype != torch.bfloat16:
+            return False
+        rot = self.position.rot_dim if self.position.inv_freq is not None else 0
+        if rot not in (0, self.hd) or writes != (self.qkv.n == (self.nq + 2 * self.nkv) * self.hd):
+            return False
+        T = batch.n_tokens
+        if T < PROMPT_FUSED_MIN_TOKENS:
+            return False
+        q = torch.empty((T, self.nq * self.hd), dtype=torch.bfloat16, device=xn.device)
+        if not kernels.gemm_tcgen05_qkv_rope(
+                xn, self.qkv.weight, q, self.nq, self.nkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+                self.position.cos_sin(batch) if rot else None, batch.positions, batch.slot_of_token,
+                view.block_table, view.k, view.v, self.qkv.bias, T):
+            return False
+        self.attend(q, out, batch, view, window)
+        return True
 
     def _decode_fused(self, proj, out, batch, view, window, writes, rowscale=None, row_width=0) -> bool:
         """One token per sequence, head size 128, float32 projections: the attention kernel itself

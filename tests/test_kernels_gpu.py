@@ -129,6 +129,70 @@ def test_gemm_tcgen05_adds_into_the_residual_stream(M, N, K, S, wdt):
                                          torch.zeros((65, N), device=DEV), S) is False
 
 
+@pytest.mark.parametrize("M,nq,nkv,K,norm,rope,bias,writes", [
+    (300, 4, 2, 512, True, True, False, True), (1000, 6, 1, 264, True, True, True, True),
+    (513, 2, 2, 1024, False, True, False, True), (257, 4, 2, 256, True, False, False, False)])
+def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rope, bias, writes):
+    """A prompt's q | k | v projection whose epilogue does the per-head norm, the rotation and the cache
+    write, against the same arithmetic in float64; some tokens are padding and must leave no trace."""
+    from rocml_b200 import kernels
+    hd = 128
+    g = torch.Generator().manual_seed(M + K)
+    N = (nq + 2 * nkv) * hd if writes else nq * hd
+    x = (torch.randn((M, K), generator=g) * 0.5).bfloat16()
+    w = (torch.randn((N, K), generator=g) * 0.05).bfloat16()
+    b = torch.randn((N,), generator=g) * 0.1 if bias else None
+    qw = 1 + 0.1 * torch.randn(hd, generator=g) if norm else None
+    kw = 1 + 0.1 * torch.randn(hd, generator=g) if norm else None
+    # three sequences interleaved token by token: every (slot, page) has a page of its own and every
+    # token its own place in it
+    pos = torch.arange(M, dtype=torch.int32) // 3 + 40
+    slot = torch.arange(M, dtype=torch.int32) % 3
+    table = torch.full((3, 12), -1, dtype=torch.int32)
+    table[:, :10] = torch.randperm(30, generator=g).reshape(3, 10).to(torch.int32)
+    slot[5] = -1
+    slot[M - 1] = -1
+    n_pages = 31
+    kc = torch.zeros((n_pages, max(nkv, 1), 64, hd), dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    inv_freq = (1e4 ** (-torch.arange(0, hd // 2, dtype=torch.float64) * 2 / hd)).float().to(DEV)
+    cs = kernels.rope_table(pos.to(DEV), inv_freq, M) if rope else None
+    q = torch.zeros((M, nq * hd), dtype=torch.bfloat16, device=DEV)
+    assert kernels.gemm_tcgen05_qkv_rope(
+        x.to(DEV), w.to(DEV), q, nq, nkv, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, 1e-6, cs,
+        pos.to(DEV), slot.to(DEV), table.to(DEV) if writes else None, kc if writes else None, vc if writes else None,
+        b.to(DEV) if bias else None)
+    kernels.check_status(DEV)
+    proj = x.double() @ w.double().t() + (b.double() if bias else 0)
+    heads = proj.reshape(M, -1, hd)
+
+    def finish(h, wn):
+        if wn is not None:
+            h = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + 1e-6) * wn.double()
+        if rope:
+            ang = pos.double()[:, None] * inv_freq.cpu().double()[None, :]
+            c, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            lo, hi = h[..., :64], h[..., 64:]
+            h = torch.cat([lo * c - hi * sn, lo * sn + hi * c], -1)
+        return h
+    want_q = finish(heads[:, :nq], qw)
+    live = slot >= 0
+    got_q = q.cpu().double().reshape(M, nq, hd)
+    assert ((got_q[live] - want_q[live]).abs() / want_q[live].abs().clamp_min(1.0)).max() < 2 ** -7
+    assert got_q[~live].abs().sum() == 0
+    if writes:
+        want_k, want_v = finish(heads[:, nq:nq + nkv], kw), heads[:, nq + nkv:]
+        seen = 0
+        for t in range(M):
+            if slot[t] < 0:
+                continue
+            page, r = int(table[slot[t], pos[t] // 64]), int(pos[t] % 64)
+            assert ((kc[page, :, r].cpu().double() - want_k[t]).abs() / want_k[t].abs().clamp_min(1.0)).max() < 2 ** -7
+            assert ((vc[page, :, r].cpu().double() - want_v[t]).abs() / want_v[t].abs().clamp_min(1.0)).max() < 2 ** -7
+            seen += 1
+        assert int((kc.float().abs().sum(-1) > 0).sum()) <= seen * nkv     # nothing written elsewhere
+
+
 def test_gemm_tcgen05_refuses_unaligned_k():
     from rocml_b200 import kernels
     x = rnd((4, 100), 1, torch.bfloat16).to(DEV)  # K = 100: rows are not a multiple of 16 bytes

@@ -260,3 +260,27 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps():
         assert (torch.stack(got_a) - plain(a)[4:]).abs().max() < 1e-4
         assert (torch.stack(got_b) - plain(b)[10:]).abs().max() < 1e-4
         eng.release(sa); eng.release(sb)
+
+
+def test_prompt_projection_fused_and_separate_agree(tmp_path, monkeypatch):
+    """Long prompt pieces take the projection whose epilogue normalises, rotates and caches; shorter
+    ones the plain product and the rotation kernel.  Same logits either way, and both are the plain
+    implementation's."""
+    from plain_qwen3 import PlainQwen3
+    from rocml_b200 import Engine, StepEntry
+    from rocml_b200.parts import attention as A
+    from tiny_models import CONFIGS, prompt, write_model
+    folder = str(tmp_path / "m")
+    write_model(folder, CONFIGS["E"], seed=9, std=0.08)      # head size 128, a window on one layer
+    plain = PlainQwen3(folder, dtype=torch.float32)
+    ids = prompt(4, 600, CONFIGS["E"]["vocab_size"])
+    want = plain.logits(ids)[[0, 299, 599]]
+    got = {}
+    for name, least in (("fused", 1), ("separate", 10 ** 9)):
+        monkeypatch.setattr(A, "PROMPT_FUSED_MIN_TOKENS", least)
+        eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024)
+        s = eng.new_sequence()
+        got[name] = eng.step([StepEntry(s, ids, [0, 299, 599])]).float().cpu()
+        scale = want.abs().amax(-1, keepdim=True)
+        assert float(((got[name] - want).abs() / scale).max()) < 2.5e-2
+    assert float((got["fused"] - got["separate"]).abs().max() / want.abs().max()) < 2.5e-2
