@@ -182,10 +182,11 @@ def generate(executor: Executor, requests: Sequence[Request], default_stop: Iter
                              [s["req"].sampling for s in seqs], [s["rng"] for s in seqs],
                              [s["history"] for s in seqs], feed_from=feed_from)
 
+        t_batch = time.perf_counter()
         flying, handle = live, launch(live)      # the step whose tokens are read next
         first = True
         while flying:
-            t0 = time.perf_counter()
+            t0 = t_batch if first else time.perf_counter()     # the prompts' time includes their launch
             ahead = None
             if pipelined and all(_goes_on_for_sure(s, limit) for s in flying):
                 ahead = launch(flying, feed_from=handle)
