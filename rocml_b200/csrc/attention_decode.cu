@@ -136,7 +136,12 @@ __device__ __forceinline__ uint2 pack4_bf16(const float* v) {
     return raw;
 }
 
-template <int HD, bool CL, bool FQ>
+// PROP (long contexts of unequal lengths): the grid's x blocks of a head group are not tied to one
+// sequence each; they are shared out among the sequences in proportion to their pages, so that every
+// block reads about the same number of bytes whatever the lengths.  grid = (blocks, groups, 1).
+constexpr int PROP_MAX_SEQS = 256;
+
+template <int HD, bool CL, bool FQ, bool PROP>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
@@ -144,7 +149,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
                         float scale, int window, int n_chunks, int ppb, float* __restrict__ part_acc,
                         float* __restrict__ part_ml, int* __restrict__ counters,
-                        __nv_bfloat16* __restrict__ out, int o_stride, const Projections pj) {
+                        __nv_bfloat16* __restrict__ out, int o_stride, const Projections pj, int n_seqs) {
     pdl_trigger();
     // Everything up to pdl_wait() below may run while the kernels before this one in the stream are
     // still running.  It reads the step's integers (copied to the device before the step's first
@@ -160,24 +165,63 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __shared__ float s_m[WARPS][ROWS], s_l[WARPS][ROWS];
     __shared__ int s_last;
 
-    const int c = blockIdx.x;
     const int g = nq / nkv;
     const int head_chunks = (g + ROWS - 1) / ROWS;
     const int kvh = blockIdx.y / head_chunks;
     const int hc = blockIdx.y % head_chunks;
     const int h0 = kvh * g + hc * ROWS;                     // first query head of this block
     const int rows_valid = min(ROWS, g - hc * ROWS);
-    const int b = blockIdx.z;
+    int c = blockIdx.x, b = blockIdx.z;
+    int share = 0;                                          // PROP: blocks this sequence was given
+    if (PROP) {
+        // every block works out the same sharing: a block for every sequence that has pages, the
+        // rest in proportion to the pages
+        __shared__ int s_pages[PROP_MAX_SEQS];
+        for (int i = threadIdx.x; i < n_seqs; i += WARPS * 32) {
+            const int ps = kv_len[i] - 1;
+            int P = 0;
+            if (seq_slot[i] >= 0 && ps >= 0) P = ps / CHUNK - (window > 0 ? max(0, ps - window + 1) / CHUNK : 0) + 1;
+            s_pages[i] = P;
+        }
+        __syncthreads();
+        long long total = 0;
+        int nz = 0;
+        for (int i = 0; i < n_seqs; ++i) { total += s_pages[i]; nz += s_pages[i] > 0; }
+        const long long spare = (long long)gridDim.x - nz;  // the host launches at least a block a sequence
+        int first_block = 0;
+        b = -1;
+        for (int i = 0; i < n_seqs; ++i) {
+            if (s_pages[i] == 0) continue;
+            const int n_i = 1 + (int)((long long)s_pages[i] * spare / total);
+            if ((int)blockIdx.x < first_block + n_i) { b = i; c = (int)blockIdx.x - first_block; share = n_i; break; }
+            first_block += n_i;
+        }
+        if (b < 0) return;                                  // a block that was not needed
+    }
     const int slot = seq_slot[b];
     if (slot < 0) return;
     const int t = cu_q[b];
     const int pos = kv_len[b] - 1;
-    // this block's pages: [c * ppb, (c + 1) * ppb), cut at the sequence's end
-    const int page_first = c * ppb;
-    // beyond the sequence: takes no part in the merge; in a cluster it stays, with an empty result
-    if (!CL && page_first * CHUNK > pos) return;
-    const int page_last = min(pos / CHUNK, page_first + ppb - 1);
     const int win_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    // this block's pages: [c * ppb, (c + 1) * ppb), cut at the sequence's end; PROP: the sequence's
+    // visited pages cut into `share` runs of equal length
+    int page_first, page_last, parts_lo, parts_hi;         // and the parts that exist of this (sequence, group)
+    if (PROP) {
+        const int first = win_lo / CHUNK, P = pos / CHUNK - first + 1;
+        ppb = (P + share - 1) / share;
+        parts_lo = 0;
+        parts_hi = (P + ppb - 1) / ppb - 1;
+        if (c > parts_hi) return;
+        page_first = first + c * ppb;
+        page_last = min(pos / CHUNK, page_first + ppb - 1);
+    } else {
+        page_first = c * ppb;
+        // beyond the sequence: takes no part in the merge; in a cluster it stays, with an empty result
+        if (!CL && page_first * CHUNK > pos) return;
+        page_last = min(pos / CHUNK, page_first + ppb - 1);
+        parts_hi = pos / (CHUNK * ppb);
+        parts_lo = win_lo / (CHUNK * ppb);
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;
@@ -422,7 +466,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const int active = pos / (CHUNK * ppb) + 1;
+        const int active = PROP ? parts_hi + 1 : pos / (CHUNK * ppb) + 1;
         int* ctr = counters + (size_t)b * gridDim.y + blockIdx.y;
         const int old = atomicAdd(ctr, 1);
         s_last = old == active - 1;
@@ -434,8 +478,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // First every chunk's (maximum, sum) of every row goes to shared memory in one parallel sweep;
     // then each thread owns one (row, dimension) and adds the chunks in ascending order.  Loads of
     // different chunks do not depend on one another, so they overlap.
-    const int c_hi = pos / (CHUNK * ppb);
-    const int c_lo = window > 0 ? max(0, pos - window + 1) / (CHUNK * ppb) : 0;
+    const int c_hi = parts_hi, c_lo = parts_lo;
     const int n_act = c_hi - c_lo + 1;
     float* s_pm = reinterpret_cast<float*>(KVs);            // [rows][n_act]
     float* s_pl = s_pm + rows_valid * n_act;            // the host checked that both fit
@@ -473,12 +516,12 @@ bool cluster_enabled() {
     return on;
 }
 
-template <int HD, bool CL, bool FQ>
+template <int HD, bool CL, bool FQ, bool PROP = false>
 int launch_variant(dim3 grid, size_t smem, cudaStream_t s, const void* q, int q_stride, const void* k_cache,
                    const void* v_cache, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                    const int* kv_len, int nq, int nkv, float scale, int window, int n_chunks, int ppb, float* part_acc,
-                   float* part_ml, int* counters, void* out, int o_stride, const Projections& pj) {
-    auto k = attention_decode_kernel<HD, CL, FQ>;
+                   float* part_ml, int* counters, void* out, int o_stride, const Projections& pj, int n_seqs) {
+    auto k = attention_decode_kernel<HD, CL, FQ, PROP>;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -493,12 +536,12 @@ int launch_variant(dim3 grid, size_t smem, cudaStream_t s, const void* q, int q_
         cudaError_t e = launch_clustered(k, grid, dim3(WARPS * 32), dim3(grid.x, 1, 1), smem, s, (const __nv_bfloat16*)q,
                                          q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                                          block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
-                                         n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj);
+                                         n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj, n_seqs);
         return e == cudaSuccess ? RB_OK : (int)e;
     } else {
         RB_LAUNCH((k), grid, dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
                   (const __nv_bfloat16*)v_cache, block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,
-                  n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj);
+                  n_chunks, ppb, part_acc, part_ml, counters, (__nv_bfloat16*)out, o_stride, pj, n_seqs);
         return RB_OK;
     }
 }
@@ -509,7 +552,9 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
            float scale, int window, int n_chunks, int ppb, float* part_acc, float* part_ml, int* counters,
            void* out, int o_stride, const Projections& pj, cudaStream_t s) {
     const int g = nq / nkv;
-    dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), B);
+    const bool proportional = ppb == 0;     // n_chunks blocks a head group, shared out among the sequences
+    if (proportional && (n_chunks < B || B > PROP_MAX_SEQS)) return RB_ERR_BAD_SIZE;
+    dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), proportional ? 1 : B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     const size_t kv_bytes = (size_t)WARPS * 4 * WK * HD * sizeof(__nv_bfloat16);   // two buffers per warp
     const size_t merge_bytes = (size_t)WARPS * ROWS * HD * sizeof(float);
@@ -518,21 +563,24 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     const int rows_max = g < ROWS ? g : ROWS;
     if ((size_t)n_chunks * rows_max * 2 * sizeof(float) > region) return RB_ERR_BAD_SIZE;  // the merge's work space
     // up to 16 blocks per (sequence, head group): one cluster, merged through shared memory
-    const bool clustered = n_chunks > 1 && n_chunks <= MAX_CLUSTER && cluster_enabled();
+    const bool clustered = !proportional && n_chunks > 1 && n_chunks <= MAX_CLUSTER && cluster_enabled();
     const bool fused = pj.proj != nullptr;
     if (fused && HD != 128) return RB_ERR_BAD_SIZE;
-#define RB_ADV(CL, FQ) launch_variant<HD, CL, FQ>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table, max_pages, \
-                                                   seq_slot, cu_q, kv_len, nq, nkv, scale, window, n_chunks, ppb,        \
-                                                   part_acc, part_ml, counters, out, o_stride, pj)
-    if (HD == 128 && fused) return clustered ? RB_ADV(true, (HD == 128)) : RB_ADV(false, (HD == 128));
-    return clustered ? RB_ADV(true, false) : RB_ADV(false, false);
+#define RB_ADV(CL, FQ, PROP) launch_variant<HD, CL, FQ, PROP>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table,       \
+                                                         max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,         \
+                                                         n_chunks, ppb, part_acc, part_ml, counters, out, o_stride, pj, B)
+    if (proportional) return (HD == 128 && fused) ? RB_ADV(false, (HD == 128), true) : RB_ADV(false, false, true);
+    if (HD == 128 && fused) return clustered ? RB_ADV(true, (HD == 128), false) : RB_ADV(false, (HD == 128), false);
+    return clustered ? RB_ADV(true, false, false) : RB_ADV(false, false, false);
 #undef RB_ADV
 }
 }  // namespace
 
 // One query token per sequence (token index cu_q[b]).  A block takes `pages_per_block` pages of 64
 // keys; n_chunks = ceil(pages of the longest sequence / pages_per_block) blocks cover a sequence;
-// with n_chunks == 1 the result is written to `out` directly.
+// with n_chunks == 1 the result is written to `out` directly.  pages_per_block == 0: n_chunks blocks
+// (at least B, B <= 256) per key/value head group are shared out among the sequences in proportion to
+// their pages, for long contexts of unequal lengths.
 // Work space: part_acc [T, nq, n_chunks, hd], part_ml [T, nq, n_chunks, 2] and `counters`, at least
 // B * nkv * ceil(group / 16) ints that are ZERO on entry and are left zero on exit.
 // Returns RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 and for contexts whose chunk list does
@@ -544,7 +592,7 @@ static int decode_entry(const void* q, int q_stride, const void* k_cache, const 
                         int n_chunks, int pages_per_block, float* part_acc, float* part_ml,
                         int* counters, void* out, int o_stride, const Projections& pj, void* stream) {
     if (B <= 0) return RB_OK;
-    if (nkv <= 0 || nq % nkv || n_chunks < 1 || n_chunks > 1024 || pages_per_block < 1) return RB_ERR_BAD_SIZE;
+    if (nkv <= 0 || nq % nkv || n_chunks < 1 || n_chunks > 1024 || pages_per_block < 0) return RB_ERR_BAD_SIZE;
     if (n_chunks > 1 && (!part_acc || !part_ml || !counters)) return RB_ERR_BAD_SIZE;
     if (((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return RB_ERR_BAD_ALIGN;
     if (pj.proj == nullptr && (((uintptr_t)q & 15) || (q_stride % 8))) return RB_ERR_BAD_ALIGN;

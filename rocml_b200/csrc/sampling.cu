@@ -161,6 +161,29 @@ __device__ __forceinline__ unsigned long long fixed_of(float p) {
     return (unsigned long long)(p * FIX);
 }
 
+// Every thread visits the elements tid, tid + ST, ... of a row; four loads are issued before the
+// first element is worked on (a pass over a row is bound by the latency of its loads otherwise).
+template <typename F>
+__device__ __forceinline__ void for_each_strided(const float* row, int V, int tid, F f) {
+    int i = tid;
+    for (; i + 3 * ST < V; i += 4 * ST) {
+        const float a = row[i], b = row[i + ST], c = row[i + 2 * ST], d = row[i + 3 * ST];
+        f(i, a); f(i + ST, b); f(i + 2 * ST, c); f(i + 3 * ST, d);
+    }
+    for (; i < V; i += ST) f(i, row[i]);
+}
+
+// hist[bucket] += w in shared memory with 32-bit atomics only (64-bit ones are slow under the
+// contention a histogram sees): the low word takes the low half, and the high word is touched only
+// when the weight has a high half or the low word wrapped, which is rare.  Exact whatever the order.
+__device__ __forceinline__ void hist_add(unsigned long long* hist, int bucket, unsigned long long w) {
+    unsigned int* words = reinterpret_cast<unsigned int*>(hist + bucket);      // little-endian: [0] low, [1] high
+    const unsigned int lo = (unsigned int)w, hi = (unsigned int)(w >> 32);
+    const unsigned int old = atomicAdd(words, lo);
+    const unsigned int carry = old + lo < old ? 1u : 0u;
+    if (hi + carry) atomicAdd(words + 1, hi + carry);
+}
+
 struct Shared {
     unsigned long long hist[256];
     unsigned long long scan[ST];
@@ -177,23 +200,55 @@ struct Shared {
 
 // Threshold key T with weight(key > T) < target <= weight(key >= T) over the elements whose
 // key is >= min_key; weight is 1 (BY_MASS = false) or the fixed-point probability.
+// A coarse ranking that every pass computes the same way from the value alone: how far below the row's
+// maximum the (scaled) logit lies, in eighths, 255 for everything 32 or more below.  Smaller = larger.
+__device__ __forceinline__ int coarse_bin(float s, float max_s) {
+    const float d = (max_s - s) * 8.f;
+    return d >= 255.f ? 255 : (d > 0.f ? (int)d : 0);
+}
+
 template <bool BY_MASS>
 __device__ uint32_t radix_select(const float* row, int V, float inv_temp, float max_s, uint32_t min_key,
                                  unsigned long long target, Shared& sh, unsigned long long* w_greater) {
+    // First a histogram over the coarse bins.  The logits of a row share a few exponents, so a
+    // radix pass over the keys' top bits piles every atomic onto a handful of counters; the distance
+    // below the maximum spreads them over the bins, and the bin that holds the threshold is found with
+    // one pass.  The radix passes that follow only look at that bin's few elements.
+    if (threadIdx.x < 256) sh.hist[threadIdx.x] = 0;
+    __syncthreads();
+    for_each_strided(row, V, threadIdx.x, [&](int, float v) {
+        const float s = v * inv_temp;
+        if (key_of(s) >= min_key) {
+            hist_add(sh.hist, coarse_bin(s, max_s), BY_MASS ? fixed_of(expf(s - max_s)) : 1ull);
+        }
+    });
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long acc = 0;
+        int b = 0;
+        for (; b < 255; ++b) {                              // bin 0 holds the largest values
+            if (acc + sh.hist[b] >= target) break;
+            acc += sh.hist[b];
+        }
+        sh.chosen = b;
+        sh.acc = acc;
+    }
+    __syncthreads();
+    const int bin = sh.chosen;
     uint32_t prefix = 0, mask = 0;
-    unsigned long long above = 0;
+    unsigned long long above = sh.acc;
+    __syncthreads();
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
         if (threadIdx.x < 256) sh.hist[threadIdx.x] = 0;
         __syncthreads();
-        for (int i = threadIdx.x; i < V; i += ST) {
-            const float s = row[i] * inv_temp;
+        for_each_strided(row, V, threadIdx.x, [&](int, float v) {
+            const float s = v * inv_temp;
             const uint32_t key = key_of(s);
-            if (key >= min_key && (key & mask) == prefix) {
-                const unsigned long long w = BY_MASS ? fixed_of(expf(s - max_s)) : 1ull;
-                atomicAdd(&sh.hist[(key >> shift) & 255u], w);
+            if (key >= min_key && (key & mask) == prefix && coarse_bin(s, max_s) == bin) {
+                hist_add(sh.hist, (int)((key >> shift) & 255u), BY_MASS ? fixed_of(expf(s - max_s)) : 1ull);
             }
-        }
+        });
         __syncthreads();
         if (threadIdx.x == 0) {
             unsigned long long acc = above;
@@ -292,10 +347,9 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
 
     // the largest logit, first index on ties
     Best b{-INFINITY, 0x7fffffff};
-    for (int i = tid; i < V; i += ST) {
-        const float v = row[i];
+    for_each_strided(row, V, tid, [&](int i, float v) {
         if (v > b.v) { b.v = v; b.i = i; }
-    }
+    });
     b = warp_best(b);
     if (lane == 0) { sh.red_v[warp] = b.v; sh.red_i[warp] = b.i; }
     __syncthreads();
@@ -326,7 +380,7 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
         if (tid == 0) sh.count = 0;
         __syncthreads();
         int mine = 0;
-        for (int i = tid; i < V; i += ST) mine += key_of(row[i] * inv_temp) >= min_key;
+        for_each_strided(row, V, tid, [&](int, float v) { mine += key_of(v * inv_temp) >= min_key; });
         mine = (int)rb::warp_sum((float)mine);  // counts are small integers: exact in float
         if (lane == 0) atomicAdd(&sh.count, mine);
         __syncthreads();
@@ -340,14 +394,14 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
         sh.cand_val[tid] = -INFINITY;
         sh.cand_idx[tid] = 0x7fffffff;
         __syncthreads();
-        for (int i = tid; i < V; i += ST) {
-            const float s = row[i] * inv_temp;
+        for_each_strided(row, V, tid, [&](int i, float v) {
+            const float s = v * inv_temp;
             if (key_of(s) >= min_key) {
                 const int pos = atomicAdd(&sh.count, 1);
                 sh.cand_val[pos] = s;
                 sh.cand_idx[pos] = i;
             }
-        }
+        });
         __syncthreads();
         const int n = sh.count;
         // bitonic sort of MAX_CAND entries, one per thread; empty entries sort last
@@ -397,10 +451,10 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
     // ---- route 2: thresholds by radix selection over the whole row ------------------------------
     // total mass of the kept candidates
     unsigned long long part = 0;
-    for (int i = tid; i < V; i += ST) {
-        const float s = row[i] * inv_temp;
+    for_each_strided(row, V, tid, [&](int, float v) {
+        const float s = v * inv_temp;
         if (key_of(s) >= min_key) part += fixed_of(expf(s - max_s));
-    }
+    });
     if (tid == 0) sh.acc = 0;
     __syncthreads();
     atomicAdd(&sh.acc, part);

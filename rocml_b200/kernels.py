@@ -311,13 +311,17 @@ def decode_split(n_seqs: int, n_kv_groups: int, n_pages: int, device=0):
     sequences times key/value head groups within the resident slots), because a second, partly filled
     wave costs a whole block's latency.  A large batch therefore walks many pages per block (one
     partial result and one merge for all of them) and a single sequence spreads over the device.
-    Up to 16 blocks per sequence form a thread-block cluster and merge through shared memory, which
+    Contexts beyond 4,096 tokens in a batch: see below.  Up to 16 blocks per sequence form a thread-block cluster and merge through shared memory, which
     is quicker than through global memory: a finer split is cut back to 16 where that leaves a block
     at most four pages."""
     key = torch.device(device).index or 0
     if key not in _sm_count:
         _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
     slots = 3 * _sm_count[key]
+    if n_pages > 64 and 2 <= n_seqs <= 256:
+        # long contexts, which may differ a lot in length: one wave of blocks a head group, shared out
+        # among the sequences in proportion to their pages (pages per block 0 says so to the kernel)
+        return max(n_seqs, min(1024, slots // max(1, n_kv_groups))), 0
     blocks = max(1, min(n_pages, slots // max(1, n_seqs * n_kv_groups)))
     if blocks > DECODE_CLUSTER_MAX and -(-n_pages // DECODE_CLUSTER_MAX) <= 4:
         blocks = DECODE_CLUSTER_MAX

@@ -438,7 +438,7 @@ DEC_CASES = [
 
 
 @pytest.mark.parametrize("case", range(len(DEC_CASES)))
-@pytest.mark.parametrize("fast", [True, False, 3, 100])
+@pytest.mark.parametrize("fast", [True, False, 3, 100, "shared"])
 def test_attention_decode_split_kv(case, fast):
     """One query per sequence, keys in chunks of 128, merged: the bfloat16 kernel and the plain kernel."""
     from rocml_b200 import kernels
@@ -453,7 +453,11 @@ def test_attention_decode_split_kv(case, fast):
     out = torch.full_like(q, float("nan"))
     d = {k: v.to(DEV) for k, v in meta.items()}
     ppb = 1 if fast in (True, False) else fast        # pages per block of the bfloat16 kernel
-    n_chunks = ((max(lens) + 63) // 64 + ppb - 1) // ppb + 1     # one more than needed, as a padded graph would have
+    if fast == "shared":
+        # a fixed number of blocks a head group, shared out among the sequences by their lengths
+        ppb, n_chunks = 0, len(lens) + 6
+    else:
+        n_chunks = ((max(lens) + 63) // 64 + ppb - 1) // ppb + 1     # one more than needed, as a padded graph would have
     acc = torch.full((B, nq, n_chunks, hd), float("nan"), dtype=torch.float32, device=DEV)
     ml = torch.full((B, nq, n_chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
     pos = (d["kv_len"] - 1).to(torch.int32)
@@ -474,6 +478,7 @@ def test_attention_decode_split_kv(case, fast):
     ([300, 131, 65], 8, 2, None, 1, True, True, (2, 3)),               # clusters of 2
     ([513, 40], 6, 3, 70, 3, False, True, (1, 1)),                    # a window, no per-head norm
     ([1100], 40, 2, None, 2, True, False, (1, 1)),                     # 20 query heads per group: two blocks a group; 18 chunks: merged through global memory
+    ([900, 70, 300, 5], 8, 2, None, 4, True, True, (0, 9)),            # nine blocks a group shared out by length
 ])
 def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S, norm, rope, grid):
     """Head size 128: the decode kernel is given the projection's partial sums and does the
@@ -493,8 +498,8 @@ def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S,
     inv_freq = (1e6 ** (-torch.arange(0, hd // 2, dtype=torch.float64) * 2 / hd)).float().to(DEV) if rope else None
     cs = kernels.rope_table(pos, inv_freq, B) if rope else None
     scale = 1.0 / math.sqrt(hd)
-    ppb, _ = grid
-    n_chunks = ((max(lens) + 63) // 64 + ppb - 1) // ppb
+    ppb, shared_blocks = grid
+    n_chunks = shared_blocks if ppb == 0 else ((max(lens) + 63) // 64 + ppb - 1) // ppb
     outs, caches = [], []
     for fused in (False, True):
         k2, v2 = kc.clone().to(DEV), vc.clone().to(DEV)
