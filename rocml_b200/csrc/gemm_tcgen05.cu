@@ -356,6 +356,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     if (CS != 0) {
         // every thread of both blocks, whatever happened to it above
+        // what the first round below reads from global memory is requested before the barrier, so that it
+        // arrives while the blocks wait for one another (a block is the only writer of its residual rows)
+        float first_r = 0.f, first_w = 1.f, first_b = 0.f;
+        if (CS >= 4 && warp >= 2) {
+            constexpr int RPC = 128 / (CS >= 4 ? CS : 4);
+            const int e = (warp & 3) * 32 + lane;
+            const int tok = b0 + e / RPC, n = a0 + (int)blockIdx.z * RPC + e % RPC;
+            if (e < RPC * BN && tok < p.b_rows && n < p.a_rows) {
+                first_r = p.resid[(size_t)tok * p.resid_ld + n];
+                if (p.bias != nullptr) first_b = p.bias[n];
+                if (p.xhat != nullptr)
+                    first_w = p.next_w_f32 ? static_cast<const float*>(p.next_w)[n]
+                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p.next_w)[n]);
+            }
+        }
         __syncwarp();
         cluster_arrive();
         cluster_wait();
@@ -373,12 +388,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 float sq = 0.f;
                 if (valid) {
                     float* rp = p.resid + (size_t)tok * p.resid_ld + n;
-                    const float r_new = *rp + val + (p.bias != nullptr ? p.bias[n] : 0.f);
+                    const bool pre = idx == e;                      // the first round's values are here already
+                    const float r_new = (pre ? first_r : *rp) + val + (pre ? first_b : (p.bias != nullptr ? p.bias[n] : 0.f));
                     *rp = r_new;
                     sq = r_new * r_new;
                     if (p.xhat != nullptr) {
-                        const float wn = p.next_w_f32 ? static_cast<const float*>(p.next_w)[n]
-                                                      : __bfloat162float(static_cast<const __nv_bfloat16*>(p.next_w)[n]);
+                        const float wn = pre ? first_w
+                                             : (p.next_w_f32 ? static_cast<const float*>(p.next_w)[n]
+                                                             : __bfloat162float(static_cast<const __nv_bfloat16*>(p.next_w)[n]));
                         p.xhat[(size_t)tok * p.xhat_ld + n] = __float2bfloat16_rn(r_new * wn);
                     }
                 }
