@@ -36,6 +36,14 @@ constexpr int MAX_CLUSTER = 16;   // blocks of one (sequence, head group) that c
 constexpr float NEG_BIG = -1e30f;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x on the special-function unit, one instruction (x <= 0 here, -inf gives 0); the library's exp2f
+// adds range handling that the softmax does not need.
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Blocks of one (sequence, head group) as one thread-block cluster (CL): see the merge below.
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -319,30 +327,45 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_bf16(s[j], qa1, b2, b3);
             }
         }
-        // every row is the same token: one mask for all rows
+        // The kernel is bound by the instructions a warp issues per page, so what a page rarely needs is
+        // skipped with a vote: the mask (only a sequence's last page and a window's first can need one;
+        // every row is the same token, so one mask serves all rows) and the rescaling of the output
+        // (the running maximum seldom moves after the first pages).
         float mx[2] = {NEG_BIG, NEG_BIG};
+        if (j0 >= win_lo && j0 + WK - 1 <= hi) {
 #pragma unroll
-        for (int j = 0; j < WK / 8; ++j) {
+            for (int j = 0; j < WK / 8; ++j) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = j0 + j * 8 + tq * 2 + (e & 1);
-                const bool ok = key >= win_lo && key <= hi;
-                s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
+                for (int e = 0; e < 4; ++e) s[j][e] *= sl2;
+                mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
             }
-            mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
-            mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < WK / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = j0 + j * 8 + tq * 2 + (e & 1);
+                    const bool ok = key >= win_lo && key <= hi;
+                    s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
+                }
+                mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
+            }
         }
         float alpha[2];
+        bool moved = false;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m_w[r], mx[r]);
-            alpha[r] = exp2f(m_w[r] - m_new);
+            moved = moved || m_new != m_w[r];
+            alpha[r] = ex2(m_w[r] - m_new);
             m_w[r] = m_new;
             l_w[r] *= alpha[r];
         }
-        if (pg > page_first) {
+        if (pg > page_first && __any_sync(0xffffffffu, moved)) {
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i) {
                 o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
@@ -352,8 +375,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         uint32_t pa[WK / 16][4];
 #pragma unroll
         for (int j = 0; j < WK / 8; ++j) {
-            const float p0 = exp2f(s[j][0] - m_w[0]), p1 = exp2f(s[j][1] - m_w[0]);
-            const float p2 = exp2f(s[j][2] - m_w[1]), p3 = exp2f(s[j][3] - m_w[1]);
+            const float p0 = ex2(s[j][0] - m_w[0]), p1 = ex2(s[j][1] - m_w[0]);
+            const float p2 = ex2(s[j][2] - m_w[1]), p3 = ex2(s[j][3] - m_w[1]);
             l_w[0] += p0 + p1;
             l_w[1] += p2 + p3;
             pa[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
