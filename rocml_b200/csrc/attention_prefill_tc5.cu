@@ -4,15 +4,16 @@
 // shuffles are needed for row maxima and sums).  Head size 128.
 //
 // A block takes 128 query tokens of one sequence and one query head and walks the keys page by page
-// (a page of the cache is one 64-key tile).  Roles: warp 0 issues TMA loads (Q once, K in a ring of
-// two, V in a ring of one), warp 1 issues the MMAs, warps 2-5 are the 128 softmax threads.
+// (a page of the cache is one 64-key tile).  Roles: warp 0 issues TMA loads (Q once, K and V in rings
+// of two, so that a tile's copies never wait for the products of the tile before), warp 1 issues
+// the MMAs, warps 2-5 are the 128 softmax threads.
 // Per tile: S_j = Q K_j^T into one of two TMEM buffers (so the tensor core can already form S_{j+1}
 // while the softmax works on S_j); the softmax threads read their row, scale, mask (causal,
 // inclusive; window), update the running maximum and sum in float32 (base 2), write P as bfloat16
 // into shared memory in the operand layout, and, only when some row's maximum has grown by more than
 // 2^8, rescale the O accumulator in tensor memory (otherwise the stale maximum stays in use, which is
 // exact: numerator and denominator carry the same factor); O += P V_j with V read in its natural
-// [key][dimension] order (MN-major operand).  Two blocks share a multiprocessor (96 KB of shared
+// [key][dimension] order (MN-major operand).  Two blocks share a multiprocessor (112 KB of shared
 // memory and 256 TMEM columns each), so one block's softmax overlaps the other's MMAs.
 //
 // Same mathematics as the reference's attn_prefill_flash_* (rocml-kernels/kernels/
@@ -34,16 +35,21 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1e30f;
 constexpr float RESCALE_AT = 8.0f;   // rescale O when a row maximum grew by more than 2^8
 
-// shared memory (bytes): Q 2 x [128][64], K ring 2 x (2 x [64][64]), V 2 x [64][64], P [128][64]
+// shared memory (bytes): Q 2 x [128][64], K ring 2 x (2 x [64][64]), V ring 2 x (2 x [64][64]), P [128][64]
 constexpr int Q_BYTES = 2 * BMQ * 64 * 2;       // 32 KB
 constexpr int KV_TILE = 2 * BNK * 64 * 2;       // 16 KB
 constexpr int P_BYTES = BMQ * BNK * 2;          // 16 KB
-constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_TILE + KV_TILE + P_BYTES + 1024 + 256;
+// Two blocks must fit a multiprocessor's 228 KB (each block is charged 1 KB on top of what it asks
+// for): 112 KB of tiles, the barriers, and what is left of the allowance as slack for aligning the
+// tiles to 1 KB (the launch's shared memory normally starts on such a boundary; the kernel checks).
+constexpr int TILE_BYTES = Q_BYTES + 2 * KV_TILE + 2 * KV_TILE + P_BYTES;
+constexpr int SMEM_BYTES = (228 * 1024) / 2 - 1024;
+static_assert(SMEM_BYTES >= TILE_BYTES + 128, "the tiles and the barriers must fit");
 // tensor memory columns: S0 [0, 64), S1 [64, 128), O [128, 256)
 constexpr int TMEM_COLS = 256;
 
 struct Barriers {
-    uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full, o_done;
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_done;
     uint32_t tmem_slot, abort_flag;
 };
 
@@ -57,10 +63,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     rb::pdl_wait();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    if (smem + TILE_BYTES + sizeof(Barriers) > smem_raw + SMEM_BYTES) {   // never seen: the window starts on 1 KB
+        if (threadIdx.x == 0) atomicExch(status, RB_ERR_BAD_ALIGN);
+        return;
+    }
     uint8_t* Qs = smem;
     uint8_t* Ks = Qs + Q_BYTES;               // [2 stages][16 KB]
     uint8_t* Vs = Ks + 2 * KV_TILE;
-    uint8_t* Ps = Vs + KV_TILE;
+    uint8_t* Ps = Vs + 2 * KV_TILE;           // V: [2 stages][16 KB]
     Barriers* bar = (Barriers*)(Ps + P_BYTES);
 
     const int b = blockIdx.z, head = blockIdx.y;
@@ -82,9 +92,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
 
     if (threadIdx.x == 0) {
         mbar_init(&bar->q_full, 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(&bar->k_full[i], 1); mbar_init(&bar->k_empty[i], 1); mbar_init(&bar->s_full[i], 1); }
-        mbar_init(&bar->v_full, 1);
-        mbar_init(&bar->v_empty, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar->k_full[i], 1); mbar_init(&bar->k_empty[i], 1); mbar_init(&bar->s_full[i], 1);
+            mbar_init(&bar->v_full[i], 1); mbar_init(&bar->v_empty[i], 1);
+        }
         mbar_init(&bar->p_full, 128);
         mbar_init(&bar->o_done, 1);
         bar->abort_flag = 0;
@@ -117,11 +128,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 mbar_arrive_expect_tx(&bar->k_full[s], KV_TILE);
                 tma_load_2d(Ks + s * KV_TILE, &map_k, 0, row, &bar->k_full[s]);
                 tma_load_2d(Ks + s * KV_TILE + KV_TILE / 2, &map_k, 64, row, &bar->k_full[s]);
-                ok = mbar_wait(&bar->v_empty, (j & 1) ^ 1);
+                ok = mbar_wait(&bar->v_empty[s], ((j >> 1) & 1) ^ 1);
                 if (!ok) break;
-                mbar_arrive_expect_tx(&bar->v_full, KV_TILE);
-                tma_load_2d(Vs, &map_v, 0, row, &bar->v_full);
-                tma_load_2d(Vs + KV_TILE / 2, &map_v, 64, row, &bar->v_full);
+                mbar_arrive_expect_tx(&bar->v_full[s], KV_TILE);
+                tma_load_2d(Vs + s * KV_TILE, &map_v, 0, row, &bar->v_full[s]);
+                tma_load_2d(Vs + s * KV_TILE + KV_TILE / 2, &map_v, 64, row, &bar->v_full[s]);
             }
             if (!ok) { atomicExch(status, RB_ERR_TIMEOUT); atomicExch(&bar->abort_flag, 1u); }
         }
@@ -151,17 +162,18 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (ok) { tc_fence_after(); ok = issue_s(0); }
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
-                ok = mbar_wait(&bar->p_full, j & 1) && mbar_wait(&bar->v_full, j & 1);
+                ok = mbar_wait(&bar->p_full, j & 1) && mbar_wait(&bar->v_full[j & 1], (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t v_tile = v_addr + (j & 1) * KV_TILE;
 #pragma unroll
                 for (int k = 0; k < BNK / 16; ++k) {
                     // A = P [128 rows][64 keys], K-major: 32 bytes per 16 keys.  B = V [64 keys][128 dims],
                     // MN-major: 64-dimension blocks 8 KB apart, groups of 8 keys 1 KB apart, 16 keys = 2 KB.
                     mma_bf16(tmem_base + 2 * BNK, smem_desc_sw128(p_addr + k * 32),
-                             smem_desc_sw128_ex(v_addr + k * 2048, KV_TILE / 2, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                             smem_desc_sw128_ex(v_tile + k * 2048, KV_TILE / 2, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                 }
-                mma_commit(&bar->v_empty);
+                mma_commit(&bar->v_empty[j & 1]);
                 mma_commit(&bar->o_done);
             }
             if (!ok) {
@@ -246,11 +258,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (j == n_tiles - 1) {
                 const int valid = min(BNK, len - key0);
                 if (valid < BNK) {
-                    alive = __all_sync(0xffffffffu, mbar_wait(&bar->v_full, j & 1));
+                    alive = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[j & 1], (j >> 1) & 1));
                     if (!alive) break;
+                    uint8_t* Vt = Vs + (j & 1) * KV_TILE;
                     for (int idx = threadIdx.x - 64; idx < (BNK - valid) * 16; idx += 128) {
                         const int vr = valid + idx / 16, ch = idx % 16;      // row vr, 16-byte chunk ch of its 256 bytes
-                        *reinterpret_cast<uint4*>(Vs + (ch >> 3) * (KV_TILE / 2) + vr * 128 + (((ch & 7) ^ (vr & 7)) << 4)) =
+                        *reinterpret_cast<uint4*>(Vt + (ch >> 3) * (KV_TILE / 2) + vr * 128 + (((ch & 7) ^ (vr & 7)) << 4)) =
                             make_uint4(0, 0, 0, 0);
                     }
                 }
