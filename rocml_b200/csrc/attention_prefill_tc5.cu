@@ -48,6 +48,19 @@ static_assert(SMEM_BYTES >= TILE_BYTES + 128, "the tiles and the barriers must f
 // tensor memory columns: S0 [0, 64), S1 [64, 128), O [128, 256)
 constexpr int TMEM_COLS = 256;
 
+// 2^x on the special-function unit, one instruction (x <= 0 here, -inf gives 0); the library's exp2f
+// adds range handling that the softmax does not need.
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 struct Barriers {
     uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_done;
     uint32_t tmem_slot, abort_flag;
@@ -200,35 +213,42 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             float sv[BNK];
 #pragma unroll
             for (int c = 0; c < BNK / 16; ++c) tmem_ld16(lane_base + s * BNK + c * 16, sv + c * 16);
+            // The softmax threads are bound by the instructions they issue.  Scores stay raw: the scale is
+            // positive, so the maximum is taken first (three inputs an instruction) and the scale is
+            // folded into the exponent's multiply-add, p = 2^(s * scale * log2 e - m), with the bare
+            // special-function instruction for 2^x.
             float mx = NEG_BIG;
             // a tile that every row of this warp sees whole needs no mask
             const int warp_first_pos = pos0 + m0 + quarter * 32;
-            if (key0 + BNK - 1 <= warp_first_pos && (window <= 0 || key0 > warp_first_pos + 31 - window)) {
-#pragma unroll
-                for (int i = 0; i < BNK; ++i) { sv[i] *= sl2; mx = fmaxf(mx, sv[i]); }
-            } else {
+            if (!(key0 + BNK - 1 <= warp_first_pos && (window <= 0 || key0 > warp_first_pos + 31 - window))) {
 #pragma unroll
                 for (int i = 0; i < BNK; ++i) {
                     const int key = key0 + i;
                     const bool ok = key <= row_pos && (window <= 0 || key > row_pos - window);
-                    sv[i] = ok ? sv[i] * sl2 : -INFINITY;
-                    mx = fmaxf(mx, sv[i]);
+                    sv[i] = ok ? sv[i] : -INFINITY;
                 }
             }
+#pragma unroll
+            for (int i = 0; i < BNK; i += 2) mx = max3(mx, sv[i], sv[i + 1]);
+            mx *= sl2;
             // the maximum in use only moves when it would otherwise let p exceed 2^8
             const bool grow = mx - m_used > RESCALE_AT;
             const float m_new = grow ? mx : m_used;
-            const float alpha = exp2f(m_used - m_new);          // 1 when the maximum stays
+            const float alpha = ex2(m_used - m_new);            // 1 when the maximum stays
             m_used = m_new;
             l_sum *= alpha;
             uint32_t packed[BNK / 2];
+            const float neg_m = -m_used;
+            float l0 = 0.f, l1 = 0.f;
 #pragma unroll
             for (int i = 0; i < BNK; i += 2) {
-                const float p0 = exp2f(sv[i] - m_used), p1 = exp2f(sv[i + 1] - m_used);
-                l_sum += p0 + p1;
+                const float p0 = ex2(fmaf(sv[i], sl2, neg_m)), p1 = ex2(fmaf(sv[i + 1], sl2, neg_m));
+                l0 += p0;
+                l1 += p1;
                 __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                 packed[i / 2] = *reinterpret_cast<uint32_t*>(&h);
             }
+            l_sum += l0 + l1;
             // before P_j replaces P_{j-1} and before O is touched, the MMAs of tile j-1 must be done
             if (j > 0) {
                 alive = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, (j - 1) & 1));
