@@ -360,6 +360,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // arrives while the blocks wait for one another (a block is the only writer of its residual rows)
         float first_r = 0.f, first_w = 1.f, first_b = 0.f;
         if (CS >= 4 && warp >= 2) {
+            rb::pdl_wait();   // these threads read what earlier kernels wrote (the residual): returns at once by now
             constexpr int RPC = 128 / (CS >= 4 ? CS : 4);
             const int e = (warp & 3) * 32 + lane;
             const int tok = b0 + e / RPC, n = a0 + (int)blockIdx.z * RPC + e % RPC;
@@ -773,6 +774,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const bool vec_ok = (((uintptr_t)out | ((uintptr_t)p.ldo * sizeof(OT))) & 15) == 0;
             OT* row = out + (size_t)(ar < p.a_rows ? ar : 0) * p.ldo;
             if (EPI == 2) {
+                rb::pdl_wait();   // these threads read what an earlier kernel wrote (the angles' table): returns at once by now
                 int slot = -1, pos = 0, page = -2;         // page -2: not looked up yet
                 if (ar < p.a_rows) { slot = p.slot_of_token[ar]; pos = p.positions[ar]; }
 #pragma unroll 1
