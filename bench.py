@@ -261,6 +261,44 @@ def micro(which):
         raise SystemExit(f"unknown --micro {which!r}: gemm-decode, gemm-prefill or timeline")
 
 
+def sampler_times():
+    """Time of one sampling step (kernel, copy of the ids to the host, the host's own part) over logits of the
+    benchmark's vocabulary, for the ways of sampling and a few batch sizes; beside it the kernel's own time,
+    launched back to back."""
+    import torch
+    from rocml_b200.config import CATALOG, config_from_dict
+    from rocml_b200.sampling import Sampler, SamplingParams
+    from rocml_b200.sampling.params import XorShift64Star
+    vocab = config_from_dict(CATALOG[MODEL].config).vocab_size
+    dev = "cuda:0"
+    ways = [("greedy", SamplingParams()), ("temperature 0.6, top-k 20, top-p 0.95", SamplingParams(0.6, top_k=20, top_p=0.95)),
+            ("temperature 0.8", SamplingParams(0.8)), ("temperature 0.8, top-p 0.9", SamplingParams(0.8, top_p=0.9)),
+            ("temperature 0.8, top-k 2000", SamplingParams(0.8, top_k=2000))]
+    for batch in (1, 8, 64):
+        logits = torch.randn(batch, vocab, device=dev) * 2.0
+        s = Sampler(dev, max_batch=64)
+        for name, sp in ways:
+            rngs = [XorShift64Star(i) for i in range(batch)]
+            for _ in range(3):
+                s.sample(logits, [sp] * batch, rngs, [[]] * batch)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(20):
+                s.sample(logits, [sp] * batch, rngs, [[]] * batch)
+            wall = (time.perf_counter() - t0) / 20 * 1e6
+            # the kernel alone, on the rows that the last step left on the device
+            from rocml_b200 import kernels
+            run = (lambda: kernels.argmax(logits, s._out, batch)) if sp.is_greedy else \
+                (lambda: kernels.sample(logits, batch, s._rows, s._hist, s._out))
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(20):
+                run()
+            b.record()
+            torch.cuda.synchronize()
+            print(f"batch {batch:3d}  {name:40s} {wall:8.1f} us a step, kernel {a.elapsed_time(b) / 20 * 1e3:7.1f} us")
+
+
 def timeline(batch=BATCH, layers=4):
     """Where a decode step's time goes, kernel by kernel, as the step really runs (inside its CUDA
     graph, kernels overlapping their predecessors through programmatic dependent launch): start and
@@ -307,12 +345,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--micro", default=None,
-                    help="instead of the bench: gemm-decode, gemm-prefill (kernel microbenchmarks) or timeline "
-                         "(every kernel of one decode step with its start and end)")
+                    help="instead of the bench: gemm-decode, gemm-prefill (kernel microbenchmarks), timeline "
+                         "(every kernel of one decode step with its start and end) or sampler (a sampling step)")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of --micro timeline")
     args = ap.parse_args()
     if args.micro == "timeline":
         timeline(args.batch, args.layers or 4)
+        return 0
+    if args.micro == "sampler":
+        sampler_times()
         return 0
     if args.micro:
         micro(args.micro)

@@ -161,10 +161,29 @@ __device__ __forceinline__ unsigned long long fixed_of(float p) {
     return (unsigned long long)(p * FIX);
 }
 
-// Every thread visits the elements tid, tid + ST, ... of a row; four loads are issued before the
-// first element is worked on (a pass over a row is bound by the latency of its loads otherwise).
+// Every element of a row is handed to f(index, value) once, by some thread, in no particular order.
+// One block reads the row, and what bounds it is how many bytes it keeps in flight: four 16-byte
+// loads a thread are requested before the first element is worked on (rows that are not 16-byte
+// aligned or whose length is no multiple of 4 fall back to single elements).
 template <typename F>
 __device__ __forceinline__ void for_each_strided(const float* row, int V, int tid, F f) {
+    if ((((uintptr_t)row & 15) | (V & 3)) == 0) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const int V4 = V >> 2;
+        int i = tid;
+        for (; i + 3 * ST < V4; i += 4 * ST) {
+            const float4 a = r4[i], b = r4[i + ST], c = r4[i + 2 * ST], d = r4[i + 3 * ST];
+            f(4 * i, a.x); f(4 * i + 1, a.y); f(4 * i + 2, a.z); f(4 * i + 3, a.w);
+            f(4 * (i + ST), b.x); f(4 * (i + ST) + 1, b.y); f(4 * (i + ST) + 2, b.z); f(4 * (i + ST) + 3, b.w);
+            f(4 * (i + 2 * ST), c.x); f(4 * (i + 2 * ST) + 1, c.y); f(4 * (i + 2 * ST) + 2, c.z); f(4 * (i + 2 * ST) + 3, c.w);
+            f(4 * (i + 3 * ST), d.x); f(4 * (i + 3 * ST) + 1, d.y); f(4 * (i + 3 * ST) + 2, d.z); f(4 * (i + 3 * ST) + 3, d.w);
+        }
+        for (; i < V4; i += ST) {
+            const float4 a = r4[i];
+            f(4 * i, a.x); f(4 * i + 1, a.y); f(4 * i + 2, a.z); f(4 * i + 3, a.w);
+        }
+        return;
+    }
     int i = tid;
     for (; i + 3 * ST < V; i += 4 * ST) {
         const float a = row[i], b = row[i + ST], c = row[i + 2 * ST], d = row[i + 3 * ST];
@@ -186,7 +205,7 @@ __device__ __forceinline__ void hist_add(unsigned long long* hist, int bucket, u
 
 struct Shared {
     unsigned long long hist[256];
-    unsigned long long scan[ST];
+    unsigned long long scan[ST / 32];
     float cand_val[MAX_CAND];
     float cand_p[MAX_CAND];
     int cand_idx[MAX_CAND];
@@ -195,11 +214,67 @@ struct Shared {
     unsigned long long acc;
     int chosen;
     int count;
-    int token;
+    int flag;
 };
 
-// Threshold key T with weight(key > T) < target <= weight(key >= T) over the elements whose
-// key is >= min_key; weight is 1 (BY_MASS = false) or the fixed-point probability.
+// ---- a row shared by the blocks of a cluster ------------------------------------------------------
+// One block reads a row of 150,000 logits at a small fraction of the device's bandwidth, and a sampler
+// makes eight or so passes over it.  So the row is cut into C contiguous parts, one per block of a
+// thread-block cluster; every pass runs on the parts side by side, and what a pass finds (a maximum, a
+// sum, a histogram) is combined through distributed shared memory so that EVERY block holds the same
+// result and takes the same decisions.  C = 1 is the plain one-block kernel.
+template <int C>
+struct Team {
+    unsigned rank;
+    __device__ void barrier() const {
+        if (C > 1) {
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        } else {
+            __syncthreads();
+        }
+    }
+    template <typename T>
+    __device__ T peer(const T* local, unsigned r) const {          // the value `local` has in block r
+        if (C == 1) return *local;
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                     : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(r));
+        T v;
+        if (sizeof(T) == 8) {
+            unsigned long long raw;
+            asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(raw) : "r"(remote) : "memory");
+            v = *reinterpret_cast<T*>(&raw);
+        } else {
+            unsigned int raw;
+            asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(raw) : "r"(remote) : "memory");
+            v = *reinterpret_cast<T*>(&raw);
+        }
+        return v;
+    }
+    // every block's *value (written by one of its threads before the call) -> the sum over the blocks, in
+    // every block
+    template <typename T>
+    __device__ T sum(T* value) const {
+        barrier();
+        T t = 0;
+        for (unsigned r = 0; r < (unsigned)C; ++r) t += peer(value, r);
+        barrier();                                                  // everyone has read before anyone writes again
+        return t;
+    }
+    // every block's histogram -> their sum, in every block
+    __device__ void sum_hist(unsigned long long* hist) const {
+        if (C == 1) { __syncthreads(); return; }
+        barrier();
+        unsigned long long t = 0;
+        if (threadIdx.x < 256)
+            for (unsigned r = 0; r < (unsigned)C; ++r) t += peer(&hist[threadIdx.x], r);
+        barrier();
+        if (threadIdx.x < 256) hist[threadIdx.x] = t;
+        __syncthreads();
+    }
+};
+
 // A coarse ranking that every pass computes the same way from the value alone: how far below the row's
 // maximum the (scaled) logit lies, in eighths, 255 for everything 32 or more below.  Smaller = larger.
 __device__ __forceinline__ int coarse_bin(float s, float max_s) {
@@ -207,113 +282,176 @@ __device__ __forceinline__ int coarse_bin(float s, float max_s) {
     return d >= 255.f ? 255 : (d > 0.f ? (int)d : 0);
 }
 
-template <bool BY_MASS>
-__device__ uint32_t radix_select(const float* row, int V, float inv_temp, float max_s, uint32_t min_key,
-                                 unsigned long long target, Shared& sh, unsigned long long* w_greater) {
+// Where the running sum over the 256 bins, started at `above` (< target), reaches `target`: bins taken
+// from 255 down (descending) or from 0 up; the last bin in that order is the answer if no earlier one is.
+// One thread a bin and a scan over them.  Leaves the bin in sh.chosen and the sum before it in sh.acc,
+// for every thread.
+__device__ __forceinline__ void find_bin(Shared& sh, unsigned long long above, unsigned long long target,
+                                         bool descending) {
+    const int j = threadIdx.x, lane = j & 31;
+    unsigned long long v = 0, incl = 0;
+    if (j < 256) {
+        v = sh.hist[descending ? 255 - j : j];
+        incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) sh.scan[j >> 5] = incl;
+    }
+    __syncthreads();
+    if (j < 256) {
+        for (int w = 0; w < (j >> 5); ++w) incl += sh.scan[w];
+        const unsigned long long before = above + incl - v;
+        if (before < target && (above + incl >= target || j == 255)) {      // true for exactly one bin
+            sh.chosen = descending ? 255 - j : j;
+            sh.acc = before;
+        }
+    }
+    __syncthreads();
+}
+
+// Threshold key T with weight(key > T) < target <= weight(key >= T) over the elements whose
+// key is >= min_key; weight is 1 (BY_MASS = false) or the fixed-point probability.
+// `part` is this block's part of the row (n elements).  *w_greater: weight(key > T); *w_equal:
+// weight(key == T).
+template <bool BY_MASS, int C>
+__device__ uint32_t radix_select(const Team<C>& team, const float* part, int n, float inv_temp, float max_s,
+                                 uint32_t min_key, unsigned long long target, Shared& sh,
+                                 unsigned long long* w_greater, unsigned long long* w_equal) {
     // First a histogram over the coarse bins.  The logits of a row share a few exponents, so a
     // radix pass over the keys' top bits piles every atomic onto a handful of counters; the distance
     // below the maximum spreads them over the bins, and the bin that holds the threshold is found with
-    // one pass.  The radix passes that follow only look at that bin's few elements.
-    if (threadIdx.x < 256) sh.hist[threadIdx.x] = 0;
+    // one pass.  That bin's elements are then copied to shared memory, and the radix passes over the
+    // key's bytes run on the copy (on the row itself if some block's share of the bin does not fit).
+    const int tid = threadIdx.x;
+    if (tid < 256) sh.hist[tid] = 0;
+    if (tid == 0) sh.count = 0;
     __syncthreads();
-    for_each_strided(row, V, threadIdx.x, [&](int, float v) {
+    for_each_strided(part, n, tid, [&](int, float v) {
         const float s = v * inv_temp;
-        if (key_of(s) >= min_key) {
-            hist_add(sh.hist, coarse_bin(s, max_s), BY_MASS ? fixed_of(expf(s - max_s)) : 1ull);
+        if (key_of(s) >= min_key) hist_add(sh.hist, coarse_bin(s, max_s), BY_MASS ? fixed_of(expf(s - max_s)) : 1ull);
+    });
+    team.sum_hist(sh.hist);
+    find_bin(sh, 0ull, target, false);                      // bin 0 holds the largest values
+    const int bin = sh.chosen;
+    unsigned long long above = sh.acc;
+    for_each_strided(part, n, tid, [&](int, float v) {
+        const float s = v * inv_temp;
+        if (key_of(s) >= min_key && coarse_bin(s, max_s) == bin) {
+            const int pos = atomicAdd(&sh.count, 1);
+            if (pos < MAX_CAND) sh.cand_val[pos] = s;
         }
     });
     __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned long long acc = 0;
-        int b = 0;
-        for (; b < 255; ++b) {                              // bin 0 holds the largest values
-            if (acc + sh.hist[b] >= target) break;
-            acc += sh.hist[b];
-        }
-        sh.chosen = b;
-        sh.acc = acc;
-    }
-    __syncthreads();
-    const int bin = sh.chosen;
+    const int n_list = sh.count;
+    if (tid == 0) sh.flag = n_list > MAX_CAND;
+    const bool listed = team.sum(&sh.flag) == 0;            // the same answer in every block
     uint32_t prefix = 0, mask = 0;
-    unsigned long long above = sh.acc;
-    __syncthreads();
+    unsigned long long equal = 0;
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
-        if (threadIdx.x < 256) sh.hist[threadIdx.x] = 0;
+        if (tid < 256) sh.hist[tid] = 0;
         __syncthreads();
-        for_each_strided(row, V, threadIdx.x, [&](int, float v) {
-            const float s = v * inv_temp;
-            const uint32_t key = key_of(s);
-            if (key >= min_key && (key & mask) == prefix && coarse_bin(s, max_s) == bin) {
-                hist_add(sh.hist, (int)((key >> shift) & 255u), BY_MASS ? fixed_of(expf(s - max_s)) : 1ull);
+        if (listed) {
+            for (int j = tid; j < n_list; j += ST) {
+                const float s = sh.cand_val[j];
+                const uint32_t key = key_of(s);
+                if ((key & mask) == prefix)
+                    hist_add(sh.hist, (int)((key >> shift) & 255u), BY_MASS ? fixed_of(expf(s - max_s)) : 1ull);
             }
-        });
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned long long acc = above;
-            int b = 255;
-            for (; b > 0; --b) {
-                if (acc + sh.hist[b] >= target) break;
-                acc += sh.hist[b];
-            }
-            sh.chosen = b;
-            sh.acc = acc;
+        } else {
+            for_each_strided(part, n, tid, [&](int, float v) {
+                const float s = v * inv_temp;
+                const uint32_t key = key_of(s);
+                if (key >= min_key && (key & mask) == prefix && coarse_bin(s, max_s) == bin)
+                    hist_add(sh.hist, (int)((key >> shift) & 255u), BY_MASS ? fixed_of(expf(s - max_s)) : 1ull);
+            });
         }
-        __syncthreads();
+        team.sum_hist(sh.hist);
+        find_bin(sh, above, target, true);
         prefix |= (uint32_t)sh.chosen << shift;
         mask |= 255u << shift;
         above = sh.acc;
+        equal = sh.hist[sh.chosen];
         __syncthreads();
     }
     *w_greater = above;
+    *w_equal = equal;
     return prefix;
 }
 
 
-// Walk the row in index order and return the first index at which the running weight reaches
-// thr (>= 1).  MODE 0: weight = fixed-point probability of elements with key >= key_ref;
-// MODE 1: weight = 1 for elements with key == key_ref.  Each thread sums a contiguous range,
-// the ranges are scanned, and the thread whose range holds the crossing walks it.
-template <int MODE>
-__device__ int index_walk(const float* row, int V, float inv_temp, float max_s, uint32_t key_ref,
-                          unsigned long long thr, Shared& sh, int fallback) {
-    const int tid = threadIdx.x;
-    const int per = (V + ST - 1) / ST;
-    const int lo = tid * per, hi = min(V, lo + per);
-    unsigned long long part = 0;
-    for (int i = lo; i < hi; ++i) {
-        const float s = row[i] * inv_temp;
+// Walk the row in index order and write to *out the first index at which the running weight reaches
+// thr (>= 1), or `fallback` if it never does.  MODE 0: weight = fixed-point probability of elements with
+// key >= key_ref; MODE 1: weight = 1 for elements with key == key_ref.  Every warp sums one contiguous
+// stretch of its block's part (its lanes side by side, so the reads coalesce), the stretches' sums are
+// scanned over the warps and over the blocks, and the one warp whose stretch holds the crossing walks
+// it 256 elements at a time with a scan across its lanes.  The weights are integers, so no sum depends
+// on the order it was formed in.  `first` is the row index of the part's first element.
+template <int MODE, int C>
+__device__ void index_walk(const Team<C>& team, const float* part, int n, int first, float inv_temp, float max_s,
+                           uint32_t key_ref, unsigned long long thr, Shared& sh, int fallback, int* out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int WARPS_ = ST / 32;
+    const int per = ((n + WARPS_ - 1) / WARPS_ + 31) & ~31;        // a warp's stretch, a multiple of 32
+    const int lo = warp * per, hi = min(n, lo + per);
+    auto weight = [&](int i) -> unsigned long long {
+        if (i >= hi) return 0ull;
+        const float s = part[i] * inv_temp;
         const uint32_t key = key_of(s);
-        if (MODE == 0) { if (key >= key_ref) part += fixed_of(expf(s - max_s)); }
-        else { if (key == key_ref) part += 1; }
+        if (MODE == 0) return key >= key_ref ? fixed_of(expf(s - max_s)) : 0ull;
+        return key == key_ref ? 1ull : 0ull;
+    };
+    unsigned long long mine = 0;
+    for (int i = lo + lane; i < hi; i += 32) mine += weight(i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    __syncthreads();
+    if (lane == 0) sh.scan[warp] = mine;
+    __syncthreads();
+    unsigned long long before = 0, block_total = 0;
+    for (int w = 0; w < WARPS_; ++w) {
+        if (w < warp) before += sh.scan[w];
+        block_total += sh.scan[w];
     }
-    __syncthreads();
-    sh.scan[tid] = part;
-    if (tid == 0) sh.token = 0x7fffffff;
-    __syncthreads();
     if (tid == 0) {
-        unsigned long long run = 0;
-        for (int t = 0; t < ST; ++t) { const unsigned long long v = sh.scan[t]; sh.scan[t] = run; run += v; }
+        sh.acc = block_total;
+        if (team.rank == 0) *out = fallback;                        // stands unless a warp finds the crossing
     }
-    __syncthreads();
-    const unsigned long long before = sh.scan[tid];
-    if (before < thr && thr <= before + part) {
+    team.barrier();                                                 // the blocks' totals are there; the fallback is written
+    for (unsigned r = 0; r < team.rank; ++r) before += team.peer(&sh.acc, r);
+    if (before < thr && thr <= before + mine) {                   // this warp's stretch holds the crossing
+        // 256 elements at a time, 8 neighbours a lane: the loads of a round are all in flight together
         unsigned long long run = before;
-        for (int i = lo; i < hi; ++i) {
-            const float s = row[i] * inv_temp;
-            const uint32_t key = key_of(s);
-            unsigned long long w = 0;
-            if (MODE == 0) { if (key >= key_ref) w = fixed_of(expf(s - max_s)); }
-            else { if (key == key_ref) w = 1; }
-            run += w;
-            if (w && run >= thr) { sh.token = i; break; }
+        for (int base = lo; base < hi; base += 256) {
+            unsigned long long w[8], sum = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { w[k] = weight(base + lane * 8 + k); sum += w[k]; }
+            unsigned long long incl = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const unsigned long long round = __shfl_sync(0xffffffffu, incl, 31);
+            if (run + round >= thr) {
+                unsigned long long cum = run + incl - sum;
+                if (cum < thr && thr <= cum + sum) {
+                    int k = 0;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        if (cum < thr) { cum += w[q]; k = q; }
+                    }
+                    *out = first + base + lane * 8 + k;
+                }
+                break;
+            }
+            run += round;
         }
     }
-    __syncthreads();
-    const int tok = sh.token == 0x7fffffff ? fallback : sh.token;
-    __syncthreads();
-    return tok;
+    team.barrier();                                                 // nobody leaves while its total may still be read
 }
 
 __device__ __forceinline__ float value_of_key(uint32_t key) {
@@ -326,29 +464,42 @@ __device__ __forceinline__ bool cand_before(float va, int ia, float vb, int ib, 
     return ia < ib;
 }
 
-__global__ void __launch_bounds__(ST)
+template <int C>
+__global__ void __launch_bounds__(ST, 2)
 sample_kernel(float* __restrict__ logits, long long row_stride, int V, const SampleRow* __restrict__ rows,
               const int* __restrict__ history, int* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
     __shared__ Shared sh;
-    const SampleRow r = rows[blockIdx.x];
-    float* row = logits + (size_t)blockIdx.x * row_stride;
+    const int row_id = blockIdx.x / C;
+    Team<C> team;
+    team.rank = blockIdx.x % C;                               // = the block's rank in its cluster of C
+    const SampleRow r = rows[row_id];
+    float* row = logits + (size_t)row_id * row_stride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // this block's part of the row: a multiple of 4 elements, so that 16-byte loads stay aligned
+    const int per = (((V + C - 1) / C) + 3) & ~3;
+    const int first = min(V, (int)team.rank * per);
+    const int n = min(V, first + per) - first;
+    const float* part = row + first;
+    int* result = out + row_id;
 
     // repeat penalty, once per occurrence, in history order
-    if (r.penalty > 0.f && fabsf(r.penalty - 1.f) >= 1.1920929e-7f && tid == 0) {
-        for (int j = 0; j < r.hist_len; ++j) {
-            const int id = history[r.hist_begin + j];
-            if (id >= 0 && id < V) row[id] = row[id] > 0.f ? row[id] / r.penalty : row[id] * r.penalty;
+    if (r.penalty > 0.f && fabsf(r.penalty - 1.f) >= 1.1920929e-7f) {
+        if (tid == 0 && team.rank == 0) {
+            for (int j = 0; j < r.hist_len; ++j) {
+                const int id = history[r.hist_begin + j];
+                if (id >= 0 && id < V) row[id] = row[id] > 0.f ? row[id] / r.penalty : row[id] * r.penalty;
+            }
+            __threadfence();
         }
+        team.barrier();
     }
-    __syncthreads();
 
     // the largest logit, first index on ties
     Best b{-INFINITY, 0x7fffffff};
-    for_each_strided(row, V, tid, [&](int i, float v) {
-        if (v > b.v) { b.v = v; b.i = i; }
+    for_each_strided(part, n, tid, [&](int i, float v) {
+        if (v > b.v) { b.v = v; b.i = first + i; }
     });
     b = warp_best(b);
     if (lane == 0) { sh.red_v[warp] = b.v; sh.red_i[warp] = b.i; }
@@ -356,15 +507,17 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
     if (warp == 0) {
         Best c{sh.red_v[lane], sh.red_i[lane]};
         c = warp_best(c);
-        if (lane == 0) { sh.red_v[0] = c.v; sh.red_i[0] = c.i == 0x7fffffff ? 0 : c.i; }
+        if (lane == 0) { sh.red_v[0] = c.v; sh.red_i[0] = c.i; }
     }
-    __syncthreads();
-    const float max_logit = sh.red_v[0];
-    const int arg = sh.red_i[0];
-    __syncthreads();
+    team.barrier();
+    Best top{-INFINITY, 0x7fffffff};
+    for (unsigned q = 0; q < (unsigned)C; ++q) top = better(top, Best{team.peer(&sh.red_v[0], q), team.peer(&sh.red_i[0], q)});
+    team.barrier();
+    const float max_logit = top.v;
+    const int arg = top.i == 0x7fffffff ? 0 : top.i;
     if (r.temperature <= 0.f) {
-        if (tid == 0) out[blockIdx.x] = arg;
-        return;
+        if (tid == 0 && team.rank == 0) *result = arg;
+        return;                                               // every block of the cluster takes this way together
     }
     const float inv_temp = 1.0f / r.temperature;
     const float max_s = max_logit * inv_temp;
@@ -374,18 +527,10 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
     uint32_t min_key = 0;
     unsigned long long n_keep = (unsigned long long)V;
     if (r.top_k > 0 && r.top_k < V) {
-        unsigned long long greater;
-        min_key = radix_select<false>(row, V, inv_temp, max_s, 0u, (unsigned long long)r.top_k, sh, &greater);
-        // how many reach the threshold (ties included)
-        if (tid == 0) sh.count = 0;
-        __syncthreads();
-        int mine = 0;
-        for_each_strided(row, V, tid, [&](int, float v) { mine += key_of(v * inv_temp) >= min_key; });
-        mine = (int)rb::warp_sum((float)mine);  // counts are small integers: exact in float
-        if (lane == 0) atomicAdd(&sh.count, mine);
-        __syncthreads();
-        n_keep = (unsigned long long)sh.count;
-        __syncthreads();
+        // how many reach the threshold (ties included) comes out of the selection itself
+        unsigned long long greater, equal;
+        min_key = radix_select<false>(team, part, n, inv_temp, max_s, 0u, (unsigned long long)r.top_k, sh, &greater, &equal);
+        n_keep = greater + equal;
     }
 
     if (r.top_k > 0 && n_keep <= (unsigned long long)MAX_CAND) {
@@ -394,21 +539,35 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
         sh.cand_val[tid] = -INFINITY;
         sh.cand_idx[tid] = 0x7fffffff;
         __syncthreads();
-        for_each_strided(row, V, tid, [&](int i, float v) {
+        for_each_strided(part, n, tid, [&](int i, float v) {
             const float s = v * inv_temp;
             if (key_of(s) >= min_key) {
                 const int pos = atomicAdd(&sh.count, 1);
                 sh.cand_val[pos] = s;
-                sh.cand_idx[pos] = i;
+                sh.cand_idx[pos] = first + i;
             }
         });
-        __syncthreads();
-        const int n = sh.count;
-        // bitonic sort of MAX_CAND entries, one per thread; empty entries sort last
-        for (int size = 2; size <= MAX_CAND; size <<= 1) {
-            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        team.barrier();
+        if (team.rank == 0) {
+            // the other blocks' candidates come over; the order does not matter, the sort below settles it
+            int have = sh.count;
+            for (unsigned q = 1; q < (unsigned)C; ++q) {
+                const int theirs = team.peer(&sh.count, q);
+                for (int j = tid; j < theirs; j += ST) {
+                    sh.cand_val[have + j] = team.peer(&sh.cand_val[j], q);
+                    sh.cand_idx[have + j] = team.peer(&sh.cand_idx[j], q);
+                }
+                have += theirs;
+            }
+            __syncthreads();
+            const int total = have;
+            // bitonic sort, one entry per thread, of the smallest power of two that holds the candidates;
+            // empty entries sort last.  Up to 32 entries are one warp's own business.
+            int sort_n = 32;
+            while (sort_n < total) sort_n <<= 1;
+            auto exchange = [&](int size, int stride) {
                 const int partner = tid ^ stride;
-                if (partner > tid) {
+                if (partner > tid && partner < sort_n) {
                     const bool up = (tid & size) == 0;
                     const float va = sh.cand_val[tid], vb = sh.cand_val[partner];
                     const int ia = sh.cand_idx[tid], ib = sh.cand_idx[partner];
@@ -418,54 +577,75 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
                         sh.cand_idx[tid] = ib; sh.cand_idx[partner] = ia;
                     }
                 }
-                __syncthreads();
-            }
-        }
-        if (tid == 0) {
-            float sum = 0.f;
-            for (int j = 0; j < n; ++j) { sh.cand_p[j] = expf(sh.cand_val[j] - max_s); sum += sh.cand_p[j]; }
-            if (sum > 0.f) for (int j = 0; j < n; ++j) sh.cand_p[j] /= sum;
-            int keep = n;
-            float eff = 0.f;
-            if (use_p) {
-                float cum = 0.f;
-                for (int j = 0; j < n; ++j) {
-                    cum += sh.cand_p[j];
-                    if (cum >= top_p) { keep = j + 1; break; }
+            };
+            if (sort_n == 32) {
+                if (warp == 0) {
+                    for (int size = 2; size <= 32; size <<= 1)
+                        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                            exchange(size, stride);
+                            __syncwarp();
+                        }
                 }
-                keep = keep < 1 ? 1 : keep;
+                __syncthreads();
+            } else {
+                for (int size = 2; size <= sort_n; size <<= 1)
+                    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                        exchange(size, stride);
+                        __syncthreads();
+                    }
             }
-            for (int j = 0; j < keep; ++j) eff += sh.cand_p[j];
-            const float thr = r.u * fmaxf(eff, 1.17549435e-38f);
-            float acc = 0.f;
-            int pick = sh.cand_idx[0];
-            for (int j = 0; j < keep; ++j) {
-                acc += sh.cand_p[j];
-                if (acc >= thr) { pick = sh.cand_idx[j]; break; }
+            if (tid == 0) {
+                float sum = 0.f;
+                for (int j = 0; j < total; ++j) { sh.cand_p[j] = expf(sh.cand_val[j] - max_s); sum += sh.cand_p[j]; }
+                if (sum > 0.f) for (int j = 0; j < total; ++j) sh.cand_p[j] /= sum;
+                int keep = total;
+                float eff = 0.f;
+                if (use_p) {
+                    float cum = 0.f;
+                    for (int j = 0; j < total; ++j) {
+                        cum += sh.cand_p[j];
+                        if (cum >= top_p) { keep = j + 1; break; }
+                    }
+                    keep = keep < 1 ? 1 : keep;
+                }
+                for (int j = 0; j < keep; ++j) eff += sh.cand_p[j];
+                const float thr = r.u * fmaxf(eff, 1.17549435e-38f);
+                float acc = 0.f;
+                int pick = sh.cand_idx[0];
+                for (int j = 0; j < keep; ++j) {
+                    acc += sh.cand_p[j];
+                    if (acc >= thr) { pick = sh.cand_idx[j]; break; }
+                }
+                *result = pick;
             }
-            out[blockIdx.x] = pick;
         }
+        team.barrier();                                       // the others stay until their candidates have been read
         return;
     }
 
     // ---- route 2: thresholds by radix selection over the whole row ------------------------------
     // total mass of the kept candidates
-    unsigned long long part = 0;
-    for_each_strided(row, V, tid, [&](int, float v) {
+    unsigned long long mass = 0;
+    for_each_strided(part, n, tid, [&](int, float v) {
         const float s = v * inv_temp;
-        if (key_of(s) >= min_key) part += fixed_of(expf(s - max_s));
+        if (key_of(s) >= min_key) mass += fixed_of(expf(s - max_s));
     });
-    if (tid == 0) sh.acc = 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mass += __shfl_xor_sync(0xffffffffu, mass, o);
     __syncthreads();
-    atomicAdd(&sh.acc, part);
+    if (lane == 0) sh.scan[warp] = mass;
     __syncthreads();
-    unsigned long long eff = sh.acc;   // >= 2^40: the maximum itself has probability weight 1
-    __syncthreads();
+    if (tid == 0) {
+        unsigned long long t = 0;
+        for (int w = 0; w < ST / 32; ++w) t += sh.scan[w];
+        sh.acc = t;
+    }
+    unsigned long long eff = team.sum(&sh.acc);   // >= 2^40: the maximum itself has probability weight 1
     if (use_p) {
         unsigned long long target = (unsigned long long)((double)top_p * (double)eff);
         target = target < 1 ? 1 : (target > eff ? eff : target);
-        unsigned long long greater;
-        const uint32_t tp = radix_select<true>(row, V, inv_temp, max_s, min_key, target, sh, &greater);
+        unsigned long long greater, equal;
+        const uint32_t tp = radix_select<true>(team, part, n, inv_temp, max_s, min_key, target, sh, &greater, &equal);
         min_key = tp > min_key ? tp : min_key;
         // candidates that tie with the threshold enter one by one, in index order, until the
         // cumulative mass reaches the target
@@ -475,19 +655,17 @@ sample_kernel(float* __restrict__ logits, long long row_stride, int V, const Sam
     }
     unsigned long long thr = (unsigned long long)((double)r.u * (double)eff);
     thr = thr < 1 ? 1 : (thr > eff ? eff : thr);
-    int token;
     if (use_p) {
         // walk in descending order: the value at which the mass from the top reaches thr, then the
         // j-th candidate of that value in index order
-        unsigned long long greater;
-        const uint32_t td = radix_select<true>(row, V, inv_temp, max_s, min_key, thr, sh, &greater);
+        unsigned long long greater, equal;
+        const uint32_t td = radix_select<true>(team, part, n, inv_temp, max_s, min_key, thr, sh, &greater, &equal);
         const unsigned long long q = fixed_of(expf(value_of_key(td) - max_s));
         const unsigned long long j = q ? (thr - greater + q - 1) / q : 1;
-        token = index_walk<1>(row, V, inv_temp, max_s, td, j < 1 ? 1 : j, sh, arg);
+        index_walk<1>(team, part, n, first, inv_temp, max_s, td, j < 1 ? 1 : j, sh, arg, result);
     } else {
-        token = index_walk<0>(row, V, inv_temp, max_s, min_key, thr, sh, arg);
+        index_walk<0>(team, part, n, first, inv_temp, max_s, min_key, thr, sh, arg, result);
     }
-    if (tid == 0) out[blockIdx.x] = token;
 }
 }  // namespace
 
@@ -497,7 +675,14 @@ extern "C" int rb_sample(float* logits, long long row_stride, int n, int V, cons
                          int* out, void* stream) {
     if (n <= 0) return RB_OK;
     if (V <= 0) return RB_ERR_BAD_SIZE;
-    RB_LAUNCH((sample_kernel), dim3(n), dim3(ST), 0, (cudaStream_t)stream, logits, row_stride, V, (const SampleRow*)rows, history, out);
+    // wide rows: eight blocks a row, as a cluster (see Team)
+    constexpr int TEAM = 8;
+    if (V >= 16384) {
+        cudaError_t e = rb::launch_clustered(sample_kernel<TEAM>, dim3(n * TEAM), dim3(ST), dim3(TEAM, 1, 1), 0,
+                                             (cudaStream_t)stream, logits, row_stride, V, (const SampleRow*)rows, history, out);
+        return e == cudaSuccess ? RB_OK : (int)e;
+    }
+    RB_LAUNCH((sample_kernel<1>), dim3(n), dim3(ST), 0, (cudaStream_t)stream, logits, row_stride, V, (const SampleRow*)rows, history, out);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

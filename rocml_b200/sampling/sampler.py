@@ -12,7 +12,6 @@ ring: a launch never writes host memory that an earlier launch's copies may stil
 """
 from __future__ import annotations
 
-import struct
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -21,6 +20,11 @@ import torch
 
 from .. import kernels
 from .params import SamplingParams, XorShift64Star
+
+
+# one row's record as the kernel reads it (8 x 4 bytes)
+_ROW = np.dtype([("temperature", "<f4"), ("top_k", "<i4"), ("top_p", "<f4"), ("u", "<f4"), ("penalty", "<f4"),
+                 ("hist_begin", "<i4"), ("hist_len", "<i4"), ("pad", "<i4")])
 
 
 @dataclass
@@ -70,22 +74,28 @@ class Sampler:
             if all(p.is_greedy and p.repeat_penalty is None for p in params):
                 kernels.argmax(logits, self._out, n)
             else:
-                rows = slot["rows"].numpy()
+                rec = slot["rows"].numpy().view(_ROW)
                 hist = slot["hist"].numpy()
+                key = tuple(map(id, params))
+                if slot.get("key") != key:
+                    # what does not change from step to step is written once per set of parameters
+                    rec["temperature"][:n] = [float(p.temperature) for p in params]
+                    rec["top_k"][:n] = [int(p.top_k or 0) for p in params]
+                    rec["top_p"][:n] = [-1.0 if p.top_p is None else float(p.top_p) for p in params]
+                    rec["penalty"][:n] = [0.0 if p.repeat_penalty is None else float(p.repeat_penalty) for p in params]
+                    rec["hist_begin"][:n] = 0
+                    rec["hist_len"][:n] = 0
+                    slot["key"] = key
+                    slot["params"] = list(params)        # keeps the ids alive, so that a key names one set only
+                rec["u"][:n] = [0.0 if p.is_greedy else rngs[i].next_f32() for i, p in enumerate(params)]
                 h_used = 0
                 for i, p in enumerate(params):
-                    u = 0.0 if p.is_greedy else rngs[i].next_f32()
-                    pen, hb, hl = 0.0, 0, 0
                     if p.repeat_penalty is not None:
                         w = min(p.repeat_penalty_window, self.max_window)
                         tail = list(histories[i][-w:]) if w > 0 else []
-                        hb, hl = h_used, len(tail)
-                        hist[hb:hb + hl] = tail
-                        h_used += hl
-                        pen = float(p.repeat_penalty)
-                    rec = struct.pack("<fifffiii", float(p.temperature), int(p.top_k or 0),
-                                      -1.0 if p.top_p is None else float(p.top_p), u, pen, hb, hl, 0)
-                    rows[i * 8:(i + 1) * 8] = np.frombuffer(rec, dtype=np.int32)
+                        hist[h_used:h_used + len(tail)] = tail
+                        rec["hist_begin"][i], rec["hist_len"][i] = h_used, len(tail)
+                        h_used += len(tail)
                 self._rows[: n * 8].copy_(slot["rows"][: n * 8], non_blocking=True)
                 if h_used:
                     self._hist[:h_used].copy_(slot["hist"][:h_used], non_blocking=True)
