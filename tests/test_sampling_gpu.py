@@ -102,3 +102,45 @@ def test_repeat_penalty():
     want = plain_sample(logits.numpy(), [3, 3, 1], rng=PlainRng(2), window=64, **rng_kw)
     got = gpu_draws(logits, 1, seed=2, history=[3, 3, 1], **{k: v for k, v in rng_kw.items()})
     assert got == [want]
+
+
+@pytest.mark.parametrize("kw", [dict(temperature=1.0), dict(temperature=0.7, top_p=0.9),
+                                dict(temperature=1.5, top_k=3000), dict(temperature=1.0, top_k=3000, top_p=0.8),
+                                dict(temperature=0.9, top_k=40, top_p=0.7)])
+def test_wide_rows_with_ties_and_masked_stretches(kw):
+    """A row wide enough to be cut over several blocks, whose values repeat thousands of times (so that
+    thresholds fall inside runs of equal values, which enter in index order, and a bin holds more
+    elements than fit in shared memory) and of which a stretch across two parts is masked out."""
+    from rocml_b200.sampling import XorShift64Star
+    V = 40004
+    logits = (make_logits(9, V, scale=2.0) * 4).round() / 4
+    logits[4900:10300] = -float("inf")
+    got = gpu_draws(logits, 60, seed=5, **kw)
+    rng = XorShift64Star(5)
+    want = [exact_reference(logits, rng.next_f32(), **kw) for _ in range(60)]
+    assert got == want
+
+
+def test_rows_of_a_batch_sample_each_in_its_own_way():
+    """Wide rows of one launch with different parameters, a penalty among them, in a matrix whose rows
+    do not start on 16-byte boundaries: every row equals the same row sampled alone."""
+    from rocml_b200.sampling import Sampler, SamplingParams, XorShift64Star
+    V = 30001
+    ways = [SamplingParams(), SamplingParams(0.8, top_k=30, top_p=0.9, seed=1), SamplingParams(1.1, seed=2),
+            SamplingParams(0.7, top_p=0.8, seed=3, repeat_penalty=1.5, repeat_penalty_window=8),
+            SamplingParams(repeat_penalty=50.0), SamplingParams(1.0, top_k=2000, seed=4)]
+    rows = [make_logits(20 + i, V, scale=2.0) for i in range(len(ways))]
+    top = int(rows[4].argmax())
+    histories = [[], [], [], [int(rows[3].argmax()), 5, 6], [top], []]
+    alone = []
+    for sp, row, h in zip(ways, rows, histories):
+        s = Sampler(DEV, max_batch=8)
+        rng = XorShift64Star(sp.seed)
+        alone.append([s.sample(row.to(DEV)[None].clone(), [sp], [rng], [h])[0] for _ in range(5)])
+    assert alone[4][0] != top                                        # the penalty moved the maximum
+    s = Sampler(DEV, max_batch=8)
+    rngs = [XorShift64Star(sp.seed) for sp in ways]
+    together = []
+    for _ in range(5):
+        together.append(s.sample(torch.stack(rows).to(DEV), ways, rngs, histories))
+    assert [list(col) for col in zip(*together)] == alone
