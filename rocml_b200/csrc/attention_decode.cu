@@ -144,13 +144,14 @@ __device__ __forceinline__ uint2 pack4_bf16(const float* v) {
     return raw;
 }
 
-// PROP (long contexts of unequal lengths): the grid's x blocks of a head group are not tied to one
-// sequence each; they are shared out among the sequences in proportion to their pages, so that every
-// block reads about the same number of bytes whatever the lengths.  grid = (blocks, groups, 1).
+// PROP (long contexts of unequal lengths; more sequences than blocks fit the device at once): the grid's
+// x blocks of a head group are not tied to one sequence each; the sequences' pages, laid end to end, are
+// cut into equal runs, one per block, so that every block reads the same number of bytes whatever the
+// lengths and the batch.  grid = (blocks, groups, 1).
 constexpr int PROP_MAX_SEQS = 256;
 
 template <int HD, bool CL, bool FQ, bool PROP>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, HD <= 128 ? 3 : 1)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
@@ -180,11 +181,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int h0 = kvh * g + hc * ROWS;                     // first query head of this block
     const int rows_valid = min(ROWS, g - hc * ROWS);
     int c = blockIdx.x, b = blockIdx.z;
-    int share = 0;                                          // PROP: blocks this sequence was given
+    // PROP: the pages that the sequences of this head group visit, laid end to end, are cut into equal
+    // runs, one per block of the grid's x; a run may end one sequence and begin the next, so a block works
+    // in rounds, one per sequence that its run touches
+    long long run_lo = 0, run_hi = 0, seq_start = 0, total = 0;
+    int n_runs = 1, seq_next = 0;
+    __shared__ int s_pages[PROP ? PROP_MAX_SEQS : 1];
     if (PROP) {
-        // every block works out the same sharing: a block for every sequence that has pages, the
-        // rest in proportion to the pages
-        __shared__ int s_pages[PROP_MAX_SEQS];
         for (int i = threadIdx.x; i < n_seqs; i += WARPS * 32) {
             const int ps = kv_len[i] - 1;
             int P = 0;
@@ -192,36 +195,41 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             s_pages[i] = P;
         }
         __syncthreads();
-        long long total = 0;
-        int nz = 0;
-        for (int i = 0; i < n_seqs; ++i) { total += s_pages[i]; nz += s_pages[i] > 0; }
-        const long long spare = (long long)gridDim.x - nz;  // the host launches at least a block a sequence
-        int first_block = 0;
-        b = -1;
-        for (int i = 0; i < n_seqs; ++i) {
-            if (s_pages[i] == 0) continue;
-            const int n_i = 1 + (int)((long long)s_pages[i] * spare / total);
-            if ((int)blockIdx.x < first_block + n_i) { b = i; c = (int)blockIdx.x - first_block; share = n_i; break; }
-            first_block += n_i;
-        }
-        if (b < 0) return;                                  // a block that was not needed
+        for (int i = 0; i < n_seqs; ++i) total += s_pages[i];
+        n_runs = (int)min((long long)gridDim.x, total);     // every run holds a page at least
+        if ((int)blockIdx.x >= n_runs) return;
+        run_lo = (long long)blockIdx.x * total / n_runs;
+        run_hi = (long long)(blockIdx.x + 1) * total / n_runs;
+    }
+  for (;;) {
+   {
+    int page_first, page_last, parts_lo, parts_hi;         // this block's pages, and the parts that exist of this (sequence, group)
+    if (PROP) {
+        // the next sequence that the run touches
+        while (seq_next < n_seqs && seq_start + s_pages[seq_next] <= run_lo) seq_start += s_pages[seq_next++];
+        if (seq_next >= n_seqs || seq_start >= run_hi) return;
+        b = seq_next;
     }
     const int slot = seq_slot[b];
     if (slot < 0) return;
     const int t = cu_q[b];
     const int pos = kv_len[b] - 1;
     const int win_lo = window > 0 ? max(0, pos - window + 1) : 0;
-    // this block's pages: [c * ppb, (c + 1) * ppb), cut at the sequence's end; PROP: the sequence's
-    // visited pages cut into `share` runs of equal length
-    int page_first, page_last, parts_lo, parts_hi;         // and the parts that exist of this (sequence, group)
+    // this block's pages: [c * ppb, (c + 1) * ppb), cut at the sequence's end; PROP: what the run holds
+    // of the sequence's visited pages
     if (PROP) {
-        const int first = win_lo / CHUNK, P = pos / CHUNK - first + 1;
-        ppb = (P + share - 1) / share;
+        const long long P = s_pages[b];
+        const int first = win_lo / CHUNK;
+        page_first = first + (int)(max(run_lo, seq_start) - seq_start);
+        page_last = first + (int)(min(run_hi, seq_start + P) - seq_start) - 1;
+        // the runs that hold the sequence's first and last page: its parts are numbered from the first
+        const int x_first = (int)(((seq_start + 1) * n_runs + total - 1) / total) - 1;
+        const int x_last = (int)(((seq_start + P) * n_runs + total - 1) / total) - 1;
+        c = (int)blockIdx.x - x_first;
         parts_lo = 0;
-        parts_hi = (P + ppb - 1) / ppb - 1;
-        if (c > parts_hi) return;
-        page_first = first + c * ppb;
-        page_last = min(pos / CHUNK, page_first + ppb - 1);
+        parts_hi = x_last - x_first;
+        seq_start += P;                                     // the round after this one starts at the next sequence
+        ++seq_next;
     } else {
         page_first = c * ppb;
         // beyond the sequence: takes no part in the merge; in a cluster it stays, with an empty result
@@ -441,7 +449,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (CL) {
             s_part[r * HD + d] = A;
             if (d == 0) { s_pm_own[r] = M; s_pl_own[r] = L; }
-        } else if (n_chunks > 1) {
+        } else if (PROP ? parts_hi > 0 : n_chunks > 1) {
             const size_t pidx = (row0 + head) * n_chunks + c;
             part_acc[pidx * HD + d] = A;
             if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
@@ -483,7 +491,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         cluster_sync_all();                                  // nobody leaves while its part may still be read
         return;
     }
-    if (n_chunks <= 1) return;
+    if (PROP ? parts_hi == 0 : n_chunks <= 1) goto round_done;
 
     // the block that arrives last merges the chunks of this (sequence, head group)
     __threadfence();
@@ -496,7 +504,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (s_last) *ctr = 0;              // ready for the next launch
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) goto round_done;
     __threadfence();
     // First every chunk's (maximum, sum) of every row goes to shared memory in one parallel sweep;
     // then each thread owns one (row, dimension) and adds the chunks in ascending order.  Loads of
@@ -529,6 +537,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
         out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
     }
+   }
+round_done:
+    if (!PROP) return;
+    __syncthreads();                                        // the shared memory is free for the next round
+  }
 }
 
 bool cluster_enabled() {
@@ -576,7 +589,7 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
            void* out, int o_stride, const Projections& pj, cudaStream_t s) {
     const int g = nq / nkv;
     const bool proportional = ppb == 0;     // n_chunks blocks a head group, shared out among the sequences
-    if (proportional && (n_chunks < B || B > PROP_MAX_SEQS)) return RB_ERR_BAD_SIZE;
+    if (proportional && B > PROP_MAX_SEQS) return RB_ERR_BAD_SIZE;
     dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), proportional ? 1 : B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     const size_t kv_bytes = (size_t)WARPS * 4 * WK * HD * sizeof(__nv_bfloat16);   // two buffers per warp
@@ -602,8 +615,8 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 // One query token per sequence (token index cu_q[b]).  A block takes `pages_per_block` pages of 64
 // keys; n_chunks = ceil(pages of the longest sequence / pages_per_block) blocks cover a sequence;
 // with n_chunks == 1 the result is written to `out` directly.  pages_per_block == 0: n_chunks blocks
-// (at least B, B <= 256) per key/value head group are shared out among the sequences in proportion to
-// their pages, for long contexts of unequal lengths.
+// per key/value head group share the pages of all B sequences (B <= 256) equally, a block working on
+// the end of one sequence and the beginning of the next where its share says so.
 // Work space: part_acc [T, nq, n_chunks, hd], part_ml [T, nq, n_chunks, 2] and `counters`, at least
 // B * nkv * ceil(group / 16) ints that are ZERO on entry and are left zero on exit.
 // Returns RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 and for contexts whose chunk list does

@@ -311,17 +311,21 @@ def decode_split(n_seqs: int, n_kv_groups: int, n_pages: int, device=0):
     sequences times key/value head groups within the resident slots), because a second, partly filled
     wave costs a whole block's latency.  A large batch therefore walks many pages per block (one
     partial result and one merge for all of them) and a single sequence spreads over the device.
-    Contexts beyond 4,096 tokens in a batch: see below.  Up to 16 blocks per sequence form a thread-block cluster and merge through shared memory, which
+    Contexts beyond 4,096 tokens in a batch, and batches too large for one block a (sequence, head
+    group): see below.  Up to 16 blocks per sequence form a thread-block cluster and merge through shared memory, which
     is quicker than through global memory: a finer split is cut back to 16 where that leaves a block
     at most four pages."""
     key = torch.device(device).index or 0
     if key not in _sm_count:
         _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
     slots = 3 * _sm_count[key]
-    if n_pages > 64 and 2 <= n_seqs <= 256:
-        # long contexts, which may differ a lot in length: one wave of blocks a head group, shared out
-        # among the sequences in proportion to their pages (pages per block 0 says so to the kernel)
-        return max(n_seqs, min(1024, slots // max(1, n_kv_groups))), 0
+    pairs = n_seqs * n_kv_groups
+    if 2 <= n_seqs <= 256 and (n_pages > 64 or (n_pages >= 8 and slots < pairs <= slots + slots // 3)):
+        # long contexts, which may differ a lot in length, or a few more (sequence, head group) pairs
+        # than blocks run at once (the second, thinly filled wave would take nearly as long as the first;
+        # with more pairs than that, waves of whole sequences measured faster): one wave of blocks a head
+        # group, which share the pages of all sequences equally (pages per block 0 says so to the kernel)
+        return max(1, min(1024, slots // max(1, n_kv_groups))), 0
     blocks = max(1, min(n_pages, slots // max(1, n_seqs * n_kv_groups)))
     if blocks > DECODE_CLUSTER_MAX and -(-n_pages // DECODE_CLUSTER_MAX) <= 4:
         blocks = DECODE_CLUSTER_MAX
@@ -344,6 +348,13 @@ def decode_counters(device) -> torch.Tensor:
     return _counters[key]
 
 
+def _check_parts(part_acc, part_ml, n_chunks: int, what: str) -> None:
+    """The kernel numbers a row's partial results up to n_chunks - 1 and strides by n_chunks."""
+    if n_chunks > 1 and (part_acc is None or part_ml is None or part_acc.shape[2] < n_chunks
+                         or part_ml.shape[2] < n_chunks or part_acc.shape[2] != part_ml.shape[2]):
+        raise KernelError(f"{what}: work space for {n_chunks} partial results a row is needed")
+
+
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                      n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
@@ -359,6 +370,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
         return False
     if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:
         raise KernelError("attention_decode: cache must be [pages, nkv, 64, hd]")
+    _check_parts(part_acc, part_ml, n_chunks, "attention_decode")
     rc = _lib().rb_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _i32(block_table, "block_table"), block_table.shape[1],
         _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), _i32(kv_len, "kv_len"), n_seqs, nq, nkv, hd, float(scale),
@@ -404,6 +416,7 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
         w_f32 = 1 if q_norm_w.dtype == torch.float32 else 0
     if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.numel() < n_seqs * hd):
         raise KernelError("attention_decode_fused: cos_sin must be float32 [T, 64, 2]")
+    _check_parts(part_acc, part_ml, n_chunks, "attention_decode_fused")
     rc = _lib().rb_attention_decode_fused(
         _ptr(proj), n_in, in_stride, row_stride, _ptr(q_norm_w), _ptr(k_norm_w), w_f32, float(eps), _ptr(cos_sin),
         1 if write_kv else 0, *_row_scale(rowscale, n_seqs, "attention_decode_fused"), int(row_width),

@@ -166,8 +166,9 @@ class Attention(Mixer):
         acc = ml = None
         if n_pages > 1:
             T = batch.n_tokens
-            acc = torch.empty((T, self.nq, n_pages, self.hd), dtype=torch.float32, device=out.device)
-            ml = torch.empty((T, self.nq, n_pages, 2), dtype=torch.float32, device=out.device)
+            parts = max(n_pages, n_blocks)          # the kernel strides a row's partial results by n_blocks
+            acc = torch.empty((T, self.nq, parts, self.hd), dtype=torch.float32, device=out.device)
+            ml = torch.empty((T, self.nq, parts, 2), dtype=torch.float32, device=out.device)
         return kernels.attention_decode_fused(
             proj, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q, batch.kv_len, batch.n_seqs,
             self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
@@ -185,8 +186,9 @@ class Attention(Mixer):
             n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages, q.device)
             acc = ml = None
             if n_pages > 1:
-                acc = torch.empty((T, self.nq, n_pages, self.hd), dtype=torch.float32, device=q.device)
-                ml = torch.empty((T, self.nq, n_pages, 2), dtype=torch.float32, device=q.device)
+                parts = max(n_pages, n_blocks)
+                acc = torch.empty((T, self.nq, parts, self.hd), dtype=torch.float32, device=q.device)
+                ml = torch.empty((T, self.nq, parts, 2), dtype=torch.float32, device=q.device)
             fast = kernels.attention_decode(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                             batch.kv_len, batch.n_seqs, self.nq, self.nkv, self.hd, self.scale,
                                             window, n_blocks, acc, ml, ppb)

@@ -14,9 +14,14 @@ def sms(monkeypatch):
 @pytest.mark.parametrize("n_pages", [1, 2, 17, 20, 64])
 def test_equal_split_covers_every_page_in_one_wave(n_seqs, groups, n_pages):
     blocks, ppb = kernels.decode_split(n_seqs, groups, n_pages)
+    resident = 3 * 148
+    if ppb == 0:
+        # more (sequence, head group) pairs than run at once: one wave of blocks shares all pages
+        assert n_pages >= 8 and resident < n_seqs * groups <= resident * 4 // 3 and 2 <= n_seqs <= 256
+        assert 1 <= blocks and blocks * groups <= resident
+        return
     assert ppb >= 1 and blocks >= 1
     assert blocks * ppb >= n_pages > (blocks - 1) * ppb          # every page, no empty block
-    resident = 3 * 148
     assert blocks == 1 or blocks * n_seqs * groups <= resident    # one wave, unless one block a sequence is already too many
 
 
@@ -24,15 +29,18 @@ def test_a_finer_split_is_cut_back_to_a_cluster_where_blocks_stay_short():
     assert kernels.decode_split(1, 8, 20) == (10, 2)      # 20 blocks would fit; 16 -> two pages a block -> ten blocks
     assert kernels.decode_split(1, 8, 64) == (16, 4)
     assert kernels.decode_split(8, 8, 20) == (5, 4)       # the wave allows six blocks a sequence
-    assert kernels.decode_split(64, 8, 20) == (1, 20)
+    assert kernels.decode_split(48, 8, 20) == (1, 20)
+    assert kernels.decode_split(64, 8, 20) == (55, 0)     # 512 pairs do not run at once: 55 blocks a group share the pages
+    assert kernels.decode_split(64, 8, 4) == (1, 4)       # too short to be worth it
+    assert kernels.decode_split(100, 8, 20) == (1, 20)    # nearly two full waves of whole sequences
 
 
-@pytest.mark.parametrize("n_seqs,groups,n_pages", [(2, 8, 65), (4, 8, 496), (64, 8, 100), (256, 2, 80)])
+@pytest.mark.parametrize("n_seqs,groups,n_pages", [(2, 8, 65), (4, 8, 496), (64, 8, 100), (256, 2, 80), (64, 8, 17)])
 def test_long_contexts_in_a_batch_share_the_blocks(n_seqs, groups, n_pages):
     blocks, ppb = kernels.decode_split(n_seqs, groups, n_pages)
-    assert ppb == 0                                       # pages per block 0: shared out by length on the device
-    assert n_seqs <= blocks <= 1024
-    assert blocks * groups <= max(3 * 148, n_seqs * groups)
+    assert ppb == 0                                       # pages per block 0: the pages are shared out on the device
+    assert 1 <= blocks <= 1024
+    assert blocks * groups <= 3 * 148
 
 
 def test_one_long_sequence_and_very_many_sequences_keep_the_equal_split():

@@ -438,7 +438,7 @@ DEC_CASES = [
 
 
 @pytest.mark.parametrize("case", range(len(DEC_CASES)))
-@pytest.mark.parametrize("fast", [True, False, 3, 100, "shared"])
+@pytest.mark.parametrize("fast", [True, False, 3, 100, "shared", "shared-2", "shared-1"])
 def test_attention_decode_split_kv(case, fast):
     """One query per sequence, keys in chunks of 128, merged: the bfloat16 kernel and the plain kernel."""
     from rocml_b200 import kernels
@@ -453,13 +453,16 @@ def test_attention_decode_split_kv(case, fast):
     out = torch.full_like(q, float("nan"))
     d = {k: v.to(DEV) for k, v in meta.items()}
     ppb = 1 if fast in (True, False) else fast        # pages per block of the bfloat16 kernel
-    if fast == "shared":
-        # a fixed number of blocks a head group, shared out among the sequences by their lengths
-        ppb, n_chunks = 0, len(lens) + 6
+    if isinstance(fast, str):
+        # a fixed number of blocks a head group, which share the pages of all sequences equally: more
+        # blocks than sequences, or fewer (a block then ends one sequence and begins the next)
+        ppb, n_chunks = 0, (len(lens) + 6 if fast == "shared" else int(fast[-1]))
     else:
         n_chunks = ((max(lens) + 63) // 64 + ppb - 1) // ppb + 1     # one more than needed, as a padded graph would have
     acc = torch.full((B, nq, n_chunks, hd), float("nan"), dtype=torch.float32, device=DEV)
     ml = torch.full((B, nq, n_chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
+    if n_chunks == 1:
+        acc = ml = None
     pos = (d["kv_len"] - 1).to(torch.int32)
     if fast:
         assert kernels.attention_decode(q, out, kc.to(DEV), vc.to(DEV), d["table"], d["seq_slot"], d["cu_q"],
@@ -478,7 +481,9 @@ def test_attention_decode_split_kv(case, fast):
     ([300, 131, 65], 8, 2, None, 1, True, True, (2, 3)),               # clusters of 2
     ([513, 40], 6, 3, 70, 3, False, True, (1, 1)),                    # a window, no per-head norm
     ([1100], 40, 2, None, 2, True, False, (1, 1)),                     # 20 query heads per group: two blocks a group; 18 chunks: merged through global memory
-    ([900, 70, 300, 5], 8, 2, None, 4, True, True, (0, 9)),            # nine blocks a group shared out by length
+    ([900, 70, 300, 5], 8, 2, None, 4, True, True, (0, 9)),            # nine blocks a group share the pages
+    ([900, 70, 300, 5, 64, 65, 200], 8, 2, None, 4, True, True, (0, 3)),  # fewer blocks than sequences
+    ([130, 70, 300], 8, 2, 100, 2, True, True, (0, 2)),                # the same with a window
 ])
 def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S, norm, rope, grid):
     """Head size 128: the decode kernel is given the projection's partial sums and does the
