@@ -284,3 +284,124 @@ def test_prompt_projection_fused_and_separate_agree(tmp_path, monkeypatch):
         scale = want.abs().amax(-1, keepdim=True)
         assert float(((got[name] - want).abs() / scale).max()) < 2.5e-2
     assert float((got["fused"] - got["separate"]).abs().max() / want.abs().max()) < 2.5e-2
+
+
+def test_a_toy_position_encoding_and_a_toy_routed_feed_forward_register_build_and_step():
+    """Two more parts defined HERE: a position encoding (a stretched rotation of half of every head:
+    another table behind the same interface, which the attention part's kernels then use) and a
+    feed-forward with routing (a router picks one of three small experts per token).  A model of two
+    layers built from them is stepped whole, token by token and two sequences at once, and equals
+    the same arithmetic in float64."""
+    from rocml_b200 import kernels
+    from rocml_b200.config import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
+                                   ScheduleEntry)
+    from rocml_b200.engine import Engine, Model, StepEntry
+    from rocml_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position
+    from rocml_b200.weights import TensorDecl
+    from rocml_b200.weights.random_init import random_tensor
+
+    @register_position("toy_stretched_rope")
+    class StretchedRope(PositionEncoding):
+        graph_safe = True
+
+        def __init__(self, spec, head_dim, env):
+            self.rot_dim = int(spec.rot_dim)
+            self.stretch = float(spec.params["stretch"])
+            i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+            self.inv_freq = (torch.pow(torch.tensor(spec.theta, dtype=torch.float64), -2.0 * i / self.rot_dim)
+                             / self.stretch).float().to(env.device)
+
+        def cos_sin(self, batch):
+            key = ("toy_stretched_rope", self.rot_dim, self.stretch)
+            if key not in batch.scratch:
+                batch.scratch[key] = kernels.rope_table(batch.positions, self.inv_freq, batch.n_tokens)
+            return batch.scratch[key]
+
+    @register_feed_forward("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        graph_safe = False
+
+        def __init__(self, spec, hidden, env):
+            self.hidden, self.n, self.inner = hidden, spec.params["experts"], spec.params["intermediate"]
+
+        def declare(self, prefix):
+            out = [TensorDecl(f"{prefix}router.weight", (self.n, self.hidden))]
+            for e in range(self.n):
+                out += [TensorDecl(f"{prefix}experts.{e}.up.weight", (self.inner, self.hidden)),
+                        TensorDecl(f"{prefix}experts.{e}.down.weight", (self.hidden, self.inner))]
+            return out
+
+        def load(self, tensors, prefix):
+            self.router = tensors[f"{prefix}router.weight"].float()
+            self.up = [tensors[f"{prefix}experts.{e}.up.weight"].float() for e in range(self.n)]
+            self.down = [tensors[f"{prefix}experts.{e}.down.weight"].float() for e in range(self.n)]
+
+        def forward(self, xn, batch):
+            x = xn.float()
+            p = torch.softmax(x @ self.router.t(), -1)               # router logits and softmax in 32-bit
+            weight, choice = p.max(-1)
+            out = torch.zeros((1, batch.n_tokens, self.hidden), dtype=torch.float32, device=x.device)
+            for e in range(self.n):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    out[0, rows] = weight[rows, None] * (torch.relu(x[rows] @ self.up[e].t()) @ self.down[e].t())
+            return out
+
+    H, nq, nkv, hd, V, E, I, rot, theta, stretch = 40, 6, 2, 16, 83, 3, 24, 8, 1e4, 3.0
+    norm = NormSpec("rmsnorm", 1e-5)
+    pos = PositionSpec("toy_stretched_rope", theta=theta, rot_dim=rot, params_items=(("stretch", stretch),))
+    att = MixerSpec.make("attention", position=pos, n_heads=nq, n_kv_heads=nkv, head_dim=hd, bias=False,
+                         qk_norm=False, window=None, scale=None)
+    ff = FeedForwardSpec.make("toy_top1_experts", experts=E, intermediate=I)
+    layers = tuple(LayerSpec(f"model.layers.{i}", att, ff, norm, norm) for i in range(2))
+    spec = ModelSpec("ToyRouted", H, V, 128, layers, (ScheduleEntry(0), ScheduleEntry(1)), norm, tie_embeddings=True)
+    model = Model(spec, env(torch.float32))
+    assert not model.graph_safe
+    tensors = {d.name: random_tensor(d, 3).float() * (4.0 if d.role == "matrix" else 1.0) for d in model.declare()}
+    model.load({k: v.to(DEV) for k, v in tensors.items()})
+    eng = Engine(model, max_tokens=256, max_slots=2)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    def rotate(x, T):
+        half = rot // 2
+        inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / rot)
+        ang = torch.arange(T, dtype=torch.float64)[:, None] * (inv.float() / stretch).double()[None, :]
+        cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        x0, x1 = x[..., :half], x[..., half:rot]
+        return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos, x[..., rot:]], -1)
+
+    def plain(ids):
+        T = len(ids)
+        x = w["model.embed_tokens.weight"][ids]
+        picks = []
+        for i in range(2):
+            p = f"model.layers.{i}."
+            xn = P.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-5)
+            q = rotate(P.linear(xn, w[p + "self_attn.q_proj.weight"]).view(T, nq, hd), T)
+            k = rotate(P.linear(xn, w[p + "self_attn.k_proj.weight"]).view(T, nkv, hd), T)
+            v = P.linear(xn, w[p + "self_attn.v_proj.weight"]).view(T, nkv, hd)
+            x = x + P.linear(P.attention(q, k, v).reshape(T, nq * hd), w[p + "self_attn.o_proj.weight"])
+            xn = P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+            pr = torch.softmax(xn @ w[p + "mlp.router.weight"].t(), -1)
+            weight, choice = pr.max(-1)
+            picks.append(choice)
+            y = torch.stack([weight[t] * (torch.relu(xn[t] @ w[p + f"mlp.experts.{int(choice[t])}.up.weight"].t())
+                                          @ w[p + f"mlp.experts.{int(choice[t])}.down.weight"].t()) for t in range(T)])
+            x = x + y
+        return P.linear(P.rmsnorm(x, w["model.norm.weight"], 1e-5), w["model.embed_tokens.weight"]), picks
+
+    a, b = prompt(31, 30, V), prompt(32, 21, V)
+    want_a, picks = plain(a)
+    want_b, _ = plain(b)
+    assert all(len(set(c.tolist())) > 1 for c in picks)            # the router does route
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    out = eng.step([StepEntry(sa, a[:17], list(range(17))), StepEntry(sb, b[:9], [8])]).cpu().double()
+    got_a, got_b = [out[:17]], [out[17:]]
+    for t in range(12):
+        out = eng.step([StepEntry(sa, [a[17 + t]], [0]), StepEntry(sb, [b[9 + t]], [0])]).cpu().double()
+        got_a.append(out[:1]); got_b.append(out[1:])
+    out = eng.step([StepEntry(sa, [a[29]], [0])]).cpu().double()      # the shorter one has ended
+    got_a.append(out)
+    scale = want_a.abs().max()
+    assert (torch.cat(got_a) - want_a).abs().max() < 1e-4 * scale
+    assert (torch.cat(got_b) - want_b[8:]).abs().max() < 1e-4 * scale
