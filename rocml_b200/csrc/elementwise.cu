@@ -156,16 +156,21 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_rows_kernel(float* __rest
         const int i = threadIdx.x + j * THREADS;
         v[j] = i < H4 ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int s = 0; s < n_delta; ++s) {                     // partial sums in their order
+    for (int s = 0; s < n_delta; s += 2) {                  // partial sums in their order, two in flight
         const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)s * delta_stride + (size_t)row * H);
-        float4 d[8];
+        const float4* e4 = reinterpret_cast<const float4*>(delta + (size_t)(s + 1) * delta_stride + (size_t)row * H);
+        const bool second = s + 1 < n_delta;
+        float4 d[8], e[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int i = threadIdx.x + j * THREADS;
             d[j] = i < H4 ? d4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            e[j] = second && i < H4 ? e4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) { v[j].x += d[j].x; v[j].y += d[j].y; v[j].z += d[j].z; v[j].w += d[j].w; }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[j].x += e[j].x; v[j].y += e[j].y; v[j].z += e[j].z; v[j].w += e[j].w; }
     }
     float ss = 0.f;
 #pragma unroll
@@ -188,10 +193,11 @@ static int launch_add_rmsnorm(float* resid, const float* delta, int n_delta, siz
                               const void* w, void* out, const int* rows, int n_rows, int H, float eps,
                               int write_back, cudaStream_t s) {
     // many rows: the register kernel, when everything is 16-byte aligned and a row fits its threads
+    // (up to 256 rows are at most one wave of the kernel below, whose 1,024 threads a row finish sooner)
     const bool aligned = (H & 3) == 0 && (delta_stride & 3) == 0 &&
                          ((((uintptr_t)resid | (uintptr_t)delta) & 15) == 0) &&
                          ((((uintptr_t)out | ((size_t)H * sizeof(OT))) & 15) == 0) && (((uintptr_t)w & (4 * sizeof(WT) - 1)) == 0);
-    if (n_rows > 64 && aligned && H <= 8 * 4 * 256) {
+    if (n_rows > (H >= 4096 ? 256 : 64) && aligned && H <= 8 * 4 * 256) {
         if (H <= 8 * 4 * 128)
             RB_LAUNCH((add_rmsnorm_rows_kernel<OT, WT, 128>), dim3(n_rows), dim3(128), 0, s, resid, delta, n_delta,
                       delta_stride, (const WT*)w, (OT*)out, rows, H, eps, write_back);

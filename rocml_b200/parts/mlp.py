@@ -10,7 +10,7 @@ from ..config.specs import FeedForwardSpec
 from ..errors import ConfigError
 from ..weights.decl import TensorDecl
 from .base import BuildEnv, DeferredNorm, FeedForward, register_feed_forward
-from .linear import Linear
+from .linear import GATED_PAIR_MAX_ROWS, Linear
 
 
 @register_feed_forward("gated_mlp")
@@ -51,7 +51,7 @@ class GatedMLP(FeedForward):
         """Whether forward() can be handed a DeferredNorm for this step: only the product of two blocks
         that applies the activation itself also applies the rows' 1/RMS."""
         T = batch.n_tokens
-        return (self.gate_up.paired and T <= 32 and self.gate_up.weight.dtype == torch.bfloat16
+        return (self.gate_up.paired and T <= GATED_PAIR_MAX_ROWS and self.gate_up.weight.dtype == torch.bfloat16
                 and self.gate_up._splits(T) == 2 and self.gate_up.k > 64)
 
     def forward(self, xn, batch, sink=None):
