@@ -155,11 +155,20 @@ class Linear:
         partial sums); each split keeps at least five 64-wide K blocks, at most 8 splits, and the
         float32 partial results stay below a sixth of the weight's own bytes.  A product over a
         very deep K (24 or more K blocks left per split) is split twice as often, as long as all
-        its blocks still fit on the device at once (four per multiprocessor).  The count depends
-        on the weight's shape, the step's row count and the device only."""
-        if m > 128 or self.k % 8:
+        its blocks still fit on the device at once (four per multiprocessor).  More than 128 rows:
+        see below.  The count depends on the weight's shape, the step's row count and the device only."""
+        if self.k % 8:
             return 1
         sms = _sm_count(self.env.device)
+        if m > 128:
+            # A few hundred rows: the output has fewer 128 x 256 tiles than the device has
+            # multiprocessors, and each block would stream its share of the weight alone.  The sum over
+            # K is split until the blocks fill one wave (measured at 160 to 1,024 rows: whenever tiles
+            # times splits stays within the multiprocessors the split wins, up to 2.7 times; beyond, it
+            # loses to the kernels for many rows).
+            tiles = ((m + 127) // 128) * ((self.n + 255) // 256)
+            s = min(sms // max(1, tiles), (self.k // 64) // 8, 8)
+            return s if s >= 2 else 1
         tiles = (self.n + 127) // 128
         k_blocks = self.k // 64
         by_blocks = -(-2 * sms // tiles)
