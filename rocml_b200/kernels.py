@@ -311,24 +311,28 @@ def decode_split(n_seqs: int, n_kv_groups: int, n_pages: int, device=0):
     sequences times key/value head groups within the resident slots), because a second, partly filled
     wave costs a whole block's latency.  A large batch therefore walks many pages per block (one
     partial result and one merge for all of them) and a single sequence spreads over the device.
-    Contexts beyond 4,096 tokens in a batch, and batches too large for one block a (sequence, head
-    group): see below.  Up to 16 blocks per sequence form a thread-block cluster and merge through shared memory, which
-    is quicker than through global memory: a finer split is cut back to 16 where that leaves a block
-    at most four pages."""
+    Contexts beyond 4,096 tokens in a batch of four or more, and batches too large for one block a
+    (sequence, head group): see below.  Up to 16 blocks per sequence form a thread-block cluster and
+    merge through shared memory, which is so much quicker than through global memory that a finer
+    split is always cut back to 16."""
     key = torch.device(device).index or 0
     if key not in _sm_count:
         _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
     slots = 3 * _sm_count[key]
     pairs = n_seqs * n_kv_groups
-    if 2 <= n_seqs <= 256 and (n_pages > 64 or (n_pages >= 8 and slots < pairs <= slots + slots // 3)):
-        # long contexts, which may differ a lot in length, or a few more (sequence, head group) pairs
-        # than blocks run at once (the second, thinly filled wave would take nearly as long as the first;
-        # with more pairs than that, waves of whole sequences measured faster): one wave of blocks a head
-        # group, which share the pages of all sequences equally (pages per block 0 says so to the kernel)
+    if (4 <= n_seqs <= 256 and n_pages > 64) or \
+            (2 <= n_seqs <= 256 and n_pages >= 8 and slots < pairs <= slots + slots // 3):
+        # several long contexts, which may differ a lot in length, or a few more (sequence, head group)
+        # pairs than blocks run at once (the second, thinly filled wave would take nearly as long as the
+        # first; with more pairs than that, waves of whole sequences measured faster): one wave of blocks
+        # a head group, which share the pages of all sequences equally (pages per block 0 says so to the
+        # kernel)
         return max(1, min(1024, slots // max(1, n_kv_groups))), 0
-    blocks = max(1, min(n_pages, slots // max(1, n_seqs * n_kv_groups)))
-    if blocks > DECODE_CLUSTER_MAX and -(-n_pages // DECODE_CLUSTER_MAX) <= 4:
-        blocks = DECODE_CLUSTER_MAX
+    blocks = max(1, min(n_pages, slots // max(1, pairs)))
+    # more than 16 blocks would merge through global memory, which costs more than the longer blocks
+    # of a cluster do (one sequence of 8,192 tokens: 15 us with 16 blocks of 8 pages, 26 us with 43 of 3;
+    # at 32,000 tokens 38 against 41)
+    blocks = min(blocks, DECODE_CLUSTER_MAX)
     ppb = -(-n_pages // blocks)
     return -(-n_pages // ppb), ppb
 

@@ -35,7 +35,7 @@ def test_a_finer_split_is_cut_back_to_a_cluster_where_blocks_stay_short():
     assert kernels.decode_split(100, 8, 20) == (1, 20)    # nearly two full waves of whole sequences
 
 
-@pytest.mark.parametrize("n_seqs,groups,n_pages", [(2, 8, 65), (4, 8, 496), (64, 8, 100), (256, 2, 80), (64, 8, 17)])
+@pytest.mark.parametrize("n_seqs,groups,n_pages", [(4, 8, 65), (4, 8, 496), (64, 8, 100), (256, 2, 80), (64, 8, 17)])
 def test_long_contexts_in_a_batch_share_the_blocks(n_seqs, groups, n_pages):
     blocks, ppb = kernels.decode_split(n_seqs, groups, n_pages)
     assert ppb == 0                                       # pages per block 0: the pages are shared out on the device
@@ -44,5 +44,7 @@ def test_long_contexts_in_a_batch_share_the_blocks(n_seqs, groups, n_pages):
 
 
 def test_one_long_sequence_and_very_many_sequences_keep_the_equal_split():
-    assert kernels.decode_split(1, 8, 512)[1] > 0
+    assert kernels.decode_split(1, 8, 512) == (16, 32)    # never more blocks than a cluster holds
+    assert kernels.decode_split(1, 8, 128) == (16, 8)
+    assert kernels.decode_split(3, 8, 500) == (16, 32)    # up to three long sequences: a cluster each
     assert kernels.decode_split(300, 8, 100)[1] > 0
