@@ -14,6 +14,7 @@
 //
 // It stands where the reference has gemv_f16 (decode) and gemm_xwt_f16 (prefill):
 // rocml-kernels/kernels/gemv_f16.hip:8-36, gemm_f16.hip:10-41.
+#include <type_traits>
 #include "common.cuh"
 #include "sm100.cuh"
 #include "api.h"
@@ -86,6 +87,13 @@ __device__ __forceinline__ void store16(float* dst, const float* v) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
         reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+__device__ __forceinline__ void load16(const float* src, float* v) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 f = reinterpret_cast<const float4*>(src)[i];
+        v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+    }
 }
 __device__ __forceinline__ void store16(__nv_bfloat16* dst, const float* v) {
     uint32_t w[8];
@@ -650,7 +658,8 @@ constexpr int PAIR_STAGE = 2 * BM * BK * 2;       // A 128 x 64 + B half 128 x 6
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE + 1024 + 256;
 
-// EPI: 0 plain, 1 SiLU(gate) * up (rows of the weight interleaved by 16), 2 a prompt's q | k | v projection
+// EPI: 0 plain, 3 added into `out` (the float32 residual stream) instead of written, 1 SiLU(gate) * up (rows
+// of the weight interleaved by 16), 2 a prompt's q | k | v projection
 // with heads of 128: a tile's 256 columns are two whole heads and an epilogue thread owns a token, so
 // the per-head RMSNorm and the rotation (pairs i, i + 64) are done on the accumulator itself, and
 // the queries go to their own tensor, keys and values straight into their cache pages.
@@ -866,7 +875,43 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         }
                     }
                 }
-            } else {
+            } else if (EPI == 3) {
+                // out is the residual stream: out += product.  Every element belongs to one tile and one
+                // thread, so nothing else touches it meanwhile; the old values of two column groups are
+                // requested before the accumulator is read, so their latency overlaps it.
+                if constexpr (std::is_same<OT, float>::value) {
+                    rb::pdl_wait();   // these threads read what earlier kernels wrote (the residual): returns at once by now
+#pragma unroll 1
+                    for (int c = 0; c < BN / 16; c += 2) {
+                        const int f0 = b0 + c * 16;
+                        const bool whole = vec_ok && f0 + 32 <= p.b_rows && ar < p.a_rows;
+                        float r[32];
+                        if (whole) {
+                            load16(row + f0, r);
+                            load16(row + f0 + 16, r + 16);
+                        }
+                        float v[32];
+                        tmem_ld16(lane_addr + c * 16, v);
+                        tmem_ld16(lane_addr + (c + 1) * 16, v + 16);
+                        if (ar < p.a_rows) {
+                            if (add_bias) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] += (f0 + i < p.b_rows) ? p.bias[f0 + i] : 0.f;
+                            }
+                            if (whole) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] += r[i];
+                                store16(row + f0, v);
+                                store16(row + f0 + 16, v + 16);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (f0 + i < p.b_rows) row[f0 + i] += v[i];
+                            }
+                        }
+                    }
+                }
+} else {
 #pragma unroll 1
                 for (int c = 0; c < BN / 16; ++c) {
                     float v[16];
@@ -1105,7 +1150,8 @@ struct ResidualOut {
 static int gemm_entry(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
                       int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
                       int stages, int gated, int* status, void* stream, int cluster_split,
-                      const ResidualOut* ro = nullptr, const RowScale* rsc = nullptr, const RopeOut* rope = nullptr) {
+                      const ResidualOut* ro = nullptr, const RowScale* rsc = nullptr, const RopeOut* rope = nullptr,
+                      bool accumulate = false) {
     if (M <= 0 || N <= 0) return RB_OK;
     if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
     if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
@@ -1193,10 +1239,13 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
         if ((rc = tensor_map(w, N, K, K, BM, &mb_half)) != RB_OK) return rc;
         return launch_pair<__nv_bfloat16, 2>(ma, mb_half, nullptr, p, s);
     }
+    if (accumulate && (swap || splits != 1 || bn != 256 || M <= 256 || !pair_enabled() || out_dtype != RB_F32 || gated))
+        return RB_ERR_BAD_SIZE;            // only the kernel of CTA pairs adds into its output
     if (!swap && splits == 1 && bn == 256 && M > 256 && pair_enabled()) {
         // many tokens and a wide weight: pairs of CTAs; the weight is read in boxes of 128 rows (a half tile)
         CUtensorMap mb_half;
         if ((rc = tensor_map(w, N, K, K, BM, &mb_half)) != RB_OK) return rc;
+        if (accumulate) return launch_pair<float, 3>(ma, mb_half, out, p, s);
         if (out_dtype == RB_BF16)
             return gated ? launch_pair<__nv_bfloat16, 1>(ma, mb_half, out, p, s)
                          : launch_pair<__nv_bfloat16, 0>(ma, mb_half, out, p, s);
@@ -1233,6 +1282,16 @@ extern "C" int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, 
                                int stages, int gated, int* status, void* stream) {
     return gemm_entry(x, w, bias, out, out_dtype, M, N, K, ldx, ldo, splits, split_stride, stages, gated, status,
                       stream, 0);
+}
+
+// resid[M, N] += x[M, K] . w[N, K]^T (+ bias) for more than 256 rows and N >= 256: the product is added
+// into the float32 residual stream (row stride ld_resid) in the epilogue of the kernel of CTA pairs, so
+// no delta goes through memory.  RB_ERR_BAD_SIZE for other sizes (the caller writes a delta instead),
+// RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
+extern "C" int rb_gemm_tcgen05_add(const void* x, const void* w, const float* bias, float* resid, int M, int N, int K,
+                                   long long ldx, long long ld_resid, int stages, int* status, void* stream) {
+    return gemm_entry(x, w, bias, resid, RB_F32, M, N, K, ldx, ld_resid, 1, 0, stages, 0, status, stream, 0, nullptr,
+                      nullptr, nullptr, true);
 }
 
 // h[M, N / 2] = silu(gate) * up (bfloat16, row stride ldh) for at most 32 rows and a gate/up weight

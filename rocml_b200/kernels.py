@@ -98,6 +98,7 @@ def _lib():
                                                   _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_sample.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp]
         lib.rb_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _i, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05_add.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _i, _ll, _f, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_qkv_rope.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _vp,
                                                  _vp, _i, _f, _vp, _i, _i, _i, _vp, _vp]
@@ -575,6 +576,30 @@ def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, b
     if rc in (10001, 10003):
         return False
     _check(rc, "gemm_tcgen05_gated_pair")
+    return True
+
+
+def gemm_tcgen05_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                     m: Optional[int] = None) -> bool:
+    """resid += x . w^T (+ bias) for many rows (more than 256, N at least 256): the product is added into
+    the float32 residual stream in its own epilogue, so no delta goes through memory.  Returns False
+    when the kernel refuses the sizes or the layout (write a delta instead)."""
+    M = x.shape[0] if m is None else m
+    N, K = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
+            or x.shape[1] != K:
+        raise KernelError("gemm_tcgen05_add: x and w must be bfloat16, K-major, with matching K")
+    if resid.dtype != torch.float32 or resid.shape[1] != N or resid.stride(1) != 1 or resid.shape[0] < M:
+        raise KernelError("gemm_tcgen05_add: resid must be float32 [>= M, N] with unit inner stride")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tcgen05_add: bias must be float32 [N]")
+    if M <= 256 or N < 256:
+        return False
+    rc = _lib().rb_gemm_tcgen05_add(_ptr(x), _ptr(w), _ptr(bias), _ptr(resid), M, N, K, x.stride(0), resid.stride(0), 0,
+                                    _ptr(status_word(x.device)), _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "gemm_tcgen05_add")
     return True
 
 

@@ -97,7 +97,9 @@ class Attention(Mixer):
                 and self.qkv._splits(batch.n_tokens) > 1
                 and (self.position.inv_freq is None or self.position.rot_dim == self.hd))
 
-    def forward(self, xn, batch, view, sink=None):
+    can_add_into = True    # forward() accepts add_into=residual (see parts.base)
+
+    def forward(self, xn, batch, view, sink=None, add_into=None):
         T = batch.n_tokens
         dev, act = self.env.device, self.env.act_dtype
         qd = self.nq * self.hd
@@ -127,6 +129,8 @@ class Attention(Mixer):
             deferred = self.o.forward_residual(attn, T, sink)
             if deferred is not None:
                 return deferred
+        if add_into is not None and self.o.forward_add(attn, T, add_into):
+            return None
         return self.o.forward_delta(attn, T)
 
     def _prompt_fused(self, xn, out, batch, view, window, writes) -> bool:

@@ -43,6 +43,11 @@ class ResidualSink:
     norm: "Norm"
 
 
+# A second, simpler offer is made for prompts: ``forward(..., add_into=resid)`` to parts that set
+# ``can_add_into``.  The part may add its result into ``resid`` [T, H] float32 itself and return None
+# (nothing is pending then), or ignore the offer and return a delta as always.
+
+
 @dataclass
 class DeferredNorm:
     """The output of a norm whose division by the rows' RMS has not happened yet: ``x`` is

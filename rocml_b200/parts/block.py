@@ -11,6 +11,11 @@ from ..weights.decl import TensorDecl
 from .base import BuildEnv, ResidualSink, build_feed_forward, build_mixer, build_norm, register_arrangement
 
 
+# From this many tokens in a step a part is offered to add into the residual itself (the products of
+# fewer rows are split over K or run as kernels without that epilogue).
+ADD_INTO_MIN_TOKENS = 256
+
+
 @register_arrangement("pre_norm")
 class PreNormBlock:
     """x += mixer(norm1(x)); x += ff(norm2(x)) (rocml/src/forward/mod.rs:281-340).
@@ -58,18 +63,26 @@ class PreNormBlock:
         result into the residual itself and prepared this layer's first norm.  For a decode step of
         up to 16 tokens the parts are offered to do the same for the norm that follows them
         (ResidualSink), when the part after that norm can take the deferred rows: the norm kernels
-        then disappear from the step.  RB_DEFER=0 turns the offers off."""
+        then disappear from the step.  RB_DEFER=0 turns the offers off (and those to prompts, below)."""
         T = batch.n_tokens
         offers = batch.is_decode and T <= 16 and _defer_enabled()     # beyond 16 tokens the norm kernels are cheaper (measured)
+        # Prompts: a part may be told to add its result into the residual itself (``add_into``; it then
+        # returns None, nothing is pending, and the following norm only normalises): the delta of a
+        # few thousand rows then never goes through memory.  Parts that set ``can_add_into`` get the offer.
+        adds = not batch.is_decode and T > ADD_INTO_MIN_TOKENS and _defer_enabled()
         xn = self.mixer_norm.forward(resid, pending, T)
         if offers and getattr(self.mixer, "can_sink", False) and _takes(self.ff, batch):
             delta = self.mixer.forward(xn, batch, view, sink=ResidualSink(resid, self.ff_norm))
+        elif adds and getattr(self.mixer, "can_add_into", False):
+            delta = self.mixer.forward(xn, batch, view, add_into=resid)
         else:
             delta = self.mixer.forward(xn, batch, view)
         xn = self.ff_norm.forward(resid, delta, T)
         nxt = getattr(next_block, "mixer", None)
         if offers and nxt is not None and getattr(self.ff, "can_sink", False) and _takes(nxt, batch):
             return self.ff.forward(xn, batch, sink=ResidualSink(resid, next_block.mixer_norm))
+        if adds and getattr(self.ff, "can_add_into", False):
+            return self.ff.forward(xn, batch, add_into=resid)
         return self.ff.forward(xn, batch)
 
 

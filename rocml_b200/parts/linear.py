@@ -128,6 +128,13 @@ class Linear:
             return None
         return DeferredNorm(xhat, sumsq, norm.eps, self.n, norm, sink.resid)
 
+    def forward_add(self, x: torch.Tensor, m: int, resid: torch.Tensor) -> bool:
+        """resid += x . W^T (+ bias) for many rows, inside the product's epilogue.  False when this step's
+        product cannot be done that way (use ``forward_delta``)."""
+        if not self._tensor_core(x) or self._splits(m) != 1:
+            return False
+        return kernels.gemm_tcgen05_add(x, self.weight, resid, self.bias, m)
+
     def adopt(self, weight: torch.Tensor) -> None:
         """Use an existing tensor as the weight (a tied head reads the embedding table)."""
         if tuple(weight.shape) != (self.n, self.k):

@@ -54,7 +54,9 @@ class GatedMLP(FeedForward):
         return (self.gate_up.paired and T <= GATED_PAIR_MAX_ROWS and self.gate_up.weight.dtype == torch.bfloat16
                 and self.gate_up._splits(T) == 2 and self.gate_up.k > 64)
 
-    def forward(self, xn, batch, sink=None):
+    can_add_into = True    # forward() accepts add_into=residual (see parts.base)
+
+    def forward(self, xn, batch, sink=None, add_into=None):
         T = batch.n_tokens
         dev, act = self.env.device, self.env.act_dtype
         h = None
@@ -77,4 +79,6 @@ class GatedMLP(FeedForward):
             deferred = self.down.forward_residual(h, T, sink)
             if deferred is not None:
                 return deferred
+        if add_into is not None and self.down.forward_add(h, T, add_into):
+            return None
         return self.down.forward_delta(h, T)

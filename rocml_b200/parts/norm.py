@@ -43,5 +43,7 @@ class RMSNorm(Norm):
             delta = None
         n = (rows.numel() if rows is not None else resid.shape[0]) if n_rows is None else n_rows
         out = torch.empty((n, self.size), dtype=self.env.act_dtype, device=resid.device)
+        if delta is None:
+            write_back = False          # nothing is added: the residual stays as it is
         kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows, n_rows=n, write_back=write_back)
         return out

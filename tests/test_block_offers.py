@@ -146,3 +146,32 @@ def test_no_offer_when_the_next_part_cannot_take_the_rows(monkeypatch):
     monkeypatch.setenv("RB_DEFER", "0")
     resid, log = run([block("toy_smart_mixer", "toy_smart_ff") for _ in range(2)], batch(2, True))
     assert log == ["norm runs"] * 4
+
+
+@register_feed_forward("toy_adding_ff")
+class AddingFF(FeedForward):
+    """Takes the offer made for prompts: adds its result into the residual itself and returns None."""
+    can_add_into = True
+
+    def __init__(self, spec, hidden, env):
+        pass
+
+    def forward(self, xn, batch, add_into=None):
+        delta = torch.ones((1,) + tuple(xn.shape))
+        if add_into is None:
+            return delta
+        add_into += delta.sum(0)
+        LOG.append(("AddingFF adds", 0))
+        return None
+
+
+def test_prompts_offer_the_residual_itself(monkeypatch):
+    blocks = [block("toy_plain_mixer", "toy_adding_ff") for _ in range(2)]
+    resid, log = run(blocks, batch(300, False))          # a prompt of more than 256 tokens
+    assert log == ["norm runs", "norm runs", "AddingFF adds", "norm runs", "norm runs", "AddingFF adds"]
+    assert torch.equal(resid, torch.full((300, 4), 4.0))
+    for b in (batch(300, True), batch(200, False)):     # decode steps and short prompts: no offer
+        resid, log = run(blocks, b)
+        assert "AddingFF adds" not in log and torch.equal(resid, torch.full((b.n_tokens, 4), 4.0))
+    monkeypatch.setenv("RB_DEFER", "0")
+    assert "AddingFF adds" not in run(blocks, batch(300, False))[1]

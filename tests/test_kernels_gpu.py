@@ -129,6 +129,31 @@ def test_gemm_tcgen05_adds_into_the_residual_stream(M, N, K, S, wdt):
                                          torch.zeros((65, N), device=DEV), S) is False
 
 
+@pytest.mark.parametrize("M,N,K,bias", [(300, 512, 320, True), (257, 400, 1024, False), (2048, 4096, 512, False),
+                                        (700, 264, 4096, True)])
+def test_gemm_tcgen05_many_rows_add_into_the_residual_stream(M, N, K, bias):
+    """The product of many rows is added into the float32 residual by the product's own epilogue: the
+    same sums as the separate product followed by the addition, rows and columns beyond the tiles'
+    edges included, rows past M untouched."""
+    from rocml_b200 import kernels
+    x = rnd((M, K), 4, torch.bfloat16).to(DEV)
+    w = rnd((N, K), 5, torch.bfloat16, 0.05).to(DEV)
+    b = rnd((N,), 6).to(DEV) if bias else None
+    resid0 = rnd((M + 3, N), 8)
+    resid = resid0.clone().to(DEV)
+    assert kernels.gemm_tcgen05_add(x, w, resid, b, M)
+    kernels.check_status(DEV)
+    want = resid0[:M].double() + x.cpu().double() @ w.cpu().double().t() + (b.cpu().double() if bias else 0.0)
+    scale = (x.cpu().double().abs() @ w.cpu().double().abs().t()).clamp_min(1.0)     # as for the plain product
+    assert ((resid[:M].cpu().double() - want).abs() / scale).max().item() < 1e-5
+    assert torch.equal(resid[M:].cpu(), resid0[M:])
+    # and bit for bit what the plain product and a float32 addition give
+    delta = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    assert kernels.gemm_tcgen05(x, w, delta, b, M)
+    assert torch.equal(resid[:M], resid0[:M].to(DEV) + delta)
+    assert kernels.gemm_tcgen05_add(x[:200], w, resid, b, 200) is False          # few rows: other kernels
+
+
 @pytest.mark.parametrize("M,nq,nkv,K,norm,rope,bias,writes", [
     (300, 4, 2, 512, True, True, False, True), (1000, 6, 1, 264, True, True, True, True),
     (513, 2, 2, 1024, False, True, False, True), (257, 4, 2, 256, True, False, False, False)])
