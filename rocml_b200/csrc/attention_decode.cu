@@ -588,7 +588,7 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
            float scale, int window, int n_chunks, int ppb, float* part_acc, float* part_ml, int* counters,
            void* out, int o_stride, const Projections& pj, cudaStream_t s) {
     const int g = nq / nkv;
-    const bool proportional = ppb == 0;     // n_chunks blocks a head group, shared out among the sequences
+    const bool proportional = ppb == 0;     // n_chunks blocks a head group share the pages of all sequences equally
     if (proportional && B > PROP_MAX_SEQS) return RB_ERR_BAD_SIZE;
     dim3 grid(n_chunks, nkv * ((g + ROWS - 1) / ROWS), proportional ? 1 : B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;

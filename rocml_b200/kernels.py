@@ -367,8 +367,10 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      pages_per_block: int = 1) -> bool:
     """bfloat16 decode attention, one query token per sequence; a block takes ``pages_per_block``
     pages of 64 keys, ``n_chunks`` blocks cover the longest sequence and are merged by the kernel
-    itself; part_acc / part_ml are its work space when n_chunks > 1.  Returns
-    False when the kernel does not take the head size or the alignment (use attention_generic)."""
+    itself; part_acc / part_ml [T, nq, >= n_chunks, ...] are its work space when n_chunks > 1.
+    ``pages_per_block`` 0: ``n_chunks`` blocks a key/value head group share the pages of all sequences
+    equally, whatever their lengths (see ``decode_split``).  Returns False when the kernel does not
+    take the head size or the alignment (use attention_generic)."""
     if n_seqs * nq > _COUNTER_INTS:
         return False
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or q.stride(-1) != 1 or out.stride(-1) != 1:
