@@ -62,7 +62,7 @@ int rb_attention_prefill(const void* q, int q_stride, void* out, int o_stride, c
 int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride, const void* k_cache,
                              const void* v_cache, int n_pages, const int* block_table, int max_pages,
                              const int* seq_slot, const int* cu_q, const int* kv_len, int B, int max_q_len, int nq,
-                             int nkv, int hd, float scale, int window, int* status, void* stream);
+                             int nkv, int hd, float scale, int window, int heads_first, int* status, void* stream);
 
 int rb_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,

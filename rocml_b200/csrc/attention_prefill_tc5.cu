@@ -71,7 +71,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int o_stride,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                              const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
-                             float scale, int window, int* __restrict__ status) {
+                             float scale, int window, int heads_first, int* __restrict__ status) {
     rb::pdl_trigger();
     rb::pdl_wait();
     extern __shared__ uint8_t smem_raw[];
@@ -86,11 +86,16 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint8_t* Ps = Vs + 2 * KV_TILE;           // V: [2 stages][16 KB]
     Barriers* bar = (Barriers*)(Ps + P_BYTES);
 
-    const int b = blockIdx.z, head = blockIdx.y;
+    // Blocks are handed out with x running fastest.  The last query tiles see the most keys and start
+    // first.  heads_first, grid = (heads, sequences, query tiles): the long blocks of ALL heads and
+    // sequences start first and the short ones fill the grid's tail (one head's tiles after another's
+    // leave a long block of the last head to the end).  Otherwise grid = (query tiles, heads, sequences):
+    // the blocks that run together read the keys and values of one or two heads, which matters once
+    // all heads' keys and values together no longer fit the L2 cache.
+    const int b = heads_first ? blockIdx.y : blockIdx.z, head = heads_first ? blockIdx.x : blockIdx.y;
     const int slot = seq_slot[b];
     const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
-    // late query tiles see the most keys: they are scheduled first so that the grid's tail is short
-    const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * BMQ;
+    const int m0 = heads_first ? (int)(gridDim.z - 1 - blockIdx.z) * BMQ : (int)(gridDim.x - 1 - blockIdx.x) * BMQ;
     if (slot < 0 || m0 >= q_len) return;
     const int len = kv_len[b];
     const int pos0 = len - q_len;
@@ -377,13 +382,14 @@ int make_map(const void* ptr, long long rows, long long cols, long long ld, int 
 }
 }  // namespace
 
-// q rows [T, q_stride] bfloat16 (T = tokens of the step), caches [n_pages, nkv, 64, 128].  Head size 128
+// q rows [T, q_stride] bfloat16 (T = tokens of the step), caches [n_pages, nkv, 64, 128].  heads_first: the order
+// in which blocks start (see the kernel); it changes no result.  Head size 128
 // only; RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).
 extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride,
                                         const void* k_cache, const void* v_cache, int n_pages,
                                         const int* block_table, int max_pages, const int* seq_slot,
                                         const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv,
-                                        int hd, float scale, int window, int* status, void* stream) {
+                                        int hd, float scale, int window, int heads_first, int* status, void* stream) {
     if (B <= 0 || max_q_len <= 0 || T <= 0) return RB_OK;
     if (hd != HD || nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15) ||
@@ -402,9 +408,10 @@ extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    dim3 grid((max_q_len + BMQ - 1) / BMQ, nq, B);
+    const int q_tiles = (max_q_len + BMQ - 1) / BMQ;
+    dim3 grid = heads_first ? dim3(nq, B, q_tiles) : dim3(q_tiles, nq, B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((k), grid, dim3(192), SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
-              block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, status);
+              block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, heads_first, status);
     return RB_OK;
 }

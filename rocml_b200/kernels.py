@@ -90,7 +90,7 @@ def _lib():
         lib.rb_attention_prefill.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                                              _f, _i, _vp]
         lib.rb_attention_prefill_tc5.argtypes = [_vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i,
-                                                 _i, _i, _i, _f, _i, _vp, _vp]
+                                                 _i, _i, _i, _f, _i, _i, _vp, _vp]
         lib.rb_attention_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
                                             _i, _vp, _vp, _vp, _vp, _i, _vp]
         lib.rb_attention_decode_fused.argtypes = [_vp, _i, _ll, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _i, _ll, _f, _i,
@@ -262,11 +262,27 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _check(rc, "attention_generic")
 
 
+PREFILL_L2_BYTES = 96 << 20     # keys and values that stay in the 126 MB L2 cache beside everything else
+
+
+def prefill_heads_first(n_seqs: int, nkv: int, hd: int, max_kv_len: int, window: int = 0) -> bool:
+    """Whether a prompt step's attention starts the longest blocks of all heads first (best balance) or
+    runs one head after another (the blocks that run together share keys and values): the first while
+    the bfloat16 keys and values of the step's contexts fit the L2 cache (measured: 26 % faster at 2,048
+    tokens, 6 % at 16,384, 6 % slower at 32,768, where 134 MB are read by every query tile)."""
+    span = min(max_kv_len, window) if window and window > 0 else max_kv_len
+    return n_seqs * nkv * span * hd * 4 <= PREFILL_L2_BYTES
+
+
 def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                           block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
-                          n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0) -> bool:
+                          n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
+                          max_kv_len: Optional[int] = None) -> bool:
     """bfloat16 flash attention with tcgen05 (accumulators in tensor memory, TMA loads), head size 128.
-    Returns False when the kernel does not take the head size or the alignment."""
+    ``max_kv_len`` (the longest context of the step; the longest query if not given) only decides the
+    order in which blocks start: the longest blocks of all heads first while the keys and values that
+    the step reads fit the L2 cache, one head after another beyond.  Returns False when the kernel
+    does not take the head size or the alignment."""
     if hd != 128 or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
             q.stride(-1) != 1 or out.stride(-1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
         return False
@@ -276,6 +292,7 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
         _ptr(q), q.stride(0), n_tokens, _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0],
         _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"),
         _i32(kv_len, "kv_len"), n_seqs, max_q_len, nq, nkv, hd, float(scale), int(window),
+        1 if prefill_heads_first(n_seqs, nkv, hd, max_q_len if max_kv_len is None else max_kv_len, window) else 0,
         _ptr(status_word(q.device)), _stream())
     if rc in (10001, 10003):
         return False

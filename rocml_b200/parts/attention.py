@@ -208,7 +208,7 @@ class Attention(Mixer):
                 return
         if kernels.attention_prefill_tc5(q, batch.n_tokens, out, view.k, view.v, view.block_table, batch.seq_slot,
                                          batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv,
-                                         self.hd, self.scale, window):
+                                         self.hd, self.scale, window, max_kv_len=batch.max_kv_len):
             return
         if kernels.attention_prefill(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
                                      batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,
