@@ -213,3 +213,69 @@ def test_decode_without_norm_kernels(tmp_path, monkeypatch, graphs):
             assert calls["residual"] == 0
     for j in range(2):
         assert rel_err(results["1"][j], results["0"][j].double().cpu()) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("blocks", [1, 2, 5])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_decode_attention_with_pages_shared_out_equally(tmp_path, monkeypatch, blocks, graphs):
+    """Large batches and long contexts make decode attention cut the pages of all sequences into equal
+    runs, one per block, a block finishing one sequence and starting the next.  The library picks that
+    from the batch and the device; here a small model is made to do it with fewer blocks than
+    sequences, as many, and more: three sequences of unequal lengths after prompts of unequal lengths,
+    the shortest ending first, against the plain implementation."""
+    from plain_qwen3 import PlainQwen3
+    from rocml_b200 import Engine, StepEntry, kernels
+    folder = str(tmp_path / "m")
+    write_model(folder, DEFER_CFG, seed=8, std=0.06)
+    plain = PlainQwen3(folder, dtype=torch.float32)
+    monkeypatch.setattr(kernels, "decode_split", lambda n_seqs, groups, n_pages, device=0: (blocks, 0))
+    vocab = DEFER_CFG["vocab_size"]
+    ids = [prompt(11, 300, vocab), prompt(12, 150, vocab), prompt(13, 70, vocab)]
+    starts = [250, 70, 3]
+    want = [plain.logits(x) for x in ids]
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024, use_graphs=graphs)
+    slots = [eng.new_sequence() for _ in ids]
+    out = eng.step([StepEntry(s, x[:n], [n - 1]) for s, x, n in zip(slots, ids, starts)])
+    got = [[out[j].clone()] for j in range(3)]
+    for t in range(80):
+        live = [j for j in range(3) if starts[j] + t < len(ids[j])]
+        if not live:
+            break
+        out = eng.step([StepEntry(slots[j], [ids[j][starts[j] + t]], [0]) for j in live])
+        for r, j in enumerate(live):
+            got[j].append(out[r].clone())
+    for j in range(3):
+        g = torch.stack(got[j])
+        assert rel_err(g, want[j][starts[j] - 1:starts[j] - 1 + len(g)]) < TOL["bfloat16"]
+    kernels.check_status("cuda:0")
+
+
+def test_prompts_add_into_the_residual_inside_the_products(tmp_path, monkeypatch):
+    """A prompt of more than 256 tokens: the o- and down-projection add into the residual stream in
+    their own epilogue and the norms after them only normalise.  Same logits as the plain
+    implementation, and as the same engine with the offers turned off; a second, shorter prompt
+    beside the first keeps the plain path for neither."""
+    from plain_qwen3 import PlainQwen3
+    from rocml_b200 import Engine, StepEntry, kernels
+    folder = str(tmp_path / "m")
+    write_model(folder, DEFER_CFG, seed=21, std=0.06)
+    plain = PlainQwen3(folder, dtype=torch.float32)
+    calls = {"add": 0}
+    real_add = kernels.gemm_tcgen05_add
+    monkeypatch.setattr(kernels, "gemm_tcgen05_add",
+                        lambda *a, **k: calls.__setitem__("add", calls["add"] + 1) or real_add(*a, **k))
+    vocab = DEFER_CFG["vocab_size"]
+    ids = [prompt(31, 400, vocab), prompt(32, 77, vocab)]
+    rows = [[0, 255, 256, 399], [0, 76]]
+    want = torch.cat([plain.logits(x)[r] for x, r in zip(ids, rows)])
+    got = {}
+    for defer in ("1", "0"):
+        monkeypatch.setenv("RB_DEFER", defer)
+        calls["add"] = 0
+        eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024)
+        slots = [eng.new_sequence(), eng.new_sequence()]
+        got[defer] = eng.step([StepEntry(s, x, r) for s, x, r in zip(slots, ids, rows)]).float().cpu()
+        assert rel_err(got[defer], want) < TOL["bfloat16"]
+        assert calls["add"] == (2 * DEFER_CFG["num_hidden_layers"] if defer == "1" else 0)
+    assert rel_err(got["1"], got["0"].double()) < TOL["bfloat16"]
+    kernels.check_status("cuda:0")
