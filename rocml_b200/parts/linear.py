@@ -160,10 +160,12 @@ class Linear:
         row tiles (128 rows each) are multiplied by K splits until about two blocks per
         multiprocessor are in flight (more gains little and costs the consumer, which adds the
         partial sums); each split keeps at least five 64-wide K blocks, at most 8 splits, and the
-        float32 partial results stay below a sixth of the weight's own bytes.  A product over a
-        very deep K (24 or more K blocks left per split) is split twice as often, as long as all
-        its blocks still fit on the device at once (four per multiprocessor).  More than 128 rows:
-        see below.  The count depends on the weight's shape, the step's row count and the device only."""
+        float32 partial results stay below a third of the weight's own bytes (they stay in the L2
+        cache).  A product over a very deep K (24 or more K blocks left per split) is split twice
+        as often, as long as all its blocks still fit on the device at once (four per
+        multiprocessor) and the partial results stay below a sixth of the weight's bytes.  More
+        than 128 rows: see below.  The count depends on the weight's shape, the step's row count
+        and the device only."""
         if self.k % 8:
             return 1
         sms = _sm_count(self.env.device)
@@ -180,9 +182,9 @@ class Linear:
         k_blocks = self.k // 64
         by_blocks = -(-2 * sms // tiles)
         by_depth = k_blocks // 5
-        by_bytes = int(0.075 * self.k / max(m, 1))
+        by_bytes = int(0.15 * self.k / max(m, 1))
         s = max(1, min(by_blocks, by_depth, by_bytes, 8))
-        if k_blocks // s >= 24 and 2 * s <= by_bytes and 2 * s * tiles <= 4 * sms:
+        if k_blocks // s >= 24 and 4 * s <= by_bytes and 2 * s * tiles <= 4 * sms:
             s *= 2
         return s
 
