@@ -183,6 +183,8 @@ class Linear:
         by_blocks = -(-2 * sms // tiles)
         by_depth = k_blocks // 5
         by_bytes = int(0.15 * self.k / max(m, 1))
+        if m > 64 and tiles >= sms:
+            return 1        # a block a multiprocessor already, and partial sums of many rows cost more than they gain (measured)
         s = max(1, min(by_blocks, by_depth, by_bytes, 8))
         if k_blocks // s >= 24 and 4 * s <= by_bytes and 2 * s * tiles <= 4 * sms:
             s *= 2
