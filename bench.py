@@ -299,6 +299,51 @@ def sampler_times():
             print(f"batch {batch:3d}  {name:40s} {wall:8.1f} us a step, kernel {a.elapsed_time(b) / 20 * 1e3:7.1f} us")
 
 
+def sweep(cases=None, steps=32):
+    """Decode steps at other batch sizes and context lengths than the bench line's: milliseconds a step,
+    tokens a second, and the bytes a step has to read (weights once, the live cache) over its time, as a
+    fraction of the measured copy bandwidth.  All layers of the configuration; prompts are fed in pieces
+    of at most 4,096 tokens."""
+    import torch
+    from rocml_b200 import StepEntry, kernels
+    global CTX
+    cases = cases or [(1, 1024), (1, 8192), (1, 32000), (4, 16000), (8, 1024), (8, 8192), (8, 32000), (16, 2048),
+                      (32, 1024), (32, 8192), (64, 1024), (64, 4000), (128, 1024), (256, 1024)]
+    pk = peaks()
+    print("batch  context  ms/step    tok/s   GB/step   GB/s  of %s copy bandwidth" % pk["source"])
+    for batch, ctx in cases:
+        CTX = ctx + 256
+        cfg, n_full, eng = build_engine(0, batch * ((ctx + 256 + 63) // 64 * 64), batch)
+        slots = [eng.new_sequence() for _ in range(batch)]
+        ps = prompts(batch, ctx, cfg.vocab_size, 3)
+        tok = torch.zeros(batch, dtype=torch.int32, device=eng.device)
+        piece = max(64, (4096 // batch) // 64 * 64)
+        for lo in range(0, ctx, piece):
+            hi = min(ctx, lo + piece)
+            logits = eng.step([StepEntry(s, p[lo:hi], [hi - lo - 1]) for s, p in zip(slots, ps)])
+        kernels.argmax(logits, tok, batch)
+
+        def one():
+            kernels.argmax(eng.step([StepEntry(s, [0], [0]) for s in slots], device_tokens=tok), tok, batch)
+
+        for _ in range(6):
+            one()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            one()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        gb = (eng.model.weight_bytes_per_step() + batch * (ctx + 6 + steps / 2) * eng.kv_bytes_per_token()) / 1e9
+        print(f"{batch:5d} {ctx:8d} {ms:8.3f} {batch / ms * 1e3:8.0f} {gb:9.2f} {gb / ms * 1e3:6.0f}  {gb / ms * 1e3 / pk['hbm_gbs']:.2f}",
+              flush=True)
+        kernels.check_status(eng.device)
+        del eng, slots, logits
+        torch.cuda.empty_cache()
+
+
 def timeline(batch=BATCH, layers=4):
     """Where a decode step's time goes, kernel by kernel, as the step really runs (inside its CUDA
     graph, kernels overlapping their predecessors through programmatic dependent launch): start and
@@ -346,7 +391,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--micro", default=None,
                     help="instead of the bench: gemm-decode, gemm-prefill (kernel microbenchmarks), timeline "
-                         "(every kernel of one decode step with its start and end) or sampler (a sampling step)")
+                         "(every kernel of one decode step with its start and end), sampler (a sampling step) or "
+                         "sweep (decode steps at other batch sizes and context lengths)")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of --micro timeline")
     args = ap.parse_args()
     if args.micro == "timeline":
@@ -354,6 +400,9 @@ def main():
         return 0
     if args.micro == "sampler":
         sampler_times()
+        return 0
+    if args.micro == "sweep":
+        sweep()
         return 0
     if args.micro:
         micro(args.micro)
