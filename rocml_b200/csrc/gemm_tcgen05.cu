@@ -40,7 +40,7 @@ struct Cfg {
     static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static constexpr int SMEM = STAGES * STAGE + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /*align slack*/ + 256 /*barriers*/;   // the persistent kernel's
 };
 
 struct Params {
@@ -1046,14 +1046,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, Params p, in
     }
     dim3 grid((p.a_rows + BM - 1) / BM, (p.b_rows + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
-    if (CS != 0) {
+    if constexpr (CS != 0) {
         if (splits != CS) return RB_ERR_BAD_SIZE;
         cudaError_t e = rb::launch_clustered(k, grid, dim3(192), dim3(1, 1, CS), smem_bytes, s, ma, mb, (OT*)out, p);
         return e == cudaSuccess ? RB_OK : (int)e;
+    } else {
+        RB_LAUNCH((k), dim3(grid), dim3(192), smem_bytes, s, ma, mb, (OT*)out, p);
+        RB_LAUNCH_CHECK();
+        return RB_OK;
     }
-    RB_LAUNCH((k), dim3(grid), dim3(192), smem_bytes, s, ma, mb, (OT*)out, p);
-    RB_LAUNCH_CHECK();
-    return RB_OK;
 }
 
 template <int BN, typename OT, bool GATED>
