@@ -382,6 +382,7 @@ def timeline(batch=BATCH, layers=4):
 
 
 def main():
+    global MODEL
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
     ap.add_argument("--steps", type=int, default=128)
@@ -394,7 +395,13 @@ def main():
                          "(every kernel of one decode step with its start and end), sampler (a sampling step) or "
                          "sweep (decode steps at other batch sizes and context lengths)")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of --micro timeline")
+    ap.add_argument("--model", default=MODEL, help="catalog entry whose layer sizes --micro sweep and timeline use")
     args = ap.parse_args()
+    if args.micro:
+        MODEL = args.model
+    elif args.model != MODEL:
+        print("bench.py: --model only applies to --micro runs; the bench line is for %s" % MODEL)
+        return 2
     if args.micro == "timeline":
         timeline(args.batch, args.layers or 4)
         return 0
@@ -402,7 +409,7 @@ def main():
         sampler_times()
         return 0
     if args.micro == "sweep":
-        sweep()
+        sweep(None if args.model == "qwen3-8b" else [(1, 1024), (8, 1024), (8, 8192), (64, 1024)])
         return 0
     if args.micro:
         micro(args.micro)
