@@ -87,7 +87,7 @@ struct Projections {
 // One head of 128 values, 4 per lane: the sum of the partial sums, then (what != 2) RMSNorm with `w`
 // and the rotation by the token's angles.  what: 0 query, 1 key, 2 value.
 __device__ __forceinline__ void project_head(const Projections& pj, const float* src, int what, int t, int lane,
-                                             float rstd, float* v) {
+                                             float sumsq_share, float* v) {
     v[0] = v[1] = v[2] = v[3] = 0.f;
     // the norm's weights and the token's angles do not depend on the sums: their loads go out first
     const void* w = what == 0 ? pj.q_norm_w : (what == 1 ? pj.k_norm_w : nullptr);
@@ -120,7 +120,11 @@ __device__ __forceinline__ void project_head(const Projections& pj, const float*
 #pragma unroll
         for (int j = 0; j < 8; ++j) { v[0] += f[j].x; v[1] += f[j].y; v[2] += f[j].z; v[3] += f[j].w; }
     }
-    v[0] *= rstd; v[1] *= rstd; v[2] *= rstd; v[3] *= rstd;
+    // the rows' 1/RMS, if it is still to be applied: reduced here, after the loads above went out
+    if (pj.row_sumsq != nullptr) {
+        const float rstd = rsqrtf(warp_sum(sumsq_share) * pj.row_inv_width + pj.row_eps);
+        v[0] *= rstd; v[1] *= rstd; v[2] *= rstd; v[3] *= rstd;
+    }
     if (w != nullptr) {
         const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
         const float inv = rsqrtf(ss / 128.f + pj.eps);
@@ -269,39 +273,45 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     pdl_wait();
     if (FQ) {
         const float* row = pj.proj + (size_t)t * pj.row_stride;
-        float rstd = 1.f;
-        if (pj.row_sumsq != nullptr) {                      // every warp for itself: a few loads and a reduction
-            float acc = 0.f;
-            for (int gi = lane; gi < pj.row_groups; gi += 32) acc += pj.row_sumsq[(size_t)gi * pj.row_sumsq_ld + t];
-            rstd = rsqrtf(warp_sum(acc) * pj.row_inv_width + pj.row_eps);
+        float share = 0.f;                                  // this lane's share of the row's sum of squares
+        if (pj.row_sumsq != nullptr)
+            for (int gi = lane; gi < pj.row_groups; gi += 32) share += pj.row_sumsq[(size_t)gi * pj.row_sumsq_ld + t];
+        // The new token's key and value first, by the one block that reads their page (its last two
+        // warps), so that the page's copies are on their way while the query heads are made.
+        const bool owner = pj.write_kv && hc == 0 && page_first <= new_page && new_page <= page_last;
+        if (owner) {
+            if (warp >= WARPS - 2) {
+                const int page = table[new_page];
+                if (page >= 0) {
+                    float v[4];
+                    const bool is_k = warp == WARPS - 2;
+                    const int head = is_k ? nq + kvh : nq + nkv + kvh;
+                    project_head(pj, row + (size_t)head * HD + lane * 4, is_k ? 1 : 2, t, lane, share, v);
+                    __nv_bfloat16* dst = (is_k ? pj.k_out : pj.v_out) +
+                                         (((size_t)page * nkv + kvh) * RB_PAGE + (pos % RB_PAGE)) * HD;
+                    *reinterpret_cast<uint2*>(dst + lane * 4) = pack4_bf16(v);
+                    __threadfence_block();
+                }
+            }
+            __syncthreads();                                // before the page of the new token is copied
         }
+        if (!early0) issue(page_first, 0);
+        if (!early1) issue(page_first + 1, 1);              // commits an empty group beyond page_last
         for (int r = warp; r < ROWS; r += WARPS) {          // the query heads of this block
             float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (r < rows_valid) project_head(pj, row + (size_t)(h0 + r) * HD + lane * 4, 0, t, lane, rstd, v);
+            if (r < rows_valid) project_head(pj, row + (size_t)(h0 + r) * HD + lane * 4, 0, t, lane, share, v);
             const int chunk = lane >> 1;                    // 8 values per 16-byte chunk, 4 per lane
             *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(Qs) + r * (HD * 2) + ((chunk ^ (r & 7)) << 4) +
                                       (lane & 1) * 8) = pack4_bf16(v);
         }
-        // the new token's key and value, by the one block that reads their page
-        if (pj.write_kv && hc == 0 && page_first <= new_page && new_page <= page_last && warp < 2) {
-            const int page = table[new_page];
-            if (page >= 0) {
-                float v[4];
-                const int head = warp == 0 ? nq + kvh : nq + nkv + kvh;
-                project_head(pj, row + (size_t)head * HD + lane * 4, warp == 0 ? 1 : 2, t, lane, rstd, v);
-                __nv_bfloat16* dst = (warp == 0 ? pj.k_out : pj.v_out) +
-                                     (((size_t)page * nkv + kvh) * RB_PAGE + (pos % RB_PAGE)) * HD;
-                *reinterpret_cast<uint2*>(dst + lane * 4) = pack4_bf16(v);
-                __threadfence_block();
-            }
-        }
-        __syncthreads();                                    // before the page of the new token is copied
     } else {
         load_tile<HD>(Qs, q + (size_t)t * q_stride + (size_t)h0 * HD, HD, ROWS, rows_valid, threadIdx.x, WARPS * 32);
     }
-    cp_async_commit();                                      // a group of its own: the wait below covers committed groups only
-    if (!early0) issue(page_first, 0);
-    if (!early1) issue(page_first + 1, 1);                  // commits an empty group beyond page_last
+    if (!FQ) {
+        cp_async_commit();                                  // a group of its own: the wait below covers committed groups only
+        if (!early0) issue(page_first, 0);
+        if (!early1) issue(page_first + 1, 1);              // commits an empty group beyond page_last
+    }
     cp_async_wait<0>();
     __syncthreads();                                        // the query heads are in place for every warp
 
