@@ -174,7 +174,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float* s_o = reinterpret_cast<float*>(KVs);                            // reused after the products: [4][16][HD]
     float* s_part = s_o + WARPS * ROWS * HD;                               // beside it (CL): this block's part [16][HD]
     __shared__ float s_pm_own[ROWS], s_pl_own[ROWS];                       // its maxima and sums
-    __shared__ float s_gm[ROWS * MAX_CLUSTER], s_gl[ROWS * MAX_CLUSTER];                       // those of all blocks of the cluster
     __shared__ float s_m[WARPS][ROWS], s_l[WARPS][ROWS];
     __shared__ int s_last;
 
@@ -274,8 +273,18 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if (FQ) {
         const float* row = pj.proj + (size_t)t * pj.row_stride;
         float share = 0.f;                                  // this lane's share of the row's sum of squares
-        if (pj.row_sumsq != nullptr)
-            for (int gi = lane; gi < pj.row_groups; gi += 32) share += pj.row_sumsq[(size_t)gi * pj.row_sumsq_ld + t];
+        if (pj.row_sumsq != nullptr) {
+            for (int g0 = 0; g0 < pj.row_groups; g0 += 256) {   // eight loads a lane in flight, not one after another
+                float x[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int gi = g0 + j * 32 + lane;
+                    x[j] = gi < pj.row_groups ? pj.row_sumsq[(size_t)gi * pj.row_sumsq_ld + t] : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) share += x[j];
+            }
+        }
         // The new token's key and value first, by the one block that reads their page (its last two
         // warps), so that the page's copies are on their way while the query heads are made.
         const bool owner = pj.write_kv && hc == 0 && page_first <= new_page && new_page <= page_last;
@@ -433,13 +442,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         s_m[warp][gq] = m_w[0]; s_m[warp][gq + 8] = m_w[1];
         s_l[warp][gq] = l_w[0]; s_l[warp][gq + 8] = l_w[1];
     }
+    {   // only the rows that hold a query head are read again (a group of 4 fills 4 of the tile's 16 rows)
+        const bool lo_row = gq < rows_valid, hi_row = gq + 8 < rows_valid;
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-        const int d = i * 8 + tq * 2;
-        float* r0 = s_o + ((size_t)warp * ROWS + gq) * HD + d;
-        float* r1 = s_o + ((size_t)warp * ROWS + gq + 8) * HD + d;
-        r0[0] = o[i][0]; r0[1] = o[i][1];
-        r1[0] = o[i][2]; r1[1] = o[i][3];
+        for (int i = 0; i < HD / 8; ++i) {
+            const int d = i * 8 + tq * 2;
+            if (lo_row) *reinterpret_cast<float2*>(s_o + ((size_t)warp * ROWS + gq) * HD + d) = make_float2(o[i][0], o[i][1]);
+            if (hi_row) *reinterpret_cast<float2*>(s_o + ((size_t)warp * ROWS + gq + 8) * HD + d) = make_float2(o[i][2], o[i][3]);
+        }
     }
     __syncthreads();
     const size_t row0 = (size_t)t * nq;
@@ -473,28 +483,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         // size, reading every block's part (in ascending order) through distributed shared memory.
         // Nothing goes through global memory, no counter is needed.
         cluster_sync_all();
-        const int n = (int)gridDim.x;                        // = the cluster's size
-        for (int idx = threadIdx.x; idx < rows_valid * n; idx += WARPS * 32) {
-            const int r = idx / n, i = idx % n;
-            s_gm[idx] = ld_cluster(&s_pm_own[r], (unsigned)i);
-            s_gl[idx] = ld_cluster(&s_pl_own[r], (unsigned)i);
-        }
-        __syncthreads();
+        const int n = (int)gridDim.x;                        // = the cluster's size, at most MAX_CLUSTER
         const int d_lo = c * HD / n, d_hi = (c + 1) * HD / n;
         const int width = d_hi - d_lo;
         for (int idx = threadIdx.x; idx < rows_valid * width; idx += WARPS * 32) {
             const int r = idx / width, d = d_lo + idx % width;
-            const float* pm = s_gm + r * n;
-            const float* pl = s_gl + r * n;
+            // every block's maximum, sum and value for this (row, dimension): all remote reads go out
+            // together, one round trip
+            float pm[MAX_CLUSTER], pl[MAX_CLUSTER], pa[MAX_CLUSTER];
+#pragma unroll
+            for (int i = 0; i < MAX_CLUSTER; ++i) {
+                if (i < n) {
+                    pm[i] = ld_cluster(&s_pm_own[r], (unsigned)i);
+                    pl[i] = ld_cluster(&s_pl_own[r], (unsigned)i);
+                    pa[i] = ld_cluster(&s_part[r * HD + d], (unsigned)i);
+                }
+            }
             float MM = NEG_BIG;
-            for (int i = 0; i < n; ++i)
-                if (pl[i] > 0.f) MM = fmaxf(MM, pm[i]);
+#pragma unroll
+            for (int i = 0; i < MAX_CLUSTER; ++i)
+                if (i < n && pl[i] > 0.f) MM = fmaxf(MM, pm[i]);
             float L = 0.f, A = 0.f;
-#pragma unroll 8
-            for (int i = 0; i < n; ++i) {
-                const float wt = pl[i] > 0.f ? exp2f(pm[i] - MM) : 0.f;
-                L = fmaf(wt, pl[i], L);
-                A = fmaf(wt, ld_cluster(&s_part[r * HD + d], (unsigned)i), A);
+#pragma unroll
+            for (int i = 0; i < MAX_CLUSTER; ++i) {          // in ascending order of the keys
+                if (i < n) {
+                    const float wt = pl[i] > 0.f ? exp2f(pm[i] - MM) : 0.f;
+                    L = fmaf(wt, pl[i], L);
+                    A = fmaf(wt, pa[i], A);
+                }
             }
             out[(size_t)t * o_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
         }
