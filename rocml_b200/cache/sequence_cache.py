@@ -50,7 +50,9 @@ class KVGroup:
         self.table_host = np.full((max_slots, max_pages_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
         self._dirty = set()
-        self._pin = None
+        self._pins: List[torch.Tensor] = []        # ring of pinned staging copies of the table
+        self._pin_events: List[Optional[torch.cuda.Event]] = []
+        self._pin_next = 0
         self._released_upto: Dict[int, int] = {}  # slot -> first page a window has not released
 
     @property
@@ -77,6 +79,39 @@ class KVGroup:
             row[p] = self.pool.alloc()
         if todo:
             self._dirty.add(slot)
+
+    def plan(self, pieces, lengths: Sequence[int]) -> None:
+        """The page count of ``ensure`` and ``release_out_of_window`` over a run of pieces (see
+        SequenceCache.plan), on numbers only: a sequence holds the pages [first, end) of its row."""
+        free = self.pool.n_free
+        state: Dict[int, List[int]] = {}
+        for n_piece, piece in enumerate(pieces):
+            for slot, n_new in piece:
+                if slot not in state:
+                    held = np.nonzero(self.table_host[slot] >= 0)[0]
+                    end = int(held[-1]) + 1 if len(held) else 0
+                    state[slot] = [self._released_upto.get(slot, 0), end, lengths[slot]]
+                st = state[slot]
+                st[2] += n_new
+                need = pages_for(st[2])
+                if need > self.max_pages_per_seq:
+                    raise ContextOverflow(st[2], self.max_pages_per_seq * PAGE)
+                todo = max(0, need - max(st[0], st[1]))
+                if todo > free:
+                    raise CacheFull(
+                        f"the cache has {free} free pages of {PAGE} tokens when piece {n_piece} of the step "
+                        f"starts, {todo} are needed (group of {self.n_entries} layers, {self.n_pages} pages in all"
+                        + (f", window of {self.window} tokens" if self.window else "") + ")")
+                free -= todo
+                st[1] = max(st[1], need)
+            if self.window is None:
+                continue
+            for slot, _ in piece:
+                st = state[slot]
+                keep_from = max(0, st[2] - self.window + 1) // PAGE
+                if keep_from > st[0]:
+                    free += max(0, min(keep_from, st[1]) - st[0])
+                    st[0] = keep_from
 
     def release_out_of_window(self, slot: int, length: int) -> None:
         """After a step that left the sequence ``length`` long: the next query sits at a
@@ -106,15 +141,29 @@ class KVGroup:
         if not self._dirty:
             return
         if self.table.is_cuda:
-            if self._pin is None:
-                self._pin = torch.empty(self.table_host.shape, dtype=torch.int32, pin_memory=True)
+            # The copies are asynchronous and the loop above may run a step ahead: each flush stages its
+            # rows in the next buffer of a ring and waits for that buffer's previous copies first, so a
+            # row that a queued copy still reads is never rewritten (a window group's row may by then
+            # name a page that the queued step must not see).
+            if not self._pins:
+                self._pins = [torch.empty(self.table_host.shape, dtype=torch.int32, pin_memory=True)
+                              for _ in range(4)]
+                self._pin_events = [None] * len(self._pins)
+            i = self._pin_next
+            self._pin_next = (i + 1) % len(self._pins)
+            if self._pin_events[i] is not None:
+                self._pin_events[i].synchronize()
+            pin = self._pins[i]
             if len(self._dirty) > 8:
-                self._pin.numpy()[:] = self.table_host
-                self.table.copy_(self._pin, non_blocking=True)
+                pin.numpy()[:] = self.table_host
+                self.table.copy_(pin, non_blocking=True)
             else:
                 for s in sorted(self._dirty):
-                    self._pin.numpy()[s] = self.table_host[s]
-                    self.table[s].copy_(self._pin[s], non_blocking=True)
+                    pin.numpy()[s] = self.table_host[s]
+                    self.table[s].copy_(pin[s], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._pin_events[i] = ev
         else:
             self.table.copy_(torch.from_numpy(self.table_host))
         self._dirty.clear()
@@ -273,6 +322,23 @@ class SequenceCache:
         for g in self.kv_groups:
             g.ensure(slot, new)
         return old
+
+    def plan(self, pieces: Sequence[Sequence[tuple]]) -> None:
+        """Would this run of ``grow`` and ``commit`` calls succeed?  ``pieces`` is a list of pieces, each a
+        list of (slot, n_new): every sequence of a piece is grown, the piece runs, every sequence is
+        committed (a window group then takes back the pages that fell out of the window), and the
+        next piece follows.  Nothing is changed; ContextOverflow or CacheFull is raised for the first
+        piece that would not fit, so a step that is cut into pieces fails before its first launch
+        or not at all."""
+        lengths: Dict[int, int] = {}
+        for piece in pieces:
+            for slot, n_new in piece:
+                self._held(slot)
+                lengths[slot] = lengths.get(slot, self.lengths[slot]) + n_new
+                if lengths[slot] > self.max_seq_len:
+                    raise ContextOverflow(lengths[slot], self.max_seq_len)
+        for g in self.kv_groups:
+            g.plan(pieces, self.lengths)
 
     def commit(self, slot: int, n_new: int) -> None:
         """The step has been issued: the sequence is n_new longer."""

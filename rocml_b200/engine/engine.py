@@ -157,22 +157,24 @@ class Engine:
             for w in e.want:
                 if not 0 <= w < len(e.tokens):
                     raise RocmlError(f"slot {e.slot}: wanted place {w} is outside the {len(e.tokens)} tokens given")
-        # room for everything, before anything launches
-        old_lens = [self.cache.grow(e.slot, len(e.tokens)) for e in entries]
+        total = sum(len(e.tokens) for e in entries)
+        if total <= self.max_step_tokens:
+            pieces = [[(i, 0, len(e.tokens)) for i, e in enumerate(entries)]]
+        else:
+            pieces = self._cut(entries)
+        # Room for everything, before anything launches.  Pages are then taken piece by piece: a
+        # layer that keeps a window of keys gives pages back between the pieces of a long prompt, and
+        # its group holds only a window and a piece for each sequence.
+        self.cache.plan([[(entries[i].slot, b - a) for i, a, b in piece] for piece in pieces])
 
         with torch.cuda.device(self.device):
-            total = sum(len(e.tokens) for e in entries)
-            if total <= self.max_step_tokens:
-                pieces = [[(i, 0, len(e.tokens)) for i, e in enumerate(entries)]]
-            else:
-                pieces = self._cut(entries)
             outs, order = [], []
             for piece in pieces:
                 slots, olds, toks, wants = [], [], [], []
                 for i, a, b in piece:
                     e = entries[i]
                     slots.append(e.slot)
-                    olds.append(old_lens[i] + a)
+                    olds.append(self.cache.grow(e.slot, b - a))
                     toks.append(e.tokens[a:b])
                     w_here = sorted(w for w in set(e.want) if a <= w < b)
                     wants.append([w - a for w in w_here])

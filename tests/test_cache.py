@@ -126,3 +126,91 @@ def test_random_traffic_keeps_the_books_straight():
         c.free_slot(s)
     c.check_invariants()
     assert all(g.pool.n_held == 0 for g in c.kv_groups) and c.slots.n_held == 0
+
+
+def _pieces(lens, slots, step):
+    """The way the engine cuts a step: sequence after sequence, pieces of at most ``step`` tokens."""
+    pieces, cur, room = [], [], step
+    for slot, n in zip(slots, lens):
+        a = 0
+        while a < n:
+            take = min(room, n - a)
+            cur.append((slot, take))
+            a += take
+            room -= take
+            if room == 0:
+                pieces.append(cur)
+                cur, room = [], step
+    if cur:
+        pieces.append(cur)
+    return pieces
+
+
+def test_a_long_prompt_on_a_window_group_goes_in_piece_by_piece():
+    """Window 128, pieces of 256 tokens, one slot, a prompt of 3,000 tokens: the window group holds
+    pages for a window and a piece only, so the prompt fits piece by piece and not at once."""
+    c = make(max_tokens=3072, max_slots=1, max_seq=3072, step=256,
+             reqs=[KVRequirement(1, 16, window=128), KVRequirement(1, 16)])
+    win = next(g for g in c.kv_groups if g.window)
+    assert win.n_pages == pages_for(128 + 256) + 1
+    s = c.alloc_slot()
+    with pytest.raises(CacheFull):
+        c.plan([[(s, 3000)]])
+    with pytest.raises(CacheFull):
+        c.grow(s, 3000)
+    c.check_invariants()
+    assert win.pool.n_held == 0
+    pieces = _pieces([3000], [s], 256)
+    c.plan(pieces)
+    peak = 0
+    for piece in pieces:
+        for slot, n in piece:
+            c.grow(slot, n)
+        peak = max(peak, win.pool.n_held)
+        for slot, n in piece:
+            c.commit(slot, n)
+        c.check_invariants()
+    assert c.length(s) == 3000 and peak <= win.n_pages
+    assert win.pool.n_held <= pages_for(128) + 1
+    c.free_slot(s)
+    c.check_invariants()
+
+
+def test_plan_agrees_with_what_growth_then_does():
+    """plan() says yes exactly when the same pieces, grown and committed one after another, fit;
+    and it changes nothing."""
+    rng = random.Random(11)
+    for trial in range(200):
+        step = rng.choice([64, 100, 256])
+        window = rng.choice([24, 70, 128, 300])
+        max_slots = rng.choice([1, 2, 3])
+        c = make(max_tokens=64 * rng.choice([6, 12, 30]), max_slots=max_slots, max_seq=64 * 30, step=step,
+                 reqs=[KVRequirement(1, 16, window=window), KVRequirement(1, 16)])
+        slots = [c.alloc_slot() for _ in range(max_slots)]
+        for s in slots:                          # some history first
+            n = rng.choice([0, 1, 63, 64, 200])
+            try:
+                c.plan([[(s, n)]]) if n else None
+                c.grow(s, n); c.commit(s, n)
+            except (CacheFull, ContextOverflow):
+                pass
+        before = [g.pool.n_free for g in c.kv_groups], list(c.lengths)
+        lens = [rng.choice([1, 5, 64, 65, 200, 700, 1500]) for _ in slots]
+        pieces = _pieces(lens, slots, step)
+        try:
+            c.plan(pieces)
+            ok = True
+        except (CacheFull, ContextOverflow):
+            ok = False
+        assert ([g.pool.n_free for g in c.kv_groups], list(c.lengths)) == before
+        try:
+            for piece in pieces:
+                for slot, n in piece:
+                    c.grow(slot, n)
+                for slot, n in piece:
+                    c.commit(slot, n)
+            did = True
+        except (CacheFull, ContextOverflow):
+            did = False
+        assert ok == did, (trial, step, window, lens)
+        c.check_invariants()
