@@ -452,7 +452,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     }
     __syncthreads();
-    const size_t row0 = (size_t)t * nq;
+    const size_t row0 = (size_t)b * nq;                   // the work space is indexed by sequence, whatever cu_q says
     for (int idx = threadIdx.x; idx < rows_valid * HD; idx += WARPS * 32) {
         const int r = idx / HD, d = idx % HD;
         float M = NEG_BIG;
@@ -628,6 +628,10 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     const bool clustered = !proportional && n_chunks > 1 && n_chunks <= MAX_CLUSTER && cluster_enabled();
     const bool fused = pj.proj != nullptr;
     if (fused && HD != 128) return RB_ERR_BAD_SIZE;
+    // More than 16 query heads a key/value head: several blocks read the page of the new token, and only
+    // one of them writes the token's key and value into it, with nothing that orders the others' reads
+    // after that write.  The caller writes the cache with the kernel of its own and calls again.
+    if (fused && pj.write_kv && g > ROWS) return RB_ERR_BAD_SIZE;
 #define RB_ADV(CL, FQ, PROP) launch_variant<HD, CL, FQ, PROP>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table,       \
                                                          max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,         \
                                                          n_chunks, ppb, part_acc, part_ml, counters, out, o_stride, pj, B)
@@ -643,7 +647,8 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 // with n_chunks == 1 the result is written to `out` directly.  pages_per_block == 0: n_chunks blocks
 // per key/value head group share the pages of all B sequences (B <= 256) equally, a block working on
 // the end of one sequence and the beginning of the next where its share says so.
-// Work space: part_acc [T, nq, n_chunks, hd], part_ml [T, nq, n_chunks, 2] and `counters`, at least
+// Work space: part_acc [B, nq, n_chunks, hd], part_ml [B, nq, n_chunks, 2] (indexed by the sequence's
+// place in the batch, not by its token index) and `counters`, at least
 // B * nkv * ceil(group / 16) ints that are ZERO on entry and are left zero on exit.
 // Returns RB_ERR_BAD_SIZE for head sizes other than 64, 128, 256 and for contexts whose chunk list does
 // not fit the merge's shared memory (65536 tokens at a group of 4 and head size 128); the caller then

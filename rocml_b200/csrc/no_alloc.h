@@ -21,9 +21,14 @@
 // limit; nothing is launched.  The function calls no cudaMalloc, cudaFree or other allocating
 // routine.
 //
+// The work space is indexed by a sequence's place in the batch (0 .. n_seqs - 1), never by the
+// token indices in cu_q, so the limits above hold whatever cu_q contains (the queries may be rows
+// taken from a larger packed buffer).
+//
 // Set-up: the first call on a device looks up the array's device address
 // (cudaGetSymbolAddress, with that device current) and remembers it; make that first call before
-// any stream capture begins on the device.
+// any stream capture begins on the device.  The address is looked up for the device that is
+// CURRENT in the calling thread (cudaGetDevice), so `stream` must belong to that device.
 //
 // Sharing: there is ONE array per device and every call uses it.  It keeps whatever the last call
 // left; the counters this call will use are cleared (cudaMemsetAsync on `stream`) before the kernel

@@ -95,6 +95,7 @@ class Attention(Mixer):
         return (batch.is_decode and self.hd == 128 and not self.bias and self.env.act_dtype == torch.bfloat16
                 and self.qkv.weight is not None and self.qkv.weight.dtype == torch.bfloat16
                 and self.qkv._splits(batch.n_tokens) > 1
+                and (self.shares_cache or self.nq // self.nkv <= 16)     # wider groups: the kernel does not write the cache
                 and (self.position.inv_freq is None or self.position.rot_dim == self.hd))
 
     can_add_into = True    # forward() accepts add_into=residual (see parts.base)

@@ -157,9 +157,12 @@ def test_gemm_tcgen05_many_rows_add_into_the_residual_stream(M, N, K, bias):
 @pytest.mark.parametrize("M,nq,nkv,K,norm,rope,bias,writes", [
     (300, 4, 2, 512, True, True, False, True), (1000, 6, 1, 264, True, True, True, True),
     (513, 2, 2, 1024, False, True, False, True), (257, 4, 2, 256, True, False, False, False)])
-def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rope, bias, writes):
+@pytest.mark.parametrize("eps", [1e-6, 1e-1])
+def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rope, bias, writes, eps):
     """A prompt's q | k | v projection whose epilogue does the per-head norm, the rotation and the cache
-    write, against the same arithmetic in float64; some tokens are padding and must leave no trace."""
+    write, against the same arithmetic in float64; some tokens are padding and must leave no trace.
+    The second eps is as large as the heads' mean squares, so that an eps that is dropped or added in
+    the wrong place shows above the bfloat16 tolerance (the 32-bit path never runs this kernel)."""
     from rocml_b200 import kernels
     hd = 128
     g = torch.Generator().manual_seed(M + K)
@@ -184,7 +187,7 @@ def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rop
     cs = kernels.rope_table(pos.to(DEV), inv_freq, M) if rope else None
     q = torch.zeros((M, nq * hd), dtype=torch.bfloat16, device=DEV)
     assert kernels.gemm_tcgen05_qkv_rope(
-        x.to(DEV), w.to(DEV), q, nq, nkv, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, 1e-6, cs,
+        x.to(DEV), w.to(DEV), q, nq, nkv, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, eps, cs,
         pos.to(DEV), slot.to(DEV), table.to(DEV) if writes else None, kc if writes else None, vc if writes else None,
         b.to(DEV) if bias else None)
     kernels.check_status(DEV)
@@ -193,7 +196,7 @@ def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rop
 
     def finish(h, wn):
         if wn is not None:
-            h = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + 1e-6) * wn.double()
+            h = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * wn.double()
         if rope:
             ang = pos.double()[:, None] * inv_freq.cpu().double()[None, :]
             c, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
@@ -505,15 +508,17 @@ def test_attention_decode_split_kv(case, fast):
     ([700, 1, 129, 64, 128], 32, 8, None, 7, True, True, (1, 1)),      # one page per block: clusters of up to 12
     ([300, 131, 65], 8, 2, None, 1, True, True, (2, 3)),               # clusters of 2
     ([513, 40], 6, 3, 70, 3, False, True, (1, 1)),                    # a window, no per-head norm
-    ([1100], 40, 2, None, 2, True, False, (1, 1)),                     # 20 query heads per group: two blocks a group; 18 chunks: merged through global memory
+    ([1100], 32, 2, None, 2, True, False, (1, 1)),                     # 16 query heads per group: a full tile; 18 chunks: merged through global memory
     ([900, 70, 300, 5], 8, 2, None, 4, True, True, (0, 9)),            # nine blocks a group share the pages
     ([900, 70, 300, 5, 64, 65, 200], 8, 2, None, 4, True, True, (0, 3)),  # fewer blocks than sequences
     ([130, 70, 300], 8, 2, 100, 2, True, True, (0, 2)),                # the same with a window
 ])
-def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S, norm, rope, grid):
+@pytest.mark.parametrize("eps", [1e-6, 1e-1])
+def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S, norm, rope, grid, eps):
     """Head size 128: the decode kernel is given the projection's partial sums and does the
     per-head norm, the rotation and the cache write of the new token itself.  Same output and same
-    cache as the two kernels one after the other."""
+    cache as the two kernels one after the other, and the right output by float64.  The second eps is
+    of the size of the heads' mean squares, so that a dropped or misplaced eps shows."""
     from rocml_b200 import kernels
     hd, B = 128, len(lens)
     ks, vs, qs, kc, vc, meta = paged_case(31, lens, [1] * B, nq, nkv, hd, torch.bfloat16)
@@ -538,11 +543,11 @@ def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S,
         ml = torch.empty((B, nq, n_chunks, 2), dtype=torch.float32, device=DEV)
         if fused:
             assert kernels.attention_decode_fused(proj, out, k2, v2, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
-                                                  B, nq, nkv, hd, qw, kw, 1e-6, cs, True, scale, window or 0,
+                                                  B, nq, nkv, hd, qw, kw, eps, cs, True, scale, window or 0,
                                                   n_chunks, acc, ml, ppb)
         else:
             q = torch.empty((B, nq * hd), dtype=torch.bfloat16, device=DEV)
-            kernels.qk_norm_rope_cache(proj, q, B, nq, nkv, hd, qw, kw, 1e-6, inv_freq, hd if rope else 0, pos,
+            kernels.qk_norm_rope_cache(proj, q, B, nq, nkv, hd, qw, kw, eps, inv_freq, hd if rope else 0, pos,
                                        slot_of_token, d["table"], k2, v2, write_kv=True, cos_sin=cs)
             assert kernels.attention_decode(q, out, k2, v2, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"], B, nq,
                                             nkv, hd, scale, window or 0, n_chunks, acc, ml, ppb)
@@ -552,6 +557,48 @@ def test_attention_decode_takes_the_projections_itself(lens, nq, nkv, window, S,
     assert torch.isfinite(outs[1]).all()
     assert torch.equal(caches[0][0], caches[1][0]) and torch.equal(caches[0][1], caches[1][1])
     assert (outs[0] - outs[1]).abs().max().item() < 1e-2
+    # float64: the new token's key and value from the summed projections, the other keys from the cache
+    import plain_qwen3 as P
+    summed = proj.double().sum(0).cpu().reshape(B, nq + 2 * nkv, hd)
+    qh, kh, vh = summed[:, :nq], summed[:, nq:nq + nkv], summed[:, nq + nkv:]
+    if norm:
+        qh, kh = P.rmsnorm(qh, qw.double().cpu(), eps), P.rmsnorm(kh, kw.double().cpu(), eps)
+    if rope:
+        qh = torch.stack([P.rope_neox(qh[b:b + 1], [lens[b] - 1], 1e6)[0] for b in range(B)])
+        kh = torch.stack([P.rope_neox(kh[b:b + 1], [lens[b] - 1], 1e6)[0] for b in range(B)])
+    for b, n in enumerate(lens):
+        keys = torch.cat([ks[b][:n - 1].double(), kh[b:b + 1].bfloat16().double()])       # [n, nkv, hd]
+        vals = torch.cat([vs[b][:n - 1].double(), vh[b:b + 1].bfloat16().double()])
+        lo = max(0, n - window) if window else 0
+        for h in range(nq):
+            kv = h // (nq // nkv)
+            sc = (keys[lo:, kv] @ qh[b, h].bfloat16().double()) * scale
+            want = torch.softmax(sc, 0) @ vals[lo:, kv]
+            assert (outs[1][b, h * hd:(h + 1) * hd].double() - want).abs().max().item() < 2e-2, (b, h)
+
+
+def test_attention_decode_leaves_wide_groups_to_the_two_kernels():
+    """More than 16 query heads a key/value head: several blocks would read the new token's page while
+    one of them writes it, so the kernel that takes the projections declines (the caller then writes
+    the cache with the kernel of its own); when it only reads a cache that is written already it runs."""
+    from rocml_b200 import kernels
+    hd, nq, nkv, lens = 128, 40, 2, [200, 70]
+    B = len(lens)
+    ks, vs, qs, kc, vc, meta = paged_case(3, lens, [1] * B, nq, nkv, hd, torch.bfloat16)
+    d = {k: v.to(DEV) for k, v in meta.items()}
+    n_chunks = (max(lens) + 63) // 64
+    out = torch.zeros((B, nq * hd), dtype=torch.bfloat16, device=DEV)
+    acc = torch.empty((B, nq, n_chunks, hd), dtype=torch.float32, device=DEV)
+    ml = torch.empty((B, nq, n_chunks, 2), dtype=torch.float32, device=DEV)
+    k2, v2 = kc.clone().to(DEV), vc.clone().to(DEV)
+    before = k2.clone()
+    for writes, expect in ((True, False), (False, True)):
+        proj = torch.randn((2, B, (nq + (2 * nkv if writes else 0)) * hd), device=DEV)
+        got = kernels.attention_decode_fused(proj, out, k2, v2, d["table"], d["seq_slot"], d["cu_q"], d["kv_len"],
+                                             B, nq, nkv, hd, None, None, 1e-6, None, writes, 0.1, 0, n_chunks, acc, ml, 1)
+        assert got is expect
+    assert torch.equal(torch.nan_to_num(k2.float()), torch.nan_to_num(before.float()))
+    kernels.check_status(DEV)
 
 
 def test_attention_decode_refuses_other_head_sizes():

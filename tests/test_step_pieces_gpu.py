@@ -86,7 +86,7 @@ def test_unequal_batch_cut_in_mid_sequence(model_folder, plain, dtype, piece):
         ndec = [8, 5, 2]
         seqs = [prompt(900 + 10 * round_ + j, n + d, vocab) for j, (n, d) in enumerate(zip(lens, ndec))]
         want = [plain.logits(x) for x in seqs]
-        places = [[lens[0] - 1, 0, 63, 64, piece - 1, piece, 150 % lens[0], 63], [69, 3, 3, 0], [4, 0]]
+        places = [[p % lens[0] for p in (lens[0] - 1, 0, 63, 64, piece - 1, piece, 150, 63)], [69, 3, 3, 0], [4, 0]]
         slots = [eng.new_sequence() for _ in seqs]
         out = eng.step([StepEntry(s, x[:n], w) for s, x, n, w in zip(slots, seqs, lens, places)])
         ref = torch.cat([want[j][places[j]] for j in range(3)])
