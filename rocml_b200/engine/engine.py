@@ -23,6 +23,7 @@ from ..cache import SequenceCache
 from ..config import load_model_spec
 from ..errors import CacheError, ConfigError, KernelError, RocmlError
 from ..parts import BuildEnv
+from ..profile import profiler as _profiler
 from .batch import BatchBuffers, HostBatch, StepBatch, pack_entries
 from .model import Model
 
@@ -224,8 +225,17 @@ class Engine:
         host = HostBatch(list(slots), q_lens, list(kv_len), list(want_rows))
         self.cache.flush()
         self.launches += 1
+        prof = _profiler.ACTIVE
+        if prof is not None:
+            # a profiled step runs its kernels one by one, without a graph (rocml_b200.profile.profiler)
+            with prof.step("decode" if is_decode else "prefill", q_lens, kv_len):
+                return self._run_eager(packed, host, slots, q_lens, T, B, W, is_decode)
         if is_decode and self.use_graphs:
             return self._run_graph(packed, host, T, B, W)
+        return self._run_eager(packed, host, slots, q_lens, T, B, W, is_decode)
+
+    def _run_eager(self, packed, host, slots, q_lens, T, B, W, is_decode) -> Optional[torch.Tensor]:
+        kv_len = packed[4]
         key = (_bucket(T, 64), _bucket(B, 8))
         if key not in self._eager:
             self._eager[key] = BatchBuffers(key[0], key[1], key[0], self.device)
@@ -303,11 +313,23 @@ class Engine:
                 raise RocmlError("feed_from must hold one token for each sequence of the step")
             tokens = [[0]] * len(slots)
             device_tokens = feed_from.device_tokens
-        logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)], device_tokens=device_tokens)
         if self._sampler is None:
             from ..sampling import Sampler
             self._sampler = Sampler(self.device, max_batch=max(self.cache.max_slots, 1))
         from .. import kernels
+        prof = _profiler.ACTIVE
+        if prof is not None:
+            # the sampling belongs to the step it follows (one piece assumed; a cut prompt opens steps of its own)
+            phase = "decode" if all(len(t) == 1 for t in tokens) else "prefill"
+            single = sum(len(t) for t in tokens) <= self.max_step_tokens
+            if single:
+                with prof.step(phase, [], []):
+                    logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)],
+                                       device_tokens=device_tokens)
+                    with prof.scope(op="sampling"):
+                        return self._sampler.launch(logits, params, rngs, histories,
+                                                    status=kernels.status_word(self.device))
+        logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)], device_tokens=device_tokens)
         return self._sampler.launch(logits, params, rngs, histories, status=kernels.status_word(self.device))
 
     def collect(self, handle) -> List[int]:

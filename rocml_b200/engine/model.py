@@ -12,6 +12,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import kernels
+from ..profile import scope
 from ..config.specs import MixerSpec, ModelSpec
 from ..errors import ConfigError
 from ..parts import BuildEnv, build_block, build_norm
@@ -99,24 +100,43 @@ class Model:
         n = sum(self.blocks[e.layer].weight_bytes() for e in self.spec.schedule)
         return n + self.final_norm.weight_bytes() + self.head.weight_bytes()
 
+    def step_cost(self, q_lens, kv_lens, n_want: int):
+        """(bytes, floating-point operations) a step has to move and do at least: every scheduled
+        block's weights once and its products and attention over the given sequences (``q_lens`` new
+        tokens each, ``kv_lens`` long afterwards, whose keys and values are read once), the final norm,
+        and the head on ``n_want`` rows.  Asked of the parts, so it holds for any arrangement."""
+        nbytes = flops = 0
+        for e in self.spec.schedule:
+            block = self.blocks[e.layer]
+            if hasattr(block, "cost"):
+                b, f = block.cost(q_lens, kv_lens)
+            else:
+                b, f = block.weight_bytes(), 0
+            nbytes, flops = nbytes + b, flops + f
+        hb, hf = self.head.cost(n_want)
+        return nbytes + self.final_norm.weight_bytes() + hb, flops + hf
+
     # ---- the pass ---------------------------------------------------------------------------------
     def forward(self, batch, cache) -> Optional[torch.Tensor]:
         T = batch.n_tokens
         resid = torch.empty((T, self.hidden), dtype=torch.float32, device=self.env.device)
-        kernels.embedding(batch.token_ids, self.embed, resid, self.status)
+        with scope(op="embedding"):
+            kernels.embedding(batch.token_ids, self.embed, resid, self.status)
         pending = None
         sched = self.spec.schedule
         for i, e in enumerate(sched):
             block = self.blocks[e.layer]
-            if getattr(block, "chains", False):
-                # a block may prepare the first norm of the block that follows it
-                nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
-                pending = block.forward(resid, pending, batch, cache.views[i], next_block=nxt)
-            else:
-                pending = block.forward(resid, pending, batch, cache.views[i])
+            with scope(layer=i):
+                if getattr(block, "chains", False):
+                    # a block may prepare the first norm of the block that follows it
+                    nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
+                    pending = block.forward(resid, pending, batch, cache.views[i], next_block=nxt)
+                else:
+                    pending = block.forward(resid, pending, batch, cache.views[i])
         if batch.n_want == 0:
             return None
-        xn = self.final_norm.forward(resid, pending, n_rows=batch.n_want, rows=batch.want_rows, write_back=False)
+        with scope(op="final_norm"):
+            xn = self.final_norm.forward(resid, pending, n_rows=batch.n_want, rows=batch.want_rows, write_back=False)
         logits = torch.empty((batch.n_want, self.vocab), dtype=torch.float32, device=self.env.device)
         self.head.forward(xn, logits, batch.n_want)
         return logits

@@ -7,12 +7,16 @@ current CUDA stream to the C entry point, and turns a non-zero return into
 from __future__ import annotations
 
 import ctypes
+import functools
+import inspect
 from typing import Optional
 
 import torch
 
 from .csrc.build import library
 from .errors import KernelError
+from .profile import cost as _cost
+from .profile import profiler as _profiler
 
 F32, BF16 = 0, 1
 PAGE = 64  # tokens per cache page (RB_PAGE in csrc/common.cuh)
@@ -60,6 +64,51 @@ def _check(rc: int, what: str):
         if rc in _CODES:
             raise KernelError(f"{what}: {_CODES[rc]} (code {rc})")
         raise KernelError(f"{what}: CUDA error {rc}")
+
+
+# ---- profiling: each wrapper below can be timed with what it had to move and compute ------------------
+
+def _profiled(cost_of):
+    """While a profiler is active (rocml_b200.profile), bracket the wrapped launch with a pair of CUDA
+    events and file its bytes and operations: ``cost_of(a)`` gets the call's arguments by name and
+    returns (bytes, flops).  A wrapper that returns False launched nothing and files nothing."""
+    def deco(fn):
+        sig = inspect.signature(fn)
+
+        @functools.wraps(fn)
+        def wrapper(*args, **kwargs):
+            prof = _profiler.ACTIVE
+            if prof is None:
+                return fn(*args, **kwargs)
+            start = prof.begin()
+            result = fn(*args, **kwargs)
+            if result is not False:
+                bound = sig.bind(*args, **kwargs)
+                bound.apply_defaults()
+                nbytes, flops = cost_of(bound.arguments, prof.facts)
+                prof.end(start, fn.__name__, nbytes, flops)
+            return result
+        return wrapper
+    return deco
+
+
+def _esz(t) -> int:
+    return t.element_size()
+
+
+def _n_in(x) -> int:
+    return x.shape[0] if x.dim() == 3 else 1
+
+
+def _rows(a, x="x") -> int:
+    return a[x].shape[0] if a.get("m") is None else a["m"]
+
+
+def _attention_cost(a, facts, q="q"):
+    window = a.get("window") or None
+    n = a["n_seqs"]
+    q_lens, kv_lens = facts.q_lens[:n], facts.kv_lens[:n]
+    return _cost.attention(q_lens, kv_lens, a["nq"], a["nkv"], a["hd"], _esz(a["k_cache"]), window)
 
 
 def _i32(t: torch.Tensor, name: str):
@@ -110,6 +159,7 @@ def _lib():
 
 # ---- embedding --------------------------------------------------------------------------------
 
+@_profiled(lambda a, facts: _cost.embedding(a["out"].shape[0], a["out"].shape[1], _esz(a["table"])))
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None):
     """out[t, :] = float32(table[ids[t], :]); out is [T, H] float32."""
     T, H = out.shape
@@ -124,6 +174,10 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status:
 
 # ---- fused residual add + RMSNorm ---------------------------------------------------------------
 
+@_profiled(lambda a, facts: _cost.add_norm(
+    a["n_rows"] if a["n_rows"] is not None else (a["rows"].numel() if a["rows"] is not None else a["resid"].shape[0]),
+    a["resid"].shape[1], a["delta"].shape[0] if a["delta"] is not None else 0, _esz(a["out"]),
+    bool(a["write_back"]) and a["delta"] is not None, _esz(a["weight"])))
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
                 write_back: bool = True):
@@ -159,6 +213,7 @@ def _partials(x: torch.Tensor, what: str):
     return 1, 0, x.stride(0)
 
 
+@_profiled(lambda a, facts: _cost.silu_mul(a["out"].shape[0], a["out"].shape[1], _n_in(a["x"]), _esz(a["x"]), _esz(a["out"])))
 def silu_mul(x: torch.Tensor, out: torch.Tensor, paired: bool = False):
     """x [T, 2I] = [gate | up], or [S, T, 2I] partial sums to be added first -> out [T, I] = silu(gate) * up.
     ``paired``: gates and ups alternate in blocks of 16 columns instead of lying in two halves."""
@@ -170,6 +225,7 @@ def silu_mul(x: torch.Tensor, out: torch.Tensor, paired: bool = False):
                               I2 // 2, 1 if paired else 0, _stream()), "silu_mul")
 
 
+@_profiled(lambda a, facts: (a["x"].numel() * (_esz(a["x"]) + _esz(a["out"])), 0))
 def cast(x: torch.Tensor, out: torch.Tensor):
     if x.numel() != out.numel() or not x.is_contiguous() or not out.is_contiguous():
         raise KernelError("cast: shapes do not fit")
@@ -178,6 +234,8 @@ def cast(x: torch.Tensor, out: torch.Tensor):
 
 # ---- q/k norm + rotary + cache write --------------------------------------------------------------
 
+@_profiled(lambda a, facts: _cost.qk_norm_rope(a["n_tokens"], a["nq"], a["nkv"], a["hd"], _n_in(a["proj"]), _esz(a["proj"]),
+                                                  _esz(a["q_out"]), bool(a["write_kv"])))
 def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, nq: int, nkv: int, hd: int,
                        q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                        inv_freq: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
@@ -217,6 +275,7 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, n
     _check(rc, "qk_norm_rope_cache")
 
 
+@_profiled(lambda a, facts: _cost.rope_table(a["n_tokens"], a["inv_freq"].numel()))
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, n_tokens: int) -> torch.Tensor:
     """float32 [T, half, 2]: (cos, sin) of positions[t] * inv_freq[i], full-precision sincosf."""
     half = inv_freq.numel()
@@ -228,6 +287,7 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, n_tokens: int) -
 
 # ---- matrix products ---------------------------------------------------------------------------------
 
+@_profiled(lambda a, facts: _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], _esz(a["w"]), _esz(a["x"]), _esz(a["out"])))
 def gemm_generic(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  m: Optional[int] = None):
     """out[M, N] = x[M, K] . w[N, K]^T (+ bias float32 [N]) on the CUDA cores, 32-bit accumulation."""
@@ -244,6 +304,7 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
 
 # ---- attention ------------------------------------------------------------------------------------------
 
+@_profiled(lambda a, facts: _attention_cost(a, facts))
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                       n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
@@ -274,6 +335,7 @@ def prefill_heads_first(n_seqs: int, nkv: int, hd: int, max_kv_len: int, window:
     return n_seqs * nkv * span * hd * 4 <= PREFILL_L2_BYTES
 
 
+@_profiled(lambda a, facts: _attention_cost(a, facts))
 def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                           block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                           n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
@@ -300,6 +362,7 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
     return True
 
 
+@_profiled(lambda a, facts: _attention_cost(a, facts))
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                       n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0) -> bool:
@@ -377,6 +440,7 @@ def _check_parts(part_acc, part_ml, n_chunks: int, what: str) -> None:
         raise KernelError(f"{what}: work space for {n_chunks} partial results a row is needed")
 
 
+@_profiled(lambda a, facts: _attention_cost(a, facts))
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                      n_seqs: int, nq: int, nkv: int, hd: int, scale: float, window: int, n_chunks: int,
@@ -407,6 +471,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     return True
 
 
+@_profiled(lambda a, facts: tuple(map(sum, zip(_attention_cost(a, facts), (a["proj"].numel() * 4, 0)))))
 def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                            block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                            n_seqs: int, nq: int, nkv: int, hd: int, q_norm_w: Optional[torch.Tensor],
@@ -454,6 +519,7 @@ def attention_decode_fused(proj: torch.Tensor, out: torch.Tensor, k_cache: torch
     return True
 
 
+@_profiled(lambda a, facts: (a["part_acc"].numel() * 4 + a["part_ml"].numel() * 4 + a["n_tokens"] * a["nq"] * a["hd"] * _esz(a["out"]), 0))
 def attention_merge(part_acc: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                     slot_of_token: torch.Tensor, n_tokens: int, nq: int, hd: int, chunk: int, n_chunks: int,
                     window: int = 0):
@@ -468,6 +534,7 @@ def attention_merge(part_acc: torch.Tensor, part_ml: torch.Tensor, out: torch.Te
 _ARGMAX_SLICES = 64
 
 
+@_profiled(lambda a, facts: _cost.sample(a["logits"].shape[0] if a["rows"] is None else a["rows"], a["logits"].shape[1]))
 def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
     """out[r] = index of the first largest value of logits[r, :]; logits float32 [R, V].  Wide rows
     are searched by 64 blocks each, through a small work space."""
@@ -485,6 +552,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
            "argmax")
 
 
+@_profiled(lambda a, facts: _cost.sample(a["n"], a["logits"].shape[1]))
 def sample(logits: torch.Tensor, n: int, rows: torch.Tensor, history: Optional[torch.Tensor], out: torch.Tensor):
     """One token per row of float32 logits [>= n, V].  ``rows`` holds n records of 8 x 32 bits
     {temperature f32, top_k i32 (0 off), top_p f32 (< 0 off), u f32, penalty f32 (<= 0 off),
@@ -527,6 +595,8 @@ def check_status(device) -> None:
         raise_for_status(int(_status[key].item()), device)
 
 
+@_profiled(lambda a, facts: (_cost.gated_linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, _esz(a["out"])) if a["gated"] else
+                         _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, _esz(a["out"]), _n_in(a["out"]))))
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  m: Optional[int] = None, stages: int = 0, gated: bool = False) -> bool:
     """out = x . w^T on the tensor cores; x, w bfloat16, out bfloat16 [M, N] or float32 [M, N] or
@@ -569,6 +639,7 @@ def _row_scale(rowscale, m: int, what: str):
     return _ptr(sumsq), sumsq.shape[0], sumsq.stride(0), float(eps)
 
 
+@_profiled(lambda a, facts: _cost.gated_linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, 2))
 def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, bias: Optional[torch.Tensor] = None,
                             m: Optional[int] = None, rowscale=None) -> bool:
     """h = silu(gate) * up for at most 32 rows, w's rows alternating in blocks of 16 between gate and
@@ -598,6 +669,7 @@ def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, b
     return True
 
 
+@_profiled(lambda a, facts: _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, 4, 1, True))
 def gemm_tcgen05_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Optional[torch.Tensor] = None,
                      m: Optional[int] = None) -> bool:
     """resid += x . w^T (+ bias) for many rows (more than 256, N at least 256): the product is added into
@@ -622,6 +694,8 @@ def gemm_tcgen05_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias
     return True
 
 
+@_profiled(lambda a, facts: tuple(map(sum, zip(_cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, 4, 1, True),
+                                                       (_rows(a) * a["w"].shape[0] * 2 if a["xhat"] is not None else 0, 0)))))
 def gemm_tcgen05_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, splits: int,
                           bias: Optional[torch.Tensor] = None, next_w: Optional[torch.Tensor] = None,
                           xhat: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None,
@@ -661,6 +735,7 @@ def gemm_tcgen05_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor,
     return True
 
 
+@_profiled(lambda a, facts: _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, 2))
 def gemm_tcgen05_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, nq: int, nkv: int,
                           q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                           cos_sin: Optional[torch.Tensor], positions: torch.Tensor, slot_of_token: torch.Tensor,

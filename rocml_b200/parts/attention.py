@@ -87,6 +87,14 @@ class Attention(Mixer):
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()
 
+    def cost(self, q_lens, kv_lens):
+        from ..profile import cost as C
+        T = sum(q_lens)
+        esz = 4 if self.env.mode == "float32" else 2
+        parts = [self.qkv.cost(T), self.o.cost(T),
+                 C.attention(q_lens, kv_lens, self.nq, self.nkv, self.hd, esz, int(self.window) if self.window else None)]
+        return sum(p[0] for p in parts), sum(p[1] for p in parts)
+
     can_sink = True        # forward() accepts sink=ResidualSink (see parts.base)
 
     def takes_deferred(self, batch) -> bool:

@@ -87,6 +87,12 @@ class Part:
         """Bytes of weights one forward pass reads (for the roofline)."""
         return 0
 
+    def cost(self, q_lens, kv_lens):
+        """(bytes, floating-point operations) one forward pass has to move and do at least, for
+        sequences that bring ``q_lens`` tokens and are ``kv_lens`` long afterwards.  The default
+        counts the weights once and no arithmetic; parts with products say more."""
+        return self.weight_bytes(), 0
+
 
 class Norm(Part):
     """forward(resid [T, H] float32, delta None | [S, T, H] float32, ...) adds the delta into the

@@ -7,6 +7,7 @@ from typing import Dict, List
 import torch
 
 from ..config.specs import LayerSpec
+from ..profile import scope
 from ..weights.decl import TensorDecl
 from .base import BuildEnv, ResidualSink, build_feed_forward, build_mixer, build_norm, register_arrangement
 
@@ -56,6 +57,10 @@ class PreNormBlock:
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff))
 
+    def cost(self, q_lens, kv_lens):
+        parts = [p.cost(q_lens, kv_lens) for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff)]
+        return sum(p[0] for p in parts), sum(p[1] for p in parts)
+
     chains = True          # forward() accepts next_block (see below)
 
     def forward(self, resid, pending, batch, view, next_block=None):
@@ -70,14 +75,16 @@ class PreNormBlock:
         # returns None, nothing is pending, and the following norm only normalises): the delta of a
         # few thousand rows then never goes through memory.  Parts that set ``can_add_into`` get the offer.
         adds = not batch.is_decode and T > ADD_INTO_MIN_TOKENS and _defer_enabled()
-        xn = self.mixer_norm.forward(resid, pending, T)
+        with scope(op="mixer_norm"):
+            xn = self.mixer_norm.forward(resid, pending, T)
         if offers and getattr(self.mixer, "can_sink", False) and _takes(self.ff, batch):
             delta = self.mixer.forward(xn, batch, view, sink=ResidualSink(resid, self.ff_norm))
         elif adds and getattr(self.mixer, "can_add_into", False):
             delta = self.mixer.forward(xn, batch, view, add_into=resid)
         else:
             delta = self.mixer.forward(xn, batch, view)
-        xn = self.ff_norm.forward(resid, delta, T)
+        with scope(op="ff_norm"):
+            xn = self.ff_norm.forward(resid, delta, T)
         nxt = getattr(next_block, "mixer", None)
         if offers and nxt is not None and getattr(self.ff, "can_sink", False) and _takes(nxt, batch):
             return self.ff.forward(xn, batch, sink=ResidualSink(resid, next_block.mixer_norm))

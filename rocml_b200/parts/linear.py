@@ -12,11 +12,13 @@ call shape: ``matvec`` for one token, ``matmul`` for many
 """
 from __future__ import annotations
 
+import functools
 from typing import Dict, List, Optional, Sequence
 
 import torch
 
 from .. import kernels
+from ..profile import profiler as _profiler
 from ..errors import KernelError
 from ..weights.decl import TensorDecl
 from .base import BuildEnv, DeferredNorm
@@ -37,11 +39,24 @@ def _sm_count(device) -> int:
     return _SM_COUNT[key]
 
 
+def _labelled(fn):
+    """While a profiler is active the kernels a product launches carry the weight's name as their label."""
+    @functools.wraps(fn)
+    def inner(self, *args, **kwargs):
+        prof = _profiler.ACTIVE
+        if prof is None:
+            return fn(self, *args, **kwargs)
+        with prof.scope(op=self.label):
+            return fn(self, *args, **kwargs)
+    return inner
+
+
 class Linear:
     def __init__(self, names: Sequence[str], out_features: Sequence[int], in_features: int, bias: bool,
                  env: BuildEnv):
         """``names`` are the tensor-name stems stacked along out (e.g. q_proj, k_proj, v_proj)."""
         self.names = list(names)
+        self.label = "+".join(n.rsplit(".", 1)[-1] for n in self.names)
         self.outs = list(out_features)
         self.n = sum(self.outs)
         self.k = in_features
@@ -87,6 +102,7 @@ class Linear:
         self.paired = True
         return True
 
+    @_labelled
     def forward_gated(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """[M, N / 2] = silu(gate(x)) * up(x) in one kernel (needs ``interleave_pairs``)."""
         out = torch.empty((m, self.n // 2), dtype=torch.bfloat16, device=x.device)
@@ -94,6 +110,7 @@ class Linear:
             raise KernelError("the gated matrix product refused a layout that interleave_pairs accepted")
         return out
 
+    @_labelled
     def forward_gated_pair(self, x: torch.Tensor, m: int, rowscale=None) -> Optional[torch.Tensor]:
         """The same for few rows when the sum over K is split in two: the two halves' blocks form a
         cluster and the activation is applied where they meet, so no second kernel waits for partial
@@ -114,6 +131,7 @@ class Linear:
         s = 8 if s >= 8 else (4 if s >= 4 else 0)
         return s if s and self.k // 64 >= s else 0
 
+    @_labelled
     def forward_residual(self, x: torch.Tensor, m: int, sink) -> Optional[DeferredNorm]:
         """sink.resid += x . W^T (+ bias) for a few rows, inside the product (the K splits exchange their
         parts through shared memory), together with what ``sink.norm`` needs: returns its deferred
@@ -128,6 +146,7 @@ class Linear:
             return None
         return DeferredNorm(xhat, sumsq, norm.eps, self.n, norm, sink.resid)
 
+    @_labelled
     def forward_add(self, x: torch.Tensor, m: int, resid: torch.Tensor) -> bool:
         """resid += x . W^T (+ bias) for many rows, inside the product's epilogue.  False when this step's
         product cannot be done that way (use ``forward_delta``)."""
@@ -142,11 +161,18 @@ class Linear:
         self.weight = weight
 
     def weight_bytes(self) -> int:
+        if self.weight is None:     # not loaded: the declared shape in the type the files would be kept in
+            return self.n * self.k * (4 if self.env.mode == "float32" else 2)
         return self.weight.numel() * self.weight.element_size()
+
+    def cost(self, m: int):
+        """(bytes, operations) of the product with m rows: the weight once, 2 m n k."""
+        return self.weight_bytes(), 2 * m * self.n * self.k
 
     def _tensor_core(self, x: torch.Tensor) -> bool:
         return x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.is_cuda
 
+    @_labelled
     def forward(self, x: torch.Tensor, out: torch.Tensor, m: Optional[int] = None) -> torch.Tensor:
         """out[:M] = x[:M] . W^T (+ bias); ``out`` is [M, N] float32 or of x's type."""
         if self._tensor_core(x) and kernels.gemm_tcgen05(x, self.weight, out, self.bias, m):
@@ -190,6 +216,7 @@ class Linear:
             s *= 2
         return s
 
+    @_labelled
     def forward_delta(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """The product as float32 [S, M, N]: S partial sums over K that the consumer adds in order
         (a delta for the residual stream, or the input of a kernel that takes partial sums)."""

@@ -45,6 +45,11 @@ class GatedMLP(FeedForward):
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
+    def cost(self, q_lens, kv_lens):
+        T = sum(q_lens)
+        a, b = self.gate_up.cost(T), self.down.cost(T)
+        return a[0] + b[0], a[1] + b[1]
+
     can_sink = True        # forward() accepts sink=ResidualSink (see parts.base)
 
     def takes_deferred(self, batch) -> bool:

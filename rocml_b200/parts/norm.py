@@ -31,6 +31,8 @@ class RMSNorm(Norm):
         self.weight = tensors[f"{prefix}.weight"]
 
     def weight_bytes(self) -> int:
+        if self.weight is None:
+            return self.size * (4 if self.env.mode == "float32" else 2)
         return self.weight.numel() * self.weight.element_size()
 
     deferrable = True     # a product's epilogue can prepare this norm's input (see parts.base.DeferredNorm)
