@@ -204,8 +204,8 @@ def generate(executor: Executor, requests: Sequence[Request], default_stop: Iter
                 if emit:
                     s["out"].append(tok)
                     s["history"].append(tok)
-                    if on_token is not None and reason is None and on_token(s["i"], tok):
-                        reason = "stop"
+                    if on_token is not None and on_token(s["i"], tok) and reason is None:
+                        reason = "stop"       # the callback sees every emitted token; its answer ends a sequence that would go on
                 if reason is None:
                     s["next"] = [tok]
                     still.append(s)

@@ -15,6 +15,7 @@ The reference does the same with HIP event pairs around each operation of its fo
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -78,6 +79,8 @@ class StepRecord:
     ms: float = 0.0
     first_op: int = 0
     n_ops: int = 0
+    host_ms: float = 0.0      # what the host took to enqueue the step
+    gate_ms: float = 0.0      # how long the GPU was held back meanwhile; host_ms beyond it shows in the kernels' times
 
 
 @dataclass
@@ -88,7 +91,7 @@ class StepFacts:
 
 
 class Profiler:
-    def __init__(self, device="cuda:0", peaks: Optional[Peaks] = None, dtype: str = "bfloat16", gate_ms: float = 6.0):
+    def __init__(self, device="cuda:0", peaks: Optional[Peaks] = None, dtype: str = "bfloat16", gate_ms: float = 20.0):
         self.device = torch.device(device)
         self.peaks = peaks or load_peaks()
         self.dtype = dtype
@@ -101,6 +104,7 @@ class Profiler:
         self._depth = 0
         self._last_end = None
         self._last_end_launches = -1
+        self._host_ms: Dict[str, float] = {}      # per phase: the longest a step took to enqueue so far
 
     # ---- switching on and off ------------------------------------------------------------------
     def __enter__(self):
@@ -124,11 +128,15 @@ class Profiler:
         uses (the sampling around the model's pass) belong to the outermost."""
         return _Step(self, phase, list(q_lens), list(kv_lens))
 
-    def _gate(self):
-        # A spin of gate_ms on the stream: the host enqueues the step's launches meanwhile.
-        if self.gate_ms > 0 and self.device.type == "cuda":
-            khz = torch.cuda.get_device_properties(self.device).clock_rate
-            torch.cuda._sleep(int(self.gate_ms * khz))
+    def _gate(self, phase: str) -> float:
+        """A spin on the stream while the host enqueues the step's launches: gate_ms for the first step
+        of a phase, then one and a half times the longest enqueue seen (at most a second)."""
+        if self.gate_ms <= 0 or self.device.type != "cuda":
+            return 0.0
+        ms = min(1000.0, max(self.gate_ms, 1.5 * self._host_ms.get(phase, 0.0)))
+        khz = torch.cuda.get_device_properties(self.device).clock_rate
+        torch.cuda._sleep(int(ms * khz))
+        return ms
 
     # ---- a kernel ----------------------------------------------------------------------------------
     def begin(self):
@@ -187,7 +195,9 @@ class _Step:
             return None
         p.facts = StepFacts(self.q_lens, self.kv_lens)
         rec = StepRecord(self.phase, sum(self.q_lens), len(self.q_lens), first_op=len(p.ops))
-        p._gate()
+        p._last_end = None                      # the first kernel's time starts at the step, not at the last step's end
+        rec.gate_ms = p._gate(self.phase)
+        self._t0 = time.perf_counter()
         rec.start = torch.cuda.Event(enable_timing=True)
         rec.start.record()
         p._open_step = rec
@@ -201,6 +211,8 @@ class _Step:
         rec = p._open_step
         rec.end = torch.cuda.Event(enable_timing=True)
         rec.end.record()
+        rec.host_ms = (time.perf_counter() - self._t0) * 1e3
+        p._host_ms[rec.phase] = max(p._host_ms.get(rec.phase, 0.0), rec.host_ms)
         rec.n_ops = len(p.ops) - rec.first_op
         p.steps.append(rec)
         p._open_step = None

@@ -52,6 +52,9 @@ def build_report(prof) -> Dict:
         phases.append({
             "phase": phase, "steps": len(steps), "tokens": sum(s.n_tokens for s in steps),
             "step_ms": step_ms, "ops_ms": ops_ms, "between_kernels_ms": max(0.0, step_ms - ops_ms) if steps else 0.0,
+            # steps whose launches the host had not all enqueued when the GPU was let go: their
+            # kernels' times include the host's gaps
+            "host_bound_steps": sum(1 for s in steps if s.gate_ms > 0 and s.host_ms > s.gate_ms),
             "total": _row("(all)", recs, ops_ms, peaks, dtype),
             "by_op": sorted((_row(k, v, ops_ms, peaks, dtype) for k, v in by_op.items()),
                             key=lambda x: -x["elapsed_ms"]),
@@ -88,6 +91,9 @@ def to_human(report: Dict, layers: bool = False) -> str:
         out.append("")
         out.append(f"== {ph['phase']}: {ph['steps']} steps, {ph['tokens']} tokens, {ph['step_ms']:.3f} ms on the device, "
                    f"{ph['ops_ms']:.3f} ms in kernels, {ph['between_kernels_ms']:.3f} ms between them ==")
+        if ph.get("host_bound_steps"):
+            out.append(f"   ({ph['host_bound_steps']} of these steps took the host longer to enqueue than the GPU was "
+                       "held back: their kernels' times include launch gaps)")
         out.append("-- by kind of operation --")
         out += table(ph["by_op"] + [ph["total"]])
         if layers:

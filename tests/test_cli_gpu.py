@@ -39,7 +39,7 @@ def test_greedy_generation_equals_the_plain_implementation(tmp_path):
     write_random_model(folder, config_from_dict(entry.config), seed=4)     # what --random --seed-weights 4 writes
     ids = [5, 17, 3, 200, 41]
     want = PlainQwen3(folder, dtype=torch.float32).greedy(ids, 12)
-    stops = entry.config["eos_token_id"]
+    stops = entry.config.get("eos_token_id", [])
     stops = set(stops if isinstance(stops, list) else [stops])
     cut = next((i for i, t in enumerate(want) if t in stops), len(want))
     p = run("generate", "--model", "tiny-b", "--random", "--seed-weights", "4", "--dtype", "float32",

@@ -88,6 +88,10 @@ def test_ignore_eos_and_context_limit_and_callback():
     seen = []
     out = generate(ex, [Request([10], 100)], on_token=lambda i, t: seen.append((i, t)) or t == 12)
     assert out[0].tokens == [11, 12] and out[0].finish_reason == "stop" and seen == [(0, 11), (0, 12)]
+    # the callback sees every emitted token, the one that uses up the budget included
+    seen = []
+    out = generate(Scripted(), [Request([10], 3)], on_token=lambda i, t: seen.append(t) and False)
+    assert out[0].tokens == [11, 12, 13] == seen and out[0].finish_reason == "length"
 
 
 def test_one_batch_after_another_reuses_slots():
