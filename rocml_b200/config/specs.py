@@ -17,7 +17,18 @@ from typing import Any, Mapping, Optional, Tuple
 
 
 def _frozen_params(params: Optional[Mapping[str, Any]]) -> Tuple[Tuple[str, Any], ...]:
-    return tuple(sorted((params or {}).items()))
+    """Parameters as a sorted tuple of pairs; a mapping among the values (``names``) is frozen the same way."""
+    return tuple(sorted((k, _frozen_params(v) if isinstance(v, Mapping) else v) for k, v in (params or {}).items()))
+
+
+def tensor_names(params: Mapping[str, Any], defaults: Mapping[str, str]) -> dict:
+    """A part's tensor-name stems: ``defaults`` (role -> stem) overridden by the spec's ``names``
+    parameter.  A role the part does not know is an error: it would silently name nothing."""
+    given = dict(params.get("names") or ())
+    unknown = sorted(set(given) - set(defaults))
+    if unknown:
+        raise ValueError(f"names for unknown tensors {unknown}; this part has {sorted(defaults)}")
+    return {**defaults, **given}
 
 
 @dataclass(frozen=True)
@@ -53,7 +64,10 @@ class MixerSpec:
     Attention params: n_heads, n_kv_heads, head_dim, bias (q/k/v/o biases),
     qk_norm (per-head RMSNorm of q and k before the position encoding),
     qk_norm_eps, window (None: every earlier key; n: the last n keys, the
-    query's own position included), scale (None: 1/sqrt(head_dim)).
+    query's own position included), scale (None: 1/sqrt(head_dim)),
+    names (the tensor-name stems under the layer's mixer prefix, by role:
+    q, k, v, o, q_norm, k_norm; default q_proj, k_proj, v_proj, o_proj,
+    q_norm, k_norm).
     """
 
     kind: str
@@ -73,7 +87,9 @@ class MixerSpec:
 class FeedForwardSpec:
     """The feed-forward of a layer.  kind "gated_mlp": down(act(gate(x)) * up(x)).
 
-    gated_mlp params: intermediate, activation ("silu"), bias.
+    gated_mlp params: intermediate, activation ("silu"), bias, names (the
+    tensor-name stems under the layer's feed-forward prefix, by role: gate,
+    up, down; default gate_proj, up_proj, down_proj).
     """
 
     kind: str
@@ -93,7 +109,10 @@ class LayerSpec:
     """One layer: two norms, a mixer and a feed-forward in a named arrangement.
 
     arrangement "pre_norm": x += mixer(norm1(x)); x += ff(norm2(x)).
-    ``prefix`` is the layer's tensor-name prefix in the weight files.
+    ``prefix`` is the layer's tensor-name prefix in the weight files; under it the four parts'
+    tensors are named ``<prefix>.<mixer_norm_name>.weight``, ``<prefix>.<mixer_name><stem>...``,
+    ``<prefix>.<ff_norm_name>.weight`` and ``<prefix>.<ff_name><stem>...`` (the defaults are the
+    names of Hugging Face's Qwen3 checkpoints; another architecture gives its own).
     """
 
     prefix: str
@@ -102,6 +121,10 @@ class LayerSpec:
     mixer_norm: NormSpec
     ff_norm: NormSpec
     arrangement: str = "pre_norm"
+    mixer_norm_name: str = "input_layernorm"
+    mixer_name: str = "self_attn."
+    ff_norm_name: str = "post_attention_layernorm"
+    ff_name: str = "mlp."
 
 
 @dataclass(frozen=True)

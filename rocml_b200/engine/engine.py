@@ -13,6 +13,7 @@ a chunk of one prompt: chunk_forward.rs:62-189; the chunk loop: :33-53) and no b
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -54,22 +55,29 @@ def _ctx_bucket(n: int) -> int:
 
 class Engine:
     def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
-                 max_step_tokens: int = 4096, use_graphs: bool = True, max_seq_len: Optional[int] = None):
+                 max_step_tokens: int = 4096, use_graphs: bool = True, max_seq_len: Optional[int] = None,
+                 max_graphs: int = 8):
+        """``max_graphs``: how many captured decode graphs are kept (one per batch bucket and context
+        bucket, least recently used dropped first); each holds its own activations and logits."""
         self.model = model
         self.env = model.env
         self.device = model.env.device
         self.max_step_tokens = int(max_step_tokens)
+        if self.max_step_tokens < 1:
+            raise ConfigError("max_step_tokens must be at least 1")
+        self.max_graphs = max(1, int(max_graphs))
         max_tokens = int(max_tokens)
         if max_slots is None:
             max_slots = max(1, min((max_tokens + 63) // 64, 256))
-        self._check_budget(max_tokens)
+        self.use_graphs = bool(use_graphs) and model.graph_safe and self.device.type == "cuda"
+        self._check_budget(max_tokens, max_slots)
         self.cache = SequenceCache(
             model.cache_requirements(), model.reads_cache_of(), max_tokens, max_slots,
             min(model.spec.max_position, max_seq_len or model.spec.max_position), self.env.act_dtype,
             self.device, self.max_step_tokens)
-        self.use_graphs = bool(use_graphs) and model.graph_safe and self.device.type == "cuda"
         self._eager: Dict[Tuple[int, int], BatchBuffers] = {}
-        self._graphs: Dict[Tuple[int, int], dict] = {}
+        self._graphs: "OrderedDict[Tuple[int, int], dict]" = OrderedDict()
+        self.graphs_captured = 0
         self._pool = None
         self.launches = 0          # steps issued (sub-steps counted)
         self.last_h2d_bytes = 0
@@ -79,27 +87,39 @@ class Engine:
 
     # After the weights are resident: does the cache fit what is left, with head room for a step's
     # activations?  (The reference's check: rocml/src/forward/mod.rs:145-168, 768 MiB of head room,
-    # rocml/src/budget/mod.rs:37; a step of this engine is wider, so the head room scales with it.)
-    def _check_budget(self, max_tokens: int) -> None:
+    # rocml/src/budget/mod.rs:37.)  What a step needs is asked of the parts, so it holds for any
+    # arrangement: the widest step's buffers, one more set and its logits for every captured decode
+    # graph that may be kept, and the groups of fixed-size state.
+    def _check_budget(self, max_tokens: int, max_slots: int) -> None:
         if self.device.type != "cuda":
             return
-        reqs = [r for r, src in zip(self.model.cache_requirements(), self.model.reads_cache_of())
-                if src is None and hasattr(r, "n_kv_heads")]
         esz = 4 if self.env.act_dtype == torch.float32 else 2
-        per_token = sum(2 * r.n_kv_heads * r.head_dim * esz for r in reqs)
-        if per_token == 0:
-            return
-        widest = max([self.model.hidden] + [getattr(b.ff, "inter", 0) * 2 for b in self.model.blocks])
-        headroom = (768 << 20) + self.max_step_tokens * (widest * esz * 2 + self.model.hidden * 12)
+        per_token = state = 0
+        for r, src in zip(self.model.cache_requirements(), self.model.reads_cache_of()):
+            if src is not None or r is None:
+                continue
+            if hasattr(r, "n_kv_heads"):
+                per_token += 2 * r.n_kv_heads * r.head_dim * esz
+            elif hasattr(r, "shape"):
+                n = 1
+                for d in r.shape:
+                    n *= int(d)
+                state += n * torch.empty((), dtype=r.dtype).element_size() * max_slots
+        step = self.model.workspace_bytes(self.max_step_tokens, min(self.max_step_tokens, max_slots))
+        graphs = 0
+        if self.use_graphs:
+            graphs = self.max_graphs * self.model.workspace_bytes(_bucket(max_slots), _bucket(max_slots))
+        headroom = (768 << 20) + step + graphs
         free, total = torch.cuda.mem_get_info(self.device)
-        need = ((max_tokens + 63) // 64 * 64) * per_token
+        need = ((max_tokens + 63) // 64 * 64) * per_token + state
         if need + headroom > free:
             from ..errors import MemoryBudget
-            fit = max(0, (free - headroom) // per_token // 64 * 64)
+            fit = max(0, (free - headroom - state) // per_token // 64 * 64) if per_token else 0
             raise MemoryBudget(max_tokens, int(fit), (
-                f"{need / 2**30:.1f} GiB of keys and values ({per_token} bytes per token) + "
-                f"{headroom / 2**30:.1f} GiB head room for a step against {free / 2**30:.1f} GiB free of "
-                f"{total / 2**30:.1f} GiB"))
+                f"{need / 2**30:.1f} GiB of keys, values and state ({per_token} bytes per token) + "
+                f"{headroom / 2**30:.1f} GiB head room (a step of {self.max_step_tokens} tokens: {step / 2**30:.2f}, "
+                f"{self.max_graphs if self.use_graphs else 0} decode graphs: {graphs / 2**30:.2f}) against "
+                f"{free / 2**30:.1f} GiB free of {total / 2**30:.1f} GiB"))
 
     # ---- construction ----------------------------------------------------------------------------
     @staticmethod
@@ -262,8 +282,18 @@ class Engine:
         key = (b_pad, ctx_pad)
         g = self._graphs.get(key)
         if g is None:
+            while len(self._graphs) >= self.max_graphs:
+                # the least recently used bucket goes; its memory returns to the graphs' pool.  Work that
+                # is still queued may read it: wait before it is released.
+                _, old = self._graphs.popitem(last=False)
+                torch.cuda.current_stream().synchronize()
+                if old["graph"] is not None:
+                    old["graph"].reset()
+                old.clear()
             g = {"buffers": BatchBuffers(b_pad, b_pad, b_pad, self.device), "graph": None, "logits": None}
             self._graphs[key] = g
+        else:
+            self._graphs.move_to_end(key)
         buf: BatchBuffers = g["buffers"]
         buf.fill(*packed, host.seq_slots, pad_tokens=b_pad, pad_seqs=b_pad, pad_want=b_pad)
         if self._device_tokens is not None:
@@ -286,6 +316,7 @@ class Engine:
             if self._pool is None:
                 self._pool = graph.pool()
             g["graph"] = graph
+            self.graphs_captured += 1
             return out[:W] if W else None
         g["graph"].replay()
         self.graph_kernel_launches += g["kernels"]

@@ -100,6 +100,13 @@ class Model:
         n = sum(self.blocks[e.layer].weight_bytes() for e in self.spec.schedule)
         return n + self.final_norm.weight_bytes() + self.head.weight_bytes()
 
+    def workspace_bytes(self, n_tokens: int, n_want: int) -> int:
+        """Device memory a step of ``n_tokens`` tokens allocates besides weights and cache: the 32-bit
+        residual stream, the widest layer's buffers (asked of the parts: layers run one after another,
+        and a delta outlives its layer by one norm), and float32 logits for ``n_want`` rows."""
+        widest = max([getattr(b, "workspace_bytes", lambda n: 0)(n_tokens) for b in self.blocks] or [0])
+        return n_tokens * self.hidden * 4 * 2 + 2 * widest + n_want * (self.vocab * 4 + self.hidden * 4)
+
     def step_cost(self, q_lens, kv_lens, n_want: int):
         """(bytes, floating-point operations) a step has to move and do at least: every scheduled
         block's weights once and its products and attention over the given sequences (``q_lens`` new

@@ -18,7 +18,7 @@ import torch
 
 from .. import kernels
 from ..cache.requirements import KVRequirement
-from ..config.specs import MixerSpec
+from ..config.specs import MixerSpec, tensor_names
 from ..errors import ConfigError
 from ..weights.decl import TensorDecl
 from .base import BuildEnv, DeferredNorm, Mixer, build_position, register_mixer
@@ -29,6 +29,10 @@ from .linear import Linear
 # main loop, and the rotation kernel after a plain product is as fast or faster (measured at 1,024 and
 # 2,048 tokens against 4,096).
 PROMPT_FUSED_MIN_TOKENS = 4096
+
+# Tensor-name stems by role, unless the spec's ``names`` says otherwise (the defaults are those of
+# Hugging Face's Qwen3 checkpoints: rocml/src/weights/layer.rs:47-58 lists the same tensors under GGUF names).
+TENSOR_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm"}
 
 DECODE_CHUNK = 64   # keys per split of decode attention (one page); fixed, so a row's sums never depend on the batch
 
@@ -56,11 +60,15 @@ class Attention(Mixer):
         self.shares_cache = bool(p.get("shares_cache", False))  # set by the model for a reading layer
         self.position = build_position(spec.position, self.hd, env)
         qd, kvd = self.nq * self.hd, self.nkv * self.hd
+        try:
+            self.names = n = tensor_names(p, TENSOR_NAMES)
+        except ValueError as e:
+            raise ConfigError(f"attention: {e}") from None
         if self.shares_cache:
-            self.qkv = Linear(["q_proj"], [qd], hidden, self.bias, env)
+            self.qkv = Linear([n["q"]], [qd], hidden, self.bias, env)
         else:
-            self.qkv = Linear(["q_proj", "k_proj", "v_proj"], [qd, kvd, kvd], hidden, self.bias, env)
-        self.o = Linear(["o_proj"], [hidden], qd, self.bias, env)
+            self.qkv = Linear([n["q"], n["k"], n["v"]], [qd, kvd, kvd], hidden, self.bias, env)
+        self.o = Linear([n["o"]], [hidden], qd, self.bias, env)
         self.q_norm_w: Optional[torch.Tensor] = None
         self.k_norm_w: Optional[torch.Tensor] = None
 
@@ -70,22 +78,29 @@ class Attention(Mixer):
     def declare(self, prefix: str) -> List[TensorDecl]:
         out = self.qkv.declare(prefix) + self.o.declare(prefix)
         if self.qk_norm:
-            out.append(TensorDecl(f"{prefix}q_norm.weight", (self.hd,), "norm"))
+            out.append(TensorDecl(f"{prefix}{self.names['q_norm']}.weight", (self.hd,), "norm"))
             if not self.shares_cache:
-                out.append(TensorDecl(f"{prefix}k_norm.weight", (self.hd,), "norm"))
+                out.append(TensorDecl(f"{prefix}{self.names['k_norm']}.weight", (self.hd,), "norm"))
         return out
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         self.qkv.load(tensors, prefix)
         self.o.load(tensors, prefix)
         if self.qk_norm:
-            self.q_norm_w = tensors[f"{prefix}q_norm.weight"]
-            self.k_norm_w = self.q_norm_w if self.shares_cache else tensors[f"{prefix}k_norm.weight"]
+            self.q_norm_w = tensors[f"{prefix}{self.names['q_norm']}.weight"]
+            self.k_norm_w = self.q_norm_w if self.shares_cache else tensors[f"{prefix}{self.names['k_norm']}.weight"]
             if self.k_norm_w.dtype != self.q_norm_w.dtype:
                 self.q_norm_w, self.k_norm_w = self.q_norm_w.float(), self.k_norm_w.float()
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        """Projections, attention output and the delta (as partial sums: up to 8 of each for few tokens)."""
+        esz = 4 if self.env.mode == "float32" else 2
+        parts = 8 if n_tokens <= 128 else 1
+        return n_tokens * (self.qkv.n * max(esz, 4 * parts if parts > 1 else esz) + 2 * self.nq * self.hd * esz
+                           + self.hidden * 4 * parts + self.nq * 4 * (self.hd + 2) * (parts if parts > 1 else 0))
 
     def cost(self, q_lens, kv_lens):
         from ..profile import cost as C

@@ -87,6 +87,11 @@ class Part:
         """Bytes of weights one forward pass reads (for the roofline)."""
         return 0
 
+    def workspace_bytes(self, n_tokens: int) -> int:
+        """Device memory one forward pass over ``n_tokens`` tokens allocates for its intermediate and
+        its result (the engine sizes its head room with it)."""
+        return 0
+
     def cost(self, q_lens, kv_lens):
         """(bytes, floating-point operations) one forward pass has to move and do at least, for
         sequences that bring ``q_lens`` tokens and are ``kv_lens`` long afterwards.  The default

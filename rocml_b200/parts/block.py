@@ -34,10 +34,10 @@ class PreNormBlock:
         self.ff_norm = build_norm(spec.ff_norm, hidden, env)
         self.ff = build_feed_forward(spec.feed_forward, hidden, env)
 
-    # Tensor names of the Hugging Face layout: norms beside the parts they precede.
+    # The four parts' tensor-name prefixes, as the layer's spec gives them.
     def _names(self):
-        p = self.prefix
-        return (f"{p}.input_layernorm", f"{p}.self_attn.", f"{p}.post_attention_layernorm", f"{p}.mlp.")
+        p, s = self.prefix, self.spec
+        return (f"{p}.{s.mixer_norm_name}", f"{p}.{s.mixer_name}", f"{p}.{s.ff_norm_name}", f"{p}.{s.ff_name}")
 
     def declare(self) -> List[TensorDecl]:
         n1, mx, n2, ff = self._names()
@@ -56,6 +56,11 @@ class PreNormBlock:
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff))
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        """Each half of the layer holds its norm's rows and its part's buffers; the halves follow one another."""
+        return max(self.mixer_norm.workspace_bytes(n_tokens) + self.mixer.workspace_bytes(n_tokens),
+                   self.ff_norm.workspace_bytes(n_tokens) + self.ff.workspace_bytes(n_tokens))
 
     def cost(self, q_lens, kv_lens):
         parts = [p.cost(q_lens, kv_lens) for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff)]

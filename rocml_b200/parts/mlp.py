@@ -6,11 +6,15 @@ from typing import Dict, List
 import torch
 
 from .. import kernels
-from ..config.specs import FeedForwardSpec
+from ..config.specs import FeedForwardSpec, tensor_names
 from ..errors import ConfigError
 from ..weights.decl import TensorDecl
 from .base import BuildEnv, DeferredNorm, FeedForward, register_feed_forward
 from .linear import GATED_PAIR_MAX_ROWS, Linear
+
+
+# Tensor-name stems by role, unless the spec's ``names`` says otherwise (rocml/src/weights/layer.rs:59-62).
+TENSOR_NAMES = {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
 
 
 @register_feed_forward("gated_mlp")
@@ -30,8 +34,12 @@ class GatedMLP(FeedForward):
         if act != "silu":
             raise ConfigError(f"activation {act!r} is not built (only 'silu')")
         bias = bool(p.get("bias", False))
-        self.gate_up = Linear(["gate_proj", "up_proj"], [self.inter, self.inter], hidden, bias, env)
-        self.down = Linear(["down_proj"], [hidden], self.inter, bias, env)
+        try:
+            n = tensor_names(p, TENSOR_NAMES)
+        except ValueError as e:
+            raise ConfigError(f"gated_mlp: {e}") from None
+        self.gate_up = Linear([n["gate"], n["up"]], [self.inter, self.inter], hidden, bias, env)
+        self.down = Linear([n["down"]], [hidden], self.inter, bias, env)
 
     def declare(self, prefix: str) -> List[TensorDecl]:
         return self.gate_up.declare(prefix) + self.down.declare(prefix)
@@ -44,6 +52,12 @@ class GatedMLP(FeedForward):
 
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        """gate | up, their gated product and the delta (as partial sums: up to 8 of each for few tokens)."""
+        esz = 4 if self.env.mode == "float32" else 2
+        parts = 8 if n_tokens <= 128 else 1
+        return n_tokens * (2 * self.inter * (4 * parts if parts > 1 else esz) + self.inter * esz + self.hidden * 4 * parts)
 
     def cost(self, q_lens, kv_lens):
         T = sum(q_lens)

@@ -35,6 +35,9 @@ class RMSNorm(Norm):
             return self.size * (4 if self.env.mode == "float32" else 2)
         return self.weight.numel() * self.weight.element_size()
 
+    def workspace_bytes(self, n_tokens: int) -> int:
+        return n_tokens * self.size * (4 if self.env.mode == "float32" else 2)
+
     deferrable = True     # a product's epilogue can prepare this norm's input (see parts.base.DeferredNorm)
 
     def forward(self, resid, delta, n_rows: Optional[int] = None, rows=None, write_back=True):

@@ -2,8 +2,11 @@
 
 The model declares the tensors it needs (``TensorDecl``); the loader checks the
 whole folder against the declaration first and raises ONE ``WeightsError`` that
-lists every missing tensor, every unexpected tensor and every wrong shape, then
-moves the tensors to the device under the storage rule:
+lists every missing tensor, every unexpected tensor and every wrong shape.  A
+folder whose only fault is tensors the model does not read (checkpoints often
+carry a few: rotary tables, training leftovers) is loaded with one warning that
+names them; ``strict=True`` makes that an error too.  Then the tensors move to
+the device under the storage rule:
 
 * ``bfloat16`` mode: floating tensors are kept in bfloat16 (float16 is converted);
   a tensor the file stores in 32-bit stays 32-bit; integer tables become int32.
@@ -15,6 +18,7 @@ shape, convert, upload (rocml/src/weights/mod.rs:37-175, weights/layer.rs:34-64)
 """
 from __future__ import annotations
 
+import warnings
 from typing import Callable, Dict, Iterable, Sequence
 
 import torch
@@ -39,9 +43,14 @@ def storage_dtype(file_dtype: torch.dtype, mode: str, role: str) -> torch.dtype:
     return torch.bfloat16
 
 
+class UnexpectedTensors(UserWarning):
+    """A model folder holds tensors that the model does not read."""
+
+
 def check_against(decls: Sequence[TensorDecl], names: Iterable[str], shape_of: Callable[[str], tuple],
-                  ignorable: Iterable[str] = ()) -> None:
-    """Raise one WeightsError listing everything that does not fit."""
+                  ignorable: Iterable[str] = (), strict: bool = False) -> None:
+    """Raise one WeightsError listing everything that does not fit.  Unexpected tensors alone are a
+    warning unless ``strict``."""
     have = set(names)
     want = {d.name: d for d in decls}
     ignorable = set(ignorable)
@@ -51,15 +60,18 @@ def check_against(decls: Sequence[TensorDecl], names: Iterable[str], shape_of: C
     for n, d in want.items():
         if n in have and tuple(shape_of(n)) != tuple(d.shape):
             wrong.append((n, tuple(d.shape), tuple(shape_of(n))))
-    if missing or unexpected or wrong:
+    if missing or wrong or (unexpected and strict):
         raise WeightsError(missing, unexpected, sorted(wrong))
+    if unexpected:
+        shown = ", ".join(unexpected[:8]) + (f", ... ({len(unexpected)} in all)" if len(unexpected) > 8 else "")
+        warnings.warn(f"the folder holds tensors the model does not read: {shown}", UnexpectedTensors, stacklevel=3)
 
 
 def load_tensors(folder: str, decls: Sequence[TensorDecl], mode: str, device,
-                 ignorable: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
+                 ignorable: Iterable[str] = (), strict: bool = False) -> Dict[str, torch.Tensor]:
     """name -> device tensor for every declared tensor of the folder."""
     with ModelFiles(folder) as files:
-        check_against(decls, files.names(), files.shape, ignorable)
+        check_against(decls, files.names(), files.shape, ignorable, strict)
         bad_dtype = []
         for d in decls:
             ft = files.dtype(d.name)

@@ -105,3 +105,31 @@ def test_generation_config_adds_stop_tokens(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(TINY_A))
     (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [7, 11]}))
     assert load_model_spec(str(tmp_path)).stop_tokens == (7, 11)
+
+
+def test_tensor_names_come_from_the_spec():
+    """The parts name their tensors by role; the stems and the four prefixes of a layer are the spec's.
+    The defaults are the names of Qwen3's checkpoints; another architecture gives its own."""
+    import torch
+    from rocml_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry
+    from rocml_b200.engine.model import declared_tensors
+    from rocml_b200.errors import ConfigError
+    norm = NormSpec("rmsnorm", 1e-5)
+    att = MixerSpec.make("attention", position=PositionSpec("none"), n_heads=2, n_kv_heads=1, head_dim=16, qk_norm=True,
+                         names={"q": "wq", "k": "wk", "v": "wv", "o": "wo", "q_norm": "qn"})
+    ff = FeedForwardSpec.make("gated_mlp", intermediate=32, names={"gate": "w1", "up": "w3", "down": "w2"})
+    layer = LayerSpec("blk.0", att, ff, norm, norm, mixer_norm_name="attn_norm", mixer_name="attn.",
+                      ff_norm_name="ffn_norm", ff_name="ffn.")
+    spec = ModelSpec("Other", 24, 50, 64, (layer,), (ScheduleEntry(0),), norm, tie_embeddings=False,
+                     embedding_name="tok.weight", final_norm_name="out_norm.weight", head_name="out.weight")
+    got = sorted(d.name for d in declared_tensors(spec))
+    assert got == sorted([
+        "tok.weight", "out_norm.weight", "out.weight", "blk.0.attn_norm.weight", "blk.0.ffn_norm.weight",
+        "blk.0.attn.wq.weight", "blk.0.attn.wk.weight", "blk.0.attn.wv.weight", "blk.0.attn.wo.weight",
+        "blk.0.attn.qn.weight", "blk.0.attn.k_norm.weight",
+        "blk.0.ffn.w1.weight", "blk.0.ffn.w3.weight", "blk.0.ffn.w2.weight"])
+    hash(att), hash(layer)        # specs stay hashable with a names map inside
+    bad = MixerSpec.make("attention", n_heads=2, n_kv_heads=1, head_dim=16, names={"query": "wq"})
+    with pytest.raises(ConfigError, match="query"):
+        declared_tensors(ModelSpec("Other", 24, 50, 64, (LayerSpec("blk.0", bad, ff, norm, norm),), (ScheduleEntry(0),),
+                                   norm, tie_embeddings=True))

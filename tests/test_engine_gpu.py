@@ -279,3 +279,31 @@ def test_prompts_add_into_the_residual_inside_the_products(tmp_path, monkeypatch
         assert calls["add"] == (2 * DEFER_CFG["num_hidden_layers"] if defer == "1" else 0)
     assert rel_err(got["1"], got["0"].double()) < TOL["bfloat16"]
     kernels.check_status("cuda:0")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_graphs_are_bounded(tmp_path, monkeypatch, dtype):
+    """Decode graphs are kept per context bucket; only ``max_graphs`` of them stay, the least recently
+    used goes first, and a bucket that was dropped is captured again when a sequence comes back to it.
+    Buckets of 32 tokens here, so that a sequence of 290 tokens crosses ten of them with a cap of 3;
+    every logit row is compared with the plain implementation."""
+    from plain_qwen3 import PlainQwen3
+    from rocml_b200 import Engine, StepEntry
+    from rocml_b200.engine import engine as engine_module
+    folder = str(tmp_path / "m")
+    write_model(folder, CONFIGS["D"], seed=61, std=0.05)
+    plain = PlainQwen3(folder, dtype=torch.float64)
+    monkeypatch.setattr(engine_module, "_ctx_bucket", lambda n: max(32, -(-n // 32) * 32))
+    vocab = CONFIGS["D"]["vocab_size"]
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024, max_slots=2, max_graphs=3)
+    for round_ in range(2):              # the second sequence starts again in the first, dropped, bucket
+        ids = prompt(300 + round_, 290, vocab)
+        want = plain.logits(ids)
+        slot = eng.new_sequence()
+        got = []
+        for t, tok in enumerate(ids):
+            got.append(eng.step([StepEntry(slot, [tok], [0])]).clone())
+            assert len(eng._graphs) <= 3
+        eng.release(slot)
+        assert rel_err(torch.cat(got), want) < TOL[dtype]
+    assert eng.graphs_captured == 20 and list(eng._graphs) == [(1, 224), (1, 256), (1, 288)]

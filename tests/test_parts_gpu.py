@@ -226,12 +226,18 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps():
 
     H, V, W = 48, 77, 12
     norm = NormSpec("rmsnorm", 1e-6)
+    # the tensors' names come from the spec alone: the parts know no names of their own
     layer = LayerSpec("model.layers.0", MixerSpec.make("toy_running_sum", width=W),
-                      FeedForwardSpec.make("gated_mlp", intermediate=64, activation="silu"), norm, norm)
+                      FeedForwardSpec.make("gated_mlp", intermediate=64, activation="silu",
+                                           names={"gate": "w1", "up": "w3", "down": "w2"}), norm, norm,
+                      mixer_norm_name="ln_mix", mixer_name="mix.", ff_norm_name="ln_ff", ff_name="ffn.")
     spec = ModelSpec("ToyState", H, V, 128, (layer,), (ScheduleEntry(0),), norm, tie_embeddings=True)
     model = Model(spec, env(torch.float32))
     assert not model.graph_safe
     tensors = {d.name: random_tensor(d, 5).float() * (3.0 if d.role == "matrix" else 1.0) for d in model.declare()}
+    assert sorted(tensors) == sorted(
+        ["model.embed_tokens.weight", "model.norm.weight"] + [f"model.layers.0.{n}.weight" for n in (
+            "ln_mix", "mix.in", "mix.out", "ln_ff", "ffn.w1", "ffn.w3", "ffn.w2")])
     model.load({k: v.to(DEV) for k, v in tensors.items()})
     eng = Engine(model, max_tokens=256, max_slots=2)
     assert not eng.use_graphs and len(eng.cache.state_groups) == 1 and not eng.cache.kv_groups
@@ -240,12 +246,12 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps():
 
     def plain(ids):
         x = w["model.embed_tokens.weight"][ids]
-        xn = P.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
-        u = torch.cumsum(xn @ w["model.layers.0.self_attn.in.weight"].t(), 0)
-        x = x + u @ w["model.layers.0.self_attn.out.weight"].t()
-        xn = P.rmsnorm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-6)
-        x = x + P.linear(P.silu_mul(P.linear(xn, w["model.layers.0.mlp.gate_proj.weight"]),
-                                    P.linear(xn, w["model.layers.0.mlp.up_proj.weight"])), w["model.layers.0.mlp.down_proj.weight"])
+        xn = P.rmsnorm(x, w["model.layers.0.ln_mix.weight"], 1e-6)
+        u = torch.cumsum(xn @ w["model.layers.0.mix.in.weight"].t(), 0)
+        x = x + u @ w["model.layers.0.mix.out.weight"].t()
+        xn = P.rmsnorm(x, w["model.layers.0.ln_ff.weight"], 1e-6)
+        x = x + P.linear(P.silu_mul(P.linear(xn, w["model.layers.0.ffn.w1.weight"]),
+                                    P.linear(xn, w["model.layers.0.ffn.w3.weight"])), w["model.layers.0.ffn.w2.weight"])
         return P.linear(P.rmsnorm(x, w["model.norm.weight"], 1e-6), w["model.embed_tokens.weight"])
 
     for rnd_i in range(2):   # the second round meets the slots (and their state) of the first again

@@ -96,9 +96,32 @@ def test_tied_head_may_be_present_and_is_ignored(tmp_path):
     save_file(w, path)
     decls = declared_tensors(cfg.to_model_spec())
     with pytest.raises(WeightsError):
-        load_tensors(folder, decls, "bfloat16", "cpu")
-    out = load_tensors(folder, decls, "bfloat16", "cpu", ignorable=["lm_head.weight"])
+        load_tensors(folder, decls, "bfloat16", "cpu", strict=True)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")              # ignorable: not even a warning
+        out = load_tensors(folder, decls, "bfloat16", "cpu", ignorable=["lm_head.weight"], strict=True)
     assert "lm_head.weight" not in out
+
+
+def test_extra_tensors_alone_are_a_warning_that_names_them(tmp_path):
+    """A checkpoint with tensors the model does not read (a rotary table, say) loads, with one warning;
+    strict loading refuses it; and a folder that also lacks a tensor is refused with both listed."""
+    from safetensors.torch import load_file, save_file
+    from rocml_b200.weights.loader import UnexpectedTensors
+    cfg = config_from_dict(TINY_A)
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=1)
+    path = os.path.join(folder, "model.safetensors")
+    w = load_file(path)
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    save_file(w, path)
+    decls = declared_tensors(cfg.to_model_spec())
+    with pytest.warns(UnexpectedTensors, match="rotary_emb.inv_freq"):
+        out = load_tensors(folder, decls, "bfloat16", "cpu")
+    assert "model.layers.0.self_attn.rotary_emb.inv_freq" not in out and len(out) == len(decls)
+    with pytest.raises(WeightsError) as e:
+        load_tensors(folder, decls, "bfloat16", "cpu", strict=True)
+    assert e.value.unexpected == ("model.layers.0.self_attn.rotary_emb.inv_freq",) and not e.value.missing
 
 
 def test_storage_rule():
