@@ -306,4 +306,4 @@ def test_captured_decode_graphs_are_bounded(tmp_path, monkeypatch, dtype):
             assert len(eng._graphs) <= 3
         eng.release(slot)
         assert rel_err(torch.cat(got), want) < TOL[dtype]
-    assert eng.graphs_captured == 20 and list(eng._graphs) == [(1, 224), (1, 256), (1, 288)]
+    assert eng.graphs_captured == 20 and list(eng._graphs) == [(1, 256), (1, 288), (1, 320)]
