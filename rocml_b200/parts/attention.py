@@ -20,6 +20,7 @@ from .. import kernels
 from ..cache.requirements import KVRequirement
 from ..config.specs import MixerSpec, tensor_names
 from ..errors import ConfigError
+from ..profile import scope
 from ..weights.decl import TensorDecl
 from .base import BuildEnv, DeferredNorm, Mixer, build_position, register_mixer
 from .linear import Linear
@@ -171,11 +172,13 @@ class Attention(Mixer):
         if T < PROMPT_FUSED_MIN_TOKENS:
             return False
         q = torch.empty((T, self.nq * self.hd), dtype=torch.bfloat16, device=xn.device)
-        if not kernels.gemm_tcgen05_qkv_rope(
-                xn, self.qkv.weight, q, self.nq, self.nkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
-                self.position.cos_sin(batch) if rot else None, batch.positions, batch.slot_of_token,
-                view.block_table, view.k, view.v, self.qkv.bias, T):
-            return False
+        cos_sin = self.position.cos_sin(batch) if rot else None
+        with scope(op=self.qkv.label):
+            if not kernels.gemm_tcgen05_qkv_rope(
+                    xn, self.qkv.weight, q, self.nq, self.nkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+                    cos_sin, batch.positions, batch.slot_of_token,
+                    view.block_table, view.k, view.v, self.qkv.bias, T):
+                return False
         self.attend(q, out, batch, view, window)
         return True
 
