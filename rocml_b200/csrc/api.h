@@ -29,6 +29,11 @@ int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, 
 int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, void* out,
                     int out_dtype, int M, int N, int K, long long ldx, long long ldo, void* stream);
 
+// The limit, in clock cycles, of every barrier wait in the tensor-core products (cycles <= 0: the default,
+// about two seconds), and a switch for tests of the give-up path: while it is set a few-token product
+// never requests its first K block, so the warp that waits for it runs into the limit, records
+// RB_ERR_TIMEOUT in the status word and the block unwinds.
+void rb_gemm_tcgen05_set_wait(long long cycles, int withhold_first_stage);
 int rb_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M, int N,
                     int K, long long ldx, long long ldo, int splits, long long split_stride, int stages,
                     int gated, int* status, void* stream);

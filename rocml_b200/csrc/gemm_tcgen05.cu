@@ -51,6 +51,8 @@ struct Params {
     const float* bias;            // [features] or null; added by split 0 only
     int* status;
     int stages;                   // depth of the shared-memory ring actually used (<= Cfg::STAGES)
+    long long wait_cycles;        // after this many clock cycles a wait on a barrier gives up
+    int withhold;                 // tests only: the first stage's copies are never issued, so its barrier never completes
     // CS >= 4 (the product is added into the residual stream, see the kernel):
     float* resid;                 // [tokens][features] float32, updated in place
     long long resid_ld;
@@ -157,6 +159,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    int issued = 0;                   // K blocks whose copies the producer thread has requested
     if (warp == 0) {
         if (lane == 0) {
             tma_prefetch_desc(&map_a);
@@ -165,24 +168,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // requested at once, then the predecessor's results are waited for, then the
             // activations' tiles follow.
             const int pre = n_kb < S ? n_kb : S;
-            for (int kb = 0; kb < pre; ++kb) {
+            // p.withhold (tests only): nothing is requested for the first stage, so nothing is in flight
+            // for it and its barrier never completes: the warp that waits for it must give up
+            const int kb0 = (CS == 0 && p.withhold) ? 1 : 0;      // only the plain kernel honours the switch
+            for (int kb = kb0; kb < pre; ++kb) {
                 uint8_t* sa = smem + kb * C::STAGE;
                 mbar_arrive_expect_tx(&full[kb], C::A_BYTES + C::B_BYTES);
                 if (SWAP) tma_load_2d(sa, &map_a, k_begin + kb * BK, a0, &full[kb]);
                 else tma_load_2d(sa + C::A_BYTES, &map_b, k_begin + kb * BK, b0, &full[kb]);
             }
             rb::pdl_wait();
-            for (int kb = 0; kb < pre; ++kb) {
+            for (int kb = kb0; kb < pre; ++kb) {
                 uint8_t* sa = smem + kb * C::STAGE;
                 if (SWAP) tma_load_2d(sa + C::A_BYTES, &map_b, k_begin + kb * BK, b0, &full[kb]);
                 else tma_load_2d(sa, &map_a, k_begin + kb * BK, a0, &full[kb]);
             }
-            int issued = pre;
+            issued = pre;
             bool ok = true;
             for (int kb = pre; kb < n_kb && ok; ++kb) {
                 const int s = kb % S;
                 const uint32_t ph = (kb / S) & 1;
-                ok = mbar_wait(&empty[s], ph ^ 1);
+                ok = mbar_wait(&empty[s], ph ^ 1, p.wait_cycles);
                 if (!ok) break;
                 uint8_t* sa = smem + s * C::STAGE;
                 mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
@@ -193,10 +199,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) {
                 atomicExch(p.status, RB_ERR_TIMEOUT);
                 atomicExch(abort_flag, 1u);
-                // wait (bounded) for the copies this thread still has in flight
-                const int first = issued > S ? issued - S : 0;
-                for (int kb = first; kb < issued; ++kb)
-                    mbar_wait(&full[kb % S], (kb / S) & 1);
             }
         }
     } else if (warp == 1) {
@@ -206,7 +208,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int kb = 0; kb < n_kb; ++kb) {
                 const int s = kb % S;
                 const uint32_t ph = (kb / S) & 1;
-                ok = mbar_wait(&full[s], ph);
+                ok = mbar_wait(&full[s], ph, p.wait_cycles);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sa = smem_u32(smem + s * C::STAGE);
@@ -228,7 +230,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // epilogue warps 2..5: warp w may read TMEM lanes 32 * (w % 4) .. + 31
         const int quarter = warp & 3;
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0));  // warp-uniform
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0, p.wait_cycles));  // warp-uniform
         tc_fence_after();
         const bool aborted = !ok || *(volatile uint32_t*)abort_flag != 0;
         if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
@@ -440,6 +442,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
+    if (warp == 0 && lane == 0 && *(volatile uint32_t*)abort_flag != 0) {
+        // Somebody gave up.  Before the block leaves, the producer waits (bounded) for the copies it
+        // still has in flight into this block's shared memory: the last S it requested.
+        const int first = issued > S ? issued - S : 0;
+        for (int kb = first; kb < issued; ++kb)
+            if (!(CS == 0 && p.withhold && kb == 0)) mbar_wait(&full[kb % S], (kb / S) & 1, p.wait_cycles);
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -502,7 +511,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = (int)(it % S);
                     const uint32_t ph = (uint32_t)((it / S) & 1);
-                    ok = mbar_wait(&empty[s], ph ^ 1);
+                    ok = mbar_wait(&empty[s], ph ^ 1, p.wait_cycles);
                     if (!ok) break;
                     uint8_t* sa = smem + s * C::STAGE;
                     mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
@@ -527,7 +536,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 atomicExch(p.status, RB_ERR_TIMEOUT);
                 atomicExch(abort_flag, 1u);
                 const long long first = it > S ? it - S : 0;
-                for (long long j = first; j < it; ++j) mbar_wait(&full[(int)(j % S)], (uint32_t)((j / S) & 1));
+                for (long long j = first; j < it; ++j) mbar_wait(&full[(int)(j % S)], (uint32_t)((j / S) & 1), p.wait_cycles);
             }
         }
     } else if (warp == 1) {
@@ -539,13 +548,13 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x, ++local) {
                 const int acc = local & 1;
                 const uint32_t use = (uint32_t)(local >> 1);
-                ok = mbar_wait(&acc_empty[acc], (use & 1) ^ 1);    // the epilogue has drained this accumulator
+                ok = mbar_wait(&acc_empty[acc], (use & 1) ^ 1, p.wait_cycles);    // the epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * C::TMEM_COLS;
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = (int)(it % S);
-                    ok = mbar_wait(&full[s], (uint32_t)((it / S) & 1));
+                    ok = mbar_wait(&full[s], (uint32_t)((it / S) & 1), p.wait_cycles);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * C::STAGE);
@@ -572,7 +581,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         for (int tile = blockIdx.x; tile < n_total; tile += gridDim.x, ++local) {
             const int acc = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], use & 1));
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], use & 1, p.wait_cycles));
             tc_fence_after();
             if (!ok || *(volatile uint32_t*)abort_flag != 0) {
                 if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
@@ -714,7 +723,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const int b0 = (tile / m_pairs) * BN + (int)rank * (BN / 2);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = (int)(it % S);
-                    ok = mbar_wait(&empty[s], (uint32_t)(((it / S) & 1) ^ 1));
+                    ok = mbar_wait(&empty[s], (uint32_t)(((it / S) & 1) ^ 1), p.wait_cycles);
                     if (!ok) break;
                     uint8_t* sa = smem + s * PAIR_STAGE;
                     const uint32_t bar = smem_u32(&full[s]) & PEER_BIT_MASK;   // the leader's barrier
@@ -737,13 +746,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int tile = pair; tile < n_total && ok; tile += n_pairs, ++local) {
                 const int acc = local & 1;
                 const uint32_t use = (uint32_t)(local >> 1);
-                ok = mbar_wait(&acc_empty[acc], (use & 1) ^ 1);
+                ok = mbar_wait(&acc_empty[acc], (use & 1) ^ 1, p.wait_cycles);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = (int)(it % S);
-                    ok = mbar_wait(&full[s], (uint32_t)((it / S) & 1));
+                    ok = mbar_wait(&full[s], (uint32_t)((it / S) & 1), p.wait_cycles);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * PAIR_STAGE);
@@ -770,7 +779,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int tile = pair; tile < n_total; tile += n_pairs, ++local) {
             const int acc = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], use & 1));
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], use & 1, p.wait_cycles));
             tc_fence_after();
             if (!ok || *(volatile uint32_t*)abort_flag != 0) {
                 if (!ok && lane == 0) atomicExch(p.status, RB_ERR_TIMEOUT);
@@ -1148,6 +1157,20 @@ struct ResidualOut {
     float* sumsq; long long sumsq_ld;
 };
 
+// The limit of every wait in the kernels of this file, and the tests' switch (see Params); both are
+// read when a launch is prepared.
+static long long g_wait_cycles = RB_WAIT_CYCLES;
+static int g_withhold = 0;
+
+// cycles <= 0 restores the default (about two seconds).  withhold_first_stage != 0 makes the next
+// few-token products (at most 128 rows, one split, plain epilogue) skip the copies of their first K
+// block, so that the warp that waits for them runs into the limit: for tests of the give-up path,
+// with a limit of microseconds.  It computes nothing useful while set.
+extern "C" void rb_gemm_tcgen05_set_wait(long long cycles, int withhold_first_stage) {
+    g_wait_cycles = cycles > 0 ? cycles : RB_WAIT_CYCLES;
+    g_withhold = withhold_first_stage ? 1 : 0;
+}
+
 static int gemm_entry(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
                       int N, int K, long long ldx, long long ldo, int splits, long long split_stride,
                       int stages, int gated, int* status, void* stream, int cluster_split,
@@ -1173,6 +1196,8 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
     p.bias = bias;
     p.status = status;
     p.stages = stages;   // 0: the default of the mode
+    p.wait_cycles = g_wait_cycles;
+    p.withhold = g_withhold;
     CUtensorMap ma, mb;
     int rc;
     if (swap) {

@@ -1,9 +1,10 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) pieces the kernels use: mbarriers with
 // bounded waits, TMA tile loads, tensor memory (TMEM) allocation, tcgen05.mma / commit / ld.
 //
-// Every wait is bounded: after `RB_WAIT_CYCLES` clock cycles (about two seconds) it gives up and returns false, and the
-// caller records RB_ERR_TIMEOUT in a status word and unwinds (waits for its own copies, frees
-// TMEM, returns).  Nothing here traps or spins without limit.
+// Every wait is bounded: after a limit of clock cycles (`RB_WAIT_CYCLES`, about two seconds, unless the
+// launch names another) it gives up and returns false, and the caller records RB_ERR_TIMEOUT in a
+// status word and unwinds (waits for its own copies, frees TMEM, returns).  Nothing here traps or
+// spins without limit.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -62,11 +63,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Wait for the phase with the given parity to complete; false if the time limit ran out.
 // The limit is counted in SM clock cycles (cheap to read, unlike %globaltimer, whose read costs
 // about a microsecond and would sit in every pipeline step).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = RB_WAIT_CYCLES) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > RB_WAIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
     return true;
 }

@@ -153,6 +153,8 @@ def _lib():
                                                  _vp, _i, _f, _vp, _i, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_residual.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _ll, _vp, _i, _vp, _ll, _vp,
                                                  _ll, _i, _vp, _vp]
+        lib.rb_gemm_tcgen05_set_wait.argtypes = [_ll, _i]
+        lib.rb_gemm_tcgen05_set_wait.restype = None
         _sigs_done = True
     return lib
 
@@ -593,6 +595,15 @@ def check_status(device) -> None:
     key = torch.device(device).index or 0
     if key in _status:
         raise_for_status(int(_status[key].item()), device)
+
+
+def set_wait_limit(cycles: int = 0, withhold_first_stage: bool = False) -> None:
+    """How long (in clock cycles; 0 restores the default of about two seconds) a warp of the tensor-core
+    products waits on a barrier before it gives up, records the failure in the status word and lets
+    its block unwind.  ``withhold_first_stage`` is for tests of that path only: few-token products then
+    never request their first K block, so the wait for it must run out (with a limit of microseconds
+    this takes microseconds and leaves the device usable); they compute nothing useful while it is set."""
+    _lib().rb_gemm_tcgen05_set_wait(int(cycles), 1 if withhold_first_stage else 0)
 
 
 @_profiled(lambda a, facts: (_cost.gated_linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, _esz(a["out"])) if a["gated"] else

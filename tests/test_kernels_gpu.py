@@ -659,3 +659,42 @@ def test_qk_norm_rope_cache(dtype, wd, nq, nkv, hd, rot):
                                positions.to(DEV), slots.to(DEV), table.to(DEV), kc2, vc2)
     assert (q2[:8].cpu().double().reshape(8, nq, hd) - q[:8]).abs().max() < tol
     assert (kc2.cpu().double() - kc.cpu().double()).abs().max() < tol and torch.equal(vc2, vc)
+
+
+# ---- a bounded wait that runs out ------------------------------------------------------------------------
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """Every barrier wait in the tensor-core kernels has a limit.  Here one runs out: a one-block
+    product (8 x 128 x 128) is launched with a limit of 100,000 cycles (tens of microseconds) and
+    with its first K block never requested, so the warp that waits for that block gives up.  The
+    kernel must record the failure in the status word, let the block unwind (the producer waits for
+    the copies it did request, tensor memory is freed) and return; the host raises KernelError and
+    clears the word; and the same launch without the switch then gives the right product, which
+    shows that the device was left clean.  Nothing traps and nothing spins without limit."""
+    from rocml_b200 import kernels
+    from rocml_b200.errors import KernelError
+    M, N, K = 8, 128, 128
+    x = rnd((M, K), 1, torch.bfloat16).to(DEV)
+    w = rnd((N, K), 2, torch.bfloat16).to(DEV)
+    want = x.cpu().double() @ w.cpu().double().t()
+    kernels.check_status(DEV)                       # clean before
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.set_wait_limit(100_000, withhold_first_stage=True)
+    try:
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        assert kernels.gemm_tcgen05(x, w, out)
+        t1.record()
+        torch.cuda.synchronize()
+    finally:
+        kernels.set_wait_limit(0, False)
+    assert t0.elapsed_time(t1) < 50.0               # milliseconds: it gave up at its limit, not at two seconds
+    assert torch.isnan(out).all()                   # an abandoned product writes nothing
+    with pytest.raises(KernelError, match="bounded wait"):
+        kernels.check_status(DEV)
+    kernels.check_status(DEV)                       # reading it cleared it
+    for _ in range(2):                              # the same launch, as often as one likes
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        assert kernels.gemm_tcgen05(x, w, out)
+        kernels.check_status(DEV)
+        assert (out.cpu().double() - want).abs().max().item() < 1e-3
