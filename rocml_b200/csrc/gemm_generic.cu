@@ -2,10 +2,16 @@
 //
 // 32-bit FMA accumulation, no tensor cores and no reduced-precision mode, for every element
 // type.  It is the matrix product of the true 32-bit path, the fallback for sizes the
-// tcgen05 kernel refuses, and the reference the tcgen05 kernel is tested against.  The sum
-// over k runs in ascending order for every output element whatever M is, so a row's result
-// does not depend on what else is in the batch.  It stands where the reference has
-// gemv_f16 / gemm_xwt_f16 (rocml-kernels/kernels/gemv_f16.hip:8-36, gemm_f16.hip:10-41).
+// tcgen05 kernel refuses, and the reference the tcgen05 kernel is tested against.  In the tiled
+// kernel the sum over k runs in ascending order for every output element whatever M is.  It stands
+// where the reference has gemv_f16 / gemm_xwt_f16 (rocml-kernels/kernels/gemv_f16.hip:8-36,
+// gemm_f16.hip:10-41).
+//
+// Few rows of 32-bit operands (a decode step of the 32-bit path) take a second kernel that is bound
+// by reading the weight once: a warp owns two weight rows and streams them with 16-byte loads, every
+// lane multiplying its slice of k with the same slice of all the step's rows (which stay in the L1
+// cache), and the lanes' sums meet in a shuffle tree.  How k is dealt out over the lanes depends on
+// nothing but k, so a row's result does not depend on what else is in the batch here either.
 #include "common.cuh"
 #include "api.h"
 
@@ -70,6 +76,90 @@ gemm_tn_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* 
     }
 }
 
+// ---- few rows, 32-bit: one pass over the weight ----------------------------------------------------
+constexpr int ROWS_WARPS = 8;     // warps a block
+constexpr int ROWS_NW = 2;        // weight rows a warp
+
+__device__ __forceinline__ float4 ld_stream(const float* p) {      // read once: do not keep it in the L1
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+template <int MT>
+__global__ void __launch_bounds__(ROWS_WARPS * 32)
+gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                     float* __restrict__ out, int M, int N, int K, long long ldx, long long ldo) {
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * ROWS_WARPS + warp) * ROWS_NW;
+    if (n0 >= N) return;
+    const float* wr[ROWS_NW];
+#pragma unroll
+    for (int j = 0; j < ROWS_NW; ++j) wr[j] = w + (size_t)min(n0 + j, N - 1) * K;
+    float acc[ROWS_NW][MT];
+#pragma unroll
+    for (int j = 0; j < ROWS_NW; ++j)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[j][m] = 0.f;
+    // the weights do not depend on the kernel before this one: the first slices are requested at once
+    float4 wv[2][ROWS_NW];
+    int k = lane * 4;
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int j = 0; j < ROWS_NW; ++j)
+            wv[u][j] = k + u * 128 < K ? ld_stream(wr[j] + k + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+    pdl_wait();
+    for (; k < K; k += 256) {
+        float4 nx[2][ROWS_NW];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int j = 0; j < ROWS_NW; ++j)
+                nx[u][j] = k + 256 + u * 128 < K ? ld_stream(wr[j] + k + 256 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int kk = k + u * 128;
+            if (kk >= K) break;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m >= M) break;
+                const float4 xv = *reinterpret_cast<const float4*>(x + (size_t)m * ldx + kk);
+#pragma unroll
+                for (int j = 0; j < ROWS_NW; ++j) {
+                    acc[j][m] = fmaf(xv.x, wv[u][j].x, acc[j][m]);
+                    acc[j][m] = fmaf(xv.y, wv[u][j].y, acc[j][m]);
+                    acc[j][m] = fmaf(xv.z, wv[u][j].z, acc[j][m]);
+                    acc[j][m] = fmaf(xv.w, wv[u][j].w, acc[j][m]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int j = 0; j < ROWS_NW; ++j) wv[u][j] = nx[u][j];
+    }
+#pragma unroll
+    for (int j = 0; j < ROWS_NW; ++j)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float v = warp_sum(acc[j][m]);
+            if (lane == 0 && m < M && n0 + j < N) out[(size_t)m * ldo + n0 + j] = v + (bias ? bias[n0 + j] : 0.f);
+        }
+}
+
+template <int MT>
+int launch_rows(const float* x, const float* w, const float* bias, float* out, int M, int N, int K, long long ldx,
+                long long ldo, cudaStream_t s) {
+    const int per_block = ROWS_WARPS * ROWS_NW;
+    RB_LAUNCH((gemm_rows_f32_kernel<MT>), dim3((N + per_block - 1) / per_block), dim3(ROWS_WARPS * 32), 0, s, x, w, bias,
+              out, M, N, K, ldx, ldo);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
 template <typename XT, typename WT, typename OT>
 int launch(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, long long ldx,
            long long ldo, cudaStream_t s) {
@@ -90,7 +180,19 @@ extern "C" int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
 #define RB_G(XT, WT, OT) return launch<XT, WT, OT>(x, w, bias, out, M, N, K, ldx, ldo, s)
-    if (x_dtype == RB_F32 && w_dtype == RB_F32 && out_dtype == RB_F32) RB_G(float, float, float);
+    if (x_dtype == RB_F32 && w_dtype == RB_F32 && out_dtype == RB_F32) {
+        // few rows: one pass over the weight (16-byte loads need k, the rows' stride and the pointers to fit)
+        if (M <= 16 && K % 4 == 0 && ldx % 4 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+            const float *xf = (const float*)x, *wf = (const float*)w, *bf32 = (const float*)bias;
+            float* of = (float*)out;
+            if (M <= 1) return launch_rows<1>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
+            if (M <= 2) return launch_rows<2>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
+            if (M <= 4) return launch_rows<4>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
+            if (M <= 8) return launch_rows<8>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
+            return launch_rows<16>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
+        }
+        RB_G(float, float, float);
+    }
     if (x_dtype == RB_F32 && w_dtype == RB_BF16 && out_dtype == RB_F32) RB_G(float, bf, float);
     if (x_dtype == RB_BF16 && w_dtype == RB_BF16 && out_dtype == RB_BF16) RB_G(bf, bf, bf);
     if (x_dtype == RB_BF16 && w_dtype == RB_BF16 && out_dtype == RB_F32) RB_G(bf, bf, float);

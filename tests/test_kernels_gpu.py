@@ -247,6 +247,26 @@ def test_gemm_generic(M, N, K, xd, wd, od):
     assert ((out.cpu().double() - want).abs() / scale).max().item() < tol
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 37, 52), (2, 311, 96), (3, 5, 4), (5, 129, 1000), (8, 4096, 4096), (9, 16, 260),
+                                   (16, 1001, 12288), (8, 50, 128)])
+def test_gemm_of_few_32_bit_rows_reads_the_weight_once(M, N, K):
+    """The 32-bit path's decode product (at most 16 rows, k a multiple of 4): a kernel of its own; a
+    row's result does not depend on the rows beside it, and rows of a strided view work."""
+    from rocml_b200 import kernels
+    wide = rnd((M, K + 8), 1).to(DEV)
+    x = wide[:, :K]                                   # a row stride that is not K
+    w = rnd((N, K), 2).to(DEV)
+    bias = rnd((N,), 3).to(DEV)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_generic(x, w, out, bias)
+    want = x.cpu().double() @ w.cpu().double().t() + bias.cpu().double()
+    scale = (x.cpu().double().abs() @ w.cpu().double().abs().t()).clamp_min(1.0)
+    assert ((out.cpu().double() - want).abs() / scale).max().item() < 1e-6
+    alone = torch.empty((1, N), dtype=torch.float32, device=DEV)
+    kernels.gemm_generic(x[M - 1:M].contiguous(), w, alone, bias)
+    assert torch.equal(alone[0], out[M - 1])
+
+
 # ---- embedding, norm, activation ---------------------------------------------------------------------
 
 @pytest.mark.parametrize("wd", [torch.float32, torch.bfloat16])
