@@ -9,8 +9,8 @@
 //
 // Few rows of 32-bit operands (a decode step of the 32-bit path) take a second kernel that is bound
 // by reading the weight once: a warp owns two weight rows and streams them with 16-byte loads, every
-// lane multiplying its slice of k with the same slice of all the step's rows (which stay in the L1
-// cache), and the lanes' sums meet in a shuffle tree.  How k is dealt out over the lanes depends on
+// lane multiplying its slice of k with the same slice of all the step's rows (which a block brings
+// into shared memory tile by tile), and the lanes' sums meet in a shuffle tree.  How k is dealt out over the lanes depends on
 // nothing but k, so a row's result does not depend on what else is in the batch here either.
 #include "common.cuh"
 #include "api.h"
@@ -77,8 +77,7 @@ gemm_tn_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* 
 }
 
 // ---- few rows, 32-bit: one pass over the weight ----------------------------------------------------
-constexpr int ROWS_WARPS = 8;     // warps a block
-constexpr int ROWS_NW = 2;        // weight rows a warp
+constexpr int ROWS_PER_BLOCK = 16;   // weight rows a block: 4 warps of 4 rows (up to 8 step rows) or 8 warps of 2
 
 __device__ __forceinline__ float4 ld_stream(const float* p) {      // read once: do not keep it in the L1
     float4 v;
@@ -87,14 +86,24 @@ __device__ __forceinline__ float4 ld_stream(const float* p) {      // read once:
     return v;
 }
 
+// A block owns 16 weight rows.  k is walked in tiles of KT: the step's rows of a tile are brought
+// into shared memory once for the whole block (two buffers, so that the next tile's copy and the next
+// tile's weight loads are in flight while this tile is multiplied), and every lane takes the 16-byte
+// groups lane, lane + 32, ... of the tile.  A 16-byte group of a step row read from shared memory
+// feeds 4 * ROWS_NW multiply-adds: with 4 weight rows a warp the shared-memory reads no longer bound
+// the kernel (with 2 they did, at about half the memory's bandwidth).
 template <int MT>
-__global__ void __launch_bounds__(ROWS_WARPS * 32)
+__global__ void __launch_bounds__(MT <= 8 ? 128 : 256)
 gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                      float* __restrict__ out, int M, int N, int K, long long ldx, long long ldo) {
+    constexpr int ROWS_NW = MT <= 8 ? 4 : 2;     // weight rows a warp
+    constexpr int ROWS_WARPS = ROWS_PER_BLOCK / ROWS_NW;
+    constexpr int KT = 256;                      // floats of k a tile
+    constexpr int U = KT / 128;                  // 16-byte groups a lane takes of a tile, per row
+    __shared__ __align__(16) float xs[2][MT][KT];
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = (blockIdx.x * ROWS_WARPS + warp) * ROWS_NW;
-    if (n0 >= N) return;
     const float* wr[ROWS_NW];
 #pragma unroll
     for (int j = 0; j < ROWS_NW; ++j) wr[j] = w + (size_t)min(n0 + j, N - 1) * K;
@@ -103,30 +112,38 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
     for (int j = 0; j < ROWS_NW; ++j)
 #pragma unroll
         for (int m = 0; m < MT; ++m) acc[j][m] = 0.f;
-    // the weights do not depend on the kernel before this one: the first slices are requested at once
-    float4 wv[2][ROWS_NW];
-    int k = lane * 4;
+    auto load_w = [&](float4 (&dst)[U][ROWS_NW], int k0) {
 #pragma unroll
-    for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < U; ++u) {
+            const int k = k0 + u * 128 + lane * 4;
 #pragma unroll
-        for (int j = 0; j < ROWS_NW; ++j)
-            wv[u][j] = k + u * 128 < K ? ld_stream(wr[j] + k + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < ROWS_NW; ++j) dst[u][j] = k < K ? ld_stream(wr[j] + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto load_x = [&](int buf, int k0) {          // the whole block copies the tile's rows; beyond K or M: zeros
+        for (int i = threadIdx.x; i < MT * (KT / 4); i += ROWS_WARPS * 32) {
+            const int m = i / (KT / 4), k = k0 + (i % (KT / 4)) * 4;
+            const float4 v = (m < M && k < K) ? *reinterpret_cast<const float4*>(x + (size_t)m * ldx + k)
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(&xs[buf][m][(i % (KT / 4)) * 4]) = v;
+        }
+    };
+    // the weights do not depend on the kernel before this one: their first tile is requested at once
+    float4 wv[U][ROWS_NW];
+    load_w(wv, 0);
     pdl_wait();
-    for (; k < K; k += 256) {
-        float4 nx[2][ROWS_NW];
+    load_x(0, 0);
+    __syncthreads();
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += KT, buf ^= 1) {
+        float4 nx[U][ROWS_NW];
+        load_w(nx, k0 + KT);
+        if (k0 + KT < K) load_x(buf ^ 1, k0 + KT);
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
-#pragma unroll
-            for (int j = 0; j < ROWS_NW; ++j)
-                nx[u][j] = k + 256 + u * 128 < K ? ld_stream(wr[j] + k + 256 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int kk = k + u * 128;
-            if (kk >= K) break;
+        for (int u = 0; u < U; ++u) {
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-                if (m >= M) break;
-                const float4 xv = *reinterpret_cast<const float4*>(x + (size_t)m * ldx + kk);
+                const float4 xv = *reinterpret_cast<const float4*>(&xs[buf][m][u * 128 + lane * 4]);
 #pragma unroll
                 for (int j = 0; j < ROWS_NW; ++j) {
                     acc[j][m] = fmaf(xv.x, wv[u][j].x, acc[j][m]);
@@ -137,9 +154,10 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
             }
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int j = 0; j < ROWS_NW; ++j) wv[u][j] = nx[u][j];
+        __syncthreads();      // the next tile's rows are in place, and nobody reads this tile's any more
     }
 #pragma unroll
     for (int j = 0; j < ROWS_NW; ++j)
@@ -153,9 +171,8 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
 template <int MT>
 int launch_rows(const float* x, const float* w, const float* bias, float* out, int M, int N, int K, long long ldx,
                 long long ldo, cudaStream_t s) {
-    const int per_block = ROWS_WARPS * ROWS_NW;
-    RB_LAUNCH((gemm_rows_f32_kernel<MT>), dim3((N + per_block - 1) / per_block), dim3(ROWS_WARPS * 32), 0, s, x, w, bias,
-              out, M, N, K, ldx, ldo);
+    RB_LAUNCH((gemm_rows_f32_kernel<MT>), dim3((N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), dim3(MT <= 8 ? 128 : 256), 0, s,
+              x, w, bias, out, M, N, K, ldx, ldo);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

@@ -6,6 +6,8 @@ workloads of the same kind, and the sweeps and timelines that the notes under ``
     python -m rocml_b200.measure sampler                      one sampling step, by way of sampling and batch
     python -m rocml_b200.measure gemm-decode | gemm-prefill   the tensor-core product alone, in a CUDA graph
     python -m rocml_b200.measure workload 4b-long | 32b       a whole generation through Engine.generate
+    python -m rocml_b200.measure float32                      the 32-bit path at the benchmark's layer sizes
+    python -m rocml_b200.measure profile [--dtype float32]    the per-kernel table of --profile, random weights
 
 Everything is timed on the device with CUDA events after warm-up; weights are random, token ids
 seeded uniform-random (the reference's bench repeats a filler sentence for the same purpose,
@@ -468,15 +470,41 @@ def float32_point(layers=4, steps=16, warmup=3):
     return rec
 
 
+def profile_table(model=None, layers=0, batch=BATCH, dtype="bfloat16", prompt=PROMPT, steps=8, by_layer=False):
+    """The per-kernel table of ``--profile`` for prompts of ``prompt`` tokens and ``steps`` decode steps
+    at a catalog entry's layer sizes, random weights made on the device."""
+    from . import StepEntry
+    from .profile import Profiler, to_human
+    cfg, n_full, eng = build_engine(layers, batch * (prompt + 64 * 2), batch, model=model, dtype=dtype)
+    ps = prompts(batch, prompt + steps, cfg.vocab_size, 3)
+
+    def run():
+        slots = [eng.new_sequence() for _ in ps]
+        eng.step([StepEntry(s, p[:prompt], [prompt - 1]) for s, p in zip(slots, ps)])
+        for t in range(steps):
+            eng.step([StepEntry(s, [p[prompt + t]], [0]) for s, p in zip(slots, ps)])
+        for s in slots:
+            eng.release(s)
+    run()
+    with Profiler(eng.device, dtype=dtype) as prof:
+        run()
+    print(f"{model or MODEL} layer sizes, {cfg.num_hidden_layers} of {n_full} layers, {dtype}, batch {batch}, "
+          f"prompts of {prompt} tokens, {steps} decode steps")
+    print(to_human(prof.report(), layers=by_layer))
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m rocml_b200.measure", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["sweep", "timeline", "sampler", "gemm-decode", "gemm-prefill", "workload", "float32"])
+    ap.add_argument("what", choices=["sweep", "timeline", "sampler", "gemm-decode", "gemm-prefill", "workload", "float32",
+                                     "profile"])
     ap.add_argument("name", nargs="?", default=None, help="for workload: " + " or ".join(WORKLOADS))
     ap.add_argument("--model", default=MODEL, help="catalog entry whose layer sizes are used")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of timeline")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the entry has (0: all; timeline: 4)")
     ap.add_argument("--runs", type=int, default=1)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="of profile")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length of profile")
     args = ap.parse_args(argv)
     if args.what == "sweep":
         sweep(None if args.model == "qwen3-8b" else [(1, 1024), (8, 1024), (8, 8192), (64, 1024)], model=args.model)
@@ -488,6 +516,8 @@ def main(argv=None) -> int:
         micro(args.what, model=args.model)
     elif args.what == "float32":
         print(json.dumps(float32_point(args.layers or 4)))
+    elif args.what == "profile":
+        profile_table(args.model, args.layers, args.batch, args.dtype, args.prompt)
     else:
         if args.name not in WORKLOADS:
             ap.error("workload needs one of: " + ", ".join(WORKLOADS))

@@ -12,8 +12,8 @@ reference pins its numerics the same way, with a 32-bit cache used only by parit
 
 Sums here are 4,096 and 12,288 terms deep, the tiny models' at most 320: what the 32-bit path
 loses to the order of its sums shows at this size or not at all.  Measured on a B200: 32-bit engine
-against the plain implementation at most 4e-6 of a row's largest logit in every mode; the bound
-below leaves a factor of a few.
+against the plain implementation at most 7e-6 of a row's largest logit in every mode (the test
+prints its worst); the bound below leaves a factor of three.
 """
 import json
 import os
