@@ -87,17 +87,17 @@ class Executor(Protocol):
 
 
 class _Sync:
-    """launch/collect over an executor that only has ``run``."""
+    """launch/collect over an executor that only has ``run``: the step runs when it is collected, so
+    that the loop's clock, which brackets ``collect``, sees it."""
 
     def __init__(self, executor):
         self.run = executor.run
 
     def launch(self, slots, tokens, params, rngs, histories, feed_from=None):
-        return self.run(slots, tokens, params, rngs, histories)
+        return (list(slots), [list(t) for t in tokens], list(params), list(rngs), [h for h in histories])
 
-    @staticmethod
-    def collect(handle):
-        return handle
+    def collect(self, handle):
+        return self.run(*handle)
 
 
 def _pages(n: int) -> int:

@@ -8,6 +8,7 @@ workloads of the same kind, and the sweeps and timelines that the notes under ``
     python -m rocml_b200.measure workload 4b-long | 32b       a whole generation through Engine.generate
     python -m rocml_b200.measure float32                      the 32-bit path at the benchmark's layer sizes
     python -m rocml_b200.measure profile [--dtype float32]    the per-kernel table of --profile, random weights
+    python -m rocml_b200.measure host [--model NAME]          what the Python host costs a decode step
 
 Everything is timed on the device with CUDA events after warm-up; weights are random, token ids
 seeded uniform-random (the reference's bench repeats a filler sentence for the same purpose,
@@ -493,11 +494,57 @@ def profile_table(model=None, layers=0, batch=BATCH, dtype="bfloat16", prompt=PR
     print(to_human(prof.report(), layers=by_layer))
 
 
+def host_cost(model=None, layers=0, batches=(1, 8, 64), steps=64):
+    """What the Python host costs a decode step: the step on the device alone (CUDA events around steps
+    whose tokens never leave the device), the same through ``Engine.generate`` with the loop reading
+    every step before it enqueues the next, and with the loop running one step ahead (the default),
+    in milliseconds a step; and the host's own time for one step's bookkeeping, packing and launch."""
+    import torch
+    from . import GenerateStats, StepEntry
+    cfg, n_full, eng = build_engine(layers, 64 * (PROMPT + 64 * 4), 64, model=model)
+    print(f"{model or MODEL} layer sizes, {cfg.num_hidden_layers} layers: milliseconds a decode step")
+    print("batch   device   generate, step by step   generate, one step ahead   host work a step")
+    for b in batches:
+        dev_ms, _, _ = time_decode(eng, b, steps, 4, cfg.vocab_size, seed=b)
+        ps = prompts(b, PROMPT, cfg.vocab_size, 7)
+        out = {}
+        for ahead in (False, True):
+            eng.generate(ps, max_new_tokens=4, stop_tokens=[], ignore_eos=True, max_batch=b, run_ahead=ahead)
+            best = None
+            for _ in range(3):
+                st = GenerateStats()
+                eng.generate(ps, max_new_tokens=steps + 1, stop_tokens=[], ignore_eos=True, max_batch=b, stats=st,
+                             run_ahead=ahead)
+                ms = st.decode_seconds / steps * 1e3
+                best = ms if best is None else min(best, ms)
+            out[ahead] = best
+        # the host's part alone: bookkeeping, packing and enqueueing of a step while the GPU is held busy
+        # (three steps at a time: the ring of pinned buffers lets the host run four steps ahead)
+        slots = [eng.new_sequence() for _ in range(b)]
+        eng.step([StepEntry(s, p, [PROMPT - 1]) for s, p in zip(slots, ps)])
+        tok = torch.zeros(b, dtype=torch.int32, device=eng.device)
+        eng.step([StepEntry(s, [0], [0]) for s in slots], device_tokens=tok)
+        khz = torch.cuda.get_device_properties(0).clock_rate
+        host = []
+        for _ in range(8):
+            torch.cuda.synchronize()
+            torch.cuda._sleep(int(20 * khz))                  # 20 ms
+            t0 = time.perf_counter()
+            for _ in range(3):
+                eng.step([StepEntry(s, [0], [0]) for s in slots], device_tokens=tok)
+            host.append((time.perf_counter() - t0) / 3 * 1e3)
+        host_ms = statistics.median(host)
+        torch.cuda.synchronize()
+        for s in slots:
+            eng.release(s)
+        print(f"{b:5d} {dev_ms:8.3f} {out[False]:24.3f} {out[True]:26.3f} {host_ms:18.3f}", flush=True)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m rocml_b200.measure", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=["sweep", "timeline", "sampler", "gemm-decode", "gemm-prefill", "workload", "float32",
-                                     "profile"])
+                                     "profile", "host"])
     ap.add_argument("name", nargs="?", default=None, help="for workload: " + " or ".join(WORKLOADS))
     ap.add_argument("--model", default=MODEL, help="catalog entry whose layer sizes are used")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of timeline")
@@ -516,6 +563,8 @@ def main(argv=None) -> int:
         micro(args.what, model=args.model)
     elif args.what == "float32":
         print(json.dumps(float32_point(args.layers or 4)))
+    elif args.what == "host":
+        host_cost(args.model, args.layers)
     elif args.what == "profile":
         profile_table(args.model, args.layers, args.batch, args.dtype, args.prompt)
     else:
