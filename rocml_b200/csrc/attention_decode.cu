@@ -154,7 +154,19 @@ __device__ __forceinline__ uint2 pack4_bf16(const float* v) {
 // lengths and the batch.  grid = (blocks, groups, 1).
 constexpr int PROP_MAX_SEQS = 256;
 
-template <int HD, bool CL, bool FQ, bool PROP>
+// TR (groups of at most 8 query heads, which is every size of the architecture): the products are
+// transposed.  S^T = K Q^T has the 16 keys of a warp's slice as the rows of the MMA tile and the heads as
+// its 8 columns, and O^T = V^T P the head size as rows: half the MMAs, half the softmax arithmetic and
+// half the accumulator registers of the layout with 16 head rows, of which a group of 4 fills a quarter.
+// P leaves the first product with keys along the lanes' groups and enters the second with keys along a
+// lane's pairs: one movmatrix per 8 keys transposes it in registers.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+template <int HD, bool CL, bool FQ, bool PROP, bool TR>
 __global__ void __launch_bounds__(WARPS * 32, HD <= 128 ? 3 : 1)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
@@ -325,10 +337,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __syncthreads();                                        // the query heads are in place for every warp
 
     float m_w[2] = {NEG_BIG, NEG_BIG}, l_w[2] = {0.f, 0.f};
-    float o[HD / 8][4];
+    // TR: m_w / l_w belong to this lane's two heads (tq * 2, tq * 2 + 1) and `ot` is O^T (tile i: head size
+    // i * 16 + gq and + 8 as rows, the two heads as columns); otherwise they belong to the lane's two head
+    // rows (gq, gq + 8) and `o` is O.
+    float o[TR ? 1 : HD / 8][4];
+    float ot[TR ? HD / 16 : 1][4];
+    uint32_t qb[TR ? HD / 16 : 1][2];      // TR: the query heads as the B operand, loaded once
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    for (int i = 0; i < (TR ? 1 : HD / 8); ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < (TR ? HD / 16 : 1); ++i) { ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f; }
     const uint32_t qs_base = smem_addr(Qs);
+    if (TR) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks += 2)
+            ldmatrix_x4(tile_addr<HD>(qs_base, lane & 7, ks * 2 + (lane >> 3)), qb[ks][0], qb[ks][1], qb[ks + 1][0], qb[ks + 1][1]);
+    }
     const float sl2 = scale * LOG2E;
 
     auto attend_page = [&](int pg, int buf) {
@@ -337,6 +361,65 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (!(j0 <= hi && j0 + WK - 1 >= win_lo)) return;
         const uint32_t ks_base = smem_addr(KVw + buf * 2 * WK * HD);
         const uint32_t vs_base = ks_base + WK * HD * 2;
+        if constexpr (TR) {
+            // S^T for the slice's 16 keys: st[0], st[1] = (key gq; heads tq * 2, + 1), st[2], st[3] = (key gq + 8; ...)
+            float st[4] = {0.f, 0.f, 0.f, 0.f}, st2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ks += 2) {          // two chains of MMAs, added at the end
+                uint32_t ka[4], kb[4];
+                const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(tile_addr<HD>(ks_base, row, ks * 2 + (lane >> 4)), ka[0], ka[1], ka[2], ka[3]);
+                ldmatrix_x4(tile_addr<HD>(ks_base, row, ks * 2 + 2 + (lane >> 4)), kb[0], kb[1], kb[2], kb[3]);
+                mma_bf16(st, ka, qb[ks][0], qb[ks][1]);
+                mma_bf16(st2, kb, qb[ks + 1][0], qb[ks + 1][1]);
+            }
+            const int key0 = j0 + gq, key1 = key0 + 8;
+            if (j0 >= win_lo && j0 + WK - 1 <= hi) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) st[e] = (st[e] + st2[e]) * sl2;
+            } else {
+                const bool ok0 = key0 >= win_lo && key0 <= hi, ok1 = key1 >= win_lo && key1 <= hi;
+                st[0] = ok0 ? (st[0] + st2[0]) * sl2 : -INFINITY;
+                st[1] = ok0 ? (st[1] + st2[1]) * sl2 : -INFINITY;
+                st[2] = ok1 ? (st[2] + st2[2]) * sl2 : -INFINITY;
+                st[3] = ok1 ? (st[3] + st2[3]) * sl2 : -INFINITY;
+            }
+            float mx[2] = {fmaxf(st[0], st[2]), fmaxf(st[1], st[3])};
+            float alpha[2];
+            bool moved = false;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {                       // a head's keys lie along the lanes' groups
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
+                const float m_new = fmaxf(m_w[r], mx[r]);
+                moved = moved || m_new != m_w[r];
+                alpha[r] = ex2(m_w[r] - m_new);
+                m_w[r] = m_new;
+                l_w[r] *= alpha[r];
+            }
+            if (pg > page_first && __any_sync(0xffffffffu, moved)) {
+#pragma unroll
+                for (int i = 0; i < HD / 16; ++i) {
+                    ot[i][0] *= alpha[0]; ot[i][1] *= alpha[1];
+                    ot[i][2] *= alpha[0]; ot[i][3] *= alpha[1];
+                }
+            }
+            const float p0 = ex2(st[0] - m_w[0]), p1 = ex2(st[1] - m_w[1]);
+            const float p2 = ex2(st[2] - m_w[0]), p3 = ex2(st[3] - m_w[1]);
+            l_w[0] += p0 + p2;
+            l_w[1] += p1 + p3;
+            // P as the B operand of O^T = V^T P: (keys tq * 2, + 1; head gq) and the same for keys + 8
+            const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
+            const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+#pragma unroll
+            for (int i = 0; i < HD / 16; ++i) {
+                uint32_t va[4];
+                ldmatrix_x4_trans(tile_addr<HD>(vs_base, (lane & 7) + (lane >> 4) * 8, i * 2 + ((lane >> 3) & 1)),
+                                  va[0], va[1], va[2], va[3]);
+                mma_bf16(ot[i], va, pb0, pb1);
+            }
+        } else {
         float s[WK / 8][4];
 #pragma unroll
         for (int j = 0; j < WK / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
@@ -420,6 +503,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_bf16(o[i + 1], pa[kk], b2, b3);
             }
         }
+        }
     };
     for (int pg = page_first; pg <= page_last; ++pg) {
         const int buf = (pg - page_first) & 1;
@@ -434,15 +518,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     cp_async_wait<0>();
 #pragma unroll
     for (int r = 0; r < 2; ++r) {                           // this thread's share of the sums -> the row's sum
-        l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
-        l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
+        if (TR) {
+            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 4);
+            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 8);
+            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 16);
+        } else {
+            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
+            l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
+        }
     }
     __syncthreads();   // every warp is done with its keys and values: the space is reused for the merge
-    if (tq == 0) {
+    if (TR) {
+        if (gq == 0) {
+            s_m[warp][tq * 2] = m_w[0]; s_m[warp][tq * 2 + 1] = m_w[1];
+            s_l[warp][tq * 2] = l_w[0]; s_l[warp][tq * 2 + 1] = l_w[1];
+        }
+        const bool h_lo = tq * 2 < rows_valid, h_hi = tq * 2 + 1 < rows_valid;
+#pragma unroll
+        for (int i = 0; i < HD / 16; ++i) {
+            const int d = i * 16 + gq;
+            float* lo = s_o + ((size_t)warp * ROWS + tq * 2) * HD + d;
+            if (h_lo) { lo[0] = ot[i][0]; lo[8] = ot[i][2]; }
+            if (h_hi) { lo[HD] = ot[i][1]; lo[HD + 8] = ot[i][3]; }
+        }
+    } else if (tq == 0) {
         s_m[warp][gq] = m_w[0]; s_m[warp][gq + 8] = m_w[1];
         s_l[warp][gq] = l_w[0]; s_l[warp][gq + 8] = l_w[1];
     }
-    {   // only the rows that hold a query head are read again (a group of 4 fills 4 of the tile's 16 rows)
+    if (!TR) {   // only the rows that hold a query head are read again (a group of 4 fills 4 of the tile's 16 rows)
         const bool lo_row = gq < rows_valid, hi_row = gq + 8 < rows_valid;
 #pragma unroll
         for (int i = 0; i < HD / 8; ++i) {
@@ -578,12 +681,12 @@ bool cluster_enabled() {
     return on;
 }
 
-template <int HD, bool CL, bool FQ, bool PROP = false>
+template <int HD, bool CL, bool FQ, bool PROP, bool TR>
 int launch_variant(dim3 grid, size_t smem, cudaStream_t s, const void* q, int q_stride, const void* k_cache,
                    const void* v_cache, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                    const int* kv_len, int nq, int nkv, float scale, int window, int n_chunks, int ppb, float* part_acc,
                    float* part_ml, int* counters, void* out, int o_stride, const Projections& pj, int n_seqs) {
-    auto k = attention_decode_kernel<HD, CL, FQ, PROP>;
+    auto k = attention_decode_kernel<HD, CL, FQ, PROP, TR>;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -632,9 +735,13 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     // one of them writes the token's key and value into it, with nothing that orders the others' reads
     // after that write.  The caller writes the cache with the kernel of its own and calls again.
     if (fused && pj.write_kv && g > ROWS) return RB_ERR_BAD_SIZE;
-#define RB_ADV(CL, FQ, PROP) launch_variant<HD, CL, FQ, PROP>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table,       \
+    // groups of up to 8 heads (every size of the architecture): the transposed products (see the kernel)
+#define RB_ADV(CL, FQ, PROP) (g <= 8 ? launch_variant<HD, CL, FQ, PROP, true>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table, \
                                                          max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,         \
-                                                         n_chunks, ppb, part_acc, part_ml, counters, out, o_stride, pj, B)
+                                                         n_chunks, ppb, part_acc, part_ml, counters, out, o_stride, pj, B)  \
+                                     : launch_variant<HD, CL, FQ, PROP, false>(grid, smem, s, q, q_stride, k_cache, v_cache, block_table, \
+                                                         max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window,         \
+                                                         n_chunks, ppb, part_acc, part_ml, counters, out, o_stride, pj, B))
     if (proportional) return (HD == 128 && fused) ? RB_ADV(false, (HD == 128), true) : RB_ADV(false, false, true);
     if (HD == 128 && fused) return clustered ? RB_ADV(true, (HD == 128), false) : RB_ADV(false, (HD == 128), false);
     return clustered ? RB_ADV(true, false, false) : RB_ADV(false, false, false);
