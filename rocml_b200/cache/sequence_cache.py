@@ -62,13 +62,14 @@ class KVGroup:
     def bytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()
 
-    def ensure(self, slot: int, new_len: int) -> None:
-        """Pages for positions < new_len (those a window has released stay released)."""
+    def ensure(self, slot: int, new_len: int, old_len: int = 0) -> None:
+        """Pages for positions < new_len (those a window has released stay released).  ``old_len``: the
+        sequence's length so far, whose pages it holds already (only the pages past them are looked at)."""
         need = pages_for(new_len)
         if need > self.max_pages_per_seq:
             raise ContextOverflow(new_len, self.max_pages_per_seq * PAGE)
         row = self.table_host[slot]
-        first = self._released_upto.get(slot, 0)
+        first = max(self._released_upto.get(slot, 0), pages_for(old_len)) if old_len else self._released_upto.get(slot, 0)
         todo = [p for p in range(first, need) if row[p] < 0]
         if len(todo) > self.pool.n_free:
             raise CacheFull(
@@ -88,9 +89,8 @@ class KVGroup:
         for n_piece, piece in enumerate(pieces):
             for slot, n_new in piece:
                 if slot not in state:
-                    held = np.nonzero(self.table_host[slot] >= 0)[0]
-                    end = int(held[-1]) + 1 if len(held) else 0
-                    state[slot] = [self._released_upto.get(slot, 0), end, lengths[slot]]
+                    # a sequence holds the pages of its length so far, from the first its window has not released
+                    state[slot] = [self._released_upto.get(slot, 0), pages_for(lengths[slot]), lengths[slot]]
                 st = state[slot]
                 st[2] += n_new
                 need = pages_for(st[2])
@@ -320,7 +320,7 @@ class SequenceCache:
         if new > self.max_seq_len:
             raise ContextOverflow(new, self.max_seq_len)
         for g in self.kv_groups:
-            g.ensure(slot, new)
+            g.ensure(slot, new, old)
         return old
 
     def plan(self, pieces: Sequence[Sequence[tuple]]) -> None:
