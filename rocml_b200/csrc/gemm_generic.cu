@@ -102,15 +102,27 @@ gemm_tn_large_kernel(const XT* __restrict__ x, const WT* __restrict__ w, const f
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
     float xr[2][4], wr[2][4];
+    // 32-bit operands whose rows start on 16 bytes are read four k at a time
+    const bool x4 = sizeof(XT) == 4 && (ldx & 3) == 0 && ((uintptr_t)x & 15) == 0;
+    const bool w4 = sizeof(WT) == 4 && (K & 3) == 0 && ((uintptr_t)w & 15) == 0;
     auto fetch = [&](int k0) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int m = m0 + lr + h * 64, n = n0 + lr + h * 64;
+            const int k = k0 + lc;
+            if (x4 && m < M && k + 3 < K) {
+                const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)m * ldx + k);
+                xr[h][0] = v.x; xr[h][1] = v.y; xr[h][2] = v.z; xr[h][3] = v.w;
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int k = k0 + lc + j;
-                xr[h][j] = (m < M && k < K) ? to_f32(x[(size_t)m * ldx + k]) : 0.f;
-                wr[h][j] = (n < N && k < K) ? to_f32(w[(size_t)n * K + k]) : 0.f;
+                for (int j = 0; j < 4; ++j) xr[h][j] = (m < M && k + j < K) ? to_f32(x[(size_t)m * ldx + k + j]) : 0.f;
+            }
+            if (w4 && n < N && k + 3 < K) {
+                const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + (size_t)n * K + k);
+                wr[h][0] = v.x; wr[h][1] = v.y; wr[h][2] = v.z; wr[h][3] = v.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wr[h][j] = (n < N && k + j < K) ? to_f32(w[(size_t)n * K + k + j]) : 0.f;
             }
         }
     };
