@@ -411,3 +411,119 @@ def test_a_toy_position_encoding_and_a_toy_routed_feed_forward_register_build_an
     scale = want_a.abs().max()
     assert (torch.cat(got_a) - want_a).abs().max() < 1e-4 * scale
     assert (torch.cat(got_b) - want_b[8:]).abs().max() < 1e-4 * scale
+
+
+def test_a_toy_arrangement_and_a_toy_norm_register_build_and_step():
+    """Another arrangement of a layer (mixer and feed-forward side by side on ONE norm's output, both added
+    to the residual) and another norm (mean-centred, with a bias), both defined HERE, registered, and put
+    around the library's own attention and gated feed-forward.  The engine steps them: whole prompts,
+    pieces of a prompt, single tokens, two sequences at once.  Nothing in the library's files changes."""
+    from rocml_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry
+    from rocml_b200.engine import Engine, Model, StepEntry
+    from rocml_b200.parts import Norm, build_feed_forward, build_mixer, build_norm, register_arrangement, register_norm
+    from rocml_b200.weights import TensorDecl
+    from rocml_b200.weights.random_init import random_tensor
+
+    @register_norm("toy_layernorm")
+    class ToyLayerNorm(Norm):
+        graph_safe = True          # torch kernels on the current stream only
+
+        def __init__(self, spec, size, env):
+            self.size, self.eps = size, float(spec.eps)
+
+        def declare(self, prefix):
+            return [TensorDecl(f"{prefix}.weight", (self.size,), "norm"), TensorDecl(f"{prefix}.bias", (self.size,), "bias")]
+
+        def load(self, tensors, prefix):
+            self.w, self.b = tensors[f"{prefix}.weight"].float(), tensors[f"{prefix}.bias"].float()
+
+        def weight_bytes(self):
+            return 8 * self.size
+
+        def forward(self, resid, delta, n_rows=None, rows=None, write_back=True):
+            n = resid.shape[0] if n_rows is None else n_rows
+            if delta is not None:
+                resid[:delta.shape[1]] += delta.sum(0)              # the partial sums of the parts before
+            x = resid[:n] if rows is None else resid[rows[:n].long()]
+            mu = x.mean(-1, keepdim=True)
+            return (x - mu) * torch.rsqrt(((x - mu) ** 2).mean(-1, keepdim=True) + self.eps) * self.w + self.b
+
+    @register_arrangement("toy_parallel")
+    class ParallelBlock:
+        """x += mixer(norm(x)) + ff(norm(x)): the two results travel on as partial sums of one delta."""
+
+        def __init__(self, spec, hidden, env, mixer_spec=None):
+            self.spec = spec
+            self.norm = build_norm(spec.mixer_norm, hidden, env)
+            self.mixer = build_mixer(mixer_spec or spec.mixer, hidden, env)
+            self.ff = build_feed_forward(spec.feed_forward, hidden, env)
+
+        def _names(self):
+            p, s = self.spec.prefix, self.spec
+            return f"{p}.{s.mixer_norm_name}", f"{p}.{s.mixer_name}", f"{p}.{s.ff_name}"
+
+        def declare(self):
+            n, mx, ff = self._names()
+            return self.norm.declare(n) + self.mixer.declare(mx) + self.ff.declare(ff)
+
+        def load(self, tensors):
+            n, mx, ff = self._names()
+            self.norm.load(tensors, n); self.mixer.load(tensors, mx); self.ff.load(tensors, ff)
+
+        graph_safe = property(lambda self: self.norm.graph_safe and self.mixer.graph_safe and self.ff.graph_safe)
+
+        def weight_bytes(self):
+            return self.norm.weight_bytes() + self.mixer.weight_bytes() + self.ff.weight_bytes()
+
+        def forward(self, resid, pending, batch, view):
+            xn = self.norm.forward(resid, pending, batch.n_tokens)
+            return torch.cat([self.mixer.forward(xn, batch, view), self.ff.forward(xn, batch)], dim=0)
+
+    H, V, nq, nkv, hd, inter = 40, 91, 3, 1, 16, 56
+    norm = NormSpec("toy_layernorm", 1e-4)
+    att = MixerSpec.make("attention", position=PositionSpec("rope_neox", theta=1e4), n_heads=nq, n_kv_heads=nkv, head_dim=hd)
+    ff = FeedForwardSpec.make("gated_mlp", intermediate=inter)
+    layers = tuple(LayerSpec(f"h.{i}", att, ff, norm, norm, arrangement="toy_parallel", mixer_norm_name="ln",
+                             mixer_name="attn.", ff_name="mlp.") for i in range(2))
+    spec = ModelSpec("ToyParallel", H, V, 256, layers, (ScheduleEntry(0), ScheduleEntry(1)), norm, tie_embeddings=False,
+                     embedding_name="wte.weight", final_norm_name="ln_f.weight", head_name="head.weight")
+    model = Model(spec, env(torch.float32))
+    tensors = {d.name: random_tensor(d, 9).float() * (3.0 if d.role == "matrix" else 1.0) for d in model.declare()}
+    assert "h.1.ln.bias" in tensors and "ln_f.bias" in tensors and "h.0.attn.q_proj.weight" in tensors
+    assert not any("post_attention" in k for k in tensors)
+    model.load({k: v.to(DEV) for k, v in tensors.items()})
+    eng = Engine(model, max_tokens=512, max_slots=2, max_step_tokens=16)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    def ln(x, p):
+        mu = x.mean(-1, keepdim=True)
+        return (x - mu) * torch.rsqrt(((x - mu) ** 2).mean(-1, keepdim=True) + 1e-4) * w[p + ".weight"] + w[p + ".bias"]
+
+    def plain(ids):
+        T = len(ids)
+        x = w["wte.weight"][ids]
+        for i in range(2):
+            p = f"h.{i}."
+            xn = ln(x, p + "ln")
+            q = P.rope_neox(P.linear(xn, w[p + "attn.q_proj.weight"]).view(T, nq, hd), range(T), 1e4)
+            k = P.rope_neox(P.linear(xn, w[p + "attn.k_proj.weight"]).view(T, nkv, hd), range(T), 1e4)
+            v = P.linear(xn, w[p + "attn.v_proj.weight"]).view(T, nkv, hd)
+            a = P.linear(P.attention(q, k, v).reshape(T, nq * hd), w[p + "attn.o_proj.weight"])
+            m = P.linear(P.silu_mul(P.linear(xn, w[p + "mlp.gate_proj.weight"]), P.linear(xn, w[p + "mlp.up_proj.weight"])),
+                         w[p + "mlp.down_proj.weight"])
+            x = x + a + m
+        return P.linear(ln(x, "ln_f"), w["head.weight"])
+
+    a, b = prompt(1, 50, V), prompt(2, 23, V)
+    wa, wb = plain(a), plain(b)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    # prompts of 44 and 20 tokens in one step: four pieces of 16 tokens, the second sequence beside the end of the first
+    out = eng.step([StepEntry(sa, a[:44], [0, 15, 16, 43]), StepEntry(sb, b[:20], [19])]).cpu().double()
+    scale = wa.abs().max()
+    assert (out[:4] - wa[[0, 15, 16, 43]]).abs().max() < 2e-5 * scale
+    assert (out[4] - wb[19]).abs().max() < 2e-5 * scale
+    for t in range(3):
+        out = eng.step([StepEntry(sa, [a[44 + t]], [0]), StepEntry(sb, [b[20 + t]], [0])]).cpu().double()
+        assert (out[0] - wa[44 + t]).abs().max() < 2e-5 * scale and (out[1] - wb[20 + t]).abs().max() < 2e-5 * scale
+    eng.release(sa); eng.release(sb)
+    eng.cache.check_invariants()
