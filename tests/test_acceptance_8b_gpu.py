@@ -145,3 +145,42 @@ def test_bfloat16_against_float32_with_the_near_tie_rule(setup, f32):
     # random weights give flat rows: about a quarter have their two best logits within 1e-2; the
     # rule must still leave most rows to be compared
     assert picked > 2 * ties
+
+
+def test_a_long_prompt_in_pieces_at_full_sizes(setup):
+    """4,200 tokens at the full head counts and widths: the engine cuts the prompt at 4,096 tokens (the first
+    piece takes the projection whose epilogue normalises, rotates and caches; the second reads the first's
+    keys from the pages), then three tokens one by one.  The last rows of the prompt and the decoded
+    rows, 32-bit and bfloat16, against the plain implementation (whose head product is done on those rows
+    only)."""
+    from plain_qwen3 import PlainQwen3, linear, rmsnorm
+    from rocml_b200 import Engine, StepEntry
+    folder, _, _ = setup
+    n, n_dec = 4200, 3
+    g = torch.Generator().manual_seed(81)
+    ids = torch.randint(0, 151936, (n + n_dec,), generator=g).tolist()
+    plain = PlainQwen3(folder, dtype=torch.float32)
+    rows = [4095, 4096, n - 1, n, n + 1, n + 2]
+    hidden = plain.hidden_states(ids)[rows]
+    want = linear(rmsnorm(hidden, plain.w["model.norm.weight"], plain.eps), plain.w["lm_head.weight"])
+    del plain
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=4352, max_slots=1)
+        slot = eng.new_sequence()
+        before = eng.launches
+        out = [eng.step([StepEntry(slot, ids[:n], [4095, 4096, n - 1])]).float().cpu()]
+        assert eng.launches - before == 2                       # two pieces
+        for t in range(n_dec):
+            out.append(eng.step([StepEntry(slot, [ids[n + t]], [0])]).float().cpu())
+        got[dtype] = torch.cat(out)
+        eng.release(slot)
+        del eng
+        torch.cuda.empty_cache()
+    err32 = rel_err(got["float32"], want)
+    assert err32 < TOL_F32, err32                                # measured 7e-6: sums over 4,200 keys in another order
+    assert rel_err(got["bfloat16"], got["float32"]) < TOL_BF16
+    for t in range(len(rows)):
+        assert int(got["float32"][t].argmax()) == int(want[t].argmax()) or near_tie(want[t], 1e-4)
+        assert int(got["bfloat16"][t].argmax()) == int(got["float32"][t].argmax()) or near_tie(got["float32"][t])
+    print(f"long prompt, float32 against the plain implementation: {err32:.2e}")
