@@ -16,6 +16,8 @@ int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delt
 int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype, int rows,
                 int I, int paired, void* stream);
 
+// Keeps the stream busy for about that long (at most a second): the profiler's gate.
+int rb_hold(long long microseconds, void* stream);
 int rb_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* stream);
 
 int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, void* q_out,

@@ -153,6 +153,7 @@ def _lib():
                                                  _vp, _i, _f, _vp, _i, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_residual.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _ll, _vp, _i, _vp, _ll, _vp,
                                                  _ll, _i, _vp, _vp]
+        lib.rb_hold.argtypes = [_ll, _vp]
         lib.rb_gemm_tcgen05_set_wait.argtypes = [_ll, _i]
         lib.rb_gemm_tcgen05_set_wait.restype = None
         _sigs_done = True
@@ -595,6 +596,15 @@ def check_status(device) -> None:
     key = torch.device(device).index or 0
     if key in _status:
         raise_for_status(int(_status[key].item()), device)
+
+
+def hold(microseconds: float) -> None:
+    """Keep the current stream busy for about that long (at most a second; not counted as a launch): what is
+    enqueued behind it starts when it ends.  The profiler holds the GPU back with it while the host
+    enqueues a step."""
+    rc = _lib().rb_hold(int(microseconds), _stream())
+    if rc != 0:
+        raise KernelError(f"hold: CUDA error {rc}")
 
 
 def set_wait_limit(cycles: int = 0, withhold_first_stage: bool = False) -> None:

@@ -524,11 +524,11 @@ def host_cost(model=None, layers=0, batches=(1, 8, 64), steps=64):
         eng.step([StepEntry(s, p, [PROMPT - 1]) for s, p in zip(slots, ps)])
         tok = torch.zeros(b, dtype=torch.int32, device=eng.device)
         eng.step([StepEntry(s, [0], [0]) for s in slots], device_tokens=tok)
-        khz = torch.cuda.get_device_properties(0).clock_rate
+        from . import kernels
         host = []
         for _ in range(8):
             torch.cuda.synchronize()
-            torch.cuda._sleep(int(20 * khz))                  # 20 ms
+            kernels.hold(20e3)                                # the GPU is busy for 20 ms
             t0 = time.perf_counter()
             for _ in range(3):
                 eng.step([StepEntry(s, [0], [0]) for s in slots], device_tokens=tok)
