@@ -719,3 +719,31 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
         assert kernels.gemm_tcgen05(x, w, out)
         kernels.check_status(DEV)
         assert (out.cpu().double() - want).abs().max().item() < 1e-3
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_gemm_tcgen05_random_shapes(seed):
+    """Shapes drawn at random (any M, any N, K a multiple of 8 as the kernel asks): whole results in both
+    output types and partial sums over K, against float64.  Every kernel of the family is reached: few
+    tokens (weights on the 128-row side), many (one CTA, CTA pairs), tails in every dimension."""
+    import random
+    from rocml_b200 import kernels
+    rng = random.Random(seed)
+    M = rng.choice([rng.randint(1, 16), rng.randint(17, 128), rng.randint(129, 700), rng.randint(700, 2500)])
+    N = rng.choice([rng.randint(1, 64), rng.randint(65, 600), rng.randint(600, 3000)])
+    K = 8 * rng.choice([rng.randint(1, 8), rng.randint(9, 64), rng.randint(65, 600)])
+    x = rnd((M, K), seed, torch.bfloat16).to(DEV)
+    w = rnd((N, K), seed + 1, torch.bfloat16).to(DEV)
+    bias = rnd((N,), seed + 2).to(DEV) if rng.random() < 0.5 else None
+    want = x.cpu().double() @ w.cpu().double().t() + (bias.cpu().double() if bias is not None else 0)
+    scale = torch.maximum((x.cpu().double().abs() @ w.cpu().double().abs().t()).clamp_min(1.0), want.abs())
+    for out_dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2 ** -8)):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        assert kernels.gemm_tcgen05(x, w, out, bias)
+        assert ((out.cpu().double() - want).abs() / scale).max().item() < tol, (M, N, K, out_dtype)
+    S = rng.choice([2, 3, 4, 8])
+    if K // 64 >= S:
+        out = torch.full((S, M, N), float("nan"), dtype=torch.float32, device=DEV)
+        assert kernels.gemm_tcgen05(x, w, out, bias)
+        assert ((out.cpu().double().sum(0) - want).abs() / scale).max().item() < 1e-5, (M, N, K, S)
+    kernels.check_status(DEV)
