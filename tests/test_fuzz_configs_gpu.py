@@ -22,8 +22,11 @@ def draw(seed):
     group = rng.choice([1, 2, 3, 5, 8, 17]) if hd <= 128 else rng.choice([1, 2, 3])
     layers = rng.choice([1, 2, 3])
     cfg = {
-        "architectures": ["Qwen3ForCausalLM"], "hidden_size": 8 * rng.choice([5, 9, 12, 17, 24, 33]),
-        "intermediate_size": 16 * rng.choice([3, 7, 10, 13, 20]), "num_hidden_layers": layers,
+        # every third configuration has a width and an inner width that are multiples of nothing
+        "architectures": ["Qwen3ForCausalLM"],
+        "hidden_size": rng.choice([37, 50, 77, 101, 130, 203]) if seed % 3 == 2 else 8 * rng.choice([5, 9, 12, 17, 24, 33]),
+        "intermediate_size": rng.choice([45, 99, 150, 211]) if seed % 3 == 2 else 16 * rng.choice([3, 7, 10, 13, 20]),
+        "num_hidden_layers": layers,
         "num_attention_heads": nkv * group, "num_key_value_heads": nkv, "head_dim": hd,
         "vocab_size": rng.choice([97, 130, 255, 401, 1000, 1031]), "max_position_embeddings": 384,
         "rope_theta": rng.choice([1e4, 5e4, 1e6]), "rms_norm_eps": rng.choice([1e-6, 1e-5, 3e-4]),
