@@ -68,7 +68,9 @@ class Engine:
         self.max_graphs = max(1, int(max_graphs))
         max_tokens = int(max_tokens)
         if max_slots is None:
-            max_slots = max(1, min((max_tokens + 63) // 64, 256))
+            # every live sequence holds a page at least, so the pages bound the sequences (a slot costs a row
+            # of the block table and, where a layer keeps fixed-size state, its state)
+            max_slots = max(1, min((max_tokens + 63) // 64, 4096))
         self.use_graphs = bool(use_graphs) and model.graph_safe and self.device.type == "cuda"
         self._check_budget(max_tokens, max_slots)
         self.cache = SequenceCache(

@@ -307,3 +307,33 @@ def test_captured_decode_graphs_are_bounded(tmp_path, monkeypatch, dtype):
         eng.release(slot)
         assert rel_err(torch.cat(got), want) < TOL[dtype]
     assert eng.graphs_captured == 20 and list(eng._graphs) == [(1, 256), (1, 288), (1, 320)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_three_hundred_short_sequences_at_once(tmp_path, dtype):
+    """More live sequences than any kernel's per-batch tables were sized for by habit (256): the cache
+    gives every page's worth of budget a slot, the prompts go in one step, then three tokens each."""
+    from plain_qwen3 import PlainQwen3
+    from rocml_b200 import Engine, StepEntry
+    folder = str(tmp_path / "m")
+    write_model(folder, CONFIGS["D"], seed=71, std=0.05)
+    plain = PlainQwen3(folder, dtype=torch.float64)
+    vocab = CONFIGS["D"]["vocab_size"]
+    n_seqs = 300
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=64 * n_seqs)
+    assert eng.cache.max_slots == n_seqs
+    seqs = [prompt(5000 + j, 3 + j % 9 + 3, vocab) for j in range(n_seqs)]
+    lens = [len(s) - 3 for s in seqs]
+    slots = [eng.new_sequence() for _ in seqs]
+    out = eng.step([StepEntry(sl, s[:n], [n - 1]) for sl, s, n in zip(slots, seqs, lens)]).clone()
+    got = [[out[j]] for j in range(n_seqs)]
+    for t in range(3):
+        out = eng.step([StepEntry(sl, [s[n + t]], [0]) for sl, s, n in zip(slots, seqs, lens)]).clone()
+        for j in range(n_seqs):
+            got[j].append(out[j])
+    for j in list(range(0, n_seqs, 23)) + [255, 256, 257, n_seqs - 1]:
+        want = plain.logits(seqs[j])[lens[j] - 1:]
+        assert rel_err(torch.stack(got[j]), want) < TOL[dtype], (j, dtype)
+    for sl in slots:
+        eng.release(sl)
+    eng.cache.check_invariants()
