@@ -185,16 +185,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             issued = pre;
             bool ok = true;
-            for (int kb = pre; kb < n_kb && ok; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (kb / S) & 1;
-                ok = mbar_wait(&empty[s], ph ^ 1, p.wait_cycles);
-                if (!ok) break;
+            // a lone thread executes a dependent instruction every few cycles at best: the stage, its parity and
+            // the K coordinate are carried along instead of being divided out of kb every time
+            int s = pre == S ? 0 : pre;
+            uint32_t par = 0;                 // the parity to wait for on empty[s]: the first refill waits for use 0
+            int c0 = k_begin + pre * BK;
+            for (int kb = pre; kb < n_kb; ++kb) {
+                if (!mbar_try_wait(&empty[s], par)) {
+                    ok = mbar_wait(&empty[s], par, p.wait_cycles);
+                    if (!ok) break;
+                }
                 uint8_t* sa = smem + s * C::STAGE;
                 mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
-                tma_load_2d(sa, &map_a, k_begin + kb * BK, a0, &full[s]);
-                tma_load_2d(sa + C::A_BYTES, &map_b, k_begin + kb * BK, b0, &full[s]);
+                tma_load_2d(sa, &map_a, c0, a0, &full[s]);
+                tma_load_2d(sa + C::A_BYTES, &map_b, c0, b0, &full[s]);
                 ++issued;
+                c0 += BK;
+                if (++s == S) { s = 0; par ^= 1u; }
             }
             if (!ok) {
                 atomicExch(p.status, RB_ERR_TIMEOUT);
@@ -205,21 +212,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
             bool ok = true;
+            const uint32_t a_lo0 = smem_desc_sw128_lo(smem_u32(smem));
+            uint32_t a_lo = a_lo0, par = 0;
+            int s = 0;
             for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (kb / S) & 1;
-                ok = mbar_wait(&full[s], ph, p.wait_cycles);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t sa = smem_u32(smem + s * C::STAGE);
-                const uint64_t adesc = smem_desc_sw128(sa);
-                const uint64_t bdesc = smem_desc_sw128(sa + C::A_BYTES);
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // advancing 16 elements (32 bytes) inside the swizzle atom: +2 in 16-byte units
-                    mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                if (!mbar_try_wait(&full[s], par)) {
+                    ok = mbar_wait(&full[s], par, p.wait_cycles);
+                    if (!ok) break;
                 }
+                tc_fence_after();
+                mma_bf16_k64(tmem_base, a_lo, a_lo + (C::A_BYTES >> 4), idesc, kb == 0 ? 1u : 0u);
                 mma_commit(&empty[s]);   // the stage is free once these MMAs have read it
+                a_lo += C::STAGE >> 4;
+                if (++s == S) { s = 0; par ^= 1u; a_lo = a_lo0; }
             }
             if (!ok) {
                 atomicExch(p.status, RB_ERR_TIMEOUT);

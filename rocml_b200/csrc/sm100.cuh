@@ -133,6 +133,31 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same descriptor as two 32-bit words.  Only the address field (the low word's bits 0-13) differs
+// between tiles laid out alike, so a loop that walks through tiles keeps the low word in a register and adds
+// to it (shared memory ends below 256 KB: the field never carries into its neighbour).
+constexpr uint32_t DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_sw128_lo(uint32_t smem_addr) {
+    return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16);
+}
+// The four MMAs of a 64-wide K block (four steps of 16 elements = 32 bytes inside the swizzle atom) in one
+// block of PTX: the lone thread that issues MMAs executes a dependent instruction every few cycles at best,
+// so what it does per stage is kept short.  `fresh` != 0: the first MMA overwrites the accumulator.
+__device__ __forceinline__ void mma_bf16_k64(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t fresh) {
+    asm volatile(
+        "{\n\t.reg .pred p, t;\n\t.reg .b64 a, b;\n\t.reg .b32 al, bl;\n\t"
+        "setp.eq.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\t"
+        "mov.b64 a, {%1, %3};\n\tmov.b64 b, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, p;\n\t"
+        "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 a, {al, %3};\n\tmov.b64 b, {bl, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, t;\n\t"
+        "add.u32 al, al, 2;\n\tadd.u32 bl, bl, 2;\n\tmov.b64 a, {al, %3};\n\tmov.b64 b, {bl, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, t;\n\t"
+        "add.u32 al, al, 2;\n\tadd.u32 bl, bl, 2;\n\tmov.b64 a, {al, %3};\n\tmov.b64 b, {bl, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, t;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_SW128_HI), "r"(fresh), "r"(idesc)
+        : "memory");
+}
 // Make `bar` complete once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

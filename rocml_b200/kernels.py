@@ -806,3 +806,4 @@ def gemm_tcgen05_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor,
         return False
     _check(rc, "gemm_tcgen05_qkv_rope")
     return True
+
