@@ -158,19 +158,25 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16_f32(BMQ, BNK);          // S = Q K^T: both K-major
             constexpr uint32_t idesc_o = idesc_bf16_f32_b_mn(BMQ, HD);      // O += P V: V is MN-major
-            const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps), v_addr = smem_u32(Vs);
+            // This lone thread executes a dependent instruction every few cycles at best, and a tile's twelve
+            // MMAs take the tensor core only 640 cycles: the descriptors are kept as low words that differ
+            // from MMA to MMA by constants (sm100.cuh: mma_bf16_lo), not built anew each time.
+            const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(Qs)), k_lo0 = smem_desc_sw128_lo(smem_u32(Ks));
+            const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(Ps));
+            // V is MN-major: leading byte offset = the distance between its two 64-dimension blocks
+            const uint32_t v_lo0 = ((smem_u32(Vs) >> 4) & 0x3FFFu) | ((uint32_t)((KV_TILE / 2) >> 4) << 16);
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1;
                 if (!mbar_wait(&bar->k_full[s], (j >> 1) & 1)) return false;
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(Ks + s * KV_TILE);
+                const uint32_t k_lo = k_lo0 + s * (KV_TILE >> 4);
+                const uint32_t d = tmem_base + s * BNK;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    // dimension block k / 4 (64 dimensions each), 32 bytes per step inside it
-                    const uint32_t qo = (k >> 2) * (Q_BYTES / 2) + (k & 3) * 32;
-                    const uint32_t ko = (k >> 2) * (KV_TILE / 2) + (k & 3) * 32;
-                    mma_bf16(tmem_base + s * BNK, smem_desc_sw128(q_addr + qo), smem_desc_sw128(k_addr + ko), idesc_s,
-                             k > 0 ? 1u : 0u);
+                    // dimension block k / 4 (64 dimensions each), 32 bytes (2 units of 16) per step inside it
+                    const uint32_t qo = (k >> 2) * ((Q_BYTES / 2) >> 4) + (k & 3) * 2;
+                    const uint32_t ko = (k >> 2) * ((KV_TILE / 2) >> 4) + (k & 3) * 2;
+                    mma_bf16_lo(d, q_lo + qo, k_lo + ko, idesc_s, k > 0 ? 1u : 0u);
                 }
                 mma_commit(&bar->k_empty[s]);
                 mma_commit(&bar->s_full[s]);
@@ -183,13 +189,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 ok = mbar_wait(&bar->p_full, j & 1) && mbar_wait(&bar->v_full[j & 1], (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_tile = v_addr + (j & 1) * KV_TILE;
+                const uint32_t v_lo = v_lo0 + (j & 1) * (KV_TILE >> 4);
 #pragma unroll
                 for (int k = 0; k < BNK / 16; ++k) {
                     // A = P [128 rows][64 keys], K-major: 32 bytes per 16 keys.  B = V [64 keys][128 dims],
                     // MN-major: 64-dimension blocks 8 KB apart, groups of 8 keys 1 KB apart, 16 keys = 2 KB.
-                    mma_bf16(tmem_base + 2 * BNK, smem_desc_sw128(p_addr + k * 32),
-                             smem_desc_sw128_ex(v_tile + k * 2048, KV_TILE / 2, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    mma_bf16_lo(tmem_base + 2 * BNK, p_lo + k * 2, v_lo + k * (2048 >> 4), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                 }
                 mma_commit(&bar->v_empty[j & 1]);
                 mma_commit(&bar->o_done);

@@ -158,6 +158,16 @@ __device__ __forceinline__ void mma_bf16_k64(uint32_t tmem_d, uint32_t a_lo, uin
         ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_SW128_HI), "r"(fresh), "r"(idesc)
         : "memory");
 }
+// One MMA from descriptor low words (the high word is DESC_SW128_HI for both operands): three instructions
+// around the MMA instead of two 64-bit descriptors built from scratch.
+__device__ __forceinline__ void mma_bf16_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\tmov.b64 a, {%1, %5};\n\tmov.b64 b, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_SW128_HI)
+        : "memory");
+}
 // Make `bar` complete once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
