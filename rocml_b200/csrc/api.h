@@ -107,6 +107,17 @@ int rb_argmax(const float* logits, long long row_stride, int rows, int V, int* o
 int rb_sample(float* logits, long long row_stride, int n, int V, const void* rows, const int* history, int* out,
               void* stream);
 
+// Reader of safetensors files (safetensors_reader.cu): open and check the header, list the tensors, copy one
+// tensor's bytes to host or device memory, close.
+void* rb_st_open(const char* path, char* err, int err_len);
+int rb_st_count(const void* handle);
+int rb_st_entry(const void* handle, int i, const char** name, const char** dtype, int* rank, long long* shape,
+                long long* nbytes);
+int rb_st_metadata_count(const void* handle);
+int rb_st_metadata(const void* handle, int i, const char** key, const char** value);
+int rb_st_read(void* handle, int i, void* dst, long long dst_bytes, int on_device, void* stream);
+void rb_st_close(void* handle);
+
 #ifdef __cplusplus
 }
 #endif

@@ -15,6 +15,7 @@
 #define RB_ERR_BAD_ALIGN 10003     // a pointer or stride that breaks an alignment rule
 #define RB_ERR_TIMEOUT 10004       // a bounded wait inside a kernel ran out
 #define RB_ERR_NO_DRIVER_FN 10005  // a driver entry point could not be found
+#define RB_ERR_IO 10006            // a file could not be read
 
 #define RB_PAGE 64  // tokens per cache page
 

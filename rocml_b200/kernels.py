@@ -27,6 +27,7 @@ _CODES = {
     10003: "a pointer or stride that breaks an alignment rule",
     10004: "a bounded wait inside a kernel ran out",
     10005: "a CUDA driver entry point could not be found",
+    10006: "a file could not be read",
 }
 
 _c = ctypes

@@ -83,8 +83,17 @@ def load_tensors(folder: str, decls: Sequence[TensorDecl], mode: str, device,
         if bad_dtype:
             raise WeightsError(other=bad_dtype)
         out = {}
+        on_gpu = torch.device(device).type == "cuda"
         for d in decls:
-            t = files.tensor(d.name)
-            dt = storage_dtype(t.dtype, mode, d.role)
-            out[d.name] = t.to(device=device, dtype=dt, non_blocking=False).contiguous()
+            ft = files.dtype(d.name)
+            dt = storage_dtype(ft, mode, d.role)
+            if on_gpu:
+                # file -> pinned staging -> device by the library's own reader; a conversion, if the storage
+                # rule asks for one, happens on the device
+                with torch.cuda.device(device):
+                    raw = torch.empty(files.shape(d.name), dtype=ft, device=device)
+                    files.read_into(d.name, raw)
+                    out[d.name] = raw if ft == dt else raw.to(dt)
+            else:
+                out[d.name] = files.tensor(d.name).to(device=device, dtype=dt, non_blocking=False).contiguous()
         return out

@@ -79,6 +79,7 @@ class SafetensorsFile:
                 )
             self._entries[name] = (dtype, shape, b, en)
         self._mm = None
+        self._native = None
 
     def names(self) -> List[str]:
         return list(self._entries)
@@ -103,10 +104,90 @@ class SafetensorsFile:
         t = torch.frombuffer(self._mm, dtype=dtype, count=n, offset=self._base + b)
         return t.view(shape)
 
+    def read_into(self, name: str, dst: torch.Tensor) -> None:
+        """Fill ``dst`` (a contiguous tensor of the tensor's shape and stored type, on a CUDA device) with the
+        tensor's bytes, through the library's own reader: file -> pinned staging -> device on the current
+        stream, without a Python object in between (``csrc/safetensors_reader.cu``)."""
+        dtype, shape, b, en = self._entries[name]
+        if dst.dtype != dtype or tuple(dst.shape) != shape or not dst.is_contiguous() or not dst.is_cuda:
+            raise SafetensorsError(f"{self.path}: destination for {name!r} must be a contiguous CUDA tensor {dtype} {list(shape)}")
+        if self._native is None:
+            self._native = NativeReader(self.path)
+        self._native.read(name, dst, en - b)
+
     def close(self) -> None:
         # Tensors handed out keep the mapping alive through the buffer protocol.
         self._mm = None
         self._f.close()
+        if self._native is not None:
+            self._native.close()
+            self._native = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+class NativeReader:
+    """The library's reader of one safetensors file (``csrc/safetensors_reader.cu``): it parses and checks the
+    header itself, and copies a tensor's bytes to host or device memory."""
+
+    def __init__(self, path: str):
+        import ctypes
+        from ..csrc.build import library
+        self._c = ctypes
+        lib = self._lib = library()
+        if not getattr(lib, "_st_sigs", False):
+            vp, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+            lib.rb_st_open.argtypes = [ctypes.c_char_p, ctypes.c_char_p, i]
+            lib.rb_st_open.restype = vp
+            lib.rb_st_count.argtypes = [vp]
+            lib.rb_st_entry.argtypes = [vp, i, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_char_p),
+                                        ctypes.POINTER(i), ctypes.POINTER(ll), ctypes.POINTER(ll)]
+            lib.rb_st_metadata_count.argtypes = [vp]
+            lib.rb_st_metadata.argtypes = [vp, i, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_char_p)]
+            lib.rb_st_read.argtypes = [vp, i, vp, ll, i, vp]
+            lib.rb_st_close.argtypes = [vp]
+            lib.rb_st_close.restype = None
+            lib._st_sigs = True
+        err = ctypes.create_string_buffer(1024)
+        self._h = lib.rb_st_open(os.fsencode(path), err, len(err))
+        if not self._h:
+            raise SafetensorsError(err.value.decode("utf-8", "replace"))
+        self.path = path
+        self.entries: Dict[str, Tuple[int, str, Tuple[int, ...], int]] = {}     # name -> (index, dtype, shape, bytes)
+        name, dtype = ctypes.c_char_p(), ctypes.c_char_p()
+        rank, nbytes, shape = ctypes.c_int(), ctypes.c_longlong(), (ctypes.c_longlong * 8)()
+        for k in range(lib.rb_st_count(self._h)):
+            if lib.rb_st_entry(self._h, k, ctypes.byref(name), ctypes.byref(dtype), ctypes.byref(rank), shape,
+                               ctypes.byref(nbytes)) != 0:
+                self.close()
+                raise SafetensorsError(f"{path}: a tensor of more than 8 dimensions")
+            self.entries[name.value.decode("utf-8")] = (k, dtype.value.decode("ascii"), tuple(shape[:rank.value]), nbytes.value)
+        self.metadata = {}
+        key, value = ctypes.c_char_p(), ctypes.c_char_p()
+        for k in range(lib.rb_st_metadata_count(self._h)):
+            lib.rb_st_metadata(self._h, k, ctypes.byref(key), ctypes.byref(value))
+            self.metadata[key.value.decode("utf-8")] = value.value.decode("utf-8")
+
+    def read(self, name: str, dst: torch.Tensor, nbytes: int) -> None:
+        index, _, _, have = self.entries[name]
+        if have != nbytes or dst.numel() * dst.element_size() != nbytes:
+            raise SafetensorsError(f"{self.path}: tensor {name!r} holds {have} bytes, asked for {nbytes}")
+        if dst.is_cuda:
+            stream = self._c.c_void_p(torch._C._cuda_getCurrentRawStream(dst.device.index or 0))
+            rc = self._lib.rb_st_read(self._h, index, self._c.c_void_p(dst.data_ptr()), nbytes, 1, stream)
+        else:
+            rc = self._lib.rb_st_read(self._h, index, self._c.c_void_p(dst.data_ptr()), nbytes, 0, None)
+        if rc != 0:
+            raise SafetensorsError(f"{self.path}: reading tensor {name!r} failed (code {rc})")
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.rb_st_close(self._h)
+            self._h = None
 
     def __enter__(self):
         return self
@@ -198,6 +279,9 @@ class ModelFiles:
 
     def tensor(self, name: str) -> torch.Tensor:
         return self._where[name].tensor(name)
+
+    def read_into(self, name: str, dst: torch.Tensor) -> None:
+        self._where[name].read_into(name, dst)
 
     def close(self):
         for f in self._files:

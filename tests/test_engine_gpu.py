@@ -337,3 +337,26 @@ def test_three_hundred_short_sequences_at_once(tmp_path, dtype):
     for sl in slots:
         eng.release(sl)
     eng.cache.check_invariants()
+
+
+@pytest.mark.gpu
+def test_weights_reach_the_device_through_the_library_reader(tmp_path):
+    """File -> pinned staging -> device by the library's own reader: tensors larger than a staging buffer
+    (64 MB), of odd sizes, several in a row on one handle, and a conversion on the device afterwards."""
+    from rocml_b200.weights import ModelFiles, save_state_dict
+    g = torch.Generator().manual_seed(5)
+    state = {"big": torch.randn((5000, 4099), generator=g).bfloat16(),          # 41 MB
+             "odd": torch.randn((1234567,), generator=g),                       # 4.9 MB float32
+             "bigger": torch.randint(-100, 100, (5, 33_000_001), generator=g, dtype=torch.int8),   # 165 MB: three pieces
+             "small": torch.randn((3, 5), generator=g).half(), "none": torch.zeros((0, 7))}
+    save_state_dict(str(tmp_path / "model.safetensors"), state)
+    with ModelFiles(str(tmp_path)) as files:
+        got = {}
+        for k, v in state.items():
+            got[k] = torch.empty(v.shape, dtype=v.dtype, device="cuda")
+            files.read_into(k, got[k])
+        half = got["small"].to(torch.bfloat16)
+    torch.cuda.synchronize()
+    for k, v in state.items():
+        assert torch.equal(got[k].cpu(), v), k
+    assert torch.equal(half.cpu(), state["small"].to(torch.bfloat16))

@@ -9,7 +9,7 @@ import torch
 from rocml_b200.config import config_from_dict
 from rocml_b200.engine import declared_tensors
 from rocml_b200.errors import ModelFileMissing, SafetensorsError, WeightsError
-from rocml_b200.weights import (ModelFiles, SafetensorsFile, load_tensors, save_state_dict, storage_dtype,
+from rocml_b200.weights import (ModelFiles, NativeReader, SafetensorsFile, load_tensors, save_state_dict, storage_dtype,
                                 write_random_model)
 from tiny_models import TINY_A, TINY_B
 
@@ -141,3 +141,76 @@ def test_sharded_folder(tmp_path):
         "x": "model-00001-of-00002.safetensors", "y": "model-00002-of-00002.safetensors"}}))
     with ModelFiles(str(tmp_path)) as f:
         assert sorted(f.names()) == ["x", "y"] and torch.equal(f.tensor("y"), a["y"])
+
+
+def _needs_library():
+    """The reader below is part of the kernel library, which nvcc builds at first use (it needs no GPU)."""
+    from rocml_b200.csrc.build import library
+    from rocml_b200.errors import ExtensionMissing
+    try:
+        library()
+    except ExtensionMissing as e:
+        pytest.skip(f"the kernel library cannot be built here: {str(e)[:80]}")
+
+
+def test_the_library_reader_agrees_with_the_python_reader(tmp_path):
+    """The reader inside the kernel library (C++: header parsed and checked there, bytes copied by it) lists the
+    same tensors and hands out the same bytes; names with escapes and other alphabets, metadata, an empty
+    tensor and every stored type the loader takes."""
+    state = {"a.weight": torch.randn(3, 5).bfloat16(), "b": torch.arange(7, dtype=torch.int64),
+             'émb "q" \\ \n': torch.randn(2, 2, 2), "empty": torch.zeros(0, 4), "h": torch.randn(9).half(),
+             "i8": torch.arange(-3, 3, dtype=torch.int8), "flag": torch.tensor([True, False])}
+    p = str(tmp_path / "x.safetensors")
+    save_state_dict(p, state, {"format": "pt", "note": "two\nlines \u00e9"})
+    with SafetensorsFile(p) as f, NativeReader(p) as r:
+        assert r.metadata == f.metadata
+        assert set(r.entries) == set(f.names())
+        for k, v in state.items():
+            _, dtype, shape, nbytes = r.entries[k]
+            assert shape == tuple(v.shape) and nbytes == v.numel() * v.element_size()
+            dst = torch.empty_like(v)
+            r.read(k, dst, nbytes)
+            assert torch.equal(dst, v) and torch.equal(dst, f.tensor(k))
+        with pytest.raises(SafetensorsError, match="bytes"):
+            r.read("b", torch.empty(3, dtype=torch.int64), 24)
+
+
+def test_the_library_reader_refuses_what_the_python_reader_refuses(tmp_path):
+    _needs_library()
+    p = str(tmp_path / "x.safetensors")
+    save_state_dict(p, {"a": torch.zeros(100)})
+    raw = open(p, "rb").read()
+    open(p, "wb").write(raw[:-8])
+    with pytest.raises(SafetensorsError, match="truncated"):
+        NativeReader(p)
+    open(p, "wb").write(raw[:4])
+    with pytest.raises(SafetensorsError, match="too short"):
+        NativeReader(p)
+    open(p, "wb").write(struct.pack("<Q", 5) + b"{nope")
+    with pytest.raises(SafetensorsError, match="not valid"):
+        NativeReader(p)
+    with pytest.raises(SafetensorsError, match="cannot open"):
+        NativeReader(str(tmp_path / "nowhere.safetensors"))
+
+    def with_header(header, data=b""):
+        blob = json.dumps(header).encode()
+        open(p, "wb").write(struct.pack("<Q", len(blob)) + blob + data)
+    with_header({"a": {"dtype": "F32", "shape": [2, 3], "data_offsets": [0, 20]}}, b"\0" * 24)
+    with pytest.raises(SafetensorsError, match="shape needs 24"):
+        NativeReader(p)
+    with_header({"a": {"dtype": "Q4", "shape": [2], "data_offsets": [0, 2]}}, b"\0" * 2)
+    with pytest.raises(SafetensorsError, match="unknown element type"):
+        NativeReader(p)
+    with_header({"a": {"dtype": "F32", "shape": [2]}}, b"\0" * 8)
+    with pytest.raises(SafetensorsError, match="lacks"):
+        NativeReader(p)
+    with_header({"a": {"dtype": "F32", "shape": [1.5], "data_offsets": [0, 4]}}, b"\0" * 4)
+    with pytest.raises(SafetensorsError, match="integer"):
+        NativeReader(p)
+    with_header([1, 2, 3])
+    with pytest.raises(SafetensorsError, match="not a JSON object"):
+        NativeReader(p)
+    # keys the format does not know are skipped, whatever their values
+    with_header({"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4], "extra": {"x": [1, 2.5, None, True, "s"]}}}, b"\0" * 4)
+    with NativeReader(p) as r:
+        assert r.entries["a"][1:] == ("F32", (1,), 4)
