@@ -80,3 +80,55 @@ def test_a_random_configuration(seed, tmp_path):
                     eng.release(slots[j])
         eng.cache.check_invariants()
         assert eng.cache.slots.n_held == 0
+
+
+MEDIUM = [
+    # widths from which the products of a long prompt run in the tensor-core kernels for many rows, whose
+    # epilogues add into the residual, prepare the next norm and apply its 1/RMS; none a multiple of 256
+    dict(hidden_size=320, intermediate_size=544, num_attention_heads=4, num_key_value_heads=2, head_dim=80,
+         attention_bias=False, rms_norm_eps=1e-6, tie_word_embeddings=True),
+    dict(hidden_size=520, intermediate_size=1040, num_attention_heads=4, num_key_value_heads=1, head_dim=128,
+         attention_bias=True, rms_norm_eps=3e-3, tie_word_embeddings=False),
+]
+
+
+@pytest.mark.parametrize("which", range(len(MEDIUM)))
+@pytest.mark.parametrize("piece", [4096, 600])
+def test_long_prompts_at_medium_widths(which, piece, tmp_path, monkeypatch):
+    """Prompts of 700, 300 and 45 tokens in one step (and cut into pieces of 600): more than 256 rows a
+    product, so the layer runs without norm kernels where the sizes allow; then a few tokens one by one."""
+    from plain_qwen3 import PlainQwen3
+    from rocml_b200 import Engine, StepEntry
+    cfg = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, vocab_size=777, max_position_embeddings=1024,
+               rope_theta=1e6, hidden_act="silu", **MEDIUM[which])
+    folder = str(tmp_path / "m")
+    write_model(folder, cfg, seed=40 + which, std=0.05)
+    plain = PlainQwen3(folder, dtype=torch.float64)
+    lens, n_dec = [700, 300, 45], 3
+    seqs = [prompt(900 + j, n + n_dec, cfg["vocab_size"]) for j, n in enumerate(lens)]
+    want = [plain.logits(s) for s in seqs]
+    places = [[0, n // 2, n - 2, n - 1] for n in lens]
+    from rocml_b200 import kernels
+    norms = []
+    real = kernels.add_rmsnorm
+    monkeypatch.setattr(kernels, "add_rmsnorm", lambda *a, **k: (norms.append(1), real(*a, **k))[1])
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=2048, max_slots=3, max_step_tokens=piece)
+        slots = [eng.new_sequence() for _ in seqs]
+        del norms[:]
+        out = eng.step([StepEntry(sl, s[:n], w) for sl, s, n, w in zip(slots, seqs, lens, places)])
+        err = rel_err(out, torch.cat([w[pl] for w, pl in zip(want, places)]))
+        assert err < TOL[dtype], f"{dtype} prompts (pieces of {piece}): {err}"
+        if dtype == "bfloat16" and piece == 4096:
+            # the first layer's first norm and the final norm; the others are prepared by the products, except after
+            # the second configuration's down-projections, whose sum over K is split in two for this many rows
+            assert len(norms) == (2, 4)[which], norms
+        if dtype == "float32" and piece == 4096:
+            assert len(norms) == 2 * 3 + 1
+        for t in range(n_dec):
+            out = eng.step([StepEntry(sl, [s[n + t]], [0]) for sl, s, n in zip(slots, seqs, lens)])
+            err = rel_err(out, torch.stack([w[n + t] for w, n in zip(want, lens)]))
+            assert err < TOL[dtype], f"{dtype} token {t}: {err}"
+        for sl in slots:
+            eng.release(sl)
+        eng.cache.check_invariants()
