@@ -166,6 +166,16 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
     const int pos = positions[t];
     const int n_heads = min(HPW, heads_total - h0);
     const IT* src = in + (size_t)t * row_stride + (size_t)h0 * hd + lane * 4;
+    // What depends on the token alone is asked for before the heads' values, so that everything is in flight
+    // together: its angles, and the page of its key and value if this warp holds any.
+    float4 cs_a = make_float4(1.f, 0.f, 1.f, 0.f), cs_b = cs_a;
+    if (inv_freq && cs_table) {
+        const float4* c4 = reinterpret_cast<const float4*>(cs_table + (size_t)t * 64 + (lane & 15) * 4);
+        cs_a = c4[0];
+        cs_b = c4[1];
+    }
+    int page = -2;
+    if (write_kv && h0 + n_heads > nq) page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
     // every head's values: the loads of all heads (and of up to 8 partial sums each) are in flight together
     float v[HPW][4];
 #pragma unroll
@@ -203,15 +213,13 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
     float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
     if (inv_freq) {
         if (cs_table) {
-            const float4* c4 = reinterpret_cast<const float4*>(cs_table + (size_t)t * 64 + (lane & 15) * 4);
-            const float4 a = c4[0], b = c4[1];
+            const float4 a = cs_a, b = cs_b;
             cs[0] = a.x; sn[0] = a.y; cs[1] = a.z; sn[1] = a.w; cs[2] = b.x; sn[2] = b.y; cs[3] = b.z; sn[3] = b.w;
         } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) sincosf((float)pos * inv_freq[(lane & 15) * 4 + j], &sn[j], &cs[j]);
         }
     }
-    int page = -2;                                              // looked up when the first key or value comes
 #pragma unroll
     for (int j = 0; j < HPW; ++j) {
         if (j >= n_heads) continue;
@@ -221,7 +229,6 @@ qk_norm_rope_cache_hd128_kernel(const IT* __restrict__ in, int n_in, size_t in_s
         if (kind == 0) {
             dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
         } else {
-            if (page == -2) page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
             if (page < 0) continue;                             // no page: the host never schedules this
             const int head = kind == 1 ? h - nq : h - nq - nkv;
             dst = (kind == 1 ? k_cache : v_cache) + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hd;
