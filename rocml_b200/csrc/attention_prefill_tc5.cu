@@ -221,8 +221,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             tc_fence_after();
             const int key0 = (kt_first + j) * BNK;
             float sv[BNK];
-#pragma unroll
-            for (int c = 0; c < BNK / 16; ++c) tmem_ld16(lane_base + s * BNK + c * 16, sv + c * 16);
+            static_assert(BNK == 64, "one load of 64 columns");
+            tmem_ld64(lane_base + s * BNK, sv);
             // The softmax threads are bound by the instructions they issue.  Scores stay raw: the scale is
             // positive, so the maximum is taken first (three inputs an instruction) and the scale is
             // folded into the exponent's multiply-add, p = 2^(s * scale * log2 e - m), with the bare
