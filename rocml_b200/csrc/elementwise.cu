@@ -22,6 +22,34 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const WT* __restri
         return;
     }
     const WT* row = table + (size_t)id * H;
+    if (sizeof(WT) == 2 && H % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+        // 16 bytes a load, and a thread's loads all requested before the first is used: a row of a table of a
+        // gigabyte comes from memory, and loads taken one after the other would each wait for it
+        constexpr int UNROLL = 4;
+        const int n8 = H / 8;
+        for (int i0 = threadIdx.x; i0 < n8; i0 += blockDim.x * UNROLL) {
+            uint4 raw[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int i = i0 + u * blockDim.x;
+                raw[u] = i < n8 ? reinterpret_cast<const uint4*>(row)[i] : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int i = i0 + u * blockDim.x;
+                if (i >= n8) continue;
+                const uint32_t ws[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                float4 lo, hi;
+                lo.x = __uint_as_float(ws[0] << 16); lo.y = __uint_as_float(ws[0] & 0xFFFF0000u);
+                lo.z = __uint_as_float(ws[1] << 16); lo.w = __uint_as_float(ws[1] & 0xFFFF0000u);
+                hi.x = __uint_as_float(ws[2] << 16); hi.y = __uint_as_float(ws[2] & 0xFFFF0000u);
+                hi.z = __uint_as_float(ws[3] << 16); hi.w = __uint_as_float(ws[3] & 0xFFFF0000u);
+                reinterpret_cast<float4*>(o)[2 * i] = lo;
+                reinterpret_cast<float4*>(o)[2 * i + 1] = hi;
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
 }
 
