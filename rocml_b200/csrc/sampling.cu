@@ -64,9 +64,18 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, long lon
     const float* row = logits + (size_t)blockIdx.y * row_stride;
     const int lo = blockIdx.x * per, hi = min(V, lo + per);
     Best b{-INFINITY, 0x7fffffff};
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const float v = row[i];
-        if (v > b.v) { b.v = v; b.i = i; }
+    // eight loads a thread in flight, compared in index order: taken one by one each would wait for the one before
+    constexpr int UNROLL = 8;
+    for (int i0 = lo + threadIdx.x; i0 < hi; i0 += blockDim.x * UNROLL) {
+        float v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int i = i0 + u * blockDim.x;
+            v[u] = i < hi ? row[i] : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+            if (v[u] > b.v) { b.v = v[u]; b.i = i0 + u * blockDim.x; }
     }
     b = warp_best(b);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
