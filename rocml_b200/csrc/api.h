@@ -53,19 +53,10 @@ int rb_gemm_tcgen05_qkv_rope(const void* x, const void* w, const float* bias, in
                              void* q_out, long long q_ld, void* k_cache, void* v_cache, const int* positions,
                              const int* slot_of_token, const int* block_table, int max_pages, const void* q_norm_w,
                              const void* k_norm_w, int norm_w_f32, float norm_eps, const float* cos_sin, int nq,
-                             int nkv, const float* row_sumsq, int row_groups, long long row_sumsq_ld, float row_eps,
-                             int row_width, int stages, int* status, void* stream);
+                             int nkv, int stages, int* status, void* stream);
 
 int rb_gemm_tcgen05_add(const void* x, const void* w, const float* bias, float* resid, int M, int N, int K,
                         long long ldx, long long ld_resid, int stages, int* status, void* stream);
-
-int rb_gemm_tcgen05_add_norm(const void* x, const void* w, const float* bias, float* resid, int M, int N, int K,
-                             long long ldx, long long ld_resid, const void* next_w, int next_w_f32, void* xhat,
-                             long long ld_xhat, float* sumsq, long long ld_sumsq, int stages, int* status, void* stream);
-
-int rb_gemm_tcgen05_scaled(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M, int N,
-                           int K, long long ldx, long long ldo, int gated, const float* row_sumsq, int row_groups,
-                           long long row_sumsq_ld, float row_eps, int row_width, int stages, int* status, void* stream);
 
 int rb_attention_generic(const void* q, int q_stride, void* out, int o_stride, int dtype, const void* k_cache,
                          const void* v_cache, const int* block_table, int max_pages, const int* seq_slot,

@@ -245,18 +245,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         parts_hi = x_last - x_first;
         seq_start += P;                                     // the round after this one starts at the next sequence
         ++seq_next;
-    } else if (CL) {
-        // The blocks of a cluster share the pages that THIS sequence visits equally: the launch is sized for the
-        // longest context it may meet (a captured step serves a range of lengths), and blocks of `ppb` pages
-        // each would leave the last ones idle and the first ones with more pages than they need hold.
-        const int first = win_lo / CHUNK, P = pos / CHUNK - first + 1, n = (int)gridDim.x;
-        page_first = first + (int)((long long)c * P / n);
-        page_last = first + (int)((long long)(c + 1) * P / n) - 1;      // below page_first: an empty result
-        parts_lo = parts_hi = 0;                                         // a cluster merges through shared memory
     } else {
         page_first = c * ppb;
-        // beyond the sequence: takes no part in the merge
-        if (page_first * CHUNK > pos) return;
+        // beyond the sequence: takes no part in the merge; in a cluster it stays, with an empty result
+        if (!CL && page_first * CHUNK > pos) return;
         page_last = min(pos / CHUNK, page_first + ppb - 1);
         parts_hi = pos / (CHUNK * ppb);
         parts_lo = win_lo / (CHUNK * ppb);

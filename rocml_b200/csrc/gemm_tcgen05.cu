@@ -796,24 +796,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint32_t lane_addr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
             const bool vec_ok = (((uintptr_t)out | ((uintptr_t)p.ldo * sizeof(OT))) & 15) == 0;
             OT* row = out + (size_t)(ar < p.a_rows ? ar : 0) * p.ldo;
-            // The input rows may still lack their norm's 1/RMS (they are residual * norm weight, see EPI 3
-            // below): the product is scaled by it instead, from the shares of the rows' sums of squares.
-            float rs = 1.f;
-            if (EPI != 3 && p.row_sumsq != nullptr) {
-                rb::pdl_wait();   // written by the kernel before this one: returns at once by now
-                float acc_ss = 0.f;
-                if (ar < p.a_rows) {
-                    for (int g0 = 0; g0 < p.row_groups; g0 += 8) {      // eight loads in flight, not one after another
-                        float sh[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            sh[j] = g0 + j < p.row_groups ? p.row_sumsq[(size_t)(g0 + j) * p.row_sumsq_ld + ar] : 0.f;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) acc_ss += sh[j];
-                    }
-                }
-                rs = rsqrtf(acc_ss * p.row_inv_width + p.row_eps);
-            }
             if (EPI == 2) {
                 rb::pdl_wait();   // these threads read what an earlier kernel wrote (the angles' table): returns at once by now
                 int slot = -1, pos = 0, page = -2;         // page -2: not looked up yet
@@ -847,7 +829,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                             tmem_ld16(hbase + c * 16, v);
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
-                                const float x = v[i] * rs + (add_bias ? p.bias[col0 + c * 16 + i] : 0.f);
+                                const float x = v[i] + (add_bias ? p.bias[col0 + c * 16 + i] : 0.f);
                                 ss += x * x;
                             }
                         }
@@ -862,7 +844,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const int d = c * 16 + i;
-                            float a = lo[i] * rs, b = hi[i] * rs;
+                            float a = lo[i], b = hi[i];
                             if (add_bias) { a += p.bias[col0 + d]; b += p.bias[col0 + 64 + d]; }
                             if (w != nullptr) {
                                 const float wa = p.norm_w_f32 ? static_cast<const float*>(w)[d]
@@ -893,8 +875,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     tmem_ld16(lane_addr + (c + 1) * 16, u);
                     const int f0 = b0 + c * 16;
                     if (ar < p.a_rows && f0 + 32 <= p.b_rows) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) { g[i] *= rs; u[i] *= rs; }
                         if (add_bias) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) { g[i] += p.bias[f0 + i]; u[i] += p.bias[f0 + 16 + i]; }
@@ -915,13 +895,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 // requested before the accumulator is read, so their latency overlaps it.
                 if constexpr (std::is_same<OT, float>::value) {
                     rb::pdl_wait();   // these threads read what earlier kernels wrote (the residual): returns at once by now
-                    // With p.xhat the norm that follows is prepared too, as the few-token kernels do it (CS >= 4
-                    // above): xhat = new residual * norm weight in bfloat16, and this tile's share of the row's sum
-                    // of squares; the consumer scales its product by the row's 1/RMS (`rs` above).
-                    float ss = 0.f;
-                    __nv_bfloat16* xrow = p.xhat != nullptr ? p.xhat + (size_t)(ar < p.a_rows ? ar : 0) * p.xhat_ld : nullptr;
-                    const bool xvec = xrow != nullptr && (((uintptr_t)p.xhat | ((uintptr_t)p.xhat_ld * 2)) & 15) == 0;
-                    const bool wvec = ((uintptr_t)p.next_w & 15) == 0;
 #pragma unroll 1
                     for (int c = 0; c < BN / 16; c += 2) {
                         const int f0 = b0 + c * 16;
@@ -946,65 +919,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                 store16(row + f0 + 16, v + 16);
                             } else {
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) {
-                                    if (f0 + i < p.b_rows) { v[i] += row[f0 + i]; row[f0 + i] = v[i]; }
-                                    else v[i] = 0.f;
-                                }
-                            }
-                            if (xrow != nullptr) {
-                                float wn[32];
-                                if (wvec && f0 + 32 <= p.b_rows) {          // the norm's weights of these 32 columns as 16-byte loads
-                                    if (p.next_w_f32) {
-                                        load16(static_cast<const float*>(p.next_w) + f0, wn);
-                                        load16(static_cast<const float*>(p.next_w) + f0 + 16, wn + 16);
-                                    } else {
-                                        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.next_w) + f0);
-#pragma unroll
-                                        for (int j = 0; j < 4; ++j) {
-                                            const uint4 u = src[j];
-                                            const uint32_t ws[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                                            for (int e = 0; e < 4; ++e) {
-                                                wn[j * 8 + e * 2] = __uint_as_float(ws[e] << 16);
-                                                wn[j * 8 + e * 2 + 1] = __uint_as_float(ws[e] & 0xFFFF0000u);
-                                            }
-                                        }
-                                    }
-                                } else {
-#pragma unroll
-                                    for (int i = 0; i < 32; ++i) {
-                                        const int n = f0 + i < p.b_rows ? f0 + i : 0;
-                                        wn[i] = p.next_w_f32 ? static_cast<const float*>(p.next_w)[n]
-                                                             : __bfloat162float(static_cast<const __nv_bfloat16*>(p.next_w)[n]);
-                                    }
-                                }
-#pragma unroll
-                                for (int i = 0; i < 32; ++i) {
-                                    ss += v[i] * v[i];
-                                    v[i] *= wn[i];
-                                }
-                                if (xvec && f0 + 32 <= p.b_rows) {
-                                    store16(xrow + f0, v);
-                                    store16(xrow + f0 + 16, v + 16);
-                                } else {
-#pragma unroll
-                                    for (int i = 0; i < 32; ++i)
-                                        if (f0 + i < p.b_rows) xrow[f0 + i] = __float2bfloat16_rn(v[i]);
-                                }
+                                for (int i = 0; i < 32; ++i)
+                                    if (f0 + i < p.b_rows) row[f0 + i] += v[i];
                             }
                         }
                     }
-                    if (p.sumsq != nullptr && ar < p.a_rows) p.sumsq[(size_t)(tile / m_pairs) * p.sumsq_ld + ar] = ss;
                 }
-            } else {
+} else {
 #pragma unroll 1
                 for (int c = 0; c < BN / 16; ++c) {
                     float v[16];
                     tmem_ld16(lane_addr + c * 16, v);
                     const int f0 = b0 + c * 16;
                     if (ar < p.a_rows) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] *= rs;
                         if (add_bias) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) v[i] += (f0 + i < p.b_rows) ? p.bias[f0 + i] : 0.f;
@@ -1289,21 +1216,13 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
     }
     p.row_sumsq = nullptr; p.row_groups = 0; p.row_sumsq_ld = 0; p.row_eps = 0.f; p.row_inv_width = 0.f;
     if (rsc != nullptr && rsc->sumsq != nullptr) {
-        // the deferred 1/RMS is applied by the two-block gated kernel (few rows) and by the kernel of CTA pairs (many)
-        const bool pairs = cluster_split == 0 && !swap && splits == 1 && bn == 256 && M > 256 && pair_enabled() && !accumulate;
-        if ((cluster_split != 2 && !pairs) || rsc->groups < 1 || rsc->width < 1) return RB_ERR_BAD_SIZE;
+        if (cluster_split != 2 || rsc->groups < 1 || rsc->width < 1) return RB_ERR_BAD_SIZE;
         p.row_sumsq = rsc->sumsq; p.row_groups = rsc->groups; p.row_sumsq_ld = rsc->ld;
         p.row_eps = rsc->eps; p.row_inv_width = 1.f / (float)rsc->width;
     }
     p.resid = nullptr; p.next_w = nullptr; p.xhat = nullptr; p.sumsq = nullptr;
     p.resid_ld = p.xhat_ld = p.sumsq_ld = 0; p.next_w_f32 = 0;
-    if (ro != nullptr && accumulate) {
-        // many rows: the kernel of CTA pairs adds into `out` (the residual) and prepares the norm that follows
-        if (ro->xhat == nullptr || ro->next_w == nullptr || ro->sumsq == nullptr) return RB_ERR_BAD_SIZE;
-        p.next_w = ro->next_w; p.next_w_f32 = ro->next_w_f32;
-        p.xhat = static_cast<__nv_bfloat16*>(ro->xhat); p.xhat_ld = ro->xhat_ld;
-        p.sumsq = ro->sumsq; p.sumsq_ld = ro->sumsq_ld;
-    } else if (ro != nullptr) {
+    if (ro != nullptr) {
         if (!swap || bn > 64 || kb_total < cluster_split || ro->resid == nullptr) return RB_ERR_BAD_SIZE;
         if (ro->xhat != nullptr && ro->next_w == nullptr) return RB_ERR_BAD_SIZE;
         p.resid = ro->resid; p.resid_ld = ro->resid_ld;
@@ -1406,31 +1325,6 @@ extern "C" int rb_gemm_tcgen05_add(const void* x, const void* w, const float* bi
                       nullptr, nullptr, true);
 }
 
-// The same, and the norm that follows prepared (as rb_gemm_tcgen05_residual does for few rows): xhat[M, N] =
-// bfloat16(resid * next_w) and sumsq[ceil(N / 256) groups][>= M], each group's share of the new rows' sums of
-// squares (group g at sumsq + g * ld_sumsq).  Same refusals as rb_gemm_tcgen05_add.
-extern "C" int rb_gemm_tcgen05_add_norm(const void* x, const void* w, const float* bias, float* resid, int M, int N,
-                                        int K, long long ldx, long long ld_resid, const void* next_w, int next_w_f32,
-                                        void* xhat, long long ld_xhat, float* sumsq, long long ld_sumsq, int stages,
-                                        int* status, void* stream) {
-    ResidualOut ro{resid, ld_resid, next_w, next_w_f32, xhat, ld_xhat, sumsq, ld_sumsq};
-    return gemm_entry(x, w, bias, resid, RB_F32, M, N, K, ldx, ld_resid, 1, 0, stages, 0, status, stream, 0, &ro,
-                      nullptr, nullptr, true);
-}
-
-// rb_gemm_tcgen05 for more than 256 rows and N >= 256 (one split) whose input rows are a residual times a norm's
-// weight, not yet divided by their RMS over `row_width` values: the product is scaled by
-// rsqrt(sum of the row's row_groups shares / row_width + row_eps) before the bias (and before the gated
-// activation).  RB_ERR_BAD_SIZE for other sizes (the caller normalises the rows first).
-extern "C" int rb_gemm_tcgen05_scaled(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
-                                      int N, int K, long long ldx, long long ldo, int gated, const float* row_sumsq,
-                                      int row_groups, long long row_sumsq_ld, float row_eps, int row_width, int stages,
-                                      int* status, void* stream) {
-    if (row_sumsq == nullptr) return RB_ERR_BAD_SIZE;
-    RowScale rsc{row_sumsq, row_groups, row_sumsq_ld, row_eps, row_width};
-    return gemm_entry(x, w, bias, out, out_dtype, M, N, K, ldx, ldo, 1, 0, stages, gated, status, stream, 0, nullptr, &rsc);
-}
-
 // h[M, N / 2] = silu(gate) * up (bfloat16, row stride ldh) for at most 32 rows and a gate/up weight
 // whose rows alternate in blocks of 16, with the sum over K done in two halves by the two blocks of a
 // thread-block cluster (see the kernel).  With row_sumsq (shares [row_groups][>= M] of the sums of squares
@@ -1468,20 +1362,16 @@ extern "C" int rb_gemm_tcgen05_residual(const void* x, const void* w, const floa
 // [M][64] pairs, or null), queries go to q_out [M][nq * 128] (row stride q_ld), keys and values into
 // their pages (k_cache, v_cache [pages][nkv][64][128]; the page of token t is
 // block_table[slot_of_token[t]][positions[t] / 64]; tokens with a negative slot are skipped).
-// With row_sumsq the input rows still lack their norm's 1/RMS (see rb_gemm_tcgen05_scaled): the product is
-// scaled by it before anything else.
 // RB_ERR_BAD_SIZE when the sizes do not fit this kernel (the caller runs the product and the
 // rotation kernel one after the other), RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
 extern "C" int rb_gemm_tcgen05_qkv_rope(const void* x, const void* w, const float* bias, int M, int N, int K,
                                         long long ldx, void* q_out, long long q_ld, void* k_cache, void* v_cache,
                                         const int* positions, const int* slot_of_token, const int* block_table,
                                         int max_pages, const void* q_norm_w, const void* k_norm_w, int norm_w_f32,
-                                        float norm_eps, const float* cos_sin, int nq, int nkv,
-                                        const float* row_sumsq, int row_groups, long long row_sumsq_ld, float row_eps,
-                                        int row_width, int stages, int* status, void* stream) {
+                                        float norm_eps, const float* cos_sin, int nq, int nkv, int stages,
+                                        int* status, void* stream) {
     RopeOut rope{q_out, q_ld, k_cache, v_cache, positions, slot_of_token, block_table, max_pages,
                  q_norm_w, k_norm_w, norm_w_f32, norm_eps, cos_sin, nq, nkv};
-    RowScale rsc{row_sumsq, row_groups, row_sumsq_ld, row_eps, row_width};
     return gemm_entry(x, w, bias, nullptr, RB_BF16, M, N, K, ldx, 0, 1, 0, stages, 0, status, stream, 0, nullptr,
-                      row_sumsq != nullptr ? &rsc : nullptr, &rope);
+                      nullptr, &rope);
 }

@@ -151,11 +151,7 @@ def _lib():
         lib.rb_gemm_tcgen05_add.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_gated_pair.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _i, _ll, _f, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_qkv_rope.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _vp,
-                                                 _vp, _i, _f, _vp, _i, _i, _vp, _i, _ll, _f, _i, _i, _vp, _vp]
-        lib.rb_gemm_tcgen05_add_norm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _i, _vp, _ll, _vp, _ll, _i,
-                                                 _vp, _vp]
-        lib.rb_gemm_tcgen05_scaled.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _vp, _i, _ll, _f, _i, _i,
-                                               _vp, _vp]
+                                                 _vp, _i, _f, _vp, _i, _i, _i, _vp, _vp]
         lib.rb_gemm_tcgen05_residual.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _ll, _vp, _i, _vp, _ll, _vp,
                                                  _ll, _i, _vp, _vp]
         lib.rb_hold.argtypes = [_ll, _vp]
@@ -421,9 +417,6 @@ def decode_split(n_seqs: int, n_kv_groups: int, n_pages: int, device=0):
     # more than 16 blocks would merge through global memory, which costs more than the longer blocks
     # of a cluster do (one sequence of 8,192 tokens: 15 us with 16 blocks of 8 pages, 26 us with 43 of 3;
     # at 32,000 tokens 38 against 41)
-    if 1 < blocks <= DECODE_CLUSTER_MAX:
-        # a cluster: its blocks share the pages a sequence really visits equally, so as many blocks as fit
-        return blocks, -(-n_pages // blocks)
     blocks = min(blocks, DECODE_CLUSTER_MAX)
     ppb = -(-n_pages // blocks)
     return -(-n_pages // ppb), ppb
@@ -627,19 +620,14 @@ def set_wait_limit(cycles: int = 0, withhold_first_stage: bool = False) -> None:
 @_profiled(lambda a, facts: (_cost.gated_linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, _esz(a["out"])) if a["gated"] else
                          _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, _esz(a["out"]), _n_in(a["out"]))))
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                 m: Optional[int] = None, stages: int = 0, gated: bool = False, rowscale=None) -> bool:
+                 m: Optional[int] = None, stages: int = 0, gated: bool = False) -> bool:
     """out = x . w^T on the tensor cores; x, w bfloat16, out bfloat16 [M, N] or float32 [M, N] or
     float32 [S, M, N] (S partial sums over K, to be added by the consumer).  Returns False when the
     kernel refuses the layout (K or a row stride not a multiple of 8, a pointer off 16 bytes);
     the caller then uses the plain kernel.
 
     ``gated``: w's rows alternate in blocks of 16 between a gate and an up projection of the same
-    16 outputs, and out is bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue.
-
-    ``rowscale`` = (sumsq float32 [G, >= M], eps): x's rows are residual * norm weight, not yet divided by
-    their RMS over K values; the product is scaled by rsqrt(sum of the row's G shares / K + eps) before
-    the bias and the activation.  Only the kernel for more than 256 rows and N >= 256 does this: False for
-    other sizes (the caller normalises the rows first)."""
+    16 outputs, and out is bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue."""
     M = x.shape[0] if m is None else m
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
@@ -655,16 +643,6 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
             raise KernelError("gemm_tcgen05: output must be [M, N] (or [M, N / 2] when gated) with unit inner stride")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("gemm_tcgen05: bias must be float32 [N]")
-    if rowscale is not None:
-        if splits != 1 or M <= 256 or N < 256:
-            return False
-        rc = _lib().rb_gemm_tcgen05_scaled(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(out.dtype), M, N, K,
-                                           x.stride(0), ldo, 1 if gated else 0, *_row_scale(rowscale, M, "gemm_tcgen05"),
-                                           K, stages, _ptr(status_word(x.device)), _stream())
-        if rc in (10001, 10003):
-            return False
-        _check(rc, "gemm_tcgen05")
-        return True
     rc = _lib().rb_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
                                 ldo, splits, split_stride, stages, 1 if gated else 0, _ptr(status_word(x.device)), _stream())
     if rc == 10003:
@@ -713,17 +691,12 @@ def gemm_tcgen05_gated_pair(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, b
     return True
 
 
-@_profiled(lambda a, facts: tuple(map(sum, zip(_cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, 4, 1, True),
-                                                       (_rows(a) * a["w"].shape[0] * 2 if a["xhat"] is not None else 0, 0)))))
+@_profiled(lambda a, facts: _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, 4, 1, True))
 def gemm_tcgen05_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                     m: Optional[int] = None, next_w: Optional[torch.Tensor] = None,
-                     xhat: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None) -> bool:
+                     m: Optional[int] = None) -> bool:
     """resid += x . w^T (+ bias) for many rows (more than 256, N at least 256): the product is added into
-    the float32 residual stream in its own epilogue, so no delta goes through memory.  With ``xhat`` the
-    norm that follows is prepared in the same epilogue: xhat bfloat16 [M, N] = resid * next_w and ``sumsq``
-    float32 [ceil(N / 256), >= M], whose column m sums to the sum of squares of row m (the consumer applies
-    the rows' 1/RMS, see ``gemm_tcgen05``'s rowscale).  Returns False when the kernel refuses the sizes or
-    the layout (write a delta instead)."""
+    the float32 residual stream in its own epilogue, so no delta goes through memory.  Returns False
+    when the kernel refuses the sizes or the layout (write a delta instead)."""
     M = x.shape[0] if m is None else m
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
@@ -735,22 +708,6 @@ def gemm_tcgen05_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias
         raise KernelError("gemm_tcgen05_add: bias must be float32 [N]")
     if M <= 256 or N < 256:
         return False
-    if xhat is not None:
-        if next_w is None or next_w.numel() != N or next_w.dtype not in (torch.float32, torch.bfloat16):
-            raise KernelError("gemm_tcgen05_add: xhat needs the norm's weight [N], float32 or bfloat16")
-        if xhat.dtype != torch.bfloat16 or xhat.shape[1] != N or xhat.stride(1) != 1 or xhat.shape[0] < M:
-            raise KernelError("gemm_tcgen05_add: xhat must be bfloat16 [>= M, N] with unit inner stride")
-        if sumsq is None or sumsq.dtype != torch.float32 or sumsq.stride(1) != 1 or sumsq.shape[1] < M \
-                or sumsq.shape[0] != (N + 255) // 256:
-            raise KernelError("gemm_tcgen05_add: sumsq must be float32 [ceil(N / 256), >= M]")
-        rc = _lib().rb_gemm_tcgen05_add_norm(
-            _ptr(x), _ptr(w), _ptr(bias), _ptr(resid), M, N, K, x.stride(0), resid.stride(0), _ptr(next_w),
-            1 if next_w.dtype == torch.float32 else 0, _ptr(xhat), xhat.stride(0), _ptr(sumsq), sumsq.stride(0), 0,
-            _ptr(status_word(x.device)), _stream())
-        if rc in (10001, 10003):
-            return False
-        _check(rc, "gemm_tcgen05_add")
-        return True
     rc = _lib().rb_gemm_tcgen05_add(_ptr(x), _ptr(w), _ptr(bias), _ptr(resid), M, N, K, x.stride(0), resid.stride(0), 0,
                                     _ptr(status_word(x.device)), _stream())
     if rc in (10001, 10003):
@@ -806,13 +763,13 @@ def gemm_tcgen05_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor,
                           cos_sin: Optional[torch.Tensor], positions: torch.Tensor, slot_of_token: torch.Tensor,
                           block_table: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
                           v_cache: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
-                          m: Optional[int] = None, rowscale=None) -> bool:
+                          m: Optional[int] = None) -> bool:
     """A prompt's q | k | v projection (more than 256 rows, heads of 128) with the per-head norm, the
     rotation and the cache write done in the product's epilogue: q_out bfloat16 [M, nq * 128] receives the
     queries, the keys and values go into their pages.  w is [(nq + 2 nkv) * 128, K], or [nq * 128, K] for
     a layer that only reads a cache (then the cache arguments are unused).  ``cos_sin`` float32
-    [M, 64, 2] from rope_table, or None for no rotation.  ``rowscale`` as in ``gemm_tcgen05``.  Returns
-    False when the kernel does not take the sizes (run the product and qk_norm_rope_cache instead)."""
+    [M, 64, 2] from rope_table, or None for no rotation.  Returns False when the kernel does not take
+    the sizes (run the product and qk_norm_rope_cache instead)."""
     M = x.shape[0] if m is None else m
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
@@ -845,8 +802,7 @@ def gemm_tcgen05_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor,
         _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
         None if block_table is None else _i32(block_table, "block_table"),
         block_table.shape[1] if block_table is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), w_f32, float(eps),
-        _ptr(cos_sin), nq, nkv, *_row_scale(rowscale, M, "gemm_tcgen05_qkv_rope"), K, 0,
-        _ptr(status_word(x.device)), _stream())
+        _ptr(cos_sin), nq, nkv, 0, _ptr(status_word(x.device)), _stream())
     if rc in (10001, 10003):
         return False
     _check(rc, "gemm_tcgen05_qkv_rope")

@@ -114,11 +114,8 @@ class Attention(Mixer):
     can_sink = True        # forward() accepts sink=ResidualSink (see parts.base)
 
     def takes_deferred(self, batch) -> bool:
-        """Whether forward() can be handed a DeferredNorm for this step.  A prompt of many rows: the
-        projection's kernel scales its result by the rows' 1/RMS.  One token a sequence: the decode kernel
-        that takes the projections applies it, which a bias inside the projection would spoil."""
-        if not batch.is_decode:
-            return self.env.act_dtype == torch.bfloat16 and self.qkv.scales_rows(batch.n_tokens)
+        """Whether forward() can be handed a DeferredNorm for this step: the decode kernel that takes
+        the projections applies the rows' 1/RMS, which a bias inside the projection would spoil."""
         return (batch.is_decode and self.hd == 128 and not self.bias and self.env.act_dtype == torch.bfloat16
                 and self.qkv.weight is not None and self.qkv.weight.dtype == torch.bfloat16
                 and self.qkv._splits(batch.n_tokens) > 1
@@ -135,21 +132,14 @@ class Attention(Mixer):
         window = int(self.window) if self.window else 0
         writes = view.writes and not self.shares_cache
         done = False
-        proj = None
-        if isinstance(xn, DeferredNorm) and batch.is_decode:
+        if isinstance(xn, DeferredNorm):
             proj = self.qkv.forward_auto(xn.x, T)
             done = self._decode_fused(proj, attn, batch, view, window, writes, xn.rowscale, xn.width)
             if not done:
-                proj = None
-        elif isinstance(xn, DeferredNorm):
-            done = self._prompt_fused(xn.x, attn, batch, view, window, writes, rowscale=xn.rowscale)
-            if not done:
-                proj = self.qkv.forward_scaled(xn.x, T, xn.rowscale)
-        if not done and proj is None and isinstance(xn, DeferredNorm):
-            xn = xn.materialize()         # the kernels declined after all: the norm's own kernel, then as always
-        if not done and proj is None and not batch.is_decode and self._prompt_fused(xn, attn, batch, view, window, writes):
+                xn = xn.materialize()     # the kernel declined after all: the norm's own kernel, then as always
+        if not done and not batch.is_decode and self._prompt_fused(xn, attn, batch, view, window, writes):
             done = True
-        if not done and proj is None:
+        if not done:
             proj = self.qkv.forward_auto(xn, T)      # [T, N] or [S, T, N] partial sums
             done = batch.is_decode and self._decode_fused(proj, attn, batch, view, window, writes)
         if not done:
@@ -168,7 +158,7 @@ class Attention(Mixer):
             return None
         return self.o.forward_delta(attn, T)
 
-    def _prompt_fused(self, xn, out, batch, view, window, writes, rowscale=None) -> bool:
+    def _prompt_fused(self, xn, out, batch, view, window, writes) -> bool:
         """Many tokens, head size 128: the projection's own epilogue normalises and rotates the heads
         and writes keys and values into the cache, so the projections never go through memory.
         False: not this time (other sizes, a partial rotation, few tokens)."""
@@ -187,7 +177,7 @@ class Attention(Mixer):
             if not kernels.gemm_tcgen05_qkv_rope(
                     xn, self.qkv.weight, q, self.nq, self.nkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
                     cos_sin, batch.positions, batch.slot_of_token,
-                    view.block_table, view.k, view.v, self.qkv.bias, T, rowscale=rowscale):
+                    view.block_table, view.k, view.v, self.qkv.bias, T):
                 return False
         self.attend(q, out, batch, view, window)
         return True

@@ -75,30 +75,27 @@ class PreNormBlock:
         (ResidualSink), when the part after that norm can take the deferred rows: the norm kernels
         then disappear from the step.  RB_DEFER=0 turns the offers off (and those to prompts, below)."""
         T = batch.n_tokens
-        # beyond 16 tokens the norm kernels are cheaper (measured) until the products run in the kernel for many
-        # rows, whose epilogues add into the residual and prepare the following norm at no extra pass over memory
-        offers = ((batch.is_decode and T <= 16) or T > ADD_INTO_MIN_TOKENS) and _defer_enabled()
+        offers = batch.is_decode and T <= 16 and _defer_enabled()     # beyond 16 tokens the norm kernels are cheaper (measured)
         # Prompts: a part may be told to add its result into the residual itself (``add_into``; it then
         # returns None, nothing is pending, and the following norm only normalises): the delta of a
         # few thousand rows then never goes through memory.  Parts that set ``can_add_into`` get the offer.
         adds = not batch.is_decode and T > ADD_INTO_MIN_TOKENS and _defer_enabled()
         with scope(op="mixer_norm"):
             xn = self.mixer_norm.forward(resid, pending, T)
-        offer = {}
         if offers and getattr(self.mixer, "can_sink", False) and _takes(self.ff, batch):
-            offer["sink"] = ResidualSink(resid, self.ff_norm)
-        if adds and getattr(self.mixer, "can_add_into", False):
-            offer["add_into"] = resid                 # what is left of the first offer if the part declines it
-        delta = self.mixer.forward(xn, batch, view, **offer)
+            delta = self.mixer.forward(xn, batch, view, sink=ResidualSink(resid, self.ff_norm))
+        elif adds and getattr(self.mixer, "can_add_into", False):
+            delta = self.mixer.forward(xn, batch, view, add_into=resid)
+        else:
+            delta = self.mixer.forward(xn, batch, view)
         with scope(op="ff_norm"):
             xn = self.ff_norm.forward(resid, delta, T)
         nxt = getattr(next_block, "mixer", None)
-        offer = {}
         if offers and nxt is not None and getattr(self.ff, "can_sink", False) and _takes(nxt, batch):
-            offer["sink"] = ResidualSink(resid, next_block.mixer_norm)
+            return self.ff.forward(xn, batch, sink=ResidualSink(resid, next_block.mixer_norm))
         if adds and getattr(self.ff, "can_add_into", False):
-            offer["add_into"] = resid
-        return self.ff.forward(xn, batch, **offer)
+            return self.ff.forward(xn, batch, add_into=resid)
+        return self.ff.forward(xn, batch)
 
 
 def _takes(part, batch) -> bool:

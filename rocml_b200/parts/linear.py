@@ -31,10 +31,6 @@ _SM_COUNT = {}
 # kernels (51-57 us against 38-40 for a 24,576 x 4,096 weight).
 GATED_PAIR_MAX_ROWS = 16
 
-# Beyond this many rows a product runs in the kernel of CTA pairs, whose epilogues can add into the residual,
-# prepare the following norm and apply a deferred 1/RMS.
-ADD_NORM_MIN_ROWS = 256
-
 
 def _sm_count(device) -> int:
     key = torch.device(device).index or 0
@@ -107,27 +103,12 @@ class Linear:
         return True
 
     @_labelled
-    def forward_gated(self, x: torch.Tensor, m: int, rowscale=None) -> Optional[torch.Tensor]:
-        """[M, N / 2] = silu(gate(x)) * up(x) in one kernel (needs ``interleave_pairs``).  With ``rowscale``
-        (x's rows still lack their norm's 1/RMS) None when the kernel for this step's sizes cannot apply it."""
+    def forward_gated(self, x: torch.Tensor, m: int) -> torch.Tensor:
+        """[M, N / 2] = silu(gate(x)) * up(x) in one kernel (needs ``interleave_pairs``)."""
         out = torch.empty((m, self.n // 2), dtype=torch.bfloat16, device=x.device)
-        if not kernels.gemm_tcgen05(x, self.weight, out, self.bias, m, gated=True, rowscale=rowscale):
-            if rowscale is not None:
-                return None
+        if not kernels.gemm_tcgen05(x, self.weight, out, self.bias, m, gated=True):
             raise KernelError("the gated matrix product refused a layout that interleave_pairs accepted")
         return out
-
-    def scales_rows(self, m: int) -> bool:
-        """Whether this step's product (m rows) can be handed rows that still lack their norm's 1/RMS and scale
-        its result instead: the kernel for many rows does, for one split and at least 256 outputs."""
-        return (m > ADD_NORM_MIN_ROWS and self.n >= 256 and self.k % 8 == 0 and self.weight is not None
-                and self.weight.dtype == torch.bfloat16 and self._splits(m) == 1)
-
-    @_labelled
-    def forward_scaled(self, x: torch.Tensor, m: int, rowscale) -> Optional[torch.Tensor]:
-        """[M, N] in x's type from rows that still lack their norm's 1/RMS (see ``scales_rows``), or None."""
-        out = torch.empty((m, self.n), dtype=x.dtype, device=x.device)
-        return out if kernels.gemm_tcgen05(x, self.weight, out, self.bias, m, rowscale=rowscale) else None
 
     @_labelled
     def forward_gated_pair(self, x: torch.Tensor, m: int, rowscale=None) -> Optional[torch.Tensor]:
@@ -155,20 +136,9 @@ class Linear:
         """sink.resid += x . W^T (+ bias) for a few rows, inside the product (the K splits exchange their
         parts through shared memory), together with what ``sink.norm`` needs: returns its deferred
         rows, or None when this step's product cannot be done that way (use ``forward_delta``)."""
-        norm = sink.norm
-        if not self._tensor_core(x) or not getattr(norm, "deferrable", False) or norm.weight is None:
-            return None
-        if m > ADD_NORM_MIN_ROWS:
-            # many rows: the epilogue that adds into the residual also writes the norm's rows and their sums of squares
-            if self._splits(m) != 1 or self.n < 256:
-                return None
-            xhat = torch.empty((m, self.n), dtype=torch.bfloat16, device=x.device)
-            sumsq = torch.empty(((self.n + 255) // 256, m), dtype=torch.float32, device=x.device)
-            if not kernels.gemm_tcgen05_add(x, self.weight, sink.resid, self.bias, m, norm.weight, xhat, sumsq):
-                return None
-            return DeferredNorm(xhat, sumsq, norm.eps, self.n, norm, sink.resid)
         s = self.residual_splits(m)
-        if not s:
+        norm = sink.norm
+        if not s or not self._tensor_core(x) or not getattr(norm, "deferrable", False) or norm.weight is None:
             return None
         xhat = torch.empty((m, self.n), dtype=torch.bfloat16, device=x.device)
         sumsq = torch.empty((((self.n + 127) // 128) * s, m), dtype=torch.float32, device=x.device)

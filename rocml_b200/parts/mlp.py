@@ -70,8 +70,6 @@ class GatedMLP(FeedForward):
         """Whether forward() can be handed a DeferredNorm for this step: only the product of two blocks
         that applies the activation itself also applies the rows' 1/RMS."""
         T = batch.n_tokens
-        if self.gate_up.paired and self.gate_up.scales_rows(T):
-            return True                   # many rows: the product's own epilogue applies the 1/RMS and the activation
         return (self.gate_up.paired and T <= GATED_PAIR_MAX_ROWS and self.gate_up.weight.dtype == torch.bfloat16
                 and self.gate_up._splits(T) == 2 and self.gate_up.k > 64)
 
@@ -82,10 +80,7 @@ class GatedMLP(FeedForward):
         dev, act = self.env.device, self.env.act_dtype
         h = None
         if isinstance(xn, DeferredNorm):
-            if T > 128:
-                h = self.gate_up.forward_gated(xn.x, T, rowscale=xn.rowscale)
-            else:
-                h = self.gate_up.forward_gated_pair(xn.x, T, rowscale=xn.rowscale)
+            h = self.gate_up.forward_gated_pair(xn.x, T, rowscale=xn.rowscale)
             if h is None:
                 xn = xn.materialize()     # the kernel declined after all: the norm's own kernel, then as always
         if h is None and self.gate_up.paired and T > 128:

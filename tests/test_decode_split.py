@@ -21,17 +21,14 @@ def test_equal_split_covers_every_page_in_one_wave(n_seqs, groups, n_pages):
         assert 1 <= blocks and blocks * groups <= resident
         return
     assert ppb >= 1 and blocks >= 1
-    assert blocks * ppb >= n_pages and blocks <= n_pages          # every page, no more blocks than pages
-    if not 1 < blocks <= kernels.DECODE_CLUSTER_MAX or n_pages > (blocks - 1) * ppb:
-        assert n_pages > (blocks - 1) * ppb                       # blocks of ppb pages each: none is empty
-    # (otherwise: a cluster as large as the wave allows, whose blocks share a sequence's pages equally on the device)
+    assert blocks * ppb >= n_pages > (blocks - 1) * ppb          # every page, no empty block
     assert blocks == 1 or blocks * n_seqs * groups <= resident    # one wave, unless one block a sequence is already too many
 
 
 def test_a_finer_split_is_cut_back_to_a_cluster_where_blocks_stay_short():
     assert kernels.decode_split(1, 8, 20) == (10, 2)      # 20 blocks would fit; 16 -> two pages a block -> ten blocks
     assert kernels.decode_split(1, 8, 64) == (16, 4)
-    assert kernels.decode_split(8, 8, 20) == (6, 4)       # the wave allows six blocks a sequence: a cluster of six shares the pages
+    assert kernels.decode_split(8, 8, 20) == (5, 4)       # the wave allows six blocks a sequence
     assert kernels.decode_split(48, 8, 20) == (1, 20)
     assert kernels.decode_split(64, 8, 20) == (55, 0)     # 512 pairs do not run at once: 55 blocks a group share the pages
     assert kernels.decode_split(64, 8, 4) == (1, 4)       # too short to be worth it

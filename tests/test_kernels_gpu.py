@@ -154,75 +154,11 @@ def test_gemm_tcgen05_many_rows_add_into_the_residual_stream(M, N, K, bias):
     assert kernels.gemm_tcgen05_add(x[:200], w, resid, b, 200) is False          # few rows: other kernels
 
 
-@pytest.mark.parametrize("M,N,K,bias,wdt", [(300, 512, 320, True, torch.bfloat16), (257, 400, 1024, False, torch.float32),
-                                            (2048, 4096, 512, False, torch.bfloat16), (700, 264, 4096, True, torch.float32)])
-def test_gemm_tcgen05_many_rows_add_and_prepare_the_norm(M, N, K, bias, wdt):
-    """The same epilogue also prepares the norm that follows: residual * norm weight in bfloat16 and, per
-    tile of 256 columns, the rows' sums of squares; the residual is bit for bit what it is without."""
-    from rocml_b200 import kernels
-    x = rnd((M, K), 4, torch.bfloat16).to(DEV)
-    w = rnd((N, K), 5, torch.bfloat16, 0.05).to(DEV)
-    b = rnd((N,), 6).to(DEV) if bias else None
-    nw = (1 + 0.1 * rnd((N,), 7)).to(wdt).to(DEV)
-    resid0 = rnd((M + 3, N), 8)
-    plain = resid0.clone().to(DEV)
-    assert kernels.gemm_tcgen05_add(x, w, plain, b, M)
-    resid = resid0.clone().to(DEV)
-    xhat = torch.full((M + 3, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    sumsq = torch.full(((N + 255) // 256, M + 5), float("nan"), dtype=torch.float32, device=DEV)
-    assert kernels.gemm_tcgen05_add(x, w, resid, b, M, nw, xhat, sumsq)
-    kernels.check_status(DEV)
-    assert torch.equal(resid, plain)
-    r = resid[:M].cpu().double()
-    want_x = (resid[:M] * nw.float()).bfloat16()
-    assert torch.equal(xhat[:M], want_x)
-    assert torch.isnan(xhat[M:].float()).all() and torch.isnan(sumsq[:, M:]).all()
-    got = sumsq[:, :M].cpu().double().sum(0)
-    want = (r * r).sum(-1)
-    assert ((got - want).abs() / want).max().item() < 1e-5
-    # and each group holds its own 256 columns' share
-    for gi in range(sumsq.shape[0]):
-        part = (r[:, gi * 256:(gi + 1) * 256] ** 2).sum(-1)
-        assert ((sumsq[gi, :M].cpu().double() - part).abs() / want).max().item() < 1e-5
-
-
-@pytest.mark.parametrize("M,N,K,bias,gated,od", [(300, 512, 320, True, False, torch.bfloat16), (257, 416, 1024, False, True, torch.bfloat16),
-                                                 (1500, 4096, 512, False, True, torch.bfloat16), (700, 264, 2048, True, False, torch.float32)])
-@pytest.mark.parametrize("eps", [1e-6, 0.5])
-def test_gemm_tcgen05_many_rows_apply_a_deferred_row_scale(M, N, K, bias, gated, od, eps):
-    """Rows that still lack their norm's 1/RMS: the product is scaled by rsqrt(sum of the row's shares / K +
-    eps) before the bias and the activation.  The shares are made up (several groups, unequal), and the
-    second eps is as large as the mean squares, so a dropped or misplaced eps shows."""
-    from rocml_b200 import kernels
-    x = rnd((M, K), 4, torch.bfloat16).to(DEV)
-    w = rnd((N, K), 5, torch.bfloat16, 0.05).to(DEV)
-    b = rnd((N,), 6).to(DEV) if bias else None
-    G = 5
-    shares = (rnd((G, M + 2), 9).abs() * K / G).to(DEV)
-    rs = torch.rsqrt(shares[:, :M].cpu().double().sum(0) / K + eps)[:, None]
-    prod = (x.cpu().double() @ w.cpu().double().t()) * rs + (b.cpu().double() if bias else 0.0)
-    if gated:
-        pr = prod.reshape(M, N // 32, 2, 16)
-        gt, up = pr[:, :, 0].reshape(M, N // 2), pr[:, :, 1].reshape(M, N // 2)
-        want = gt / (1 + torch.exp(-gt)) * up
-        out = torch.full((M, N // 2), float("nan"), dtype=od, device=DEV)
-    else:
-        want = prod
-        out = torch.full((M, N), float("nan"), dtype=od, device=DEV)
-    assert kernels.gemm_tcgen05(x, w, out, b, M, gated=gated, rowscale=(shares, eps))
-    kernels.check_status(DEV)
-    tol = 2 ** -7 if od == torch.bfloat16 else 1e-4
-    assert ((out.cpu().double() - want).abs() / want.abs().clamp_min(1.0)).max().item() < tol
-    # few rows, or a narrow weight: another kernel's business
-    assert kernels.gemm_tcgen05(x[:100], w, out[:100], b, 100, gated=gated, rowscale=(shares, eps)) is False
-
-
 @pytest.mark.parametrize("M,nq,nkv,K,norm,rope,bias,writes", [
     (300, 4, 2, 512, True, True, False, True), (1000, 6, 1, 264, True, True, True, True),
     (513, 2, 2, 1024, False, True, False, True), (257, 4, 2, 256, True, False, False, False)])
 @pytest.mark.parametrize("eps", [1e-6, 1e-1])
-@pytest.mark.parametrize("scaled", [False, True])
-def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rope, bias, writes, eps, scaled):
+def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rope, bias, writes, eps):
     """A prompt's q | k | v projection whose epilogue does the per-head norm, the rotation and the cache
     write, against the same arithmetic in float64; some tokens are padding and must leave no trace.
     The second eps is as large as the heads' mean squares, so that an eps that is dropped or added in
@@ -250,16 +186,12 @@ def test_gemm_tcgen05_qkv_projection_rotates_and_caches(M, nq, nkv, K, norm, rop
     inv_freq = (1e4 ** (-torch.arange(0, hd // 2, dtype=torch.float64) * 2 / hd)).float().to(DEV)
     cs = kernels.rope_table(pos.to(DEV), inv_freq, M) if rope else None
     q = torch.zeros((M, nq * hd), dtype=torch.bfloat16, device=DEV)
-    # scaled: the rows still lack a norm's 1/RMS, given as three unequal shares of their sums of squares
-    shares = (torch.rand((3, M), generator=g) * K).to(DEV) if scaled else None
-    row_eps = 0.25
     assert kernels.gemm_tcgen05_qkv_rope(
         x.to(DEV), w.to(DEV), q, nq, nkv, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, eps, cs,
         pos.to(DEV), slot.to(DEV), table.to(DEV) if writes else None, kc if writes else None, vc if writes else None,
-        b.to(DEV) if bias else None, rowscale=(shares, row_eps) if scaled else None)
+        b.to(DEV) if bias else None)
     kernels.check_status(DEV)
-    rs = torch.rsqrt(shares.cpu().double().sum(0) / K + row_eps)[:, None] if scaled else 1.0
-    proj = (x.double() @ w.double().t()) * rs + (b.double() if bias else 0)
+    proj = x.double() @ w.double().t() + (b.double() if bias else 0)
     heads = proj.reshape(M, -1, hd)
 
     def finish(h, wn):
