@@ -31,6 +31,14 @@ constexpr int KT = 32;         // keys per tile: one per lane
 constexpr int MAX_DPL = 8;     // head dims per lane -> head size up to 256
 constexpr float NEG_BIG = -1e30f;
 
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int o_stride,
@@ -103,16 +111,45 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         hi = min(hi, (c + 1) * chunk - 1);
     }
     const int* table = block_table + (size_t)slot * max_pages;
+    // four elements a load where the head size and the caches' addresses allow (pages, heads and keys then all
+    // start on a multiple of four elements); blockDim.x is 128 (launch_attn)
+    const bool vec = (hd & 3) == 0 && (((uintptr_t)k_cache | (uintptr_t)v_cache) & (4 * sizeof(T) - 1)) == 0 &&
+                     ((ROWS * hd + KT * (hd + 1)) & 3) == 0;
 
     for (int t0 = (lo / KT) * KT; t0 <= hi; t0 += KT) {
         __syncthreads();  // previous tile fully consumed (and q_s written, first time)
         const int page = table[t0 / RB_PAGE];
         const size_t base = page >= 0 ? (((size_t)page * nkv + kvh) * RB_PAGE + (t0 % RB_PAGE)) * hd : 0;
-        for (int idx = tid; idx < KT * hd; idx += blockDim.x) {
-            const int jj = idx / hd, d = idx - jj * hd;
-            const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo;
-            k_s[jj * (hd + 1) + d] = in ? to_f32(k_cache[base + idx]) : 0.f;
-            v_s[idx] = in ? to_f32(v_cache[base + idx]) : 0.f;
+        if (vec) {
+            // A warp takes every fourth key, a lane four consecutive dimensions at a time, and all of a thread's
+            // loads are requested before the first is stored: taken one element at a time, each load waited
+            // for the one before, and a tile took as long as sixty-four trips to memory.
+            constexpr int KPW = KT / 4;                           // keys per warp (4 warps a block)
+            for (int d4 = lane; d4 < (hd >> 2); d4 += 32) {
+                float4 kk[KPW], vv[KPW];
+#pragma unroll
+                for (int u = 0; u < KPW; ++u) {
+                    const int jj = warp + 4 * u;
+                    const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo;
+                    const size_t off = base + (size_t)jj * hd + d4 * 4;
+                    kk[u] = in ? load4(k_cache + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    vv[u] = in ? load4(v_cache + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < KPW; ++u) {
+                    const int jj = warp + 4 * u;
+                    float* kd = k_s + jj * (hd + 1) + d4 * 4;
+                    kd[0] = kk[u].x; kd[1] = kk[u].y; kd[2] = kk[u].z; kd[3] = kk[u].w;
+                    *reinterpret_cast<float4*>(v_s + jj * hd + d4 * 4) = vv[u];
+                }
+            }
+        } else {
+            for (int idx = tid; idx < KT * hd; idx += blockDim.x) {
+                const int jj = idx / hd, d = idx - jj * hd;
+                const bool in = page >= 0 && t0 + jj <= hi && t0 + jj >= lo;
+                k_s[jj * (hd + 1) + d] = in ? to_f32(k_cache[base + idx]) : 0.f;
+                v_s[idx] = in ? to_f32(v_cache[base + idx]) : 0.f;
+            }
         }
         __syncthreads();
 
