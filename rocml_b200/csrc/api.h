@@ -29,7 +29,8 @@ int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_s
 int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, void* out, void* stream);
 
 int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, void* out,
-                    int out_dtype, int M, int N, int K, long long ldx, long long ldo, void* stream);
+                    int out_dtype, int M, int N, int K, long long ldx, long long ldo, int splits,
+                    long long split_stride, void* stream);
 
 // The limit, in clock cycles, of every barrier wait in the tensor-core products (cycles <= 0: the default,
 // about two seconds), and a switch for tests of the give-up path: while it is set a few-token product

@@ -192,7 +192,8 @@ __device__ __forceinline__ float4 ld_stream(const float* p) {      // read once:
 template <int MT>
 __global__ void __launch_bounds__(MT <= 8 ? 128 : 256)
 gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                     float* __restrict__ out, int M, int N, int K, long long ldx, long long ldo) {
+                     float* __restrict__ out, int M, int N, int K, long long ldx, long long ldo, int k_per_split,
+                     long long split_stride) {
     constexpr int ROWS_NW = MT <= 8 ? 4 : 2;     // weight rows a warp
     constexpr int ROWS_WARPS = ROWS_PER_BLOCK / ROWS_NW;
     constexpr int KT = 256;                      // floats of k a tile
@@ -201,6 +202,11 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = (blockIdx.x * ROWS_WARPS + warp) * ROWS_NW;
+    // blockIdx.y: this block's part of k (a multiple of KT long); its sums go to a partial result of their own,
+    // which the consumer adds in order (a narrow weight alone has too few rows to keep the memory busy)
+    const int k_lo = blockIdx.y * k_per_split;
+    const int k_end = min(K, k_lo + k_per_split);
+    out += (size_t)blockIdx.y * split_stride;
     const float* wr[ROWS_NW];
 #pragma unroll
     for (int j = 0; j < ROWS_NW; ++j) wr[j] = w + (size_t)min(n0 + j, N - 1) * K;
@@ -214,28 +220,28 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
         for (int u = 0; u < U; ++u) {
             const int k = k0 + u * 128 + lane * 4;
 #pragma unroll
-            for (int j = 0; j < ROWS_NW; ++j) dst[u][j] = k < K ? ld_stream(wr[j] + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < ROWS_NW; ++j) dst[u][j] = k < k_end ? ld_stream(wr[j] + k) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
     auto load_x = [&](int buf, int k0) {          // the whole block copies the tile's rows; beyond K or M: zeros
         for (int i = threadIdx.x; i < MT * (KT / 4); i += ROWS_WARPS * 32) {
             const int m = i / (KT / 4), k = k0 + (i % (KT / 4)) * 4;
-            const float4 v = (m < M && k < K) ? *reinterpret_cast<const float4*>(x + (size_t)m * ldx + k)
+            const float4 v = (m < M && k < k_end) ? *reinterpret_cast<const float4*>(x + (size_t)m * ldx + k)
                                               : make_float4(0.f, 0.f, 0.f, 0.f);
             *reinterpret_cast<float4*>(&xs[buf][m][(i % (KT / 4)) * 4]) = v;
         }
     };
     // the weights do not depend on the kernel before this one: their first tile is requested at once
     float4 wv[U][ROWS_NW];
-    load_w(wv, 0);
+    load_w(wv, k_lo);
     pdl_wait();
-    load_x(0, 0);
+    load_x(0, k_lo);
     __syncthreads();
     int buf = 0;
-    for (int k0 = 0; k0 < K; k0 += KT, buf ^= 1) {
+    for (int k0 = k_lo; k0 < k_end; k0 += KT, buf ^= 1) {
         float4 nx[U][ROWS_NW];
         load_w(nx, k0 + KT);
-        if (k0 + KT < K) load_x(buf ^ 1, k0 + KT);
+        if (k0 + KT < k_end) load_x(buf ^ 1, k0 + KT);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
 #pragma unroll
@@ -261,15 +267,17 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             const float v = warp_sum(acc[j][m]);
-            if (lane == 0 && m < M && n0 + j < N) out[(size_t)m * ldo + n0 + j] = v + (bias ? bias[n0 + j] : 0.f);
+            if (lane == 0 && m < M && n0 + j < N) out[(size_t)m * ldo + n0 + j] = v + (bias && blockIdx.y == 0 ? bias[n0 + j] : 0.f);
         }
 }
 
 template <int MT>
 int launch_rows(const float* x, const float* w, const float* bias, float* out, int M, int N, int K, long long ldx,
-                long long ldo, cudaStream_t s) {
-    RB_LAUNCH((gemm_rows_f32_kernel<MT>), dim3((N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), dim3(MT <= 8 ? 128 : 256), 0, s,
-              x, w, bias, out, M, N, K, ldx, ldo);
+                long long ldo, int splits, long long split_stride, cudaStream_t s) {
+    const int k_per_split = ((K + splits - 1) / splits + 255) / 256 * 256;       // a multiple of the kernel's k tile
+    // (a part that lies wholly beyond K, which the rounding to tiles can leave, is written as zeros)
+    RB_LAUNCH((gemm_rows_f32_kernel<MT>), dim3((N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, splits), dim3(MT <= 8 ? 128 : 256), 0, s,
+              x, w, bias, out, M, N, K, ldx, ldo, k_per_split, split_stride);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
@@ -296,9 +304,14 @@ int launch(const void* x, const void* w, const void* bias, void* out, int M, int
 
 extern "C" int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias,
                                void* out, int out_dtype, int M, int N, int K, long long ldx, long long ldo,
-                               void* stream) {
+                               int splits, long long split_stride, void* stream) {
     if (M <= 0 || N <= 0) return RB_OK;
-    if (K <= 0) return RB_ERR_BAD_SIZE;
+    if (K <= 0 || splits < 1) return RB_ERR_BAD_SIZE;
+    // splits > 1: float32 partial sums over parts of k at out + z * split_stride (bias in part 0), for the 32-bit
+    // product of at most 16 rows only
+    if (splits > 1 && !(x_dtype == RB_F32 && w_dtype == RB_F32 && out_dtype == RB_F32 && M <= 16 && K % 4 == 0 &&
+                        ldx % 4 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0))
+        return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
 #define RB_G(XT, WT, OT) return launch<XT, WT, OT>(x, w, bias, out, M, N, K, ldx, ldo, s)
@@ -307,11 +320,11 @@ extern "C" int rb_gemm_generic(const void* x, int x_dtype, const void* w, int w_
         if (M <= 16 && K % 4 == 0 && ldx % 4 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
             const float *xf = (const float*)x, *wf = (const float*)w, *bf32 = (const float*)bias;
             float* of = (float*)out;
-            if (M <= 1) return launch_rows<1>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
-            if (M <= 2) return launch_rows<2>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
-            if (M <= 4) return launch_rows<4>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
-            if (M <= 8) return launch_rows<8>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
-            return launch_rows<16>(xf, wf, bf32, of, M, N, K, ldx, ldo, s);
+            if (M <= 1) return launch_rows<1>(xf, wf, bf32, of, M, N, K, ldx, ldo, splits, split_stride, s);
+            if (M <= 2) return launch_rows<2>(xf, wf, bf32, of, M, N, K, ldx, ldo, splits, split_stride, s);
+            if (M <= 4) return launch_rows<4>(xf, wf, bf32, of, M, N, K, ldx, ldo, splits, split_stride, s);
+            if (M <= 8) return launch_rows<8>(xf, wf, bf32, of, M, N, K, ldx, ldo, splits, split_stride, s);
+            return launch_rows<16>(xf, wf, bf32, of, M, N, K, ldx, ldo, splits, split_stride, s);
         }
         RB_G(float, float, float);
     }

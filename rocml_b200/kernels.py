@@ -132,7 +132,7 @@ def _lib():
         lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f,
                                               _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp]
         lib.rb_rope_table.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
-        lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _vp]
+        lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp]
         lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
                                              _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp]
         lib.rb_attention_merge.argtypes = [_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
@@ -291,18 +291,31 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, n_tokens: int) -
 
 # ---- matrix products ---------------------------------------------------------------------------------
 
-@_profiled(lambda a, facts: _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], _esz(a["w"]), _esz(a["x"]), _esz(a["out"])))
+@_profiled(lambda a, facts: _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], _esz(a["w"]), _esz(a["x"]), _esz(a["out"]),
+                                         _n_in(a["out"])))
 def gemm_generic(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  m: Optional[int] = None):
-    """out[M, N] = x[M, K] . w[N, K]^T (+ bias float32 [N]) on the CUDA cores, 32-bit accumulation."""
+    """out[M, N] = x[M, K] . w[N, K]^T (+ bias float32 [N]) on the CUDA cores, 32-bit accumulation.
+    ``out`` float32 [S, M, N] with S > 1 (32-bit x and w, at most 16 rows): S partial sums over parts of K,
+    to be added in order by the consumer (bias in the first)."""
     M = x.shape[0] if m is None else m
     N, K = w.shape
-    if x.shape[1] != K or out.shape[1] != N or x.stride(1) != 1 or out.stride(1) != 1 or not w.is_contiguous():
+    splits, split_stride = 1, 0
+    if out.dim() == 3:
+        splits, split_stride = out.shape[0], out.stride(0)
+        if out.dtype != torch.float32 or out.stride(2) != 1 or out.shape[2] != N:
+            raise KernelError("gemm_generic: partial output must be float32 [S, M, N]")
+        ldo = out.stride(1)
+    else:
+        if out.shape[1] != N or out.stride(1) != 1:
+            raise KernelError("gemm_generic: shapes or strides do not fit")
+        ldo = out.stride(0)
+    if x.shape[1] != K or x.stride(1) != 1 or not w.is_contiguous():
         raise KernelError("gemm_generic: shapes or strides do not fit")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("gemm_generic: bias must be float32 [N]")
     rc = _lib().rb_gemm_generic(_ptr(x), dtype_code(x.dtype), _ptr(w), dtype_code(w.dtype), _ptr(bias), _ptr(out),
-                                dtype_code(out.dtype), M, N, K, x.stride(0), out.stride(0), _stream())
+                                dtype_code(out.dtype), M, N, K, x.stride(0), ldo, splits, split_stride, _stream())
     _check(rc, "gemm_generic")
 
 

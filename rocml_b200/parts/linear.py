@@ -216,14 +216,27 @@ class Linear:
             s *= 2
         return s
 
+    def _splits_f32(self, x: torch.Tensor, m: int) -> int:
+        """The same for the 32-bit product of at most 16 rows, in which a warp streams four weight rows: a
+        narrow weight alone has too few rows to keep the memory busy, so the sum over K is cut until about 24
+        warps a multiprocessor are at work (each part at least 1,024 values of k, at most 8 parts)."""
+        if m > 16 or x.dtype != torch.float32 or self.weight is None or self.weight.dtype != torch.float32 \
+                or self.k % 4 or not x.is_cuda:
+            return 1
+        warps = (self.n + 3) // 4
+        return max(1, min(8, -(-24 * _sm_count(self.env.device) // warps), self.k // 1024))
+
     @_labelled
     def forward_delta(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """The product as float32 [S, M, N]: S partial sums over K that the consumer adds in order
         (a delta for the residual stream, or the input of a kernel that takes partial sums)."""
         tc = self._tensor_core(x)
-        S = self._splits(m) if tc else 1
+        S = self._splits(m) if tc else self._splits_f32(x, m)
         out = torch.empty((S, m, self.n), dtype=torch.float32, device=x.device)
         if tc and kernels.gemm_tcgen05(x, self.weight, out, self.bias, m):
+            return out
+        if not tc and S > 1:
+            kernels.gemm_generic(x, self.weight, out, self.bias, m)
             return out
         if S > 1:
             out = out[:1]
@@ -233,7 +246,7 @@ class Linear:
     def forward_auto(self, x: torch.Tensor, m: int) -> torch.Tensor:
         """The product in whichever form is cheapest for the step: [S, M, N] float32 partial sums
         when few rows stream the weight, else [M, N] in the activations' type."""
-        if self._tensor_core(x) and self._splits(m) > 1:
+        if (self._tensor_core(x) and self._splits(m) > 1) or self._splits_f32(x, m) > 1:
             return self.forward_delta(x, m)
         out = torch.empty((m, self.n), dtype=x.dtype, device=x.device)
         return self.forward(x, out, m)

@@ -268,6 +268,34 @@ def test_gemm_of_few_32_bit_rows_reads_the_weight_once(M, N, K):
     assert torch.equal(alone[0], out[M - 1])
 
 
+@pytest.mark.parametrize("M,N,K,S", [(1, 37, 2048, 2), (8, 4096, 4096, 4), (5, 129, 1100, 3), (16, 1001, 12288, 8), (3, 64, 520, 2), (8, 264, 7616, 7)])
+def test_gemm_of_few_32_bit_rows_in_parts_of_k(M, N, K, S):
+    """The same product with the sum over K in S parts, each a partial result of its own (the bias in the
+    first): their sum is the product, every part is written (none stays NaN), and a part is the product
+    over its own stretch of k (a multiple of 256 long)."""
+    from rocml_b200 import kernels
+    x = rnd((M, K), 1).to(DEV)
+    w = rnd((N, K), 2).to(DEV)
+    bias = rnd((N,), 3).to(DEV)
+    out = torch.full((S, M + 1, N), float("nan"), dtype=torch.float32, device=DEV)[:, :M]
+    kernels.gemm_generic(x, w, out, bias)
+    want = x.cpu().double() @ w.cpu().double().t() + bias.cpu().double()
+    scale = (x.cpu().double().abs() @ w.cpu().double().abs().t()).clamp_min(1.0)
+    assert not torch.isnan(out).any()
+    assert ((out.cpu().double().sum(0) - want).abs() / scale).max().item() < 1e-6
+    per = -(-(-(-K // S)) // 256) * 256
+    part1 = x.cpu().double()[:, per:2 * per] @ w.cpu().double()[:, per:2 * per].t()
+    assert ((out[1].cpu().double() - part1).abs() / scale).max().item() < 1e-6
+    # parts that the rounding to tiles leaves empty are zeros; many rows are refused
+    few = torch.full((S, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_generic(x[:, :256].contiguous(), w[:, :256].contiguous(), few, bias)
+    assert torch.equal(few[1:], torch.zeros_like(few[1:]))
+    part0 = x.cpu().double()[:, :256] @ w.cpu().double()[:, :256].t() + bias.cpu().double()
+    assert ((few[0].cpu().double() - part0).abs() / scale).max().item() < 1e-6
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_generic(rnd((17, K), 4).to(DEV), w, torch.empty((S, 17, N), device=DEV), bias)
+
+
 # ---- embedding, norm, activation ---------------------------------------------------------------------
 
 @pytest.mark.parametrize("wd", [torch.float32, torch.bfloat16])
