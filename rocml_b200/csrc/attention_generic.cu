@@ -77,13 +77,35 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // rows of this block: r -> (token tok0 + r / HG, head kvh*g + hc*HG + r % HG)
-    for (int idx = tid; idx < ROWS * hd; idx += blockDim.x) {
-        const int r = idx / hd, d = idx - r * hd;
-        const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
-        float v = 0.f;
-        if (r < QB * HG && qi < q_len && hg < g)
-            v = to_f32(q[(size_t)(q0 + qi) * q_stride + (size_t)(kvh * g + hg) * hd + d]);
-        q_s[idx] = v;
+    if ((hd & 3) == 0 && (q_stride & 3) == 0 && ((uintptr_t)q & (4 * sizeof(T) - 1)) == 0) {
+        // four elements a load; the loads of a thread's rows do not wait for one another
+        const int hd4 = hd >> 2;
+        for (int i0 = tid; i0 < ROWS * hd4; i0 += blockDim.x * 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i4 = i0 + u * blockDim.x;
+                const int r = i4 / hd4, d4 = i4 - r * hd4;
+                const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i4 < ROWS * hd4 && r < QB * HG && qi < q_len && hg < g)
+                    v[u] = load4(q + (size_t)(q0 + qi) * q_stride + (size_t)(kvh * g + hg) * hd + d4 * 4);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i4 = i0 + u * blockDim.x;
+                if (i4 < ROWS * hd4) *reinterpret_cast<float4*>(q_s + i4 * 4) = v[u];
+            }
+        }
+    } else {
+        for (int idx = tid; idx < ROWS * hd; idx += blockDim.x) {
+            const int r = idx / hd, d = idx - r * hd;
+            const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
+            float v = 0.f;
+            if (r < QB * HG && qi < q_len && hg < g)
+                v = to_f32(q[(size_t)(q0 + qi) * q_stride + (size_t)(kvh * g + hg) * hd + d]);
+            q_s[idx] = v;
+        }
     }
 
     int row_pos[RW], row_lo[RW];
@@ -256,7 +278,14 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int d = lane; d < hd; d += 32) {
         float a = 0.f;
-        for (int c = c_lo; c <= c_hi; ++c) a = fmaf(w[c], part_acc[(base + c) * hd + d], a);
+        for (int c0 = c_lo; c0 <= c_hi; c0 += 8) {        // eight chunks' values in flight, added in ascending order
+            float pa[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pa[j] = c0 + j <= c_hi ? part_acc[(base + c0 + j) * hd + d] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (c0 + j <= c_hi) a = fmaf(w[c0 + j], pa[j], a);
+        }
         out[(size_t)t * o_stride + (size_t)head * hd + d] = from_f32<T>(a * inv);
     }
 }
