@@ -8,13 +8,17 @@
 // of two, so that a tile's copies never wait for the products of the tile before), warp 1 issues
 // the MMAs, warps 2-5 are the 128 softmax threads.
 // Per tile: S_j = Q K_j^T into one of two TMEM buffers (so the tensor core can already form S_{j+1}
-// while the softmax works on S_j); the softmax threads read their row, scale, mask (causal,
-// inclusive; window), update the running maximum and sum in float32 (base 2), write P as bfloat16
-// into shared memory in the operand layout, and, only when some row's maximum has grown by more than
-// 2^8, rescale the O accumulator in tensor memory (otherwise the stale maximum stays in use, which is
-// exact: numerator and denominator carry the same factor); O += P V_j with V read in its natural
-// [key][dimension] order (MN-major operand).  Two blocks share a multiprocessor (112 KB of shared
-// memory and 256 TMEM columns each), so one block's softmax overlaps the other's MMAs.
+// while the softmax works on S_j); the softmax threads read their row, mask (causal, inclusive;
+// window), update the running maximum and sum in float32 (base 2, the scale folded into the
+// exponent's multiply-add, two scores an instruction), and write P as pairs of bfloat16 back into
+// the first 32 columns of the buffer S_j came from: the tensor core reads its A operand from there
+// (no shared-memory round trip, no proxy fence; S_{j+2} overwrites the buffer only after the product
+// that read it, because one thread's MMAs run in order).  Only when some row's maximum has grown by
+// more than 2^8 does a warp wait for the last product and rescale the O accumulator in tensor memory
+// (otherwise the stale maximum stays in use, which is exact: numerator and denominator carry the
+// same factor); O += P V_j with V read in its natural [key][dimension] order (MN-major operand).
+// Two blocks share a multiprocessor (112 KB of shared memory and 256 TMEM columns each), so one
+// block's softmax overlaps the other's MMAs.
 //
 // Same mathematics as the reference's attn_prefill_flash_* (rocml-kernels/kernels/
 // attn_prefill_flash_impl.h:46-159): head h reads key/value head h / g, score = (q.k) * scale, query
@@ -35,14 +39,13 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1e30f;
 constexpr float RESCALE_AT = 8.0f;   // rescale O when a row maximum grew by more than 2^8
 
-// shared memory (bytes): Q 2 x [128][64], K ring 2 x (2 x [64][64]), V ring 2 x (2 x [64][64]), P [128][64]
+// shared memory (bytes): Q 2 x [128][64], K ring 2 x (2 x [64][64]), V ring 2 x (2 x [64][64])
 constexpr int Q_BYTES = 2 * BMQ * 64 * 2;       // 32 KB
 constexpr int KV_TILE = 2 * BNK * 64 * 2;       // 16 KB
-constexpr int P_BYTES = BMQ * BNK * 2;          // 16 KB
 // Two blocks must fit a multiprocessor's 228 KB (each block is charged 1 KB on top of what it asks
 // for): 112 KB of tiles, the barriers, and what is left of the allowance as slack for aligning the
 // tiles to 1 KB (the launch's shared memory normally starts on such a boundary; the kernel checks).
-constexpr int TILE_BYTES = Q_BYTES + 2 * KV_TILE + 2 * KV_TILE + P_BYTES;
+constexpr int TILE_BYTES = Q_BYTES + 2 * KV_TILE + 2 * KV_TILE;
 constexpr int SMEM_BYTES = (228 * 1024) / 2 - 1024;
 static_assert(SMEM_BYTES >= TILE_BYTES + 128, "the tiles and the barriers must fit");
 // tensor memory columns: S0 [0, 64), S1 [64, 128), O [128, 256)
@@ -54,6 +57,26 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// Two float32 operations in one instruction (sm_100): the softmax threads are bound by the instructions
+// they issue, and a pair of neighbouring scores sits in a pair of neighbouring registers anyway.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -83,8 +106,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint8_t* Qs = smem;
     uint8_t* Ks = Qs + Q_BYTES;               // [2 stages][16 KB]
     uint8_t* Vs = Ks + 2 * KV_TILE;
-    uint8_t* Ps = Vs + 2 * KV_TILE;           // V: [2 stages][16 KB]
-    Barriers* bar = (Barriers*)(Ps + P_BYTES);
+    Barriers* bar = (Barriers*)(Vs + 2 * KV_TILE);   // V: [2 stages][16 KB]
 
     // Blocks are handed out with x running fastest.  The last query tiles see the most keys and start
     // first.  heads_first, grid = (heads, sequences, query tiles): the long blocks of ALL heads and
@@ -162,7 +184,6 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // MMAs take the tensor core only 640 cycles: the descriptors are kept as low words that differ
             // from MMA to MMA by constants (sm100.cuh: mma_bf16_lo), not built anew each time.
             const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(Qs)), k_lo0 = smem_desc_sw128_lo(smem_u32(Ks));
-            const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(Ps));
             // V is MN-major: leading byte offset = the distance between its two 64-dimension blocks
             const uint32_t v_lo0 = ((smem_u32(Vs) >> 4) & 0x3FFFu) | ((uint32_t)((KV_TILE / 2) >> 4) << 16);
             auto issue_s = [&](int j) -> bool {
@@ -192,9 +213,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 const uint32_t v_lo = v_lo0 + (j & 1) * (KV_TILE >> 4);
 #pragma unroll
                 for (int k = 0; k < BNK / 16; ++k) {
-                    // A = P [128 rows][64 keys], K-major: 32 bytes per 16 keys.  B = V [64 keys][128 dims],
-                    // MN-major: 64-dimension blocks 8 KB apart, groups of 8 keys 1 KB apart, 16 keys = 2 KB.
-                    mma_bf16_lo(tmem_base + 2 * BNK, p_lo + k * 2, v_lo + k * (2048 >> 4), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    // A = P [128 rows][64 keys] in tensor memory, where S_j was: 16 keys = 8 columns.  B = V [64 keys]
+                    // [128 dims], MN-major: 64-dimension blocks 8 KB apart, groups of 8 keys 1 KB apart, 16 keys = 2 KB.
+                    mma_bf16_ts_lo(tmem_base + 2 * BNK, tmem_base + (j & 1) * BNK + k * 8, v_lo + k * (2048 >> 4), idesc_o,
+                                   (j > 0 || k > 0) ? 1u : 0u);
                 }
                 mma_commit(&bar->v_empty[j & 1]);
                 mma_commit(&bar->o_done);
@@ -227,7 +249,6 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // positive, so the maximum is taken first (three inputs an instruction) and the scale is
             // folded into the exponent's multiply-add, p = 2^(s * scale * log2 e - m), with the bare
             // special-function instruction for 2^x.
-            float mx = NEG_BIG;
             // a tile that every row of this warp sees whole needs no mask
             const int warp_first_pos = pos0 + m0 + quarter * 32;
             if (!(key0 + BNK - 1 <= warp_first_pos && (window <= 0 || key0 > warp_first_pos + 31 - window))) {
@@ -238,50 +259,57 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     sv[i] = ok ? sv[i] : -INFINITY;
                 }
             }
+            // four chains of maxima side by side (three inputs an instruction)
+            float mxa[4];
 #pragma unroll
-            for (int i = 0; i < BNK; i += 2) mx = max3(mx, sv[i], sv[i + 1]);
-            mx *= sl2;
+            for (int q = 0; q < 4; ++q) mxa[q] = fmaxf(sv[2 * q], sv[2 * q + 1]);
+#pragma unroll
+            for (int i = 8; i < BNK; i += 8) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mxa[q] = max3(mxa[q], sv[i + 2 * q], sv[i + 2 * q + 1]);
+            }
+            const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * sl2;
             // the maximum in use only moves when it would otherwise let p exceed 2^8
             const bool grow = mx - m_used > RESCALE_AT;
             const float m_new = grow ? mx : m_used;
             const float alpha = ex2(m_used - m_new);            // 1 when the maximum stays
             m_used = m_new;
             l_sum *= alpha;
-            uint32_t packed[BNK / 2];
-            const float neg_m = -m_used;
-            float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-            for (int i = 0; i < BNK; i += 2) {
-                const float p0 = ex2(fmaf(sv[i], sl2, neg_m)), p1 = ex2(fmaf(sv[i + 1], sl2, neg_m));
-                l0 += p0;
-                l1 += p1;
-                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                packed[i / 2] = *reinterpret_cast<uint32_t*>(&h);
-            }
-            l_sum += l0 + l1;
-            // before P_j replaces P_{j-1} and before O is touched, the MMAs of tile j-1 must be done
-            if (j > 0) {
+            // O is only touched when some row's maximum moved, and only then must the last product be done
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
                 alive = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, (j - 1) & 1));
                 if (!alive) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                    for (int c = 0; c < HD / 16; ++c) {
-                        float ov[16];
-                        tmem_ld16(lane_base + 2 * BNK + c * 16, ov);
+                for (int c = 0; c < HD / 16; ++c) {
+                    float ov[16];
+                    tmem_ld16(lane_base + 2 * BNK + c * 16, ov);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) ov[i] *= alpha;
-                        tmem_st16(lane_base + 2 * BNK + c * 16, ov);
-                    }
-                    tmem_st_wait();
+                    for (int i = 0; i < 16; ++i) ov[i] *= alpha;
+                    tmem_st16(lane_base + 2 * BNK + c * 16, ov);
                 }
             }
-            // P row r: 128 bytes = 8 chunks of 16 bytes, chunk c stored at c ^ (r & 7) (128-byte swizzle)
-            uint8_t* prow = Ps + r * 128;
+            // p = 2^(s * scale * log2 e - m), two at a time; P goes back into the columns S_j came from, as pairs
+            // of bfloat16, and the tensor core reads it from there
+            const uint64_t sl2_2 = pack2(sl2, sl2), neg_m2 = pack2(-m_used, -m_used);
+            uint64_t lacc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
-                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+            for (int c = 0; c < BNK / 32; ++c) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float x0, x1;
+                    unpack2(fma2(pack2(sv[c * 32 + e], sv[c * 32 + e + 1]), sl2_2, neg_m2), x0, x1);
+                    const float p0 = ex2(x0), p1 = ex2(x1);
+                    lacc[(e >> 1) & 3] = add2(lacc[(e >> 1) & 3], pack2(p0, p1));
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                tmem_st16u(lane_base + s * BNK + c * 16, packed);
+            }
+            float l0, l1;
+            unpack2(add2(add2(lacc[0], lacc[1]), add2(lacc[2], lacc[3])), l0, l1);
+            l_sum += l0 + l1;
             // the last tile may reach past the sequence's end: what lies there in the page is not ours, and
             // a stale NaN times a zero probability would still poison the sum, so those V rows are zeroed
             // (after the tile has landed, before the product reads it)
@@ -296,10 +324,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                         *reinterpret_cast<uint4*>(Vt + (ch >> 3) * (KV_TILE / 2) + vr * 128 + (((ch & 7) ^ (vr & 7)) << 4)) =
                             make_uint4(0, 0, 0, 0);
                     }
+                    fence_proxy_async();         // shared-memory writes become visible to the tensor core
                 }
             }
+            tmem_st_wait();
             tc_fence_before();
-            fence_proxy_async();                 // shared-memory writes become visible to the tensor core
             mbar_arrive(&bar->p_full);
         }
         if (alive) alive = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, (n_tiles - 1) & 1));

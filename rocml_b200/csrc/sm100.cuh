@@ -230,7 +230,26 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
           "r"(__float_as_uint(v[15]))
         : "memory");
 }
+// The same from 32-bit words (pairs of bfloat16: an A operand that the tensor core reads from tensor memory).
+__device__ __forceinline__ void tmem_st16u(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: A lies in tensor memory, row r of the 128 in lane r, two bfloat16 of
+// consecutive K in each 32-bit column (16 elements of K = 8 columns); B from its descriptor's low word.
+__device__ __forceinline__ void mma_bf16_ts_lo(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 b;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\tmov.b64 b, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_SW128_HI)
+        : "memory");
+}
 
 // ---- pairs of CTAs (cta_group::2) -------------------------------------------------------------------
 // Two CTAs of a cluster act as one MMA unit: the MMA of the even CTA (the leader) reads A and B

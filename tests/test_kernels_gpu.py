@@ -483,13 +483,23 @@ def test_attention_prefill_tensor_cores(case):
     assert err < 2e-2, err
 
 
-@pytest.mark.parametrize("case", [1, 2])
+TC5_CASES = [
+    PRE_CASES[1],
+    PRE_CASES[2],
+    ([1000, 333, 129, 64], [1000, 77, 129, 1], 4, 2, 128, None),   # several tiles of 256 queries; pieces that start anywhere
+    ([900], [600], 2, 1, 128, 200),                                # a window that spans tiles of 128 keys
+    ([520, 257], [520, 130], 3, 3, 128, 130),                      # a window about as wide as a tile; a last tile of one page
+    ([448, 449, 385], [448, 449, 2], 2, 2, 128, None),             # lengths around the edges of pages and tiles
+]
+
+
+@pytest.mark.parametrize("case", range(len(TC5_CASES)))
 def test_attention_prefill_tcgen05(case):
-    """The tensor-memory kernel (head size 128) on the same cases, and on a longer one."""
+    """The tensor-memory kernel (head size 128): pieces of prompts, windows, lengths around the tiles' edges."""
     from rocml_b200 import kernels
-    lens, q_lens, nq, nkv, hd, window = PRE_CASES[case]
+    lens, q_lens, nq, nkv, hd, window = TC5_CASES[case]
     dtype = torch.bfloat16
-    spike = (0, 2) if case == 1 else None
+    spike = (0, 2) if case == 0 else None
     ks, vs, qs, kc, vc, meta = paged_case(20 + case, lens, q_lens, nq, nkv, hd, dtype, spike)
     scale = 1.0 / math.sqrt(hd)
     want = reference_attention(ks, vs, qs, window, scale)
