@@ -84,8 +84,19 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+// A softmax thread's wait: the flag that another role raises when its own wait ran out is only looked at
+// while the barrier is not yet complete (the usual case finds it complete and pays for nothing else).
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, const uint32_t* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*(volatile const uint32_t*)abort_flag != 0 || clock64() - t0 > RB_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+
 struct Barriers {
-    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_done;
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_done, o_final;
     uint32_t tmem_slot, abort_flag;
 };
 
@@ -138,6 +149,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         }
         mbar_init(&bar->p_full, 128);
         mbar_init(&bar->o_done, 1);
+        mbar_init(&bar->o_final, 1);
         bar->abort_flag = 0;
         fence_barrier_init();
     }
@@ -220,11 +232,13 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 }
                 mma_commit(&bar->v_empty[j & 1]);
                 mma_commit(&bar->o_done);
+                // The softmax threads wait for O only when they rescale it, so at the end they may be two
+                // phases behind o_done, which a parity cannot tell apart: the last product has a barrier of its own.
+                if (j == n_tiles - 1) mma_commit(&bar->o_final);
             }
             if (!ok) {
                 atomicExch(status, RB_ERR_TIMEOUT);
-                atomicExch(&bar->abort_flag, 1u);
-                mma_commit(&bar->s_full[0]); mma_commit(&bar->s_full[1]); mma_commit(&bar->o_done);
+                atomicExch(&bar->abort_flag, 1u);      // the softmax threads' waits see it and give up
             }
         }
     } else {
@@ -238,7 +252,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         bool alive = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
-            alive = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[s], (j >> 1) & 1)) && *(volatile uint32_t*)&bar->abort_flag == 0;
+            alive = __all_sync(0xffffffffu, wait_or_abort(&bar->s_full[s], (j >> 1) & 1, &bar->abort_flag));
             if (!alive) break;
             tc_fence_after();
             const int key0 = (kt_first + j) * BNK;
@@ -277,7 +291,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             l_sum *= alpha;
             // O is only touched when some row's maximum moved, and only then must the last product be done
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                alive = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, (j - 1) & 1));
+                alive = __all_sync(0xffffffffu, wait_or_abort(&bar->o_done, (j - 1) & 1, &bar->abort_flag));
                 if (!alive) break;
                 tc_fence_after();
 #pragma unroll 1
@@ -316,7 +330,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (j == n_tiles - 1) {
                 const int valid = min(BNK, len - key0);
                 if (valid < BNK) {
-                    alive = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[j & 1], (j >> 1) & 1));
+                    alive = __all_sync(0xffffffffu, wait_or_abort(&bar->v_full[j & 1], (j >> 1) & 1, &bar->abort_flag));
                     if (!alive) break;
                     uint8_t* Vt = Vs + (j & 1) * KV_TILE;
                     for (int idx = threadIdx.x - 64; idx < (BNK - valid) * 16; idx += 128) {
@@ -331,7 +345,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             tc_fence_before();
             mbar_arrive(&bar->p_full);
         }
-        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, (n_tiles - 1) & 1));
+        if (alive) alive = __all_sync(0xffffffffu, wait_or_abort(&bar->o_final, 0, &bar->abort_flag));
         if (alive) {
             tc_fence_after();
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
