@@ -3,6 +3,7 @@ workloads of the same kind, and the sweeps and timelines that the notes under ``
 
     python -m rocml_b200.measure sweep [--model NAME]         decode steps over batch sizes and contexts
     python -m rocml_b200.measure timeline [--batch B]         every kernel of one decode step, start and end
+    python -m rocml_b200.measure timeline --prompt N          the same for the step that takes a prompt of N tokens
     python -m rocml_b200.measure sampler                      one sampling step, by way of sampling and batch
     python -m rocml_b200.measure gemm-decode | gemm-prefill   the tensor-core product alone, in a CUDA graph
     python -m rocml_b200.measure workload 4b-long | 32b       a whole generation through Engine.generate
@@ -332,6 +333,40 @@ def sweep(cases=None, steps=32, model=None):
         torch.cuda.empty_cache()
 
 
+def prompt_timeline(n_tokens, layers=4, model=None):
+    """The same listing for the step that takes one prompt of ``n_tokens`` tokens (no CUDA graph: a prompt's
+    kernels are long enough that the host stays ahead of them)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from . import StepEntry
+    cfg, n_full, eng = build_engine(layers, n_tokens + 256, 1, model=model)
+    p = prompts(1, n_tokens, cfg.vocab_size, 3)[0]
+
+    def one():
+        slot = eng.new_sequence()
+        eng.step([StepEntry(slot, p, [n_tokens - 1])])
+        eng.release(slot)
+
+    for _ in range(3):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            one()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                key=lambda e: e.time_range.start)
+    last = ev[-(len(ev) // 3):]
+    t0, prev_end = last[0].time_range.start, None
+    print(f"one prompt of {n_tokens} tokens, {layers} layers: start, end, added (us), kernel")
+    for e in last:
+        end = e.time_range.end
+        added = end - (prev_end if prev_end is not None else e.time_range.start)
+        prev_end = max(end, prev_end or end)
+        print(f"{e.time_range.start - t0:9.2f} {end - t0:9.2f} {added:7.2f}  {e.name[:90]}")
+    print(f"step: {prev_end - t0:.1f} us")
+
+
 def timeline(batch=BATCH, layers=4, model=None):
     """Where a decode step's time goes, kernel by kernel, as the step really runs (inside its CUDA
     graph, kernels overlapping their predecessors through programmatic dependent launch): start and
@@ -551,12 +586,15 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the entry has (0: all; timeline: 4)")
     ap.add_argument("--runs", type=int, default=1)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="of profile")
-    ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length of profile")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length of profile; of timeline: list a prompt's step instead")
     args = ap.parse_args(argv)
     if args.what == "sweep":
         sweep(None if args.model == "qwen3-8b" else [(1, 1024), (8, 1024), (8, 8192), (64, 1024)], model=args.model)
     elif args.what == "timeline":
-        timeline(args.batch, args.layers or 4, model=args.model)
+        if args.prompt != PROMPT:
+            prompt_timeline(args.prompt, args.layers or 4, model=args.model)
+        else:
+            timeline(args.batch, args.layers or 4, model=args.model)
     elif args.what == "sampler":
         sampler_times()
     elif args.what in ("gemm-decode", "gemm-prefill"):
