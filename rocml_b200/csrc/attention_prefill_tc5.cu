@@ -12,8 +12,9 @@
 // window), update the running maximum and sum in float32 (base 2, the scale folded into the
 // exponent's multiply-add, two scores an instruction), and write P as pairs of bfloat16 back into
 // the first 32 columns of the buffer S_j came from: the tensor core reads its A operand from there
-// (no shared-memory round trip, no proxy fence; S_{j+2} overwrites the buffer only after the product
-// that read it, because one thread's MMAs run in order).  Only when some row's maximum has grown by
+// (no shared-memory round trip, no proxy fence; the MMA thread forms S_{j+2} in that buffer only once
+// the product that read P_j from it is done: two MMAs that write different accumulators are not
+// sure to run in the order they were issued).  Only when some row's maximum has grown by
 // more than 2^8 does a warp wait for the last product and rescale the O accumulator in tensor memory
 // (otherwise the stale maximum stays in use, which is exact: numerator and denominator carry the
 // same factor); O += P V_j with V read in its natural [key][dimension] order (MN-major operand).
@@ -96,7 +97,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, co
 }
 
 struct Barriers {
-    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_done, o_final;
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done, o_final;
     uint32_t tmem_slot, abort_flag;
 };
 
@@ -147,7 +148,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             mbar_init(&bar->k_full[i], 1); mbar_init(&bar->k_empty[i], 1); mbar_init(&bar->s_full[i], 1);
             mbar_init(&bar->v_full[i], 1); mbar_init(&bar->v_empty[i], 1);
         }
-        mbar_init(&bar->p_full, 128);
+        mbar_init(&bar->p_full[0], 128);
+        mbar_init(&bar->p_full[1], 128);
         mbar_init(&bar->o_done, 1);
         mbar_init(&bar->o_final, 1);
         bar->abort_flag = 0;
@@ -200,6 +202,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             const uint32_t v_lo0 = ((smem_u32(Vs) >> 4) & 0x3FFFu) | ((uint32_t)((KV_TILE / 2) >> 4) << 16);
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1;
+                // S_j goes into the buffer that still holds P_{j-2}: the product that reads it must be DONE, not
+                // just issued.  MMAs of one thread are only sure to run in order when they write the same
+                // accumulator, and this one writes S while that one wrote O.
+                if (j >= 2 && !mbar_wait(&bar->o_done, (j - 2) & 1)) return false;
                 if (!mbar_wait(&bar->k_full[s], (j >> 1) & 1)) return false;
                 tc_fence_after();
                 const uint32_t k_lo = k_lo0 + s * (KV_TILE >> 4);
@@ -219,7 +225,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (ok) { tc_fence_after(); ok = issue_s(0); }
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
-                ok = mbar_wait(&bar->p_full, j & 1) && mbar_wait(&bar->v_full[j & 1], (j >> 1) & 1);
+                ok = mbar_wait(&bar->p_full[j & 1], (j >> 1) & 1) && mbar_wait(&bar->v_full[j & 1], (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t v_lo = v_lo0 + (j & 1) * (KV_TILE >> 4);
@@ -343,7 +349,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             }
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&bar->p_full);
+            // A warp may be a tile ahead of another (S_{j+1} is there before the other has handed P_j over; a warp
+            // that needs no mask and no rescaling is quicker), never two (S_{j+2} follows the product of P_j): the
+            // arrivals of even and odd tiles are counted apart, or the quick warp's next arrival would complete
+            // this tile's count while the slow warp's rows of P are still missing.
+            mbar_arrive(&bar->p_full[j & 1]);
         }
         if (alive) alive = __all_sync(0xffffffffu, wait_or_abort(&bar->o_final, 0, &bar->abort_flag));
         if (alive) {

@@ -514,9 +514,10 @@ def test_attention_prefill_tcgen05(case):
     assert err < 2e-2, err
 
 
-@pytest.mark.parametrize("nq,nkv,q_len,kv_len,spread", [(32, 8, 4096, 4096, 1.0), (4, 2, 4096, 4096, 4.0), (32, 8, 104, 4200, 1.0),
-                                                        (8, 8, 1500, 1500, 6.0)])
-def test_attention_prefill_tcgen05_with_every_multiprocessor_busy(nq, nkv, q_len, kv_len, spread):
+@pytest.mark.parametrize("nq,nkv,q_len,kv_len,spread,window", [
+    (32, 8, 4096, 4096, 1.0, 0), (4, 2, 4096, 4096, 4.0, 0), (32, 8, 104, 4200, 1.0, 0), (8, 8, 1500, 1500, 6.0, 0),
+    (32, 8, 3000, 3000, 3.0, 700)])
+def test_attention_prefill_tcgen05_with_every_multiprocessor_busy(nq, nkv, q_len, kv_len, spread, window):
     """Thousands of blocks, two a multiprocessor, and scores spread widely enough that the running maxima move
     often: what depends on the order in which a block's roles get to run shows here.  Against the mma.sync
     kernel, which shares no code with it."""
@@ -533,10 +534,10 @@ def test_attention_prefill_tcgen05_with_every_multiprocessor_busy(nq, nkv, q_len
     kv = torch.tensor([kv_len], dtype=torch.int32, device=DEV)
     got, want = torch.full_like(q, float("nan")), torch.full_like(q, float("nan"))
     scale = 1.0 / math.sqrt(hd)
-    for _ in range(3):       # the order in which roles run differs from launch to launch
-        assert kernels.attention_prefill_tc5(q, q_len, got, kc, vc, table, seq_slot, cu, kv, 1, q_len, nq, nkv, hd, scale, 0,
+    for _ in range(8):       # the order in which roles run differs from launch to launch
+        assert kernels.attention_prefill_tc5(q, q_len, got, kc, vc, table, seq_slot, cu, kv, 1, q_len, nq, nkv, hd, scale, window,
                                              max_kv_len=kv_len)
-        assert kernels.attention_prefill(q, want, kc, vc, table, seq_slot, cu, kv, 1, q_len, nq, nkv, hd, scale, 0)
+        assert kernels.attention_prefill(q, want, kc, vc, table, seq_slot, cu, kv, 1, q_len, nq, nkv, hd, scale, window)
         kernels.check_status(DEV)
         err = (got.float() - want.float()).abs().max().item()
         assert err < 3e-2, err
