@@ -184,3 +184,48 @@ def test_a_long_prompt_in_pieces_at_full_sizes(setup):
         assert int(got["float32"][t].argmax()) == int(want[t].argmax()) or near_tie(want[t], 1e-4)
         assert int(got["bfloat16"][t].argmax()) == int(got["float32"][t].argmax()) or near_tie(got["float32"][t])
     print(f"long prompt, float32 against the plain implementation: {err32:.2e}")
+
+
+@pytest.mark.parametrize("window", [None, 700])
+def test_a_batch_of_long_prompts_at_full_sizes(setup, window, tmp_path):
+    """Eight prompts of 600 to 1,024 tokens in one step (thousands of attention blocks, every multiprocessor
+    busy, two pieces of at most 4,096 tokens), then two tokens each: bfloat16 against the 32-bit engine at the
+    prompts' last places and the decoded ones, twice over so that slots and pages are used again.  What depends
+    on the order in which a busy GPU runs a kernel's blocks and warps shows here or nowhere; with a sliding
+    window in the second layer the warps of an attention block differ most in what they have to do, and a
+    token whose row went wrong in the first layer spoils every later token that sees it."""
+    from rocml_b200 import Engine, StepEntry
+    folder, _, _ = setup
+    if window is not None:
+        from rocml_b200.config import CATALOG, config_from_dict
+        from rocml_b200.weights import write_random_model
+        sizes = dict(CATALOG["qwen3-8b"].config)
+        sizes.update(num_hidden_layers=N_LAYERS, use_sliding_window=True, sliding_window=window, max_window_layers=0,
+                     layer_types=["sliding_attention", "full_attention"])
+        folder = str(tmp_path / "windowed")
+        write_random_model(folder, config_from_dict(sizes), seed=9)
+    g = torch.Generator().manual_seed(82)
+    lens = [1024, 600, 777, 1000, 913, 650, 1024, 841]
+    prompts = [torch.randint(0, 151936, (n + 2,), generator=g).tolist() for n in lens]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=8 * 1088, max_slots=8)
+        rounds = []
+        for _ in range(2):
+            slots = [eng.new_sequence() for _ in lens]
+            out = [eng.step([StepEntry(s, p[:n], [n - 1]) for s, p, n in zip(slots, prompts, lens)]).float().cpu()]
+            for t in range(2):
+                out.append(eng.step([StepEntry(s, [p[n + t]], [0]) for s, p, n in zip(slots, prompts, lens)]).float().cpu())
+            rounds.append(torch.cat(out))
+            for s in slots:
+                eng.release(s)
+        got[dtype] = rounds
+        del eng
+        torch.cuda.empty_cache()
+    assert torch.equal(got["float32"][0], got["float32"][1])         # the same work gives the same bits
+    assert torch.equal(got["bfloat16"][0], got["bfloat16"][1])
+    assert not torch.isnan(got["bfloat16"][0]).any()
+    err = rel_err(got["bfloat16"][0], got["float32"][0])
+    assert err < TOL_BF16, err
+    for r in range(got["float32"][0].shape[0]):
+        assert int(got["bfloat16"][0][r].argmax()) == int(got["float32"][0][r].argmax()) or near_tie(got["float32"][0][r])
