@@ -1,7 +1,7 @@
 // Flash attention for bfloat16 prompts over the paged cache on the 5th-generation tensor cores:
 // S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory; Q, K and V tiles
 // arrive by TMA; the softmax runs in registers, one thread per query row (a TMEM lane is a row, so no
-// shuffles are needed for row maxima and sums).  Head size 128.
+// shuffles are needed for row maxima and sums).  Head sizes 64, 128 and 256 (a template argument).
 //
 // A block takes 128 query tokens of one sequence and one query head and walks the keys page by page
 // (a page of the cache is one 64-key tile).  Roles: warp 0 issues TMA loads (Q once, K and V in rings
@@ -18,8 +18,9 @@
 // more than 2^8 does a warp wait for the last product and rescale the O accumulator in tensor memory
 // (otherwise the stale maximum stays in use, which is exact: numerator and denominator carry the
 // same factor); O += P V_j with V read in its natural [key][dimension] order (MN-major operand).
-// Two blocks share a multiprocessor (112 KB of shared memory and 256 TMEM columns each), so one
-// block's softmax overlaps the other's MMAs.
+// Up to head size 128 two blocks share a multiprocessor (112 KB of shared memory and 256 TMEM columns
+// each), so one block's softmax overlaps the other's MMAs; at head size 256 a block's tiles take 192 KB
+// and its accumulators 384 columns, so it is alone.
 //
 // Same mathematics as the reference's attn_prefill_flash_* (rocml-kernels/kernels/
 // attn_prefill_flash_impl.h:46-159): head h reads key/value head h / g, score = (q.k) * scale, query
@@ -33,24 +34,30 @@
 using namespace sm100;
 
 namespace {
-constexpr int HD = 128;
 constexpr int BMQ = 128;      // query rows per block
 constexpr int BNK = 64;       // keys per tile = one page
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1e30f;
 constexpr float RESCALE_AT = 8.0f;   // rescale O when a row maximum grew by more than 2^8
 
-// shared memory (bytes): Q 2 x [128][64], K ring 2 x (2 x [64][64]), V ring 2 x (2 x [64][64])
-constexpr int Q_BYTES = 2 * BMQ * 64 * 2;       // 32 KB
-constexpr int KV_TILE = 2 * BNK * 64 * 2;       // 16 KB
-// Two blocks must fit a multiprocessor's 228 KB (each block is charged 1 KB on top of what it asks
-// for): 112 KB of tiles, the barriers, and what is left of the allowance as slack for aligning the
-// tiles to 1 KB (the launch's shared memory normally starts on such a boundary; the kernel checks).
-constexpr int TILE_BYTES = Q_BYTES + 2 * KV_TILE + 2 * KV_TILE;
-constexpr int SMEM_BYTES = (228 * 1024) / 2 - 1024;
-static_assert(SMEM_BYTES >= TILE_BYTES + 128, "the tiles and the barriers must fit");
-// tensor memory columns: S0 [0, 64), S1 [64, 128), O [128, 256)
-constexpr int TMEM_COLS = 256;
+// What depends on the head size (64, 128 or 256): every tile is HD / 64 blocks of 64 dimensions (128 bytes a row,
+// 128-byte swizzle), one TMA box each.
+template <int HD>
+struct Sizes {
+    static constexpr int HALVES = HD / 64;                 // 64-dimension blocks a row
+    static constexpr int Q_BYTES = BMQ * HD * 2;           // Q: HALVES x [128 rows][64]; 32 KB at head size 128
+    static constexpr int KV_TILE = BNK * HD * 2;           // K or V: HALVES x [64 keys][64]; 16 KB at head size 128
+    static constexpr int Q_HALF = Q_BYTES / HALVES, KV_HALF = KV_TILE / HALVES;
+    static constexpr int TILE_BYTES = Q_BYTES + 2 * KV_TILE + 2 * KV_TILE;     // K and V in rings of two
+    // Up to head size 128 two blocks share a multiprocessor's 228 KB (each block is charged 1 KB on top of what
+    // it asks for) and its 512 tensor-memory columns; what is left of the allowance is slack for aligning
+    // the tiles to 1 KB (the launch's shared memory normally starts on such a boundary; the kernel checks).
+    static constexpr int BLOCKS_PER_SM = HD <= 128 ? 2 : 1;
+    static constexpr int SMEM_BYTES = BLOCKS_PER_SM == 2 ? (228 * 1024) / 2 - 1024 : TILE_BYTES + 2048;
+    static_assert(SMEM_BYTES >= TILE_BYTES + 1024 + 128, "the tiles, their alignment and the barriers must fit");
+    // tensor memory columns: S0 [0, 64), S1 [64, 128), O [128, 128 + HD)
+    static constexpr int TMEM_COLS = HD <= 128 ? 256 : 512;
+};
 
 // 2^x on the special-function unit, one instruction (x <= 0 here, -inf gives 0); the library's exp2f
 // adds range handling that the softmax does not need.
@@ -101,12 +108,16 @@ struct Barriers {
     uint32_t tmem_slot, abort_flag;
 };
 
-__global__ void __launch_bounds__(192, 2)
+template <int HD>
+__global__ void __launch_bounds__(192, Sizes<HD>::BLOCKS_PER_SM)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int o_stride,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                              const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
                              float scale, int window, int heads_first, int* __restrict__ status) {
+    using Z = Sizes<HD>;
+    constexpr int HALVES = Z::HALVES, Q_BYTES = Z::Q_BYTES, KV_TILE = Z::KV_TILE, Q_HALF = Z::Q_HALF, KV_HALF = Z::KV_HALF;
+    constexpr int TILE_BYTES = Z::TILE_BYTES, SMEM_BYTES = Z::SMEM_BYTES, TMEM_COLS = Z::TMEM_COLS;
     rb::pdl_trigger();
     rb::pdl_wait();
     extern __shared__ uint8_t smem_raw[];
@@ -170,8 +181,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             tma_prefetch_desc(&map_k);
             tma_prefetch_desc(&map_v);
             mbar_arrive_expect_tx(&bar->q_full, Q_BYTES);
-            tma_load_2d(Qs, &map_q, head * HD, q0 + m0, &bar->q_full);
-            tma_load_2d(Qs + Q_BYTES / 2, &map_q, head * HD + 64, q0 + m0, &bar->q_full);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) tma_load_2d(Qs + h * Q_HALF, &map_q, head * HD + h * 64, q0 + m0, &bar->q_full);
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int page = table[kt_first + j];
@@ -180,13 +191,13 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 ok = mbar_wait(&bar->k_empty[s], ((j >> 1) & 1) ^ 1);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&bar->k_full[s], KV_TILE);
-                tma_load_2d(Ks + s * KV_TILE, &map_k, 0, row, &bar->k_full[s]);
-                tma_load_2d(Ks + s * KV_TILE + KV_TILE / 2, &map_k, 64, row, &bar->k_full[s]);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_2d(Ks + s * KV_TILE + h * KV_HALF, &map_k, h * 64, row, &bar->k_full[s]);
                 ok = mbar_wait(&bar->v_empty[s], ((j >> 1) & 1) ^ 1);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&bar->v_full[s], KV_TILE);
-                tma_load_2d(Vs + s * KV_TILE, &map_v, 0, row, &bar->v_full[s]);
-                tma_load_2d(Vs + s * KV_TILE + KV_TILE / 2, &map_v, 64, row, &bar->v_full[s]);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) tma_load_2d(Vs + s * KV_TILE + h * KV_HALF, &map_v, h * 64, row, &bar->v_full[s]);
             }
             if (!ok) { atomicExch(status, RB_ERR_TIMEOUT); atomicExch(&bar->abort_flag, 1u); }
         }
@@ -199,7 +210,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // from MMA to MMA by constants (sm100.cuh: mma_bf16_lo), not built anew each time.
             const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(Qs)), k_lo0 = smem_desc_sw128_lo(smem_u32(Ks));
             // V is MN-major: leading byte offset = the distance between its two 64-dimension blocks
-            const uint32_t v_lo0 = ((smem_u32(Vs) >> 4) & 0x3FFFu) | ((uint32_t)((KV_TILE / 2) >> 4) << 16);
+            const uint32_t v_lo0 = ((smem_u32(Vs) >> 4) & 0x3FFFu) | ((uint32_t)(KV_HALF >> 4) << 16);
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1;
                 // S_j goes into the buffer that still holds P_{j-2}: the product that reads it must be DONE, not
@@ -213,8 +224,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     // dimension block k / 4 (64 dimensions each), 32 bytes (2 units of 16) per step inside it
-                    const uint32_t qo = (k >> 2) * ((Q_BYTES / 2) >> 4) + (k & 3) * 2;
-                    const uint32_t ko = (k >> 2) * ((KV_TILE / 2) >> 4) + (k & 3) * 2;
+                    const uint32_t qo = (k >> 2) * (Q_HALF >> 4) + (k & 3) * 2;
+                    const uint32_t ko = (k >> 2) * (KV_HALF >> 4) + (k & 3) * 2;
                     mma_bf16_lo(d, q_lo + qo, k_lo + ko, idesc_s, k > 0 ? 1u : 0u);
                 }
                 mma_commit(&bar->k_empty[s]);
@@ -339,9 +350,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     alive = __all_sync(0xffffffffu, wait_or_abort(&bar->v_full[j & 1], (j >> 1) & 1, &bar->abort_flag));
                     if (!alive) break;
                     uint8_t* Vt = Vs + (j & 1) * KV_TILE;
-                    for (int idx = threadIdx.x - 64; idx < (BNK - valid) * 16; idx += 128) {
-                        const int vr = valid + idx / 16, ch = idx % 16;      // row vr, 16-byte chunk ch of its 256 bytes
-                        *reinterpret_cast<uint4*>(Vt + (ch >> 3) * (KV_TILE / 2) + vr * 128 + (((ch & 7) ^ (vr & 7)) << 4)) =
+                    constexpr int CHUNKS = HD / 8;       // 16-byte chunks of a row of HD bfloat16
+                    for (int idx = threadIdx.x - 64; idx < (BNK - valid) * CHUNKS; idx += 128) {
+                        const int vr = valid + idx / CHUNKS, ch = idx % CHUNKS;   // row vr, chunk ch of its HD * 2 bytes
+                        *reinterpret_cast<uint4*>(Vt + (ch >> 3) * KV_HALF + vr * 128 + (((ch & 7) ^ (vr & 7)) << 4)) =
                             make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async();         // shared-memory writes become visible to the tensor core
@@ -438,38 +450,50 @@ int make_map(const void* ptr, long long rows, long long cols, long long ld, int 
     cache[key] = *out;
     return RB_OK;
 }
-}  // namespace
-
-// q rows [T, q_stride] bfloat16 (T = tokens of the step), caches [n_pages, nkv, 64, 128].  heads_first: the order
-// in which blocks start (see the kernel); it changes no result.  Head size 128
-// only; RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).
-extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride,
-                                        const void* k_cache, const void* v_cache, int n_pages,
-                                        const int* block_table, int max_pages, const int* seq_slot,
-                                        const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv,
-                                        int hd, float scale, int window, int heads_first, int* status, void* stream) {
-    if (B <= 0 || max_q_len <= 0 || T <= 0) return RB_OK;
-    if (hd != HD || nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
-    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15) ||
-        (q_stride % 8) || (o_stride % 8))
-        return RB_ERR_BAD_ALIGN;
+template <int HD>
+int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, const void* k_cache, const void* v_cache,
+               int n_pages, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
+               const int* kv_len, int B, int max_q_len, int nq, int nkv, float scale, int window, int heads_first,
+               int* status, cudaStream_t stream) {
     CUtensorMap mq, mk, mv;
     int rc;
     if ((rc = make_map(q, T, (long long)nq * HD, q_stride, BMQ, &mq)) != RB_OK) return rc;
     const long long cache_rows = (long long)n_pages * nkv * RB_PAGE;
     if ((rc = make_map(k_cache, cache_rows, HD, HD, BNK, &mk)) != RB_OK) return rc;
     if ((rc = make_map(v_cache, cache_rows, HD, HD, BNK, &mv)) != RB_OK) return rc;
-    auto k = attention_prefill_tc5_kernel;
+    auto k = attention_prefill_tc5_kernel<HD>;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Sizes<HD>::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
     const int q_tiles = (max_q_len + BMQ - 1) / BMQ;
     dim3 grid = heads_first ? dim3(nq, B, q_tiles) : dim3(q_tiles, nq, B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
-    RB_LAUNCH((k), grid, dim3(192), SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
+    RB_LAUNCH((k), grid, dim3(192), Sizes<HD>::SMEM_BYTES, stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
               block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, heads_first, status);
     return RB_OK;
+}
+}  // namespace
+
+// q rows [T, q_stride] bfloat16 (T = tokens of the step), caches [n_pages, nkv, 64, hd].  heads_first: the order
+// in which blocks start (see the kernel); it changes no result.  Head sizes 64, 128 and 256;
+// RB_ERR_BAD_SIZE / RB_ERR_BAD_ALIGN otherwise (the caller then uses the mma.sync kernel).
+extern "C" int rb_attention_prefill_tc5(const void* q, int q_stride, int T, void* out, int o_stride,
+                                        const void* k_cache, const void* v_cache, int n_pages,
+                                        const int* block_table, int max_pages, const int* seq_slot,
+                                        const int* cu_q, const int* kv_len, int B, int max_q_len, int nq, int nkv,
+                                        int hd, float scale, int window, int heads_first, int* status, void* stream) {
+    if (B <= 0 || max_q_len <= 0 || T <= 0) return RB_OK;
+    if ((hd != 64 && hd != 128 && hd != 256) || nkv <= 0 || nq % nkv) return RB_ERR_BAD_SIZE;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15) ||
+        (q_stride % 8) || (o_stride % 8))
+        return RB_ERR_BAD_ALIGN;
+#define RB_TC5_ARGS q, q_stride, T, out, o_stride, k_cache, v_cache, n_pages, block_table, max_pages, seq_slot, cu_q, kv_len, \
+                    B, max_q_len, nq, nkv, scale, window, heads_first, status, (cudaStream_t)stream
+    if (hd == 64) return launch_tc5<64>(RB_TC5_ARGS);
+    if (hd == 128) return launch_tc5<128>(RB_TC5_ARGS);
+    return launch_tc5<256>(RB_TC5_ARGS);
+#undef RB_TC5_ARGS
 }

@@ -357,12 +357,12 @@ def attention_prefill_tc5(q: torch.Tensor, n_tokens: int, out: torch.Tensor, k_c
                           block_table: torch.Tensor, seq_slot: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                           n_seqs: int, max_q_len: int, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
                           max_kv_len: Optional[int] = None) -> bool:
-    """bfloat16 flash attention with tcgen05 (accumulators in tensor memory, TMA loads), head size 128.
+    """bfloat16 flash attention with tcgen05 (accumulators in tensor memory, TMA loads), head sizes 64, 128 and 256.
     ``max_kv_len`` (the longest context of the step; the longest query if not given) only decides the
     order in which blocks start: the longest blocks of all heads first while the keys and values that
     the step reads fit the L2 cache, one head after another beyond.  Returns False when the kernel
     does not take the head size or the alignment."""
-    if hd != 128 or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
+    if hd not in (64, 128, 256) or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
             q.stride(-1) != 1 or out.stride(-1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
         return False
     if tuple(k_cache.shape[1:]) != (nkv, PAGE, hd) or k_cache.shape != v_cache.shape:

@@ -490,6 +490,10 @@ TC5_CASES = [
     ([900], [600], 2, 1, 128, 200),                                # a window that spans tiles of 128 keys
     ([520, 257], [520, 130], 3, 3, 128, 130),                      # a window about as wide as a tile; a last tile of one page
     ([448, 449, 385], [448, 449, 2], 2, 2, 128, None),             # lengths around the edges of pages and tiles
+    PRE_CASES[0],                                                  # head size 64
+    PRE_CASES[3],                                                  # head size 64, a window, 6:1 groups
+    PRE_CASES[4],                                                  # head size 256
+    ([700, 130], [450, 130], 4, 2, 256, 150),                      # head size 256: a piece of a prompt, a window
 ]
 
 
