@@ -223,19 +223,24 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
             for (int j = 0; j < ROWS_NW; ++j) dst[u][j] = k < k_end ? ld_stream(wr[j] + k) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
-    auto load_x = [&](int buf, int k0) {          // the whole block copies the tile's rows; beyond K or M: zeros
+    // The whole block copies the tile's rows (beyond K or M: zeros), asynchronously: a load that the thread
+    // itself had to store would hold it for a round trip to the L2 cache before every tile's arithmetic.
+    auto load_x = [&](int buf, int k0) {
         for (int i = threadIdx.x; i < MT * (KT / 4); i += ROWS_WARPS * 32) {
             const int m = i / (KT / 4), k = k0 + (i % (KT / 4)) * 4;
-            const float4 v = (m < M && k < k_end) ? *reinterpret_cast<const float4*>(x + (size_t)m * ldx + k)
-                                              : make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4*>(&xs[buf][m][(i % (KT / 4)) * 4]) = v;
+            const bool in = m < M && k < k_end;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&xs[buf][m][(i % (KT / 4)) * 4]);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(in ? x + (size_t)m * ldx + k : x),
+                         "r"(in ? 16 : 0) : "memory");          // 0 bytes read: the 16 bytes are zero-filled
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
     // the weights do not depend on the kernel before this one: their first tile is requested at once
     float4 wv[U][ROWS_NW];
     load_w(wv, k_lo);
     pdl_wait();
     load_x(0, k_lo);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     int buf = 0;
     for (int k0 = k_lo; k0 < k_end; k0 += KT, buf ^= 1) {
@@ -260,6 +265,7 @@ gemm_rows_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, c
         for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int j = 0; j < ROWS_NW; ++j) wv[u][j] = nx[u][j];
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();      // the next tile's rows are in place, and nobody reads this tile's any more
     }
 #pragma unroll
