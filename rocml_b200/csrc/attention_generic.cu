@@ -18,6 +18,7 @@
 //
 // This kernel is the attention of the true 32-bit path and the reference the tensor-core
 // kernels are tested against.
+#include <type_traits>
 #include "common.cuh"
 #include "api.h"
 #include <math.h>
@@ -40,7 +41,7 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int o_stride,
                          const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                          const int* __restrict__ block_table, int max_pages,
@@ -113,7 +114,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     float m[RW], l[RW], acc[RW][MAX_DPL];
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
-        const int r = warp * RW + i;
+        const int r = i * 4 + warp;               // the block's rows are dealt out over its four warps in turn
         const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
         row_ok[i] = r < QB * HG && qi < q_len && hg < g;
         row_pos[i] = pos0 + qi;
@@ -122,6 +123,19 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         l[i] = 0.f;
 #pragma unroll
         for (int j = 0; j < MAX_DPL; ++j) acc[i][j] = 0.f;
+    }
+
+    // A block with few rows (a decode step: one token, the group's heads) gives each warp one of them instead of
+    // all to the first warp, and a warp works on the rows it has: n_rows of them if they are its first ones
+    // (the usual case), all four otherwise.
+    int n_rows = 0;
+    {
+        bool prefix = true;
+#pragma unroll
+        for (int i = 0; i < RW; ++i) {
+            if (row_ok[i]) { if (n_rows != i) prefix = false; ++n_rows; }
+        }
+        if (!prefix) n_rows = RW;
     }
 
     // key range of the whole block, then of this chunk
@@ -176,49 +190,56 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         __syncthreads();
 
         const int j = t0 + lane;
-        float s[RW];
+        auto work = [&](auto nr) {
+            constexpr int NR = decltype(nr)::value;
+            float s[NR];
 #pragma unroll
-        for (int i = 0; i < RW; ++i) s[i] = 0.f;
-        const float* kr = k_s + lane * (hd + 1);
-        for (int d = 0; d < hd; ++d) {
-            const float kv = kr[d];
+            for (int i = 0; i < NR; ++i) s[i] = 0.f;
+            const float* kr = k_s + lane * (hd + 1);
+            for (int d = 0; d < hd; ++d) {
+                const float kv = kr[d];
 #pragma unroll
-            for (int i = 0; i < RW; ++i) s[i] = fmaf(q_s[(warp * RW + i) * hd + d], kv, s[i]);
-        }
-        float p[RW];
+                for (int i = 0; i < NR; ++i) s[i] = fmaf(q_s[(i * 4 + warp) * hd + d], kv, s[i]);
+            }
+            float p[NR];
 #pragma unroll
-        for (int i = 0; i < RW; ++i) {
-            const bool valid = row_ok[i] && j <= row_pos[i] && j >= row_lo[i] && j <= hi && j >= lo;
-            const float sv = s[i] * scale;
-            const float tmax = warp_max(valid ? sv : NEG_BIG);
-            const float m_new = fmaxf(m[i], tmax);
-            const float alpha = expf(m[i] - m_new);
-            p[i] = valid ? expf(sv - m_new) : 0.f;
-            l[i] = l[i] * alpha + warp_sum(p[i]);
-            m[i] = m_new;
+            for (int i = 0; i < NR; ++i) {
+                const bool valid = row_ok[i] && j <= row_pos[i] && j >= row_lo[i] && j <= hi && j >= lo;
+                const float sv = s[i] * scale;
+                const float tmax = warp_max(valid ? sv : NEG_BIG);
+                const float m_new = fmaxf(m[i], tmax);
+                const float alpha = expf(m[i] - m_new);
+                p[i] = valid ? expf(sv - m_new) : 0.f;
+                l[i] = l[i] * alpha + warp_sum(p[i]);
+                m[i] = m_new;
 #pragma unroll
-            for (int dd = 0; dd < MAX_DPL; ++dd) acc[i][dd] *= alpha;
-        }
-        for (int jj = 0; jj < KT; ++jj) {
-            float pj[RW];
+                for (int dd = 0; dd < MAX_DPL; ++dd) acc[i][dd] *= alpha;
+            }
+            for (int jj = 0; jj < KT; ++jj) {
+                float pj[NR];
 #pragma unroll
-            for (int i = 0; i < RW; ++i) pj[i] = __shfl_sync(0xffffffffu, p[i], jj);
+                for (int i = 0; i < NR; ++i) pj[i] = __shfl_sync(0xffffffffu, p[i], jj);
 #pragma unroll
-            for (int dd = 0; dd < MAX_DPL; ++dd) {
-                const int d = lane + 32 * dd;
-                if (d < hd) {
-                    const float vv = v_s[jj * hd + d];
+                for (int dd = 0; dd < MAX_DPL; ++dd) {
+                    const int d = lane + 32 * dd;
+                    if (d < hd) {
+                        const float vv = v_s[jj * hd + d];
 #pragma unroll
-                    for (int i = 0; i < RW; ++i) acc[i][dd] = fmaf(pj[i], vv, acc[i][dd]);
+                        for (int i = 0; i < NR; ++i) acc[i][dd] = fmaf(pj[i], vv, acc[i][dd]);
+                    }
                 }
             }
-        }
+        };
+        if (n_rows == RW) work(std::integral_constant<int, RW>());
+        else if (n_rows == 1) work(std::integral_constant<int, 1>());
+        else if (n_rows == 2) work(std::integral_constant<int, 2>());
+        else if (n_rows == 3) work(std::integral_constant<int, 3>());
     }
 
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
         if (!row_ok[i]) continue;
-        const int r = warp * RW + i;
+        const int r = i * 4 + warp;
         const int t = q0 + tok0 + r / HG;
         const int head = kvh * g + hc * HG + r % HG;
         if (chunk > 0) {
