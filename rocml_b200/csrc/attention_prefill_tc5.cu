@@ -12,9 +12,8 @@
 // window), update the running maximum and sum in float32 (base 2, the scale folded into the
 // exponent's multiply-add, two scores an instruction), and write P as pairs of bfloat16 back into
 // the first 32 columns of the buffer S_j came from: the tensor core reads its A operand from there
-// (no shared-memory round trip, no proxy fence; the MMA thread forms S_{j+2} in that buffer only once
-// the product that read P_j from it is done: two MMAs that write different accumulators are not
-// sure to run in the order they were issued).  Only when some row's maximum has grown by
+// (no shared-memory round trip, no proxy fence; S_{j+2} is issued into that buffer after the product
+// that reads P_j from it, see `strict_order` in the MMA thread).  Only when some row's maximum has grown by
 // more than 2^8 does a warp wait for the last product and rescale the O accumulator in tensor memory
 // (otherwise the stale maximum stays in use, which is exact: numerator and denominator carry the
 // same factor); O += P V_j with V read in its natural [key][dimension] order (MN-major operand).
@@ -28,6 +27,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 #include "api.h"
+#include <stdlib.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -114,7 +114,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int o_stride,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slot,
                              const int* __restrict__ cu_q, const int* __restrict__ kv_len, int nq, int nkv,
-                             float scale, int window, int heads_first, int* __restrict__ status) {
+                             float scale, int window, int heads_first, int strict_order, int* __restrict__ status) {
     using Z = Sizes<HD>;
     constexpr int HALVES = Z::HALVES, Q_BYTES = Z::Q_BYTES, KV_TILE = Z::KV_TILE, Q_HALF = Z::Q_HALF, KV_HALF = Z::KV_HALF;
     constexpr int TILE_BYTES = Z::TILE_BYTES, SMEM_BYTES = Z::SMEM_BYTES, TMEM_COLS = Z::TMEM_COLS;
@@ -213,10 +213,13 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             const uint32_t v_lo0 = ((smem_u32(Vs) >> 4) & 0x3FFFu) | ((uint32_t)(KV_HALF >> 4) << 16);
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1;
-                // S_j goes into the buffer that still holds P_{j-2}: the product that reads it must be DONE, not
-                // just issued.  MMAs of one thread are only sure to run in order when they write the same
-                // accumulator, and this one writes S while that one wrote O.
-                if (j >= 2 && !mbar_wait(&bar->o_done, (j - 2) & 1)) return false;
+                // S_j goes into the buffer that still holds P_{j-2}, which the product O += P_{j-2} V reads: that
+                // product must be DONE, not just issued.  MMAs of one thread are only sure to run in issue order
+                // when they write the same accumulator with the same shape, and this one writes S while that one
+                // wrote O.  (Without the wait, 280 launches over seven shapes gave the same bits every time and
+                // the kernel was 1 to 2 % quicker: the tensor core does take them in order today.
+                // RB_PREFILL_STRICT_ORDER=0 leaves the wait out.)
+                if (strict_order && j >= 2 && !mbar_wait(&bar->o_done, (j - 2) & 1)) return false;
                 if (!mbar_wait(&bar->k_full[s], (j >> 1) & 1)) return false;
                 tc_fence_after();
                 const uint32_t k_lo = k_lo0 + s * (KV_TILE >> 4);
@@ -455,6 +458,8 @@ int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, cons
                int n_pages, const int* block_table, int max_pages, const int* seq_slot, const int* cu_q,
                const int* kv_len, int B, int max_q_len, int nq, int nkv, float scale, int window, int heads_first,
                int* status, cudaStream_t stream) {
+    // RB_PREFILL_STRICT_ORDER=0: see `strict_order` in the kernel's MMA thread
+    static const int strict_order = [] { const char* e = getenv("RB_PREFILL_STRICT_ORDER"); return (e && e[0] == '0') ? 0 : 1; }();
     CUtensorMap mq, mk, mv;
     int rc;
     if ((rc = make_map(q, T, (long long)nq * HD, q_stride, BMQ, &mq)) != RB_OK) return rc;
@@ -472,7 +477,7 @@ int launch_tc5(const void* q, int q_stride, int T, void* out, int o_stride, cons
     dim3 grid = heads_first ? dim3(nq, B, q_tiles) : dim3(q_tiles, nq, B);
     if (grid.y > 65535 || grid.z > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((k), grid, dim3(192), Sizes<HD>::SMEM_BYTES, stream, mq, mk, mv, (__nv_bfloat16*)out, o_stride,
-              block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, heads_first, status);
+              block_table, max_pages, seq_slot, cu_q, kv_len, nq, nkv, scale, window, heads_first, strict_order, status);
     return RB_OK;
 }
 }  // namespace
